@@ -1,0 +1,344 @@
+// Attention pre-processing: per-head q/k RMSNorm, NeoX RoPE (YaRN frequencies),
+// paged-KV write — one pass over Q and K.
+//
+// Arithmetic of qwen38_qk_norm_partial_rope_cache8_kernel
+// (src/axiom_qwen38_attention.cu:481-554) with the paged addressing of
+// axiom_kv_pool_store_paged_f32_kernel (src/axiom_cuda.cu:16954-16969):
+//   ss  = sum x^2 in FP64, inv = (float)(1/sqrt(ss/D + eps))
+//   n   = (x * inv) * gamma                         FP32
+//   ang = (float)pos * inv_freq[p]; c = cosf(ang)*mscale; s = sinf(ang)*mscale
+//   out[p]      = bf16(fma(n[p], c, -(n[p+half]*s)))
+//   out[p+half] = bf16(fma(n[p], s,   n[p+half]*c))
+//   dims >= rope_dim: bf16(n)
+//
+// One CTA per token.  A lane owns 8 consecutive dims (one 16-byte chunk) of one
+// head; head_dim/8 adjacent lanes form a head.  Three phases separated by CTA
+// barriers keep the expensive scalar work out of the 16x-replicated lane code:
+//   1. load chunks, FP64 sum of squares per head (shuffle tree) -> shared
+//   2. one thread per head: inv; one thread per (pair, cos|sin): table row
+//   3. normalise, exchange with the partner lane, rotate, round, store
+// The frequency table is an input: it is evaluated once per model on the
+// device (yarn_inv_freq_kernel) instead of powf/logf per thread per call.
+#include "runtime.hpp"
+
+namespace axb {
+
+namespace {
+
+__device__ __forceinline__ void unpack8(const uint4 &v, float (&x)[8]) {
+    x[0] = bf16_lo(v.x); x[1] = bf16_hi(v.x);
+    x[2] = bf16_lo(v.y); x[3] = bf16_hi(v.y);
+    x[4] = bf16_lo(v.z); x[5] = bf16_hi(v.z);
+    x[6] = bf16_lo(v.w); x[7] = bf16_hi(v.w);
+}
+
+constexpr uint32_t kMaxHeads = 512u;
+constexpr uint32_t kMaxHeadDim = 256u;
+
+struct qk_dev_args {
+    uint4 *q;
+    const uint4 *k;
+    const uint4 *v;
+    const uint16_t *q_gamma;
+    const uint16_t *k_gamma;
+    const float *inv_freq;
+    const uint32_t *positions;
+    const int32_t *block_tables;
+    uint4 *k_pool;
+    uint4 *v_pool;
+    uint4 *k_out;
+    uint32_t *status_word;
+    uint32_t tokens, q_heads, k_heads, head_dim, rope_dim, flags;
+    float eps, mscale;
+    uint32_t block_tokens, n_layers, layer, pool_stride, tbl_stride, n_blocks;
+};
+
+// LPH = lanes per head (head_dim / 8); NPT = chunks per thread.
+template <int LPH, int NPT>
+__global__ void __launch_bounds__(512)
+qk_norm_rope_paged_kernel(const qk_dev_args a) {
+    __shared__ double ss_sh[kMaxHeads];
+    __shared__ float inv_sh[kMaxHeads];
+    __shared__ float cos_sh[kMaxHeadDim / 2];
+    __shared__ float sin_sh[kMaxHeadDim / 2];
+    __shared__ float gq_sh[kMaxHeadDim];
+    __shared__ float gk_sh[kMaxHeadDim];
+    __shared__ unsigned long long kv_base_sh;  // chunk index into the pools, ~0 = no cache write
+    constexpr uint32_t D = LPH * 8u;
+
+    const uint32_t tid = threadIdx.x;
+    const uint32_t heads = a.q_heads + a.k_heads;
+    const uint32_t total_chunks = heads * LPH;
+    const uint32_t half = a.rope_dim >> 1;
+
+    for (uint32_t i = tid; i < D; i += blockDim.x) {
+        gq_sh[i] = a.q_heads ? __uint_as_float((uint32_t)a.q_gamma[i] << 16) : 0.0f;
+        gk_sh[i] = a.k_heads ? __uint_as_float((uint32_t)a.k_gamma[i] << 16) : 0.0f;
+    }
+
+    for (uint32_t t = blockIdx.x; t < a.tokens; t += gridDim.x) {
+        const uint4 *q_row = a.q + (uint64_t)t * a.q_heads * LPH;
+        const uint4 *k_row = a.k + (uint64_t)t * a.k_heads * LPH;
+        const uint32_t q_chunks = a.q_heads * LPH;
+
+        // ---- phase 1: loads and per-head FP64 sum of squares
+        uint4 x[NPT];
+#pragma unroll
+        for (int n = 0; n < NPT; ++n) {
+            const uint32_t j = tid + blockDim.x * n;
+            x[n] = make_uint4(0u, 0u, 0u, 0u);
+            if (j < total_chunks) x[n] = j < q_chunks ? ld_stream(q_row + j) : ld_stream(k_row + (j - q_chunks));
+        }
+        const uint32_t pos = a.positions[t];
+        if (tid == 0u) {
+            unsigned long long base = ~0ull;
+            if (a.k_pool) {
+                uint32_t lb = pos / a.block_tokens;
+                bool ok = true;
+                if (a.flags & AXIOM_QK_FLAG_RING) lb %= a.tbl_stride;
+                else if (lb >= a.tbl_stride) ok = false;
+                int32_t pb = -1;
+                if (ok) {
+                    const uint64_t trow = (a.flags & AXIOM_QK_FLAG_PER_TOKEN_TABLE) ? t : 0u;
+                    pb = a.block_tables[trow * a.tbl_stride + lb];
+                    ok = pb >= 0 && (uint32_t)pb < a.n_blocks;
+                }
+                if (ok) {
+                    base = ((((uint64_t)pb * a.n_layers + a.layer) * a.block_tokens + pos % a.block_tokens) *
+                            a.pool_stride) >> 3;
+                } else if (a.status_word) {
+                    atomicCAS(a.status_word, AXIOM_STATUS_WORD_OK, AXIOM_STATUS_WORD_BAD_ADDRESS);
+                }
+            }
+            kv_base_sh = base;
+        }
+#pragma unroll
+        for (int n = 0; n < NPT; ++n) {
+            float f[8];
+            unpack8(x[n], f);
+            double s = 0.0;
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+                const double d = (double)f[i];
+                s = __fma_rn(d, d, s);
+            }
+#pragma unroll
+            for (int off = LPH / 2; off != 0; off >>= 1) s += __shfl_xor_sync(0xffffffffu, s, off);
+            const uint32_t j = tid + blockDim.x * n;
+            if (j < total_chunks && (j % LPH) == 0u) ss_sh[j / LPH] = s;
+        }
+        __syncthreads();
+
+        // ---- phase 2: one thread per head / per table entry
+        for (uint32_t e = tid; e < heads + a.rope_dim; e += blockDim.x) {
+            if (e < heads) {
+                inv_sh[e] = (float)(1.0 / sqrt(ss_sh[e] / (double)D + (double)a.eps));
+            } else {
+                const uint32_t idx = e - heads;
+                const uint32_t p = idx < half ? idx : idx - half;
+                const float angle = __fmul_rn((float)pos, a.inv_freq[p]);
+                if (idx < half) cos_sh[p] = __fmul_rn(cosf(angle), a.mscale);
+                else sin_sh[p] = __fmul_rn(sinf(angle), a.mscale);
+            }
+        }
+        __syncthreads();
+
+        // ---- phase 3: normalise, rotate, round, store
+        const unsigned long long kv_base = kv_base_sh;
+#pragma unroll
+        for (int n = 0; n < NPT; ++n) {
+            const uint32_t j = tid + blockDim.x * n;
+            const bool ok = j < total_chunks;
+            const uint32_t head = ok ? j / LPH : 0u;
+            const uint32_t l = j % LPH;
+            const uint32_t e0 = l * 8u;
+            const bool is_k = head >= a.q_heads;
+            const float *gamma = is_k ? gk_sh : gq_sh;
+            const float inv = inv_sh[head];
+            float f[8], nv[8], pv[8];
+            unpack8(x[n], f);
+#pragma unroll
+            for (int i = 0; i < 8; ++i) nv[i] = __fmul_rn(__fmul_rn(f[i], inv), gamma[e0 + i]);
+            const uint32_t partner = half >> 3;  // lane distance of the NeoX pair; 0 when nothing rotates
+#pragma unroll
+            for (int i = 0; i < 8; ++i) pv[i] = __shfl_xor_sync(0xffffffffu, nv[i], partner);
+            float o[8];
+            if (e0 < half) {
+#pragma unroll
+                for (int i = 0; i < 8; ++i) {
+                    const float c = cos_sh[e0 + i], s = sin_sh[e0 + i];
+                    o[i] = __fmaf_rn(nv[i], c, -__fmul_rn(pv[i], s));
+                }
+            } else if (e0 < a.rope_dim) {
+#pragma unroll
+                for (int i = 0; i < 8; ++i) {
+                    const float c = cos_sh[e0 - half + i], s = sin_sh[e0 - half + i];
+                    o[i] = __fmaf_rn(pv[i], s, __fmul_rn(nv[i], c));
+                }
+            } else {
+#pragma unroll
+                for (int i = 0; i < 8; ++i) o[i] = nv[i];
+            }
+            const uint4 packed = make_uint4(pack_bf16x2(o[0], o[1]), pack_bf16x2(o[2], o[3]),
+                                            pack_bf16x2(o[4], o[5]), pack_bf16x2(o[6], o[7]));
+            if (ok) {
+                if (!is_k) {
+                    st_stream(a.q + (uint64_t)t * q_chunks + j, packed);
+                } else {
+                    const uint32_t kj = j - q_chunks;  // chunk inside the token's K row
+                    if (kv_base != ~0ull) st_stream(a.k_pool + kv_base + kj, packed);
+                    if (a.k_out) st_stream(a.k_out + (uint64_t)t * a.k_heads * LPH + kj, packed);
+                }
+            }
+        }
+        // V rides along unchanged (BF16 in, BF16 cache)
+        if (a.v && a.v_pool && kv_base != ~0ull) {
+            const uint4 *v_row = a.v + (uint64_t)t * a.k_heads * LPH;
+            for (uint32_t j = tid; j < a.k_heads * LPH; j += blockDim.x) st_stream(a.v_pool + kv_base + j, ld_stream(v_row + j));
+        }
+        __syncthreads();  // shared tables are rewritten by the next token
+    }
+}
+
+// Frequency table.  The correction range (floor/ceil of the two YaRN
+// correction dims) arrives from the host; powf and the blend run here so they
+// use the same device math library as the kernels that used to evaluate them
+// per thread (src/axiom_qwen38_attention.cu:98-116).
+__global__ void yarn_inv_freq_kernel(float *out, uint32_t rope_dim, float theta, float factor, float low,
+                                     float high, int yarn) {
+    const uint32_t pair = blockIdx.x * blockDim.x + threadIdx.x;
+    if (pair >= rope_dim / 2u) return;
+    const float dim = (float)rope_dim;
+    if (!yarn) {
+        out[pair] = powf(theta, __fdiv_rn(__fmul_rn(-2.0f, (float)pair), dim));
+        return;
+    }
+    const float exponent = __fdiv_rn(__fmul_rn(2.0f, (float)pair), dim);
+    const float inv = __fdiv_rn(1.0f, powf(theta, exponent));
+    float ramp = high > low ? __fdiv_rn(__fsub_rn((float)pair, low), __fsub_rn(high, low))
+                            : ((float)pair >= high ? 1.0f : 0.0f);
+    ramp = fminf(1.0f, fmaxf(0.0f, ramp));
+    out[pair] = __fmaf_rn(inv, __fsub_rn(1.0f, ramp), __fmul_rn(__fdiv_rn(inv, factor), ramp));
+}
+
+template <int LPH>
+void launch_qk(const qk_dev_args &a, cudaStream_t stream) {
+    const uint32_t total_chunks = (a.q_heads + a.k_heads) * LPH;
+    const uint32_t grid = a.tokens;
+    if (total_chunks <= 2048u) {
+        uint32_t threads = ((total_chunks + 3u) / 4u + 31u) & ~31u;
+        if (threads < 64u) threads = 64u;
+        qk_norm_rope_paged_kernel<LPH, 4><<<grid, threads, 0, stream>>>(a);
+    } else {
+        const uint32_t threads = ((total_chunks + 7u) / 8u + 31u) & ~31u;
+        qk_norm_rope_paged_kernel<LPH, 8><<<grid, threads, 0, stream>>>(a);
+    }
+}
+
+bool is_pow2(uint32_t v) { return v && !(v & (v - 1u)); }
+
+}  // namespace
+
+int launch_qk_norm_rope_paged_bf16(const axiom_qk_rope_args *p, cudaStream_t stream) {
+    qk_dev_args a{};
+    a.q = (uint4 *)p->q_bf16;
+    a.k = (const uint4 *)p->k_bf16;
+    a.v = (const uint4 *)p->v_bf16;
+    a.q_gamma = (const uint16_t *)p->q_gamma_bf16;
+    a.k_gamma = (const uint16_t *)p->k_gamma_bf16;
+    a.inv_freq = p->inv_freq;
+    a.positions = p->positions;
+    a.block_tables = p->block_tables;
+    a.k_pool = (uint4 *)p->k_pool_bf16;
+    a.v_pool = (uint4 *)p->v_pool_bf16;
+    a.k_out = (uint4 *)p->k_out_bf16;
+    a.status_word = p->status_word;
+    a.tokens = p->tokens; a.q_heads = p->q_heads; a.k_heads = p->k_heads; a.head_dim = p->head_dim;
+    a.rope_dim = p->rope_dim; a.flags = p->flags; a.eps = p->eps; a.mscale = p->mscale;
+    a.block_tokens = p->block_tokens; a.n_layers = p->n_layers; a.layer = p->layer;
+    a.pool_stride = p->pool_stride; a.tbl_stride = p->tbl_stride; a.n_blocks = p->n_blocks;
+    switch (p->head_dim) {
+    case 64: launch_qk<8>(a, stream); break;
+    case 128: launch_qk<16>(a, stream); break;
+    default: launch_qk<32>(a, stream); break;
+    }
+    note_launch();
+    return AXIOM_OK;
+}
+
+int launch_yarn_inv_freq(const axiom_rope_config *c, float *out, cudaStream_t stream) {
+    const int yarn = c->factor > 1.0f;
+    float low = 0.0f, high = 0.0f;
+    if (yarn) {
+        // Same FP32 expression as the reference evaluates with compile-time constants.
+        const float dim = (float)c->rope_dim;
+        const float fast = dim * logf(c->original_context / (c->beta_fast * 6.283185307179586f)) / (2.0f * logf(c->theta));
+        const float slow = dim * logf(c->original_context / (c->beta_slow * 6.283185307179586f)) / (2.0f * logf(c->theta));
+        low = floorf(fast < slow ? fast : slow);
+        high = ceilf(fast > slow ? fast : slow);
+    }
+    const uint32_t pairs = c->rope_dim / 2u;
+    yarn_inv_freq_kernel<<<(pairs + 127u) / 128u, 128, 0, stream>>>(out, c->rope_dim, c->theta, c->factor, low, high, yarn);
+    note_launch();
+    return AXIOM_OK;
+}
+
+}  // namespace axb
+
+using namespace axb;
+
+extern "C" float axiom_qwen38_fused_yarn_mscale(float factor) {
+    if (!(factor > 1.0f)) return 1.0f;
+    return (float)(0.1 * std::log((double)factor) + 1.0);
+}
+
+extern "C" int axiom_qwen38_fused_yarn_inv_freq_device(int device, const axiom_rope_config *config,
+                                                       float *out_inv_freq, void *stream) {
+    if (!config || !out_inv_freq || config->abi_version != AXIOM_ABI_VERSION || config->rope_dim == 0u ||
+        (config->rope_dim & 1u) || config->rope_dim > kMaxHeadDim || !(config->theta > 1.0f) ||
+        !std::isfinite(config->theta)) {
+        return AXIOM_ERR_INVALID_ARGUMENT;
+    }
+    if (config->factor > 1.0f &&
+        (!(config->original_context > 0.0f) || !(config->beta_fast > 0.0f) || !(config->beta_slow > 0.0f))) {
+        return AXIOM_ERR_INVALID_ARGUMENT;
+    }
+    int rc = select_device(device);
+    if (rc != AXIOM_OK) return rc;
+    launch_yarn_inv_freq(config, out_inv_freq, (cudaStream_t)stream);
+    return launch_status();
+}
+
+extern "C" int axiom_qwen38_fused_qk_norm_rope_paged_bf16_device(int device, const axiom_qk_rope_args *p,
+                                                                 void *stream) {
+    if (!p || p->abi_version != AXIOM_ABI_VERSION || p->struct_size != sizeof(axiom_qk_rope_args)) {
+        return AXIOM_ERR_INVALID_ARGUMENT;
+    }
+    if (p->tokens == 0u || (p->q_heads + p->k_heads) == 0u || (p->q_heads + p->k_heads) > kMaxHeads ||
+        (uint64_t)(p->q_heads + p->k_heads) * (p->head_dim / 8u) > 4096u ||
+        (p->head_dim != 64u && p->head_dim != 128u && p->head_dim != 256u) || p->rope_dim > p->head_dim ||
+        (p->rope_dim != 0u && (!is_pow2(p->rope_dim) || p->rope_dim < 16u)) || !(p->eps > 0.0f) ||
+        !std::isfinite(p->eps) || !std::isfinite(p->mscale) || !p->positions) {
+        return AXIOM_ERR_INVALID_ARGUMENT;
+    }
+    if (p->rope_dim != 0u && !p->inv_freq) return AXIOM_ERR_INVALID_ARGUMENT;
+    if (p->q_heads && (!p->q_bf16 || !p->q_gamma_bf16 || !aligned16(p->q_bf16))) return AXIOM_ERR_INVALID_ARGUMENT;
+    if (p->k_heads && (!p->k_bf16 || !p->k_gamma_bf16 || !aligned16(p->k_bf16))) return AXIOM_ERR_INVALID_ARGUMENT;
+    if (p->k_heads && !p->k_pool_bf16 && !p->k_out_bf16) return AXIOM_ERR_INVALID_ARGUMENT;
+    if (p->k_pool_bf16) {
+        if (!p->block_tables || p->block_tokens == 0u || p->n_layers == 0u || p->layer >= p->n_layers ||
+            p->tbl_stride == 0u || p->n_blocks == 0u || p->pool_stride < p->k_heads * p->head_dim ||
+            (p->pool_stride % 8u) != 0u || !aligned16(p->k_pool_bf16)) {
+            return AXIOM_ERR_INVALID_ARGUMENT;
+        }
+        if ((p->v_bf16 == nullptr) != (p->v_pool_bf16 == nullptr)) return AXIOM_ERR_INVALID_ARGUMENT;
+        if (p->v_bf16 && (!aligned16(p->v_bf16) || !aligned16(p->v_pool_bf16))) return AXIOM_ERR_INVALID_ARGUMENT;
+    } else if (p->v_bf16 || p->v_pool_bf16) {
+        return AXIOM_ERR_INVALID_ARGUMENT;
+    }
+    if (p->k_out_bf16 && !aligned16(p->k_out_bf16)) return AXIOM_ERR_INVALID_ARGUMENT;
+    int rc = select_device(device);
+    if (rc != AXIOM_OK) return rc;
+    launch_qk_norm_rope_paged_bf16(p, (cudaStream_t)stream);
+    return launch_status();
+}

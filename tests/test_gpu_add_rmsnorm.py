@@ -1,0 +1,117 @@
+"""Fused residual add + RMSNorm + NVFP4: CUDA path vs the CPU oracle.
+
+Bars: the updated residual is bit-exact; the normalised values are within
+1 BF16 ulp of the oracle (the device rsqrtf is an approximation, the oracle's
+is correctly rounded); the NVFP4 codes and block scales are bit-exact with the
+oracle quantizer applied to the kernel's own normalised values, and the two
+kernels behind the entry point (one warp per row / one CTA per row) agree
+bit-for-bit with each other."""
+import importlib
+
+import numpy as np
+import pytest
+
+import oracle_lib as ol
+
+pytestmark = pytest.mark.gpu
+wl = importlib.import_module("axiom-kernel_b200.workloads")
+EPS = 1e-6
+
+
+def run(axk, hidden, residual, gamma, G, layout=0, want_norm=True, want_codes=True):
+    from gpu_util import Guarded, dev, host, sync
+
+    rows, cols = residual.shape
+    h = dev(hidden) if hidden is not None else None
+    r = dev(residual)
+    g = dev(gamma)
+    norm = Guarded(rows * cols * 2) if want_norm else None
+    codes = Guarded(rows * cols // 2) if want_codes else None
+    nscale = int(axk.lib().axiom_nvfp4_scale_plane_bytes(rows, cols // 16, layout))
+    scales = Guarded(nscale) if want_codes else None
+    if want_codes and layout == 1:
+        scales.raw[scales.pad:scales.pad + nscale] = 0
+    rc = axk.add_rmsnorm_nvfp4(0, h, r, g, EPS, rows, cols, G, norm.ptr if norm else None,
+                               codes.ptr if codes else None, scales.ptr if scales else None, layout)
+    sync()
+    assert rc == axk.AXIOM_OK
+    for buf in (norm, codes, scales):
+        assert buf is None or buf.guards_intact()
+    return (host(r, np.uint16).reshape(rows, cols),
+            norm.payload(np.uint16).reshape(rows, cols) if norm else None,
+            codes.payload().reshape(rows, cols // 2) if codes else None,
+            scales.payload() if scales else None)
+
+
+def check_against_oracle(axk, rows, cols, layout=0, with_add=True):
+    hidden, residual, gamma = wl.add_rmsnorm_inputs_np(rows, cols)
+    if not with_add:
+        hidden = None
+    want_res, want_norm = ol.add_rmsnorm_bf16(hidden, residual, gamma, EPS)
+    G = wl.nvfp4_global_scale(float(np.abs(wl.from_bf16_bits(want_norm)).max()))
+    res, norm, codes, scales = run(axk, hidden, residual, gamma, G, layout)
+    assert np.array_equal(res, want_res)                       # residual: bit-exact
+    a, b = wl.from_bf16_bits(norm), wl.from_bf16_bits(want_norm)
+    assert np.all(np.abs(a - b) <= ol.bf16_ulp(b))             # norm: within 1 BF16 ulp
+    assert np.mean(norm != want_norm) < 0.02
+    own_codes, own_scales = ol.nvfp4_quantize_bf16(norm, G)    # codes: bit-exact on the kernel's own values
+    assert np.array_equal(codes, own_codes)
+    if layout == 0:
+        assert np.array_equal(scales.reshape(rows, cols // 16), own_scales)
+    else:
+        assert np.array_equal(scales, ol.scales_to_tiled(own_scales))
+    _, _, full_codes, full_scales = ol.add_rmsnorm_nvfp4_bf16(hidden, residual, gamma, EPS, G)
+    assert np.mean(codes != full_codes) < 0.02                 # end-to-end oracle: only rsqrt-ulp effects differ
+    return res, norm, codes, scales
+
+
+@pytest.mark.parametrize("rows", [1, 2, 7, 8, 9, 64])
+@pytest.mark.parametrize("cols", [5120, 1024, 48, 8192])
+def test_cta_per_row_kernel(axk, cuda_device, rows, cols):
+    check_against_oracle(axk, rows, cols)
+
+
+@pytest.mark.parametrize("rows,cols", [(300, 5120), (333, 1024), (512, 2048), (297, 4096), (301, 7168), (299, 8192),
+                                        (310, 48), (305, 3072), (320, 6144)])
+def test_warp_per_row_kernel(axk, cuda_device, rows, cols):
+    check_against_oracle(axk, rows, cols)
+
+
+def test_tiled_scale_layout_and_norm_only(axk, cuda_device):
+    check_against_oracle(axk, 384, 5120, layout=1)
+    check_against_oracle(axk, 40, 5120, layout=1)
+    check_against_oracle(axk, 300, 5120, with_add=False)
+    check_against_oracle(axk, 5, 5120, with_add=False)
+
+
+def test_both_kernels_agree_bit_for_bit(axk, cuda_device):
+    """Rows 0..199 through the CTA-per-row kernel equal the same rows inside a 1024-row launch."""
+    hidden, residual, gamma = wl.add_rmsnorm_inputs_np(1024, 5120)
+    G = 150.0
+    big = run(axk, hidden, residual, gamma, G)
+    small = run(axk, hidden[:200], residual[:200], gamma, G)
+    for a, b in zip(big, small):
+        assert np.array_equal(a[:200] if a.ndim == 2 else a[:200 * 320], b)
+
+
+def test_optional_outputs(axk, cuda_device):
+    hidden, residual, gamma = wl.add_rmsnorm_inputs_np(300, 5120)
+    full = run(axk, hidden, residual, gamma, 100.0)
+    only_norm = run(axk, hidden, residual, gamma, 100.0, want_codes=False)
+    only_codes = run(axk, hidden, residual, gamma, 100.0, want_norm=False)
+    assert np.array_equal(full[1], only_norm[1]) and np.array_equal(full[2], only_codes[2])
+    assert np.array_equal(full[3], only_codes[3]) and np.array_equal(full[0], only_norm[0])
+
+
+def test_config2_full_size_properties(axk, cuda_device):
+    """8192 x 5120: residual bit-exact against the oracle, codes consistent with the kernel's own norm."""
+    rows, cols = 8192, 5120
+    hidden, residual, gamma = wl.add_rmsnorm_inputs_np(rows, cols)
+    want_res, want_norm = ol.add_rmsnorm_bf16(hidden, residual, gamma, EPS)
+    G = wl.nvfp4_global_scale(float(np.abs(wl.from_bf16_bits(want_norm)).max()))
+    res, norm, codes, scales = run(axk, hidden, residual, gamma, G)
+    assert np.array_equal(res, want_res)
+    a, b = wl.from_bf16_bits(norm), wl.from_bf16_bits(want_norm)
+    assert np.all(np.abs(a - b) <= ol.bf16_ulp(b))
+    own_codes, own_scales = ol.nvfp4_quantize_bf16(norm, G)
+    assert np.array_equal(codes, own_codes) and np.array_equal(scales.reshape(rows, cols // 16), own_scales)

@@ -1,0 +1,208 @@
+"""q/k RMSNorm + NeoX RoPE (YaRN) + paged-KV write: CUDA path vs the CPU oracle.
+
+Both sides get the SAME inv_freq table, so what remains is cosf/sinf of the
+device vs the C library (<= 3 FP32 ulp on each product).  Tolerance: one BF16
+ulp at the magnitude of the larger rotation term — |n1*c| or |n2*s| — because
+the rotation is a difference of two such terms; where no cancellation happens
+this is 1 BF16 ulp of the result.  Paged addressing is checked byte for byte:
+every K/V row must sit at the address recomputed on the host and every other
+byte of the 0xFF-poisoned pools must be untouched."""
+import importlib
+
+import numpy as np
+import pytest
+
+import oracle_lib as ol
+
+pytestmark = pytest.mark.gpu
+wl = importlib.import_module("axiom-kernel_b200.workloads")
+
+
+def tolerance(q_in, gamma, inv_freq, positions, rope_dim, mscale, eps=1e-6):
+    """Per-element bound: 1 BF16 ulp at max(|n1 c|, |n2 s|, |result|) (FP64 evaluation)."""
+    x = wl.from_bf16_bits(q_in).astype(np.float64)
+    g = wl.from_bf16_bits(gamma).astype(np.float64)
+    n = x / np.sqrt((x ** 2).mean(axis=-1, keepdims=True) + eps) * g
+    half = rope_dim // 2
+    ang = positions.astype(np.float32)[:, None] * inv_freq[None, :]
+    c = (np.cos(ang.astype(np.float64)) * mscale)[:, None, :]
+    s = (np.sin(ang.astype(np.float64)) * mscale)[:, None, :]
+    mag = np.abs(n).copy()
+    a, b = n[..., :half], n[..., half:rope_dim]
+    mag[..., :half] = np.maximum(np.abs(a * c), np.abs(b * s))
+    mag[..., half:rope_dim] = np.maximum(np.abs(a * s), np.abs(b * c))
+    return ol.bf16_ulp(mag.astype(np.float32)) * np.float32(1.01)
+
+
+def run_case(axk, tokens, q_heads, k_heads, head_dim, rope_dim, *, n_blocks=64, block_tokens=16, n_layers=2, layer=1,
+             pool_pad=0, ring=True, per_token=False, with_v=True, theta=1e6, factor=4.0, ctx=32768.0, max_base=100000,
+             seed=3):
+    import torch
+    from gpu_util import Guarded, dev, host, sync
+
+    q, k, v, qg, kg, positions, table = wl.qk_inputs_np(tokens, q_heads, k_heads, head_dim, n_blocks, seed, max_base)
+    if per_token:
+        rng = np.random.default_rng(seed + 1)
+        table = np.stack([rng.permutation(n_blocks).astype(np.int32) for _ in range(tokens)])
+        positions = rng.integers(0, n_blocks * block_tokens, tokens).astype(np.uint32)
+    inv_freq = ol.yarn_inv_freq(theta, factor, ctx, 32.0, 1.0, rope_dim) if rope_dim else np.zeros(1, np.float32)
+    mscale = float(ol.o().axo_yarn_mscale(factor))
+    kv_dim = k_heads * head_dim
+    pool_stride = kv_dim + pool_pad
+    pool_elems = n_blocks * n_layers * block_tokens * pool_stride
+    k_pool, v_pool = Guarded(pool_elems * 2), Guarded(pool_elems * 2)
+    k_out = Guarded(tokens * kv_dim * 2)
+    qd, kd, vd = dev(q), dev(k), dev(v)
+    status = torch.zeros(1, dtype=torch.int32, device="cuda")
+    flags = (axk.QK_FLAG_RING if ring else 0) | (axk.QK_FLAG_PER_TOKEN_TABLE if per_token else 0)
+    args = axk.make_qk_args(tokens=tokens, q_heads=q_heads, k_heads=k_heads, head_dim=head_dim, rope_dim=rope_dim,
+                            flags=flags, eps=1e-6, mscale=mscale, block_tokens=block_tokens, n_layers=n_layers,
+                            layer=layer, pool_stride=pool_stride, tbl_stride=table.shape[1], n_blocks=n_blocks,
+                            q=qd, k=kd, v=vd if with_v else None, q_gamma=dev(qg), k_gamma=dev(kg),
+                            inv_freq=dev(inv_freq), positions=dev(positions), block_tables=dev(table),
+                            k_pool=k_pool.ptr, v_pool=v_pool.ptr if with_v else None, k_out=k_out.ptr,
+                            status_word=status)
+    rc = axk.qk_norm_rope_paged(0, args)
+    sync()
+    assert rc == axk.AXIOM_OK
+    assert k_pool.guards_intact() and v_pool.guards_intact() and k_out.guards_intact()
+
+    # oracle on identical inputs, with poisoned pools of its own
+    o_kpool = np.full(pool_elems, 0xFFFF, np.uint16)
+    o_vpool = np.full(pool_elems, 0xFFFF, np.uint16)
+    want_q, want_k, want_status = ol.qk_norm_rope_paged(
+        q, k, v if with_v else None, qg, kg, inv_freq, positions, table, rope_dim=rope_dim, eps=1e-6, mscale=mscale,
+        block_tokens=block_tokens, n_layers=n_layers, layer=layer, pool_stride=pool_stride, n_blocks=n_blocks,
+        ring=ring, per_token_table=per_token, k_pool=o_kpool, v_pool=o_vpool if with_v else None, want_k_out=True)
+    got_q = host(qd, np.uint16).reshape(q.shape)
+    got_k = k_out.payload(np.uint16).reshape(k.shape)
+    assert int(status.item()) == want_status
+
+    for got, want, src, gamma in ((got_q, want_q, q, qg), (got_k, want_k, k, kg)):
+        a, b = wl.from_bf16_bits(got), wl.from_bf16_bits(want)
+        tol = tolerance(src, gamma, inv_freq, positions, rope_dim, mscale)
+        assert np.all(np.abs(a - b) <= tol)
+        assert np.mean(got != want) < 0.02
+        if rope_dim < head_dim:  # pass-through dims have no transcendental: bit-exact
+            assert np.array_equal(got[..., rope_dim:], want[..., rope_dim:])
+
+    # paged scatter: exactly the oracle's cells were written, with this kernel's own K rows; V is a copy
+    got_kpool, got_vpool = k_pool.payload(np.uint16), v_pool.payload(np.uint16)
+    written = o_kpool != 0xFFFF
+    expect_kpool = np.full(pool_elems, 0xFFFF, np.uint16)
+    for t in range(tokens):
+        pos = int(positions[t])
+        lb = (pos // block_tokens) % table.shape[1] if ring else pos // block_tokens
+        if lb >= table.shape[1]:
+            continue
+        pb = int(table[t if per_token else 0, lb])
+        if pb < 0 or pb >= n_blocks:
+            continue
+        base = ((pb * n_layers + layer) * block_tokens + pos % block_tokens) * pool_stride
+        expect_kpool[base:base + kv_dim] = got_k[t].reshape(-1)
+    assert np.array_equal(got_kpool, expect_kpool)
+    assert np.array_equal(got_kpool != 0xFFFF, written)
+    if with_v:
+        assert np.array_equal(got_vpool, o_vpool)  # V is copied unchanged: bit-exact
+    else:
+        assert v_pool.untouched()
+    return got_q, got_k
+
+
+@pytest.mark.parametrize("tokens", [1, 2, 7, 8, 9, 15, 16, 17, 64])
+def test_config3_geometry_small(axk, cuda_device, tokens):
+    run_case(axk, tokens, 64, 8, 128, 128, n_blocks=4096, n_layers=1, layer=0)
+
+
+@pytest.mark.parametrize("q_heads,k_heads,head_dim,rope_dim", [(24, 4, 256, 64), (40, 8, 128, 128), (3, 1, 64, 64),
+                                                                (5, 2, 64, 32), (2, 2, 256, 256), (1, 1, 128, 16),
+                                                                (16, 2, 128, 0)])
+def test_other_geometries(axk, cuda_device, q_heads, k_heads, head_dim, rope_dim):
+    run_case(axk, 33, q_heads, k_heads, head_dim, rope_dim, theta=1e7, ctx=262144.0)
+
+
+def test_pool_stride_padding_layers_and_no_v(axk, cuda_device):
+    run_case(axk, 40, 8, 2, 128, 128, n_layers=3, layer=2, pool_pad=64, n_blocks=32, max_base=300)
+    run_case(axk, 40, 8, 2, 128, 128, with_v=False, n_blocks=32, max_base=300)
+
+
+def test_per_token_tables_decode_batch(axk, cuda_device):
+    run_case(axk, 64, 64, 8, 128, 128, per_token=True, n_blocks=128)
+
+
+def test_out_of_range_addresses_raise_status_and_skip(axk, cuda_device):
+    """Without ring wrap, positions beyond the table are reported through the status word and not written."""
+    import torch
+    from gpu_util import Guarded, dev, sync
+
+    tokens, n_blocks = 24, 8
+    q, k, v, qg, kg, positions, table = wl.qk_inputs_np(tokens, 4, 2, 128, n_blocks, seed=1, max_base=1)
+    positions = (n_blocks * 16 - 8 + np.arange(tokens)).astype(np.uint32)  # the last 16 tokens fall off the table
+    table[0, 3] = 99                                                       # and one block id is out of range
+    inv_freq = ol.yarn_inv_freq(1e6, 4.0, 32768.0, 32.0, 1.0, 128)
+    kv_dim = 256
+    pool = Guarded(n_blocks * 16 * kv_dim * 2)
+    status = torch.zeros(1, dtype=torch.int32, device="cuda")
+    qd = dev(q)
+    args = axk.make_qk_args(tokens=tokens, q_heads=4, k_heads=2, head_dim=128, rope_dim=128, flags=0, eps=1e-6,
+                            mscale=1.0, block_tokens=16, n_layers=1, layer=0, pool_stride=kv_dim,
+                            tbl_stride=n_blocks, n_blocks=n_blocks, q=qd, k=dev(k), q_gamma=dev(qg), k_gamma=dev(kg),
+                            inv_freq=dev(inv_freq), positions=dev(positions), block_tables=dev(table),
+                            k_pool=pool.ptr, status_word=status)
+    assert axk.qk_norm_rope_paged(0, args) == axk.AXIOM_OK
+    sync()
+    assert int(status.item()) == axk.STATUS_WORD_BAD_ADDRESS
+    assert pool.guards_intact()
+    cells = pool.payload(np.uint16).reshape(n_blocks * 16, kv_dim)
+    assert int((cells != 0xFFFF).any(axis=1).sum()) == 8  # only the 8 in-range tokens were stored
+
+
+def test_yarn_table_kernel_matches_oracle(axk, cuda_device):
+    import torch
+    from gpu_util import sync
+
+    for theta, factor, ctx, dim in [(1e6, 4.0, 32768.0, 128), (1e7, 4.0, 262144.0, 64), (1e4, 1.0, 0.0, 128),
+                                    (5e5, 8.0, 8192.0, 256)]:
+        out = torch.empty(dim // 2, dtype=torch.float32, device="cuda")
+        assert axk.yarn_inv_freq(0, dim, theta, factor, ctx, 32.0, 1.0, out) == axk.AXIOM_OK
+        sync()
+        got = out.cpu().numpy()
+        want = ol.yarn_inv_freq(theta, factor, ctx, 32.0, 1.0, dim) if factor > 1 else \
+            np.array([np.float32(theta) ** np.float32(-2.0 * i / dim) for i in range(dim // 2)], np.float32)
+        assert np.allclose(got, want, rtol=2e-6, atol=0)
+        assert got[0] == 1.0
+
+
+def test_config3_full_size_properties(axk, cuda_device):
+    """T = 8192 at the benchmark geometry: oracle on a 256-token slab, structural properties on everything:
+    the norm of every rotated head equals mscale * the norm of gamma-weighted unit-RMS input (rotation is
+    an isometry), and every token's K row sits in its page."""
+    got_q, got_k = run_case(axk, 256, 64, 8, 128, 128, n_blocks=4096, n_layers=1, layer=0)
+    import torch
+    from gpu_util import dev, sync
+
+    tokens = 8192
+    q, k, v, qg, kg, positions, table = wl.qk_inputs_np(tokens, 64, 8, 128, 4096, seed=3)
+    inv_freq = ol.yarn_inv_freq(1e6, 4.0, 32768.0, 32.0, 1.0, 128)
+    mscale = float(ol.o().axo_yarn_mscale(4.0))
+    qd, kd = dev(q), dev(k)
+    pool = torch.full((4096 * 16 * 1024,), -1, dtype=torch.int16, device="cuda")
+    status = torch.zeros(1, dtype=torch.int32, device="cuda")
+    args = axk.make_qk_args(tokens=tokens, q_heads=64, k_heads=8, head_dim=128, rope_dim=128, flags=axk.QK_FLAG_RING,
+                            eps=1e-6, mscale=mscale, block_tokens=16, n_layers=1, layer=0, pool_stride=1024,
+                            tbl_stride=4096, n_blocks=4096, q=qd, k=kd, q_gamma=dev(qg), k_gamma=dev(kg),
+                            inv_freq=dev(inv_freq), positions=dev(positions), block_tables=dev(table), k_pool=pool,
+                            status_word=status)
+    assert axk.qk_norm_rope_paged(0, args) == axk.AXIOM_OK
+    sync()
+    assert int(status.item()) == 0
+    out = wl.from_bf16_bits(qd.cpu().numpy().view(np.uint16).reshape(tokens, 64, 128)).astype(np.float64)
+    x = wl.from_bf16_bits(q).astype(np.float64)
+    n = x / np.sqrt((x ** 2).mean(-1, keepdims=True) + 1e-6) * wl.from_bf16_bits(qg).astype(np.float64)
+    want_norm = np.sqrt((n ** 2).sum(-1)) * mscale
+    assert np.allclose(np.sqrt((out ** 2).sum(-1)), want_norm, rtol=2e-3)
+    cells = pool.cpu().numpy().view(np.uint16).reshape(4096, 16, 1024)
+    lb = (positions // 16) % 4096
+    rows = cells[table[0, lb], positions % 16]
+    assert not (rows == 0xFFFF).all(axis=1).any()
+    assert int((cells != 0xFFFF).any(axis=2).sum()) == tokens

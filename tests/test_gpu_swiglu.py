@@ -1,0 +1,133 @@
+"""SwiGLU + FP8 / NVFP4 quantize and the plain BF16 FP8 quantizer vs the CPU oracle.
+
+The plain quantizer has no transcendental and is bit-exact.  SwiGLU uses the
+device expf (<= 2 ulp) where the oracle uses the C library's, so y may differ in
+the last FP32 bits: the per-token scale must agree to 4 FP32 ulps, almost all
+codes must be identical, and EVERY code must be a correct rounding of the
+FP64-evaluated y/scale up to that FP32 slack."""
+import importlib
+
+import numpy as np
+import pytest
+
+import oracle_lib as ol
+
+pytestmark = pytest.mark.gpu
+wl = importlib.import_module("axiom-kernel_b200.workloads")
+
+
+def e4m3_table():
+    return np.array([ol.o().axo_e4m3_decode(c) for c in range(256)], np.float64)
+
+
+def run_swiglu_fp8(axk, gu):
+    from gpu_util import Guarded, dev, sync
+
+    rows, two_w = gu.shape
+    w = two_w // 2
+    x = dev(gu)
+    codes, scales = Guarded(rows * w), Guarded(rows * 4)
+    rc = axk.swiglu_fp8(0, x, rows, w, codes.ptr, scales.ptr)
+    sync()
+    assert rc == axk.AXIOM_OK and codes.guards_intact() and scales.guards_intact()
+    return codes.payload().reshape(rows, w), scales.payload(np.float32)
+
+
+def silu_mul_f64(gu):
+    w = gu.shape[1] // 2
+    g = wl.from_bf16_bits(gu[:, :w]).astype(np.float64)
+    u = wl.from_bf16_bits(gu[:, w:]).astype(np.float64)
+    return g / (1.0 + np.exp(-g)) * u
+
+
+def check_swiglu_fp8(axk, rows, width, seed=4):
+    gu = wl.swiglu_input_np(rows, width, seed)
+    codes, scales = run_swiglu_fp8(axk, gu)
+    want_codes, want_scales = ol.swiglu_fp8_bf16(gu)
+    assert np.all(np.abs(scales - want_scales) <= 4 * np.spacing(want_scales))
+    assert np.mean(codes != want_codes) < 2e-3
+    # every code is a correct rounding of y/scale (FP64) up to the FP32 slack of y
+    table = e4m3_table()
+    q = silu_mul_f64(gu) / scales.astype(np.float64)[:, None]
+    got = table[codes]
+    mag = codes & 0x7f
+    step = np.where(mag < 8, 2.0 ** -9, np.exp2(np.floor(np.log2(np.maximum(np.abs(got), 2.0 ** -9))) - 3))
+    slack = np.abs(q) * 2.0 ** -21 + 1e-30
+    sat = np.abs(q) >= 448.0
+    ok = np.abs(got - q) <= 0.5 * step + slack
+    ok |= sat & (mag == 0x7e)
+    assert np.all(ok)
+    return codes, scales
+
+
+@pytest.mark.parametrize("rows,width", [(1, 17408), (8, 17408), (5, 64), (3, 8), (64, 4096), (256, 17408),
+                                         (7, 11008), (4, 36864), (9, 4608 - 8)])
+def test_swiglu_fp8(axk, cuda_device, rows, width):
+    check_swiglu_fp8(axk, rows, width)
+
+
+def test_swiglu_fp8_special_rows(axk, cuda_device):
+    w = 256
+    x = np.zeros((6, 2 * w), np.float32)
+    x[1, :w] = 1.0                                     # up = 0 -> y = 0 -> scale 1
+    x[2, :w] = np.linspace(-90, 90, w)
+    x[2, w:] = 1.0
+    x[3, 0] = np.inf; x[3, w] = 1.0; x[3, 1] = 2.0; x[3, w + 1] = 3.0   # y = inf -> scale falls back to 1
+    x[4, 5] = np.nan; x[4, w:] = 1.0; x[4, 7] = 4.0
+    x[5, :w] = -200.0; x[5, w:] = 5.0                  # expf overflow: g/inf = -0
+    gu = wl.to_bf16_bits(x)
+    codes, scales = run_swiglu_fp8(axk, gu)
+    want_codes, want_scales = ol.swiglu_fp8_bf16(gu)
+    assert np.allclose(scales, want_scales, rtol=1e-6)
+    assert scales[0] == 1.0 and scales[1] == 1.0 and scales[3] == 1.0
+    assert np.mean(codes != want_codes) < 0.01
+    assert np.array_equal(codes[[0, 1, 3, 5]], want_codes[[0, 1, 3, 5]])
+
+
+def test_plain_fp8_quantizer_bit_exact(axk, cuda_device):
+    from gpu_util import Guarded, dev, sync
+    import torch
+
+    for rows, cols in [(1, 8), (3, 5120), (8, 17408), (130, 1024), (5, 36864)]:
+        x = wl.quantize_input_np(rows, cols, seed=cols)
+        if rows >= 3:
+            x[1, :] = 0
+            x[2, 3] = 0x7f80  # +inf: skipped by the maximum, raises the status word
+        xd = dev(x)
+        codes, scales = Guarded(rows * cols), Guarded(rows * 4)
+        status = torch.zeros(1, dtype=torch.int32, device="cuda")
+        rc = axk.fp8_quantize(0, xd, rows, cols, codes.ptr, scales.ptr, status)
+        sync()
+        assert rc == axk.AXIOM_OK
+        want_codes, want_scales, want_status = ol.fp8_quantize_bf16(x)
+        assert np.array_equal(scales.payload(np.float32), want_scales)
+        assert np.array_equal(codes.payload().reshape(rows, cols), want_codes)
+        assert int(status.item()) == want_status
+        assert codes.guards_intact() and scales.guards_intact()
+
+
+@pytest.mark.parametrize("rows,width,layout", [(1, 17408, 0), (8, 17408, 1), (3, 16, 0), (70, 1024, 1), (256, 17408, 0)])
+def test_swiglu_nvfp4(axk, cuda_device, rows, width, layout):
+    from gpu_util import Guarded, dev, sync
+
+    gu = wl.swiglu_input_np(rows, width, seed=9)
+    y = ol.swiglu_f32(gu)
+    G = wl.nvfp4_global_scale(float(np.abs(y).max()))
+    x = dev(gu)
+    codes = Guarded(rows * width // 2)
+    nscale = int(axk.lib().axiom_nvfp4_scale_plane_bytes(rows, width // 16, layout))
+    scales = Guarded(nscale)
+    if layout == 1:
+        scales.raw[scales.pad:scales.pad + nscale] = 0
+    rc = axk.swiglu_nvfp4(0, x, rows, width, G, codes.ptr, scales.ptr, layout)
+    sync()
+    assert rc == axk.AXIOM_OK and codes.guards_intact() and scales.guards_intact()
+    want_codes, want_scales = ol.swiglu_nvfp4_bf16(gu, G)
+    want_plane = want_scales.reshape(-1) if layout == 0 else ol.scales_to_tiled(want_scales)
+    assert np.mean(scales.payload() != want_plane) < 2e-3
+    assert np.mean(codes.payload().reshape(rows, width // 2) != want_codes) < 2e-3
+
+
+def test_config4_full_size_sample(axk, cuda_device):
+    """T = 16384 is exercised at full width; the oracle checks a 512-row slab of it."""
+    check_swiglu_fp8(axk, 512, 17408, seed=4)
