@@ -1,0 +1,451 @@
+#!/usr/bin/env python
+"""Benchmark of the fused elementwise / reduction / quantize path on B200.
+
+    python bench.py --gpus N --steps K --warmup W [--impl reference]
+
+Headline workload (one "step" = one pass of the hot path over one batch):
+fused residual-add + RMSNorm + NVFP4 quantize over BF16 [8192 x 5120] per GPU
+(hidden, residual ~N(0,1); gamma = 1+N(0,0.02); eps 1e-6).  Rows are
+independent, so N GPUs each process their own 8192 rows (weak scaling, no
+collective in the data path; NCCL only carries the timing reduction).
+
+The JSON line carries, besides the contract keys:
+  roofline      HBM roofline of the dominant kernel (algorithmic bytes / CUDA-event time)
+  cpu_baseline  the CPU oracle timed on a bounded sample on this box's host cores
+  e2e           same metric through the host-I/O C-ABI entry (pinned host buffers,
+                H2D + kernel + D2H inside the timed region)
+  ops           device-timed GB/s of the other benchmark configurations
+                (NVFP4 quantize, q/k-norm + RoPE + paged KV, SwiGLU + FP8, decode chain)
+
+With --impl reference the CPU restatement of the reference's arithmetic (the
+reference has no CPU path of its own for these ops) is timed on all host cores.
+"""
+from __future__ import annotations
+
+import argparse
+import importlib
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+from pathlib import Path
+
+ROOT = Path(__file__).resolve().parent
+if str(ROOT) not in sys.path:
+    sys.path.insert(0, str(ROOT))
+
+ROWS = 8192
+COLS = 5120
+NSETS = 4  # rotating buffer sets so no step finds its inputs in L2 (126 MB)
+METRIC = "fused_add_rmsnorm_nvfp4_tokens_per_s"
+UNIT = "tokens/s"
+
+
+def measured_peak_gbs():
+    p = ROOT / "MEASURED_PEAKS.json"
+    if p.exists():
+        try:
+            return float(json.loads(p.read_text())["hbm_gbs"]), "measured"
+        except Exception:
+            pass
+    return 6650.0, "fallback"
+
+
+def bytes_add_rmsnorm_nvfp4(rows, cols):
+    # hidden R + residual R + residual W + codes W + scales W + gamma R
+    return 3 * rows * cols * 2 + rows * cols // 2 + rows * cols // 16 + cols * 2
+
+
+class ClockSampler:
+    """nvidia-smi samples of SM clock and throttle reasons during the timed region."""
+    QUERY = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
+             "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+             "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index: int):
+        self.gpu_index = gpu_index
+        self.proc = None
+        self.lines = []
+        self.thread = None
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--id={self.gpu_index}", f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits",
+                 "-lms", "100"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+        except OSError:
+            self.proc = None
+            return
+        self.thread = threading.Thread(target=self._pump, daemon=True)
+        self.thread.start()
+
+    def _pump(self):
+        for line in self.proc.stdout:
+            self.lines.append(line.strip())
+
+    def stop(self):
+        if not self.proc:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        time.sleep(0.15)
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+        sm, mx, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for line in self.lines:
+            f = [x.strip() for x in line.split(",")]
+            if len(f) < 9:
+                continue
+            try:
+                sm.append(float(f[1]))
+                mx.append(float(f[2]))
+            except ValueError:
+                continue
+            for name, val in zip(names, f[5:9]):
+                if val.lower().startswith("active"):
+                    reasons.add(name)
+        sm.sort()
+        return {"sm_mhz": sm[len(sm) // 2] if sm else None, "sm_max_mhz": max(mx) if mx else None,
+                "reasons": sorted(reasons), "samples": len(sm)}
+
+
+def event_time_ms(torch, stream, fn, iters):
+    """Time `iters` calls of fn (each enqueues on `stream`) with CUDA events on that stream."""
+    start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    torch.cuda.synchronize()
+    start.record(stream)
+    for i in range(iters):
+        fn(i)
+    end.record(stream)
+    torch.cuda.synchronize()
+    return start.elapsed_time(end) / iters
+
+
+def reference_arm(args):
+    """CPU restatement of the reference's arithmetic for the headline op, all host threads."""
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return 0
+    sys.path.insert(0, str(ROOT / "tests"))
+    import numpy as np
+    import oracle_lib as ol
+
+    wl = importlib.import_module("axiom-kernel_b200.workloads")
+    sample_rows = 2048
+    hidden, residual, gamma = wl.add_rmsnorm_inputs_np(sample_rows, COLS)
+    threads = ol.o().axo_get_threads()
+    G = 100.0
+    for _ in range(max(args.warmup, 1)):
+        ol.add_rmsnorm_nvfp4_bf16(hidden, residual, gamma, 1e-6, G)
+    t0 = time.perf_counter()
+    for _ in range(args.steps):
+        ol.add_rmsnorm_nvfp4_bf16(hidden, residual, gamma, 1e-6, G)
+    dt = (time.perf_counter() - t0) / args.steps
+    value = sample_rows / dt
+    line = {
+        "impl": "reference", "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": args.gpus,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": dt * 1e3 * (ROWS / sample_rows),
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16->f32->e2m1/e4m3",
+        "data": "synthetic",
+        "config": {"workload": f"add+RMSNorm+NVFP4 BF16 [{ROWS}x{COLS}], CPU restatement of the reference arithmetic"},
+        "cpu_baseline": {"value": value, "unit": UNIT, "cores": threads, "kind": "port",
+                         "sample": f"{sample_rows} of {ROWS} rows per step, OpenMP over rows"},
+        "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    print(json.dumps(line), flush=True)
+    return 0
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=200)
+    ap.add_argument("--warmup", type=int, default=10)
+    ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
+    ap.add_argument("--skip-ops", action="store_true", help="only the headline workload")
+    ap.add_argument("--skip-e2e", action="store_true")
+    ap.add_argument("--skip-cpu", action="store_true")
+    args = ap.parse_args()
+    if args.impl == "reference":
+        return reference_arm(args)
+
+    import numpy as np
+    import torch
+
+    axk = importlib.import_module("axiom-kernel_b200")
+    wl = importlib.import_module("axiom-kernel_b200.workloads")
+    lib = axk.lib()  # raises if the CUDA library is missing: there is no fallback
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device")
+    torch.cuda.set_device(local)
+    dist = None
+    if world > 1:
+        import torch.distributed as dist_mod
+        dist = dist_mod
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+    device = torch.device("cuda", local)
+    stream = torch.cuda.Stream(device)
+    peak, peak_kind = measured_peak_gbs()
+
+    # ---- headline: add + RMSNorm + NVFP4, device resident ---------------------------------
+    sets = []
+    for s in range(NSETS):
+        hidden, residual, gamma = wl.add_rmsnorm_inputs_torch(torch, device, ROWS, COLS)
+        if s:
+            hidden = hidden.roll(s, 0)
+            residual = residual.roll(s, 0)
+        sets.append(dict(hidden=hidden, residual=residual, gamma=gamma,
+                         codes=torch.empty((ROWS, COLS // 2), dtype=torch.uint8, device=device),
+                         scales=torch.empty((ROWS, COLS // 16), dtype=torch.uint8, device=device)))
+    pristine = [s["residual"].clone() for s in sets]
+    # global scale from the normalised tensor of set 0 (calibration step, outside any timed region)
+    norm0 = torch.empty((ROWS, COLS), dtype=torch.bfloat16, device=device)
+    rc = axk.add_rmsnorm_nvfp4(local, sets[0]["hidden"], sets[0]["residual"], sets[0]["gamma"], wl.EPS, ROWS, COLS, 1.0,
+                               norm0, None, None, 0, stream)
+    axk.check(rc, "calibration")
+    torch.cuda.synchronize()
+    G = wl.nvfp4_global_scale(float(norm0.float().abs().max().item()))
+    sets[0]["residual"].copy_(pristine[0])
+    del norm0
+
+    def step(i):
+        s = sets[i % NSETS]
+        if i % (8 * NSETS) < NSETS and i >= NSETS:
+            pass
+        rc = axk.add_rmsnorm_nvfp4(local, s["hidden"], s["residual"], s["gamma"], wl.EPS, ROWS, COLS, G, None,
+                                   s["codes"], s["scales"], 0, stream)
+        if rc:
+            axk.check(rc, "add_rmsnorm_nvfp4")
+
+    for i in range(max(args.warmup, 3)):
+        step(i)
+    torch.cuda.synchronize()
+    for s, p in zip(sets, pristine):
+        s["residual"].copy_(p)
+    torch.cuda.synchronize()
+    if dist:
+        dist.barrier()
+    sampler = ClockSampler(local)
+    if rank == 0:
+        sampler.start()
+    launches0 = int(lib.axiom_b200_kernel_launch_count())
+    ms = event_time_ms(torch, stream, step, args.steps)
+    launches = int(lib.axiom_b200_kernel_launch_count()) - launches0
+    clocks = sampler.stop() if rank == 0 else None
+    if dist:
+        t = torch.tensor([ms], dtype=torch.float64, device=device)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms = float(t.item())
+        dist.barrier()
+    value = world * ROWS / (ms * 1e-3)
+    algo = bytes_add_rmsnorm_nvfp4(ROWS, COLS)
+    achieved = algo / (ms * 1e-3) / 1e9
+    line = {
+        "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
+        "warmup": max(args.warmup, 3), "ms_per_step": ms, "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": "bf16->f32->e2m1/e4m3", "data": "synthetic",
+        "config": {"workload": f"fused residual-add + RMSNorm + NVFP4 quantize, BF16 [{ROWS}x{COLS}] per GPU, "
+                               f"eps 1e-6, gamma 1+N(0,0.02)",
+                   "rows_per_gpu": ROWS, "cols": COLS, "l2": f"inputs larger than L2: {NSETS} rotating buffer sets "
+                                                               f"of {algo / 1e6:.0f} MB",
+                   "partition": "token rows, no collective"},
+        "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
+                     "traffic": None, "peak_kind": peak_kind, "kernel": "add_rmsnorm_warp_rows_kernel<20,true>",
+                     "algorithmic_bytes_per_launch": algo},
+        "gpu_launches": launches,
+        "clocks": clocks,
+    }
+
+    # ---- e2e through the host-I/O C-ABI entry ------------------------------------------------
+    if not args.skip_e2e:
+        rt = axk.Runtime(local)
+        h_hidden = sets[0]["hidden"].cpu().pin_memory()
+        h_res = pristine[0].cpu().pin_memory()
+        h_gamma = sets[0]["gamma"].cpu().pin_memory()
+        h_codes = torch.empty((ROWS, COLS // 2), dtype=torch.uint8).pin_memory()
+        h_scales = torch.empty((ROWS, COLS // 16), dtype=torch.uint8).pin_memory()
+
+        def e2e_step():
+            rc = lib.axiom_runtime_add_rmsnorm_nvfp4_bf16(rt.handle, h_hidden.data_ptr(), h_res.data_ptr(),
+                                                          h_gamma.data_ptr(), wl.EPS, ROWS, COLS, G,
+                                                          h_codes.data_ptr(), h_scales.data_ptr())
+            if rc:
+                axk.check(rc, "host-I/O add_rmsnorm_nvfp4")
+
+        for _ in range(3):
+            e2e_step()
+        torch.cuda.synchronize()
+        if dist:
+            dist.barrier()
+        e2e_steps = max(5, min(args.steps, 30))
+        t0 = time.perf_counter()
+        for _ in range(e2e_steps):
+            e2e_step()
+        torch.cuda.synchronize()
+        e2e_ms = (time.perf_counter() - t0) / e2e_steps * 1e3
+        if dist:
+            t = torch.tensor([e2e_ms], dtype=torch.float64, device=device)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            e2e_ms = float(t.item())
+        line["e2e"] = {"value": world * ROWS / (e2e_ms * 1e-3), "unit": UNIT,
+                       "h2d_bytes_per_step": 2 * ROWS * COLS * 2 + COLS * 2,
+                       "d2h_bytes_per_step": ROWS * COLS * 2 + ROWS * COLS // 2 + ROWS * COLS // 16,
+                       "ms_per_step": e2e_ms, "steps": e2e_steps,
+                       "api": "axiom_runtime_add_rmsnorm_nvfp4_bf16 (pinned host buffers in and out)"}
+        rt.close()
+        del h_hidden, h_res, h_codes, h_scales
+
+    # ---- the other configurations, device timed (rank 0 reports) ----------------------------------
+    if not args.skip_ops:
+        del sets, pristine
+        torch.cuda.empty_cache()
+        line["ops"] = bench_other_ops(torch, axk, wl, local, device, stream, peak)
+
+    # ---- CPU baseline: the oracle on a bounded sample, rank 0 at N=1 only -------------------------
+    if rank == 0 and world == 1 and not args.skip_cpu:
+        sys.path.insert(0, str(ROOT / "tests"))
+        import oracle_lib as ol
+
+        sample_rows = 2048
+        hidden, residual, gamma = wl.add_rmsnorm_inputs_np(sample_rows, COLS)
+        threads = ol.o().axo_get_threads()
+        ol.add_rmsnorm_nvfp4_bf16(hidden, residual, gamma, 1e-6, G)
+        reps, t0 = 0, time.perf_counter()
+        while reps < 3 or (time.perf_counter() - t0 < 10.0 and reps < 200):
+            ol.add_rmsnorm_nvfp4_bf16(hidden, residual, gamma, 1e-6, G)
+            reps += 1
+        dt = (time.perf_counter() - t0) / reps
+        line["cpu_baseline"] = {"value": sample_rows / dt, "unit": UNIT, "cores": threads, "kind": "port",
+                                "sample": f"{sample_rows} of {ROWS} rows, {reps} repetitions, OpenMP over rows"}
+    elif rank == 0:
+        line["cpu_baseline"] = None
+
+    if dist:
+        dist.barrier()
+        dist.destroy_process_group()
+    if rank == 0:
+        print(json.dumps(line), flush=True)
+    return 0
+
+
+def bench_other_ops(torch, axk, wl, local, device, stream, peak):
+    """Device-timed throughput of configurations 1, 3, 4 and the decode chain (5)."""
+    out = {}
+    iters, warm = 50, 5
+
+    def timed(fn, n=iters):
+        for i in range(warm):
+            fn(i)
+        return event_time_ms(torch, stream, fn, n)
+
+    def report(name, ms, algo, rows, note):
+        gbs = algo / (ms * 1e-3) / 1e9
+        out[name] = {"ms": ms, "gbs": gbs, "frac_of_peak": gbs / peak, "tokens_per_s": rows / (ms * 1e-3),
+                     "algorithmic_bytes": algo, "note": note}
+
+    # config 1: BF16 -> NVFP4, [4096 x 5120]; 8 rotating inputs (8 x 42 MB > L2)
+    rows, cols = 4096, 5120
+    xs = [wl.quantize_input_torch(torch, device, rows, cols, seed=s) for s in range(8)]
+    codes = [torch.empty((rows, cols // 2), dtype=torch.uint8, device=device) for _ in range(8)]
+    scales = [torch.empty((rows, cols // 16), dtype=torch.uint8, device=device) for _ in range(8)]
+    G = wl.nvfp4_global_scale(float(xs[0].float().abs().max().item()))
+    for layout, tag in ((0, "canonical"), (1, "tiled")):
+        ms = timed(lambda i: axk.nvfp4_quantize(local, xs[i % 8], rows, cols, G, codes[i % 8], scales[i % 8], layout, stream))
+        report(f"nvfp4_quantize_{tag}", ms, rows * cols * 2 + rows * cols // 2 + rows * cols // 16, rows,
+               "config 1, 8 rotating buffer sets")
+    del xs, codes, scales
+
+    # config 3: q/k norm + RoPE + paged KV, T = 8192; 2 rotating sets (2 x 302 MB)
+    T = 8192
+    qk_sets = []
+    inv_freq = torch.empty(64, dtype=torch.float32, device=device)
+    axk.check(axk.yarn_inv_freq(local, 128, wl.ROPE_THETA, wl.YARN_FACTOR, wl.YARN_ORIGINAL_CONTEXT, 32.0, 1.0, inv_freq, stream), "yarn")
+    pool = torch.empty((wl.KV_BLOCKS * 16 * 1024,), dtype=torch.bfloat16, device=device)
+    status = torch.zeros(1, dtype=torch.int32, device=device)
+    for s in range(2):
+        q, k, v, qg, kg, pos, tab = wl.qk_inputs_torch(torch, device, T, seed=3 + s)
+        keep = (q, k, qg, kg, pos, tab)
+        args = axk.make_qk_args(tokens=T, q_heads=64, k_heads=8, head_dim=128, rope_dim=128, flags=axk.QK_FLAG_RING,
+                                eps=1e-6, mscale=axk.yarn_mscale(4.0), block_tokens=16, n_layers=1, layer=0,
+                                pool_stride=1024, tbl_stride=wl.KV_BLOCKS, n_blocks=wl.KV_BLOCKS, q=q, k=k, q_gamma=qg,
+                                k_gamma=kg, inv_freq=inv_freq, positions=pos, block_tables=tab, k_pool=pool,
+                                status_word=status)
+        qk_sets.append((args, keep))
+    ms = timed(lambda i: axk.qk_norm_rope_paged(local, qk_sets[i % 2][0], stream))
+    report("qk_norm_rope_paged_kv", ms, 2 * T * 64 * 128 * 2 + 2 * T * 8 * 128 * 2 + T * 4 + 4096 * 4 + 512, T,
+           "config 3, Q in place, K to 16-token BF16 pages")
+    del qk_sets, pool
+
+    # config 4: SwiGLU + FP8, T = 16384 (1.43 GB per pass: larger than L2 by itself)
+    T, W = 16384, wl.FFN
+    gu = wl.swiglu_input_torch(torch, device, T, W)
+    c8 = torch.empty((T, W), dtype=torch.uint8, device=device)
+    s8 = torch.empty((T,), dtype=torch.float32, device=device)
+    ms = timed(lambda i: axk.swiglu_fp8(local, gu, T, W, c8, s8, stream), n=20)
+    report("swiglu_fp8", ms, T * 2 * W * 2 + T * W + T * 4, T, "config 4")
+    c4 = torch.empty((T, W // 2), dtype=torch.uint8, device=device)
+    s4 = torch.empty((T, W // 16), dtype=torch.uint8, device=device)
+    ms = timed(lambda i: axk.swiglu_nvfp4(local, gu, T, W, 40.0, c4, s4, 0, stream), n=20)
+    report("swiglu_nvfp4", ms, T * 2 * W * 2 + T * W // 2 + T * W // 16, T, "SwiGLU -> NVFP4 (down-projection input)")
+    del gu, c8, s8, c4, s4
+
+    # config 5: decode chain, microseconds per layer-chain, eager launches and one CUDA graph replay
+    table, _ = wl.embedding_inputs_torch(torch, device, 1)
+    chain = {}
+    for m in (1, 8, 64, 256):
+        ids = torch.randint(0, wl.VOCAB, (m,), device=device).to(torch.int32)
+        _, residual, gamma = wl.add_rmsnorm_inputs_torch(torch, device, m)
+        q, k, v, qg, kg, pos, tab = wl.qk_inputs_torch(torch, device, m)
+        gu = wl.swiglu_input_torch(torch, device, m)
+        hidden = torch.empty((m, wl.HIDDEN), dtype=torch.bfloat16, device=device)
+        codes = torch.empty((m, wl.HIDDEN // 2), dtype=torch.uint8, device=device)
+        scales = torch.empty((m, wl.HIDDEN // 16), dtype=torch.uint8, device=device)
+        pool = torch.empty((wl.KV_BLOCKS * 16 * 1024,), dtype=torch.bfloat16, device=device)
+        mc = torch.empty((m, wl.FFN // 2), dtype=torch.uint8, device=device)
+        msc = torch.empty((m, wl.FFN // 16), dtype=torch.uint8, device=device)
+        args = axk.make_qk_args(tokens=m, q_heads=64, k_heads=8, head_dim=128, rope_dim=128, flags=axk.QK_FLAG_RING,
+                                eps=1e-6, mscale=axk.yarn_mscale(4.0), block_tokens=16, n_layers=1, layer=0,
+                                pool_stride=1024, tbl_stride=wl.KV_BLOCKS, n_blocks=wl.KV_BLOCKS, q=q, k=k, q_gamma=qg,
+                                k_gamma=kg, inv_freq=inv_freq, positions=pos, block_tables=tab, k_pool=pool,
+                                status_word=status)
+
+        def run_chain(_i, s=stream):
+            axk.embedding_gather(local, table, wl.VOCAB, wl.HIDDEN, ids, m, hidden, status, s)
+            axk.add_rmsnorm_nvfp4(local, hidden, residual, gamma, wl.EPS, m, wl.HIDDEN, 90.0, None, codes, scales, 0, s)
+            axk.qk_norm_rope_paged(local, args, s)
+            axk.swiglu_nvfp4(local, gu, m, wl.FFN, 40.0, mc, msc, 0, s)
+
+        eager_us = timed(run_chain, n=200) * 1e3
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph, stream=stream):
+            run_chain(0, torch.cuda.current_stream())
+        for _ in range(5):
+            graph.replay()
+        start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        torch.cuda.synchronize()
+        start.record()
+        for _ in range(200):
+            graph.replay()
+        end.record()
+        torch.cuda.synchronize()
+        graph_us = start.elapsed_time(end) / 200 * 1e3
+        algo = m * (wl.HIDDEN * 2 * 2 + (3 * wl.HIDDEN * 2 + wl.HIDDEN // 2 + wl.HIDDEN // 16) +
+                    (2 * 64 * 128 * 2 + 2 * 8 * 128 * 2 + 4) + (2 * wl.FFN * 2 + wl.FFN // 2 + wl.FFN // 16)) + wl.HIDDEN * 2
+        chain[str(m)] = {"eager_us": eager_us, "graph_us": graph_us, "algorithmic_bytes": algo,
+                         "frac_of_peak_graph": algo / (graph_us * 1e-6) / 1e9 / peak}
+        del graph
+    out["decode_chain"] = chain
+    return out
+
+
+if __name__ == "__main__":
+    sys.exit(main())

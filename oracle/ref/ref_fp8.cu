@@ -1,0 +1,11 @@
+// Harness around the reference's per-token FP8 E4M3 quantizer kernel (test infrastructure, see ref_nvfp4_mlp.cu).
+#include "src/axiom_qwen38_fp8.cu"
+
+// input F32 [columns][cols]; the kernel handles at most AXIOM_QWEN38_FP8_BATCH (8) columns per launch
+extern "C" int ref_quantize_columns_e4m3(const float *input, uint8_t *codes, float *scales, uint32_t cols, uint32_t columns) {
+    for (uint32_t c0 = 0; c0 < columns; c0 += AXIOM_QWEN38_FP8_BATCH) {
+        const uint32_t n = columns - c0 < AXIOM_QWEN38_FP8_BATCH ? columns - c0 : AXIOM_QWEN38_FP8_BATCH;
+        quantize_columns_e4m3_kernel<<<n, kThreads>>>(input + (size_t)c0 * cols, codes + (size_t)c0 * cols, scales + c0, cols);
+    }
+    return cudaDeviceSynchronize() == cudaSuccess && cudaGetLastError() == cudaSuccess ? 0 : 3;
+}

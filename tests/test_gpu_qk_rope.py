@@ -2,9 +2,9 @@
 
 Both sides get the SAME inv_freq table, so what remains is cosf/sinf of the
 device vs the C library (<= 3 FP32 ulp on each product).  Tolerance: one BF16
-ulp at the magnitude of the larger rotation term — |n1*c| or |n2*s| — because
-the rotation is a difference of two such terms; where no cancellation happens
-this is 1 BF16 ulp of the result.  Paged addressing is checked byte for byte:
+ulp at the magnitude of the largest of the two rotation terms |n1*c|, |n2*s|
+and the result itself — the rotation is a sum/difference of two such terms, so
+where no cancellation happens this is 1 BF16 ulp of the result.  Paged addressing is checked byte for byte:
 every K/V row must sit at the address recomputed on the host and every other
 byte of the 0xFF-poisoned pools must be untouched."""
 import importlib
@@ -29,8 +29,8 @@ def tolerance(q_in, gamma, inv_freq, positions, rope_dim, mscale, eps=1e-6):
     s = (np.sin(ang.astype(np.float64)) * mscale)[:, None, :]
     mag = np.abs(n).copy()
     a, b = n[..., :half], n[..., half:rope_dim]
-    mag[..., :half] = np.maximum(np.abs(a * c), np.abs(b * s))
-    mag[..., half:rope_dim] = np.maximum(np.abs(a * s), np.abs(b * c))
+    mag[..., :half] = np.maximum(np.maximum(np.abs(a * c), np.abs(b * s)), np.abs(a * c - b * s))
+    mag[..., half:rope_dim] = np.maximum(np.maximum(np.abs(a * s), np.abs(b * c)), np.abs(a * s + b * c))
     return ol.bf16_ulp(mag.astype(np.float32)) * np.float32(1.01)
 
 
@@ -53,13 +53,15 @@ def run_case(axk, tokens, q_heads, k_heads, head_dim, rope_dim, *, n_blocks=64, 
     k_pool, v_pool = Guarded(pool_elems * 2), Guarded(pool_elems * 2)
     k_out = Guarded(tokens * kv_dim * 2)
     qd, kd, vd = dev(q), dev(k), dev(v)
+    # every device tensor is named: the argument struct only carries raw addresses
+    qgd, kgd, fd, pd, td = dev(qg), dev(kg), dev(inv_freq), dev(positions), dev(table)
     status = torch.zeros(1, dtype=torch.int32, device="cuda")
     flags = (axk.QK_FLAG_RING if ring else 0) | (axk.QK_FLAG_PER_TOKEN_TABLE if per_token else 0)
     args = axk.make_qk_args(tokens=tokens, q_heads=q_heads, k_heads=k_heads, head_dim=head_dim, rope_dim=rope_dim,
                             flags=flags, eps=1e-6, mscale=mscale, block_tokens=block_tokens, n_layers=n_layers,
                             layer=layer, pool_stride=pool_stride, tbl_stride=table.shape[1], n_blocks=n_blocks,
-                            q=qd, k=kd, v=vd if with_v else None, q_gamma=dev(qg), k_gamma=dev(kg),
-                            inv_freq=dev(inv_freq), positions=dev(positions), block_tables=dev(table),
+                            q=qd, k=kd, v=vd if with_v else None, q_gamma=qgd, k_gamma=kgd,
+                            inv_freq=fd, positions=pd, block_tables=td,
                             k_pool=k_pool.ptr, v_pool=v_pool.ptr if with_v else None, k_out=k_out.ptr,
                             status_word=status)
     rc = axk.qk_norm_rope_paged(0, args)
@@ -143,11 +145,11 @@ def test_out_of_range_addresses_raise_status_and_skip(axk, cuda_device):
     kv_dim = 256
     pool = Guarded(n_blocks * 16 * kv_dim * 2)
     status = torch.zeros(1, dtype=torch.int32, device="cuda")
-    qd = dev(q)
+    qd, kd, qgd, kgd, fd, pd, td = dev(q), dev(k), dev(qg), dev(kg), dev(inv_freq), dev(positions), dev(table)
     args = axk.make_qk_args(tokens=tokens, q_heads=4, k_heads=2, head_dim=128, rope_dim=128, flags=0, eps=1e-6,
                             mscale=1.0, block_tokens=16, n_layers=1, layer=0, pool_stride=kv_dim,
-                            tbl_stride=n_blocks, n_blocks=n_blocks, q=qd, k=dev(k), q_gamma=dev(qg), k_gamma=dev(kg),
-                            inv_freq=dev(inv_freq), positions=dev(positions), block_tables=dev(table),
+                            tbl_stride=n_blocks, n_blocks=n_blocks, q=qd, k=kd, q_gamma=qgd, k_gamma=kgd,
+                            inv_freq=fd, positions=pd, block_tables=td,
                             k_pool=pool.ptr, status_word=status)
     assert axk.qk_norm_rope_paged(0, args) == axk.AXIOM_OK
     sync()
@@ -185,13 +187,13 @@ def test_config3_full_size_properties(axk, cuda_device):
     q, k, v, qg, kg, positions, table = wl.qk_inputs_np(tokens, 64, 8, 128, 4096, seed=3)
     inv_freq = ol.yarn_inv_freq(1e6, 4.0, 32768.0, 32.0, 1.0, 128)
     mscale = float(ol.o().axo_yarn_mscale(4.0))
-    qd, kd = dev(q), dev(k)
+    qd, kd, qgd, kgd, fd, pd, td = dev(q), dev(k), dev(qg), dev(kg), dev(inv_freq), dev(positions), dev(table)
     pool = torch.full((4096 * 16 * 1024,), -1, dtype=torch.int16, device="cuda")
     status = torch.zeros(1, dtype=torch.int32, device="cuda")
     args = axk.make_qk_args(tokens=tokens, q_heads=64, k_heads=8, head_dim=128, rope_dim=128, flags=axk.QK_FLAG_RING,
                             eps=1e-6, mscale=mscale, block_tokens=16, n_layers=1, layer=0, pool_stride=1024,
-                            tbl_stride=4096, n_blocks=4096, q=qd, k=kd, q_gamma=dev(qg), k_gamma=dev(kg),
-                            inv_freq=dev(inv_freq), positions=dev(positions), block_tables=dev(table), k_pool=pool,
+                            tbl_stride=4096, n_blocks=4096, q=qd, k=kd, q_gamma=qgd, k_gamma=kgd,
+                            inv_freq=fd, positions=pd, block_tables=td, k_pool=pool,
                             status_word=status)
     assert axk.qk_norm_rope_paged(0, args) == axk.AXIOM_OK
     sync()
