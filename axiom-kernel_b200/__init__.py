@@ -126,6 +126,7 @@ SIGNATURES = {
     "axiom_nvfp4_scale_plane_bytes": (u64, [u32, u32, u32]),
     "axiom_nvfp4_scale_plane_offset": (u64, [u32, u32, u32, u32]),
     "axiom_b200_kernel_launch_count": (u64, []),
+    "axiom_b200_pipeline_faults": (u32, [i32]),
 }
 
 _lib = None

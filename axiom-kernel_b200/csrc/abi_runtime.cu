@@ -92,6 +92,12 @@ using namespace axb;
 // axiom_device_buffer flavour
 // ------------------------------------------------------------------------
 
+extern "C" uint32_t axiom_b200_pipeline_faults(int device) {
+    if (select_device(device) != AXIOM_OK) return ~0u;
+    if (cudaDeviceSynchronize() != cudaSuccess) return ~0u;
+    return add_rmsnorm_fault_word() | swiglu_fault_word() | qk_fault_word();
+}
+
 extern "C" int axiom_runtime_nvfp4_quantize_bf16_device(
         axiom_runtime *runtime, const axiom_device_buffer *input, uint64_t input_offset, uint32_t rows,
         uint32_t cols, float global_scale, axiom_device_buffer *out_codes, uint64_t codes_offset,

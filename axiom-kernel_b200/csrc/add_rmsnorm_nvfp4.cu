@@ -6,15 +6,23 @@
 // summation order: 256 partial sums over features (c + 256*k) accumulated with
 // fmaf in k order, then the tree 128/64/32/16/8/4/2/1.
 //
-// Throughput kernel: ONE WARP PER ROW.  Lane u loads the 16-byte chunks
-// u + 32*k, so each warp-wide load is 512 contiguous bytes, and the 8 values
-// of a lane's chunk are exactly partial sums 8u..8u+7 of the reference order:
-// the fmaf chains run along k in registers and the tree is a shuffle
-// butterfly (16,8,4 lanes = strides 128,64,32; 2,1 lanes = strides 16,8;
-// strides 4,2,1 inside the lane).  The merged row stays in registers as packed
-// BF16 (it is BF16-valued by construction) for the second sweep.
+// Throughput kernel (add_rmsnorm_stream_kernel): persistent CTAs, one per SM,
+// made of independent 4-warp teams.  A team owns two (or more) shared-memory
+// slots; its first thread fills a slot with one row (hidden | residual) through
+// 1-D bulk copies that complete on the slot's mbarrier, and refills it the
+// moment the team has finished with it, so the next row is always in flight
+// while the current one is processed and no arithmetic warp issues a global
+// load.  Sweep 1 (merge + sum of squares) gives thread t the feature pairs
+// 256k + 2t, 2t+1: those are partial sums 2t and 2t+1 of the reference order,
+// so the fmaf chains run along k in registers; the 256 partials meet in shared
+// memory and every warp runs the reference tree as a shuffle butterfly.  The
+// merged row is written back into the slot (it is BF16-valued by construction),
+// leaves for HBM as one bulk store, and sweep 2 (normalise + quantize) re-reads
+// it in 16-byte chunks, lane pairs forming the 16-value NVFP4 blocks.
 //
-// Latency kernel: one 256-thread CTA per row for small token counts.
+// Latency kernel (add_rmsnorm_cta_rows_kernel): one 256-thread CTA per row for
+// small token counts, the reference's own thread/feature assignment.
+#include "pipeline.cuh"
 #include "runtime.hpp"
 
 namespace axb {
@@ -28,17 +36,10 @@ __device__ __forceinline__ void unpack8(const uint4 &v, float (&x)[8]) {
     x[6] = bf16_lo(v.w); x[7] = bf16_hi(v.w);
 }
 
-__device__ __forceinline__ uint4 pack8(const float (&x)[8]) {
-    return make_uint4(pack_bf16x2(x[0], x[1]), pack_bf16x2(x[2], x[3]), pack_bf16x2(x[4], x[5]),
-                      pack_bf16x2(x[6], x[7]));
-}
-
-__device__ __forceinline__ uint4 ld_cached(const void *p) { return *reinterpret_cast<const uint4 *>(p); }
-
 struct norm_args {
     const uint4 *hidden;    // may be null
     uint4 *residual;        // read; rewritten when hidden != null
-    const uint4 *gamma;
+    const uint16_t *gamma;
     uint4 *norm_out;        // may be null
     uint32_t *codes;        // may be null
     uint8_t *scales;
@@ -50,98 +51,193 @@ struct norm_args {
     uint32_t layout;
     uint32_t groups;
     uint32_t inner_tiles;
+    uint32_t ring_slots;    // stream kernel: shared-memory slots per warp
 };
 
-constexpr uint32_t kWarpsPerCta = 4u;
-
-template <int NCH, bool kAdd>
-__global__ void __launch_bounds__(kWarpsPerCta * 32u)
-add_rmsnorm_warp_rows_kernel(const norm_args a) {
-    const uint32_t lane = threadIdx.x & 31u;
-    const uint32_t warp = blockIdx.x * kWarpsPerCta + (threadIdx.x >> 5);
-    const uint32_t warps = gridDim.x * kWarpsPerCta;
-    const float count = (float)a.cols;
-
-    for (uint32_t row = warp; row < a.rows; row += warps) {
-        const uint64_t base = (uint64_t)row * a.chunks_per_row;
-        uint4 m[NCH];  // merged row, packed BF16
-        if (kAdd) {
-            uint4 h[NCH];
-#pragma unroll
-            for (int k = 0; k < NCH; ++k) {
-                const uint32_t q = lane + 32u * k;
-                const bool ok = q < a.chunks_per_row;
-                h[k] = ok ? ld_stream(a.hidden + base + q) : make_uint4(0u, 0u, 0u, 0u);
-                m[k] = ok ? ld_stream(a.residual + base + q) : make_uint4(0u, 0u, 0u, 0u);
-            }
-#pragma unroll
-            for (int k = 0; k < NCH; ++k) {
-                float x[8], y[8];
-                unpack8(h[k], x);
-                unpack8(m[k], y);
-#pragma unroll
-                for (int i = 0; i < 8; ++i) y[i] = __fadd_rn(y[i], x[i]);
-                m[k] = pack8(y);  // bf16(bf16(res) + bf16(add)): inputs are BF16 already
-                const uint32_t q = lane + 32u * k;
-                if (q < a.chunks_per_row) st_stream(a.residual + base + q, m[k]);
-            }
-        } else {
-#pragma unroll
-            for (int k = 0; k < NCH; ++k) {
-                const uint32_t q = lane + 32u * k;
-                m[k] = q < a.chunks_per_row ? ld_stream(a.residual + base + q) : make_uint4(0u, 0u, 0u, 0u);
-            }
+// Second sweep over one row held in shared memory as BF16: n = bf16((r * inv) * gamma), optional
+// BF16 copy out, NVFP4 quantize.  kExact recomputes every chunk with IEEE divisions (taken only
+// when the straight-line pass flagged a block whose quotients div_by_shared() cannot guarantee).
+template <bool kExact>
+__device__ __forceinline__ void norm_quant_sweep(const norm_args &a, const uint4 *row_sh, const float *gamma_sh,
+                                                 const scale_lut_entry *lut, float2 inv2, uint64_t base,
+                                                 uint32_t iters, uint32_t t, uint8_t *scale_ptr,
+                                                 uint32_t scale_step, bool *needs_exact) {
+    const float4 *gamma_a = reinterpret_cast<const float4 *>(gamma_sh);
+    const float4 *gamma_b = reinterpret_cast<const float4 *>(gamma_sh + (a.cols >> 1));
+#pragma unroll 5
+    for (uint32_t k = 0; k < iters; ++k) {
+        const uint32_t q = t + 128u * k;
+        const bool ok = q < a.chunks_per_row;
+        uint4 m = make_uint4(0u, 0u, 0u, 0u);
+        float4 ga = make_float4(0.f, 0.f, 0.f, 0.f), gb = ga;
+        if (ok) {
+            m = row_sh[q];
+            ga = gamma_a[q];
+            gb = gamma_b[q];
         }
-
-        float p[8] = {0.0f, 0.0f, 0.0f, 0.0f, 0.0f, 0.0f, 0.0f, 0.0f};
-#pragma unroll
-        for (int k = 0; k < NCH; ++k) {
+        const float2 y0 = __fmul2_rn(__fmul2_rn(make_float2(bf16_lo(m.x), bf16_hi(m.x)), inv2), make_float2(ga.x, ga.y));
+        const float2 y1 = __fmul2_rn(__fmul2_rn(make_float2(bf16_lo(m.y), bf16_hi(m.y)), inv2), make_float2(ga.z, ga.w));
+        const float2 y2 = __fmul2_rn(__fmul2_rn(make_float2(bf16_lo(m.z), bf16_hi(m.z)), inv2), make_float2(gb.x, gb.y));
+        const float2 y3 = __fmul2_rn(__fmul2_rn(make_float2(bf16_lo(m.w), bf16_hi(m.w)), inv2), make_float2(gb.z, gb.w));
+        const uint4 nrm = make_uint4(pack_bf16x2(y0.x, y0.y), pack_bf16x2(y1.x, y1.y), pack_bf16x2(y2.x, y2.y), pack_bf16x2(y3.x, y3.y));
+        if (!kExact && a.norm_out && ok) st_stream(a.norm_out + base + q, nrm);
+        if (a.codes) {
             float y[8];
-            unpack8(m[k], y);
-#pragma unroll
-            for (int i = 0; i < 8; ++i) p[i] = __fmaf_rn(y[i], y[i], p[i]);
-        }
-#pragma unroll
-        for (uint32_t off = 16u; off != 0u; off >>= 1u) {
-#pragma unroll
-            for (int i = 0; i < 8; ++i) p[i] = __fadd_rn(p[i], __shfl_xor_sync(0xffffffffu, p[i], off));
-        }
-        const float s4[4] = {__fadd_rn(p[0], p[4]), __fadd_rn(p[1], p[5]), __fadd_rn(p[2], p[6]), __fadd_rn(p[3], p[7])};
-        const float total = __fadd_rn(__fadd_rn(s4[0], s4[2]), __fadd_rn(s4[1], s4[3]));
-        const float inverse = rsqrtf(__fadd_rn(__fdiv_rn(total, count), a.eps));
-
-#pragma unroll
-        for (int k = 0; k < NCH; ++k) {
-            const uint32_t q = lane + 32u * k;
-            const bool ok = q < a.chunks_per_row;
-            float y[8], w[8];
-            unpack8(m[k], y);
-            unpack8(ok ? ld_cached(a.gamma + q) : make_uint4(0u, 0u, 0u, 0u), w);
-#pragma unroll
-            for (int i = 0; i < 8; ++i) y[i] = __fmul_rn(__fmul_rn(y[i], inverse), w[i]);
-            const uint4 n = pack8(y);
-            if (a.norm_out && ok) st_stream(a.norm_out + base + q, n);
-            if (a.codes) {
-                unpack8(n, y);  // the quantizer sees the BF16-rounded values
-                float mx = fmaxf(fmaxf(fmaxf(fabsf(y[0]), fabsf(y[1])), fmaxf(fabsf(y[2]), fabsf(y[3]))),
-                                 fmaxf(fmaxf(fabsf(y[4]), fabsf(y[5])), fmaxf(fabsf(y[6]), fabsf(y[7]))));
-                mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
-                mx = fmaxf(mx, 0.0f);
-                uint32_t scale_code;
-                const uint32_t packed = nvfp4_quantize8(y, mx, a.G, &scale_code);
-                if (ok) {
-                    st_stream(a.codes + base + q, packed);
-                    if ((lane & 1u) == 0u) {
-                        a.scales[scale_offset(row, q >> 1, a.groups, a.inner_tiles, a.layout)] = (uint8_t)scale_code;
-                    }
-                }
+            unpack8(nrm, y);  // the quantizer sees the BF16-rounded values
+            float mx = fmaxf(fmaxf(fmaxf(fabsf(y[0]), fabsf(y[1])), fmaxf(fabsf(y[2]), fabsf(y[3]))),
+                             fmaxf(fmaxf(fabsf(y[4]), fabsf(y[5])), fmaxf(fabsf(y[6]), fabsf(y[7]))));
+            mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
+            mx = fmaxf(mx, 0.0f);
+            uint32_t scale_byte = 0u, packed;
+            if (kExact) packed = nvfp4_quantize8_exact(y[0], y[1], y[2], y[3], y[4], y[5], y[6], y[7], mx, a.G);
+            else packed = nvfp4_quantize8_fast(y, mx, a.G, lut, &scale_byte, needs_exact);
+            if (ok) {
+                st_stream(a.codes + base + q, packed);
+                if (!kExact && (t & 1u) == 0u) scale_ptr[(uint64_t)k * scale_step] = (uint8_t)scale_byte;
             }
         }
     }
 }
 
-// One CTA per row, thread t owns features t + 256*k (the reference's own
-// thread/feature assignment), merged row kept in shared memory as BF16.
+constexpr uint32_t kTeamThreads = 128u;
+constexpr uint32_t kMaxTeams = 8u;
+constexpr uint32_t kMaxSlotsPerTeam = 4u;
+
+__device__ __forceinline__ void team_barrier(uint32_t team) {
+    asm volatile("bar.sync %0, %1;" ::"r"(team + 1u), "r"(kTeamThreads) : "memory");
+}
+
+// Shared memory: [teams x slots x slot_bytes][gamma F32, two planes][scale table][partials teams x 256][barriers]
+template <bool kAdd>
+__global__ void __launch_bounds__(kMaxTeams * kTeamThreads, 1)
+add_rmsnorm_stream_kernel(const norm_args a) {
+    extern __shared__ __align__(128) uint8_t smem[];
+    const uint32_t teams = blockDim.x / kTeamThreads;
+    const uint32_t spt = a.ring_slots;  // slots per team
+    const uint32_t row_bytes = a.cols * 2u;
+    const uint32_t slot_bytes = kAdd ? 2u * row_bytes : row_bytes;
+    float *gamma_sh = reinterpret_cast<float *>(smem + (size_t)teams * spt * slot_bytes);
+    scale_lut_entry *lut = reinterpret_cast<scale_lut_entry *>(gamma_sh + a.cols);
+    float *partials = reinterpret_cast<float *>(lut + 128);              // [teams][256]
+    uint64_t *bars = reinterpret_cast<uint64_t *>(partials + teams * 256u);      // [teams][kMaxSlotsPerTeam]
+
+    const uint32_t tid = threadIdx.x, team = tid / kTeamThreads, t = tid % kTeamThreads, lane = tid & 31u;
+    uint64_t *my_bars = bars + team * kMaxSlotsPerTeam;
+    uint8_t *my_slots = smem + (size_t)team * spt * slot_bytes;
+    float *my_partials = partials + team * 256u;
+    if (t == 0u) {
+        for (uint32_t j = 0; j < spt; ++j) mbar_init(my_bars + j, 1u);
+        mbar_init_fence();
+    }
+    team_barrier(team);
+
+    // rows of this CTA: blockIdx.x + n * gridDim.x; this team takes n = team + teams * i
+    const uint32_t cta_rows = blockIdx.x < a.rows ? (a.rows - blockIdx.x + gridDim.x - 1u) / gridDim.x : 0u;
+    const uint32_t my_rows = team < cta_rows ? (cta_rows - team + teams - 1u) / teams : 0u;
+    const float count = (float)a.cols;
+    const uint32_t k_iters = (a.cols + 255u) / 256u;                      // sweep 1: feature pairs 256k + 2t
+    const uint32_t c_iters = (a.chunks_per_row + kTeamThreads - 1u) / kTeamThreads;  // sweep 2: chunks t + 128k
+
+    auto issue = [&](uint32_t i) {  // thread 0 of the team: start loading the team's i-th row into its slot
+        const uint64_t row = blockIdx.x + (uint64_t)(team + teams * i) * gridDim.x;
+        const uint32_t j = i % spt;
+        uint8_t *slot = my_slots + (size_t)j * slot_bytes;
+        mbar_arrive_expect_tx(my_bars + j, slot_bytes);
+        if (kAdd) bulk_load(slot, a.hidden + row * a.chunks_per_row, row_bytes, my_bars + j);
+        bulk_load(slot + (kAdd ? row_bytes : 0u), a.residual + row * a.chunks_per_row, row_bytes, my_bars + j);
+    };
+    // the first rows are already on their way while the CTA prepares gamma and the scale table
+    if (t == 0u) {
+        for (uint32_t i = 0; i < spt && i < my_rows; ++i) issue(i);
+    }
+    // gamma as F32 in two planes: plane h holds values 8q+4h .. 8q+4h+3 of every chunk q, so a warp's
+    // 16-byte reads are contiguous
+    for (uint32_t f = tid; f < a.cols; f += blockDim.x) {
+        gamma_sh[((f >> 2) & 1u) * (a.cols >> 1) + (f >> 3) * 4u + (f & 3u)] = __uint_as_float((uint32_t)a.gamma[f] << 16);
+    }
+    const bool lut_safe = build_scale_lut(lut, a.codes ? a.G : 1.0f);  // contains the CTA barrier
+
+    for (uint32_t i = 0; i < my_rows; ++i) {
+        const uint32_t j = i % spt;
+        if (!mbar_wait(my_bars + j, (i / spt) & 1u)) break;
+        const uint32_t row = blockIdx.x + (team + teams * i) * gridDim.x;
+        const uint64_t base = (uint64_t)row * a.chunks_per_row;
+        uint8_t *slot = my_slots + (size_t)j * slot_bytes;
+        const uint32_t *hid_sh = reinterpret_cast<const uint32_t *>(slot);
+        uint32_t *res_sh = reinterpret_cast<uint32_t *>(slot + (kAdd ? row_bytes : 0u));
+
+        // sweep 1: merge in place; this thread's two fmaf chains
+        float2 p = make_float2(0.f, 0.f);
+#pragma unroll 5
+        for (uint32_t k = 0; k < k_iters; ++k) {
+            const uint32_t w = 128u * k + t;  // 32-bit word = feature pair 256k + 2t
+            if (2u * w < a.cols) {
+                uint32_t m = res_sh[w];
+                if (kAdd) {
+                    const uint32_t h = hid_sh[w];
+                    const float2 sum = __fadd2_rn(make_float2(bf16_lo(m), bf16_hi(m)), make_float2(bf16_lo(h), bf16_hi(h)));
+                    m = pack_bf16x2(sum.x, sum.y);  // bf16(bf16(res) + bf16(add)): the inputs are BF16 already
+                    res_sh[w] = m;
+                }
+                const float2 v = make_float2(bf16_lo(m), bf16_hi(m));
+                p = __ffma2_rn(v, v, p);
+            }
+        }
+        reinterpret_cast<float2 *>(my_partials)[t] = p;
+        if (kAdd) fence_async_shared();
+        team_barrier(team);
+        if (kAdd && t == 0u) {
+            // the merged row leaves as one bulk store; the slot stays in use until it has been read
+            bulk_store(a.residual + base, res_sh, row_bytes);
+            bulk_commit();
+        }
+        // reference tree over the 256 partials: lane l takes 8l..8l+7, butterfly 16,8,4 lanes
+        // (= strides 128,64,32), 2,1 lanes (= 16,8), then strides 4,2,1 inside the lane
+        float s[8];
+        {
+            const float4 lo = reinterpret_cast<const float4 *>(my_partials)[2u * lane];
+            const float4 hi = reinterpret_cast<const float4 *>(my_partials)[2u * lane + 1u];
+            s[0] = lo.x; s[1] = lo.y; s[2] = lo.z; s[3] = lo.w; s[4] = hi.x; s[5] = hi.y; s[6] = hi.z; s[7] = hi.w;
+        }
+#pragma unroll
+        for (uint32_t off = 16u; off != 0u; off >>= 1u) {
+#pragma unroll
+            for (int e = 0; e < 8; ++e) s[e] = __fadd_rn(s[e], __shfl_xor_sync(0xffffffffu, s[e], off));
+        }
+        const float t0 = __fadd_rn(s[0], s[4]), t1 = __fadd_rn(s[1], s[5]), t2 = __fadd_rn(s[2], s[6]), t3 = __fadd_rn(s[3], s[7]);
+        const float total = __fadd_rn(__fadd_rn(t0, t2), __fadd_rn(t1, t3));
+        const float inverse = rsqrtf(__fadd_rn(__fdiv_rn(total, count), a.eps));
+        const float2 inv2 = make_float2(inverse, inverse);
+
+        // sweep 2: normalise, round, quantize.  Chunk t + 128k is block (t>>1) + 64k.
+        const uint32_t g0 = t >> 1;
+        uint8_t *scale_ptr;
+        uint32_t scale_step;
+        if (a.layout == AXIOM_SCALE_LAYOUT_CANONICAL) {
+            scale_ptr = a.scales + (uint64_t)row * a.groups + g0;
+            scale_step = 64u;
+        } else {
+            scale_ptr = a.scales + ((uint64_t)(row >> 7) * a.inner_tiles + (g0 >> 2)) * 512u + (row & 31u) * 16u +
+                        ((row & 127u) >> 5) * 4u + (g0 & 3u);
+            scale_step = 16u * 512u;
+        }
+        bool needs_exact = false;
+        const uint4 *row_sh = reinterpret_cast<const uint4 *>(res_sh);
+        norm_quant_sweep<false>(a, row_sh, gamma_sh, lut, inv2, base, c_iters, t, scale_ptr, scale_step, &needs_exact);
+        if (a.codes && (!lut_safe || __any_sync(0xffffffffu, needs_exact))) {
+            norm_quant_sweep<true>(a, row_sh, gamma_sh, lut, inv2, base, c_iters, t, scale_ptr, scale_step, &needs_exact);
+        }
+        // the whole team is done with the slot: refill it with the row that comes spt rows later
+        team_barrier(team);
+        if (t == 0u) {
+            if (kAdd) bulk_wait_read_all();
+            if (i + spt < my_rows) issue(i + spt);
+        }
+    }
+    if (kAdd && t == 0u) bulk_wait_read_all();
+}
+
+// One CTA per row, thread t owns features t + 256*k, merged row kept in shared memory as BF16.
 constexpr uint32_t kCtaThreads = 256u;
 
 __global__ void __launch_bounds__(kCtaThreads)
@@ -152,7 +248,7 @@ add_rmsnorm_cta_rows_kernel(const norm_args a) {
     const uint32_t tid = threadIdx.x;
     const uint16_t *hidden = reinterpret_cast<const uint16_t *>(a.hidden);
     uint16_t *residual = reinterpret_cast<uint16_t *>(a.residual);
-    const uint16_t *gamma = reinterpret_cast<const uint16_t *>(a.gamma);
+    const uint16_t *gamma = a.gamma;
     uint16_t *norm_out = reinterpret_cast<uint16_t *>(a.norm_out);
     uint8_t *codes = reinterpret_cast<uint8_t *>(a.codes);
 
@@ -160,8 +256,8 @@ add_rmsnorm_cta_rows_kernel(const norm_args a) {
         const uint64_t base = (uint64_t)row * a.cols;
         float sum = 0.0f;
         for (uint32_t f = tid; f < a.cols; f += kCtaThreads) {
-            float r = __uint_as_float((uint32_t)residual[base + f] << 16);
             uint16_t bits = residual[base + f];
+            float r = __uint_as_float((uint32_t)bits << 16);
             if (hidden) {
                 r = __fadd_rn(r, __uint_as_float((uint32_t)hidden[base + f] << 16));
                 bits = (uint16_t)(pack_bf16x2(r, 0.0f) & 0xffffu);
@@ -220,16 +316,29 @@ add_rmsnorm_cta_rows_kernel(const norm_args a) {
     }
 }
 
-template <int NCH>
-void launch_warp_rows(const norm_args &a, cudaStream_t stream) {
-    uint32_t ctas = (a.rows + kWarpsPerCta - 1u) / kWarpsPerCta;
-    const uint32_t cap = kSmCount * 4u;
-    if (ctas > cap) ctas = cap;
-    if (a.hidden) add_rmsnorm_warp_rows_kernel<NCH, true><<<ctas, kWarpsPerCta * 32u, 0, stream>>>(a);
-    else add_rmsnorm_warp_rows_kernel<NCH, false><<<ctas, kWarpsPerCta * 32u, 0, stream>>>(a);
+constexpr size_t kSmemBudget = 227u * 1024u;
+
+size_t stream_fixed_bytes(uint32_t cols, uint32_t teams) {
+    return (size_t)cols * sizeof(float) + 128u * sizeof(scale_lut_entry) + (size_t)teams * 256u * sizeof(float) +
+           (size_t)teams * kMaxSlotsPerTeam * sizeof(uint64_t);
+}
+
+template <bool kAdd>
+void launch_stream(const norm_args &a, uint32_t teams, size_t smem, cudaStream_t stream) {
+    static bool configured[64] = {};  // the attribute is per device; one process may drive several
+    int dev = 0;
+    cudaGetDevice(&dev);
+    if (dev >= 0 && dev < 64 && !configured[dev]) {
+        cudaFuncSetAttribute(add_rmsnorm_stream_kernel<kAdd>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmemBudget);
+        configured[dev] = true;
+    }
+    const uint32_t ctas = a.rows < kSmCount ? a.rows : kSmCount;
+    add_rmsnorm_stream_kernel<kAdd><<<ctas, teams * kTeamThreads, smem, stream>>>(a);
 }
 
 }  // namespace
+
+unsigned int add_rmsnorm_fault_word() { return read_and_clear_pipeline_fault(); }
 
 int launch_add_rmsnorm_nvfp4_bf16(const void *hidden, void *residual, const void *gamma, float eps, uint32_t rows,
                                   uint32_t cols, float G, void *norm_out, uint8_t *codes, uint8_t *scales,
@@ -237,7 +346,7 @@ int launch_add_rmsnorm_nvfp4_bf16(const void *hidden, void *residual, const void
     norm_args a{};
     a.hidden = (const uint4 *)hidden;
     a.residual = (uint4 *)residual;
-    a.gamma = (const uint4 *)gamma;
+    a.gamma = (const uint16_t *)gamma;
     a.norm_out = (uint4 *)norm_out;
     a.codes = (uint32_t *)codes;
     a.scales = scales;
@@ -250,21 +359,28 @@ int launch_add_rmsnorm_nvfp4_bf16(const void *hidden, void *residual, const void
     a.groups = cols / kGroup;
     a.inner_tiles = (a.groups + 3u) / 4u;
 
-    const uint32_t nch = (a.chunks_per_row + 31u) / 32u;
-    // Few rows: latency matters, spread each row over a whole CTA.  Very wide
-    // rows do not fit the register-resident warp kernel either.
-    const bool use_cta = rows < 2u * kSmCount || nch > 32u;
+    // Stream kernel shape: as many 4-warp teams as double-buffered slots fit beside the
+    // F32 gamma copy (5 teams x 2 slots of 20 KB at 5120 columns with an addend).
+    const size_t slot_bytes = (size_t)cols * 2u * (hidden ? 2u : 1u);
+    uint32_t teams = kMaxTeams;
+    while (teams != 0u && stream_fixed_bytes(cols, teams) + (size_t)teams * 2u * slot_bytes > kSmemBudget) --teams;
+    uint32_t spt = 0u;
+    if (teams != 0u) {
+        spt = (uint32_t)((kSmemBudget - stream_fixed_bytes(cols, teams)) / (teams * slot_bytes));
+        if (spt > kMaxSlotsPerTeam) spt = kMaxSlotsPerTeam;
+    }
+    // Few rows: latency matters, spread each row over a whole CTA.  Rows too
+    // wide for two double-buffered teams take that kernel as well.
+    const bool use_cta = rows < 2u * kSmCount || teams < 2u;
     if (use_cta) {
         uint32_t ctas = rows < kSmCount * 8u ? rows : kSmCount * 8u;
         add_rmsnorm_cta_rows_kernel<<<ctas, kCtaThreads, (size_t)cols * sizeof(uint16_t), stream>>>(a);
-    } else if (nch <= 4u) launch_warp_rows<4>(a, stream);
-    else if (nch <= 8u) launch_warp_rows<8>(a, stream);
-    else if (nch <= 12u) launch_warp_rows<12>(a, stream);
-    else if (nch <= 16u) launch_warp_rows<16>(a, stream);
-    else if (nch <= 20u) launch_warp_rows<20>(a, stream);
-    else if (nch <= 24u) launch_warp_rows<24>(a, stream);
-    else if (nch <= 28u) launch_warp_rows<28>(a, stream);
-    else launch_warp_rows<32>(a, stream);
+    } else {
+        a.ring_slots = spt;
+        const size_t smem = stream_fixed_bytes(cols, teams) + (size_t)teams * spt * slot_bytes;
+        if (hidden) launch_stream<true>(a, teams, smem, stream);
+        else launch_stream<false>(a, teams, smem, stream);
+    }
     note_launch();
     return AXIOM_OK;
 }

@@ -4,6 +4,7 @@
 // restructured for HBM streaming: every lane owns one 16-byte chunk (8 values,
 // half a block), the block maximum is one lane-pair shuffle, and a warp reads
 // 4 x 512 contiguous bytes before it converts anything.
+#include "pipeline.cuh"
 #include "runtime.hpp"
 
 namespace axb {
@@ -26,33 +27,58 @@ __device__ __forceinline__ float absmax8(const float (&x)[8]) {
     return fmaxf(a, b);
 }
 
+// Every warp streams one contiguous range of chunks (ranges differ by at most
+// one 128-byte step, so all warps of the persistent grid finish together).
 __global__ void __launch_bounds__(kThreads)
-nvfp4_quantize_bf16_kernel(const uint4 *__restrict__ in, uint32_t total_chunks, uint32_t chunks_per_row,
-                           float G, uint32_t *__restrict__ codes, uint8_t *__restrict__ scales,
-                           uint32_t layout, uint32_t groups, uint32_t inner_tiles) {
+nvfp4_quantize_bf16_kernel(const uint4 *__restrict__ in, uint32_t total_chunks, uint32_t chunks_per_warp,
+                           uint32_t chunks_per_row, float G, uint32_t *__restrict__ codes,
+                           uint8_t *__restrict__ scales, uint32_t layout, uint32_t groups, uint32_t inner_tiles) {
+    __shared__ scale_lut_entry lut[128];
     const uint32_t lane = threadIdx.x & 31u;
     const uint32_t warp = (blockIdx.x * kThreads + threadIdx.x) >> 5;
-    const uint32_t warps = (gridDim.x * kThreads) >> 5;
+    const uint64_t first = (uint64_t)warp * chunks_per_warp;
+    const uint64_t last = first + chunks_per_warp < total_chunks ? first + chunks_per_warp : total_chunks;
     constexpr uint32_t kTile = 32u * kUnroll;
-    for (uint64_t tile = warp; tile * kTile < total_chunks; tile += warps) {
-        uint4 v[kUnroll];
+    // the first tile is requested before the CTA builds its scale table
+    uint4 v[kUnroll];
 #pragma unroll
-        for (uint32_t j = 0; j < kUnroll; ++j) {
-            const uint64_t c = tile * kTile + j * 32u + lane;
-            v[j] = c < total_chunks ? ld_stream(in + c) : make_uint4(0u, 0u, 0u, 0u);
+    for (uint32_t j = 0; j < kUnroll; ++j) {
+        const uint64_t c = first + j * 32u + lane;
+        v[j] = c < last ? ld_stream(in + c) : make_uint4(0u, 0u, 0u, 0u);
+    }
+    const bool lut_safe = build_scale_lut(lut, G);
+    for (uint64_t tile = first; tile < last; tile += kTile) {
+        uint4 nxt[kUnroll];
+#pragma unroll
+        for (uint32_t j = 0; j < kUnroll; ++j) {  // software pipeline: next tile in flight during this one
+            const uint64_t c = tile + kTile + j * 32u + lane;
+            nxt[j] = c < last ? ld_stream(in + c) : make_uint4(0u, 0u, 0u, 0u);
         }
+        uint32_t packed[kUnroll], scale_byte[kUnroll];
+        float mx[kUnroll];
+        bool needs_exact = false;
 #pragma unroll
         for (uint32_t j = 0; j < kUnroll; ++j) {
-            const uint64_t c = tile * kTile + j * 32u + lane;
             float x[8];
             unpack8(v[j], x);
             float m = absmax8(x);
             m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, 1));
-            m = fmaxf(m, 0.0f);  // an all-NaN block has maximum 0, as a running fmaxf from 0 gives
-            uint32_t scale_code;
-            const uint32_t packed = nvfp4_quantize8(x, m, G, &scale_code);
-            if (c < total_chunks) {
-                st_stream(codes + c, packed);
+            mx[j] = fmaxf(m, 0.0f);  // an all-NaN block has maximum 0, as a running fmaxf from 0 gives
+            packed[j] = nvfp4_quantize8_fast(x, mx[j], G, lut, &scale_byte[j], &needs_exact);
+        }
+        if (!lut_safe || __any_sync(0xffffffffu, needs_exact)) {
+#pragma unroll 1
+            for (uint32_t j = 0; j < kUnroll; ++j) {
+                float x[8];
+                unpack8(v[j], x);
+                packed[j] = nvfp4_quantize8_exact(x[0], x[1], x[2], x[3], x[4], x[5], x[6], x[7], mx[j], G);
+            }
+        }
+#pragma unroll
+        for (uint32_t j = 0; j < kUnroll; ++j) {
+            const uint64_t c = tile + j * 32u + lane;
+            if (c < last) {
+                st_stream(codes + c, packed[j]);
                 if ((lane & 1u) == 0u) {
                     uint64_t off = c >> 1;
                     if (layout != AXIOM_SCALE_LAYOUT_CANONICAL) {
@@ -60,9 +86,10 @@ nvfp4_quantize_bf16_kernel(const uint4 *__restrict__ in, uint32_t total_chunks, 
                         const uint32_t group = ((uint32_t)c - row * chunks_per_row) >> 1;
                         off = scale_offset(row, group, groups, inner_tiles, layout);
                     }
-                    scales[off] = (uint8_t)scale_code;
+                    scales[off] = (uint8_t)scale_byte[j];
                 }
             }
+            v[j] = nxt[j];
         }
     }
 }
@@ -107,13 +134,17 @@ int launch_nvfp4_quantize_bf16(const void *input, uint32_t rows, uint32_t cols, 
     const uint32_t chunks_per_row = cols / 8u;
     const uint32_t total = rows * chunks_per_row;
     const uint32_t groups = cols / kGroup;
-    const uint32_t tiles = (total + 32u * kUnroll - 1u) / (32u * kUnroll);
     const uint32_t warps_per_block = kThreads / 32u;
-    uint32_t blocks = (tiles + warps_per_block - 1u) / warps_per_block;
-    const uint32_t cap = kSmCount * 16u;  // a few waves of resident CTAs, each striding over tiles
-    if (blocks > cap) blocks = cap;
+    // persistent grid: 6 CTAs of 256 threads per SM, or fewer when there is little to do
+    uint32_t blocks = kSmCount * 6u;
+    const uint32_t min_chunks_per_warp = 32u * kUnroll;
+    const uint32_t needed = (total + min_chunks_per_warp * warps_per_block - 1u) / (min_chunks_per_warp * warps_per_block);
+    if (blocks > needed) blocks = needed;
+    const uint32_t warps = blocks * warps_per_block;
+    uint32_t per_warp = (total + warps - 1u) / warps;
+    per_warp = (per_warp + 7u) & ~7u;  // ranges start on 128-byte boundaries and never split a block
     nvfp4_quantize_bf16_kernel<<<blocks, kThreads, 0, stream>>>(
-            (const uint4 *)input, total, chunks_per_row, G, (uint32_t *)codes, scales, layout, groups,
+            (const uint4 *)input, total, per_warp, chunks_per_row, G, (uint32_t *)codes, scales, layout, groups,
             (groups + 3u) / 4u);
     note_launch();
     return AXIOM_OK;

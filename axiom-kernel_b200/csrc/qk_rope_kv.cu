@@ -19,6 +19,7 @@
 //   3. normalise, exchange with the partner lane, rotate, round, store
 // The frequency table is an input: it is evaluated once per model on the
 // device (yarn_inv_freq_kernel) instead of powf/logf per thread per call.
+#include "pipeline.cuh"
 #include "runtime.hpp"
 
 namespace axb {
@@ -238,6 +239,8 @@ void launch_qk(const qk_dev_args &a, cudaStream_t stream) {
 bool is_pow2(uint32_t v) { return v && !(v & (v - 1u)); }
 
 }  // namespace
+
+unsigned int qk_fault_word() { return read_and_clear_pipeline_fault(); }
 
 int launch_qk_norm_rope_paged_bf16(const axiom_qk_rope_args *p, cudaStream_t stream) {
     qk_dev_args a{};

@@ -67,6 +67,11 @@ int launch_embedding_gather_bf16(const void *table, uint32_t vocab, uint32_t hid
 int launch_yarn_inv_freq(const axiom_rope_config *config, float *out, cudaStream_t stream);
 int launch_qk_norm_rope_paged_bf16(const axiom_qk_rope_args *args, cudaStream_t stream);
 
+// bounded-wait fault words of the pipelined kernels (read-and-clear, synchronising)
+unsigned int add_rmsnorm_fault_word();
+unsigned int swiglu_fault_word();
+unsigned int qk_fault_word();
+
 // argument validation shared by the raw, buffer and host flavours
 int check_nvfp4_quantize(const void *input, uint32_t rows, uint32_t cols, float G, const void *codes,
                          const void *scales, uint32_t layout);

@@ -11,6 +11,7 @@
 // The FP8 flavour needs the whole row before it can scale it: one CTA owns one
 // row, every thread keeps its share of y in registers across the row-max
 // reduction, so gate|up is read once and only the codes are written.
+#include "pipeline.cuh"
 #include "runtime.hpp"
 
 namespace axb {
@@ -140,6 +141,8 @@ __global__ void __launch_bounds__(kNvThreads)
 swiglu_nvfp4_kernel(const uint4 *__restrict__ in, uint32_t rows, uint32_t chunks, float G,
                     uint32_t *__restrict__ codes, uint8_t *__restrict__ scales, uint32_t layout,
                     uint32_t groups, uint32_t inner_tiles) {
+    __shared__ scale_lut_entry lut[128];
+    const bool lut_safe = build_scale_lut(lut, G);
     const uint32_t lane = threadIdx.x & 31u;
     const uint32_t warp = (blockIdx.x * kNvThreads + threadIdx.x) >> 5;
     const uint32_t warps = (gridDim.x * kNvThreads) >> 5;
@@ -170,7 +173,11 @@ swiglu_nvfp4_kernel(const uint4 *__restrict__ in, uint32_t rows, uint32_t chunks
             m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, 1));
             m = fmaxf(m, 0.0f);
             uint32_t scale_code;
-            const uint32_t packed = nvfp4_quantize8(y, m, G, &scale_code);
+            bool needs_exact = false;
+            uint32_t packed = nvfp4_quantize8_fast(y, m, G, lut, &scale_code, &needs_exact);
+            if (!lut_safe || __any_sync(0xffffffffu, needs_exact)) {
+                packed = nvfp4_quantize8_exact(y[0], y[1], y[2], y[3], y[4], y[5], y[6], y[7], m, G);
+            }
             if (c < total) {
                 st_stream(codes + c, packed);
                 if ((lane & 1u) == 0u) {
@@ -225,6 +232,8 @@ int launch_fp8_rows(const void *in, uint32_t rows, uint32_t width, uint32_t in_c
 }
 
 }  // namespace
+
+unsigned int swiglu_fault_word() { return read_and_clear_pipeline_fault(); }
 
 int launch_swiglu_fp8_bf16(const void *gate_up, uint32_t rows, uint32_t width, uint8_t *codes, float *scales,
                            cudaStream_t stream) {

@@ -170,6 +170,10 @@ def main():
     ap.add_argument("--skip-ops", action="store_true", help="only the headline workload")
     ap.add_argument("--skip-e2e", action="store_true")
     ap.add_argument("--skip-cpu", action="store_true")
+    ap.add_argument("--only", default=None,
+                    choices=["add_rmsnorm", "nvfp4_quantize", "qk", "swiglu_fp8", "swiglu_nvfp4", "chain"],
+                    help="run one configuration alone (profiling aid): device-timed, no e2e / CPU legs")
+    ap.add_argument("--rows", type=int, default=0, help="with --only: override the token count")
     args = ap.parse_args()
     if args.impl == "reference":
         return reference_arm(args)
@@ -195,6 +199,16 @@ def main():
     device = torch.device("cuda", local)
     stream = torch.cuda.Stream(device)
     peak, peak_kind = measured_peak_gbs()
+    if args.only and args.only != "add_rmsnorm":
+        res = bench_other_ops(torch, axk, wl, local, device, stream, peak, only=args.only, rows_override=args.rows,
+                              iters=args.steps, warm=args.warmup)
+        print(json.dumps({"only": args.only, "result": res}), flush=True)
+        return 0
+    global ROWS
+    if args.only == "add_rmsnorm":
+        args.skip_e2e = args.skip_ops = args.skip_cpu = True
+        if args.rows:
+            ROWS = args.rows
 
     # ---- headline: add + RMSNorm + NVFP4, device resident ---------------------------------
     sets = []
@@ -337,12 +351,15 @@ def main():
     return 0
 
 
-def bench_other_ops(torch, axk, wl, local, device, stream, peak):
+def bench_other_ops(torch, axk, wl, local, device, stream, peak, only=None, rows_override=0, iters=50, warm=5):
     """Device-timed throughput of configurations 1, 3, 4 and the decode chain (5)."""
     out = {}
-    iters, warm = 50, 5
 
-    def timed(fn, n=iters):
+    def want(name):
+        return only is None or only == name
+
+    def timed(fn, n=None):
+        n = min(n, iters) if n else iters
         for i in range(warm):
             fn(i)
         return event_time_ms(torch, stream, fn, n)
@@ -352,8 +369,20 @@ def bench_other_ops(torch, axk, wl, local, device, stream, peak):
         out[name] = {"ms": ms, "gbs": gbs, "frac_of_peak": gbs / peak, "tokens_per_s": rows / (ms * 1e-3),
                      "algorithmic_bytes": algo, "note": note}
 
+    if want("nvfp4_quantize"):
+        bench_nvfp4_quantize(torch, axk, wl, local, device, stream, timed, report, rows_override or 4096)
+    if want("qk"):
+        bench_qk(torch, axk, wl, local, device, stream, timed, report, rows_override or 8192)
+    if want("swiglu_fp8") or want("swiglu_nvfp4"):
+        bench_swiglu(torch, axk, wl, local, device, stream, timed, report, rows_override or 16384, want)
+    if want("chain"):
+        out["decode_chain"] = bench_chain(torch, axk, wl, local, device, stream, timed, peak)
+    return out
+
+
+def bench_nvfp4_quantize(torch, axk, wl, local, device, stream, timed, report, rows):
     # config 1: BF16 -> NVFP4, [4096 x 5120]; 8 rotating inputs (8 x 42 MB > L2)
-    rows, cols = 4096, 5120
+    cols = 5120
     xs = [wl.quantize_input_torch(torch, device, rows, cols, seed=s) for s in range(8)]
     codes = [torch.empty((rows, cols // 2), dtype=torch.uint8, device=device) for _ in range(8)]
     scales = [torch.empty((rows, cols // 16), dtype=torch.uint8, device=device) for _ in range(8)]
@@ -362,10 +391,10 @@ def bench_other_ops(torch, axk, wl, local, device, stream, peak):
         ms = timed(lambda i: axk.nvfp4_quantize(local, xs[i % 8], rows, cols, G, codes[i % 8], scales[i % 8], layout, stream))
         report(f"nvfp4_quantize_{tag}", ms, rows * cols * 2 + rows * cols // 2 + rows * cols // 16, rows,
                "config 1, 8 rotating buffer sets")
-    del xs, codes, scales
 
+
+def bench_qk(torch, axk, wl, local, device, stream, timed, report, T):
     # config 3: q/k norm + RoPE + paged KV, T = 8192; 2 rotating sets (2 x 302 MB)
-    T = 8192
     qk_sets = []
     inv_freq = torch.empty(64, dtype=torch.float32, device=device)
     axk.check(axk.yarn_inv_freq(local, 128, wl.ROPE_THETA, wl.YARN_FACTOR, wl.YARN_ORIGINAL_CONTEXT, 32.0, 1.0, inv_freq, stream), "yarn")
@@ -383,23 +412,30 @@ def bench_other_ops(torch, axk, wl, local, device, stream, peak):
     ms = timed(lambda i: axk.qk_norm_rope_paged(local, qk_sets[i % 2][0], stream))
     report("qk_norm_rope_paged_kv", ms, 2 * T * 64 * 128 * 2 + 2 * T * 8 * 128 * 2 + T * 4 + 4096 * 4 + 512, T,
            "config 3, Q in place, K to 16-token BF16 pages")
-    del qk_sets, pool
 
+
+def bench_swiglu(torch, axk, wl, local, device, stream, timed, report, T, want):
     # config 4: SwiGLU + FP8, T = 16384 (1.43 GB per pass: larger than L2 by itself)
-    T, W = 16384, wl.FFN
+    W = wl.FFN
     gu = wl.swiglu_input_torch(torch, device, T, W)
-    c8 = torch.empty((T, W), dtype=torch.uint8, device=device)
-    s8 = torch.empty((T,), dtype=torch.float32, device=device)
-    ms = timed(lambda i: axk.swiglu_fp8(local, gu, T, W, c8, s8, stream), n=20)
-    report("swiglu_fp8", ms, T * 2 * W * 2 + T * W + T * 4, T, "config 4")
-    c4 = torch.empty((T, W // 2), dtype=torch.uint8, device=device)
-    s4 = torch.empty((T, W // 16), dtype=torch.uint8, device=device)
-    ms = timed(lambda i: axk.swiglu_nvfp4(local, gu, T, W, 40.0, c4, s4, 0, stream), n=20)
-    report("swiglu_nvfp4", ms, T * 2 * W * 2 + T * W // 2 + T * W // 16, T, "SwiGLU -> NVFP4 (down-projection input)")
-    del gu, c8, s8, c4, s4
+    if want("swiglu_fp8"):
+        c8 = torch.empty((T, W), dtype=torch.uint8, device=device)
+        s8 = torch.empty((T,), dtype=torch.float32, device=device)
+        ms = timed(lambda i: axk.swiglu_fp8(local, gu, T, W, c8, s8, stream), n=20)
+        report("swiglu_fp8", ms, T * 2 * W * 2 + T * W + T * 4, T, "config 4")
+    if want("swiglu_nvfp4"):
+        c4 = torch.empty((T, W // 2), dtype=torch.uint8, device=device)
+        s4 = torch.empty((T, W // 16), dtype=torch.uint8, device=device)
+        ms = timed(lambda i: axk.swiglu_nvfp4(local, gu, T, W, 40.0, c4, s4, 0, stream), n=20)
+        report("swiglu_nvfp4", ms, T * 2 * W * 2 + T * W // 2 + T * W // 16, T, "SwiGLU -> NVFP4 (down-projection input)")
 
+
+def bench_chain(torch, axk, wl, local, device, stream, timed, peak):
     # config 5: decode chain, microseconds per layer-chain, eager launches and one CUDA graph replay
     table, _ = wl.embedding_inputs_torch(torch, device, 1)
+    inv_freq = torch.empty(64, dtype=torch.float32, device=device)
+    axk.check(axk.yarn_inv_freq(local, 128, wl.ROPE_THETA, wl.YARN_FACTOR, wl.YARN_ORIGINAL_CONTEXT, 32.0, 1.0, inv_freq, stream), "yarn")
+    status = torch.zeros(1, dtype=torch.int32, device=device)
     chain = {}
     for m in (1, 8, 64, 256):
         ids = torch.randint(0, wl.VOCAB, (m,), device=device).to(torch.int32)
@@ -443,8 +479,7 @@ def bench_other_ops(torch, axk, wl, local, device, stream, peak):
         chain[str(m)] = {"eager_us": eager_us, "graph_us": graph_us, "algorithmic_bytes": algo,
                          "frac_of_peak_graph": algo / (graph_us * 1e-6) / 1e9 / peak}
         del graph
-    out["decode_chain"] = chain
-    return out
+    return chain
 
 
 if __name__ == "__main__":

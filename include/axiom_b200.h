@@ -276,6 +276,12 @@ uint64_t axiom_nvfp4_scale_plane_offset(uint32_t row, uint32_t group, uint32_t g
 /* Number of kernel launches issued by this library in this process (bench bookkeeping). */
 uint64_t axiom_b200_kernel_launch_count(void);
 
+/* The pipelined kernels wait on shared-memory barriers with a bounded number of
+ * polls; a wait that runs out raises a device word instead of hanging.  This
+ * synchronises `device`, returns the OR of those words (0 = no fault) and
+ * clears them. */
+uint32_t axiom_b200_pipeline_faults(int device);
+
 #ifdef __cplusplus
 }
 #endif

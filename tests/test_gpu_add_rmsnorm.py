@@ -115,3 +115,10 @@ def test_config2_full_size_properties(axk, cuda_device):
     assert np.all(np.abs(a - b) <= ol.bf16_ulp(b))
     own_codes, own_scales = ol.nvfp4_quantize_bf16(norm, G)
     assert np.array_equal(codes, own_codes) and np.array_equal(scales.reshape(rows, cols // 16), own_scales)
+
+
+def test_no_bounded_wait_ran_out(axk, cuda_device):
+    """The pipelined kernels poll their shared-memory barriers a bounded number of times; none may have given up."""
+    hidden, residual, gamma = wl.add_rmsnorm_inputs_np(2048, 5120)
+    run(axk, hidden, residual, gamma, 100.0)
+    assert axk.lib().axiom_b200_pipeline_faults(0) == 0
