@@ -55,45 +55,52 @@ struct norm_args {
 };
 
 // Second sweep over one row held in shared memory as BF16: n = bf16((r * inv) * gamma), optional
-// BF16 copy out, NVFP4 quantize.  kExact recomputes every chunk with IEEE divisions (taken only
-// when the straight-line pass flagged a block whose quotients div_by_shared() cannot guarantee).
-template <bool kExact>
+// BF16 copy out, NVFP4 quantize.  Thread t takes the 16-byte chunks t + 128k; lane pairs form
+// the 16-value blocks.  kExact recomputes every chunk with IEEE divisions and the reference's
+// NaN-dropping maximum (taken only when the straight-line pass flagged a block).  kFull: the
+// row is a whole number of 128-chunk steps, so no bounds predicate is needed.
+template <bool kExact, bool kFull>
 __device__ __forceinline__ void norm_quant_sweep(const norm_args &a, const uint4 *row_sh, const float *gamma_sh,
                                                  const scale_lut_entry *lut, float2 inv2, uint64_t base,
                                                  uint32_t iters, uint32_t t, uint8_t *scale_ptr,
                                                  uint32_t scale_step, bool *needs_exact) {
-    const float4 *gamma_a = reinterpret_cast<const float4 *>(gamma_sh);
-    const float4 *gamma_b = reinterpret_cast<const float4 *>(gamma_sh + (a.cols >> 1));
+    const uint4 *src = row_sh + t;
+    const float4 *gamma_a = reinterpret_cast<const float4 *>(gamma_sh) + t;
+    const float4 *gamma_b = reinterpret_cast<const float4 *>(gamma_sh + (a.cols >> 1)) + t;
+    uint4 *norm_dst = a.norm_out ? a.norm_out + base + t : nullptr;
+    uint32_t *code_dst = a.codes ? a.codes + base + t : nullptr;
 #pragma unroll 5
     for (uint32_t k = 0; k < iters; ++k) {
-        const uint32_t q = t + 128u * k;
-        const bool ok = q < a.chunks_per_row;
+        const bool ok = kFull || t + 128u * k < a.chunks_per_row;
         uint4 m = make_uint4(0u, 0u, 0u, 0u);
         float4 ga = make_float4(0.f, 0.f, 0.f, 0.f), gb = ga;
         if (ok) {
-            m = row_sh[q];
-            ga = gamma_a[q];
-            gb = gamma_b[q];
+            m = src[128u * k];
+            ga = gamma_a[128u * k];
+            gb = gamma_b[128u * k];
         }
         const float2 y0 = __fmul2_rn(__fmul2_rn(make_float2(bf16_lo(m.x), bf16_hi(m.x)), inv2), make_float2(ga.x, ga.y));
         const float2 y1 = __fmul2_rn(__fmul2_rn(make_float2(bf16_lo(m.y), bf16_hi(m.y)), inv2), make_float2(ga.z, ga.w));
         const float2 y2 = __fmul2_rn(__fmul2_rn(make_float2(bf16_lo(m.z), bf16_hi(m.z)), inv2), make_float2(gb.x, gb.y));
         const float2 y3 = __fmul2_rn(__fmul2_rn(make_float2(bf16_lo(m.w), bf16_hi(m.w)), inv2), make_float2(gb.z, gb.w));
         const uint4 nrm = make_uint4(pack_bf16x2(y0.x, y0.y), pack_bf16x2(y1.x, y1.y), pack_bf16x2(y2.x, y2.y), pack_bf16x2(y3.x, y3.y));
-        if (!kExact && a.norm_out && ok) st_stream(a.norm_out + base + q, nrm);
-        if (a.codes) {
+        if (!kExact && norm_dst && ok) st_stream(norm_dst + 128u * k, nrm);
+        if (code_dst) {
             float y[8];
             unpack8(nrm, y);  // the quantizer sees the BF16-rounded values
-            float mx = fmaxf(fmaxf(fmaxf(fabsf(y[0]), fabsf(y[1])), fmaxf(fabsf(y[2]), fabsf(y[3]))),
-                             fmaxf(fmaxf(fabsf(y[4]), fabsf(y[5])), fmaxf(fabsf(y[6]), fabsf(y[7]))));
-            mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
-            mx = fmaxf(mx, 0.0f);
-            uint32_t scale_byte = 0u, packed;
-            if (kExact) packed = nvfp4_quantize8_exact(y[0], y[1], y[2], y[3], y[4], y[5], y[6], y[7], mx, a.G);
-            else packed = nvfp4_quantize8_fast(y, mx, a.G, lut, &scale_byte, needs_exact);
+            uint32_t scale_byte, packed;
+            if (kExact) {
+                float mx = absmax8_drop_nan(y);
+                mx = fmaxf(fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 1)), 0.0f);
+                packed = nvfp4_quantize8_exact(y[0], y[1], y[2], y[3], y[4], y[5], y[6], y[7], mx, a.G, &scale_byte);
+            } else {
+                float mx = absmax8_nan(y);
+                mx = max_nan(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
+                packed = nvfp4_quantize8_fast(y, mx, a.G, lut, &scale_byte, needs_exact);
+            }
             if (ok) {
-                st_stream(a.codes + base + q, packed);
-                if (!kExact && (t & 1u) == 0u) scale_ptr[(uint64_t)k * scale_step] = (uint8_t)scale_byte;
+                st_stream(code_dst + 128u * k, packed);
+                if ((t & 1u) == 0u) scale_ptr[(uint64_t)k * scale_step] = (uint8_t)scale_byte;
             }
         }
     }
@@ -108,7 +115,7 @@ __device__ __forceinline__ void team_barrier(uint32_t team) {
 }
 
 // Shared memory: [teams x slots x slot_bytes][gamma F32, two planes][scale table][partials teams x 256][barriers]
-template <bool kAdd>
+template <bool kAdd, bool kFull>
 __global__ void __launch_bounds__(kMaxTeams * kTeamThreads, 1)
 add_rmsnorm_stream_kernel(const norm_args a) {
     extern __shared__ __align__(128) uint8_t smem[];
@@ -118,10 +125,11 @@ add_rmsnorm_stream_kernel(const norm_args a) {
     const uint32_t slot_bytes = kAdd ? 2u * row_bytes : row_bytes;
     float *gamma_sh = reinterpret_cast<float *>(smem + (size_t)teams * spt * slot_bytes);
     scale_lut_entry *lut = reinterpret_cast<scale_lut_entry *>(gamma_sh + a.cols);
-    float *partials = reinterpret_cast<float *>(lut + 128);              // [teams][256]
+    float *partials = reinterpret_cast<float *>(lut + 128);                      // [teams][256]
     uint64_t *bars = reinterpret_cast<uint64_t *>(partials + teams * 256u);      // [teams][kMaxSlotsPerTeam]
 
     const uint32_t tid = threadIdx.x, team = tid / kTeamThreads, t = tid % kTeamThreads, lane = tid & 31u;
+    const uint32_t warp_in_team = t >> 5;
     uint64_t *my_bars = bars + team * kMaxSlotsPerTeam;
     uint8_t *my_slots = smem + (size_t)team * spt * slot_bytes;
     float *my_partials = partials + team * 256u;
@@ -163,24 +171,24 @@ add_rmsnorm_stream_kernel(const norm_args a) {
         const uint32_t row = blockIdx.x + (team + teams * i) * gridDim.x;
         const uint64_t base = (uint64_t)row * a.chunks_per_row;
         uint8_t *slot = my_slots + (size_t)j * slot_bytes;
-        const uint32_t *hid_sh = reinterpret_cast<const uint32_t *>(slot);
+        const uint32_t *hid_sh = reinterpret_cast<const uint32_t *>(slot) + t;
         uint32_t *res_sh = reinterpret_cast<uint32_t *>(slot + (kAdd ? row_bytes : 0u));
 
-        // sweep 1: merge in place; this thread's two fmaf chains
+        // sweep 1: merge in place; this thread's two fmaf chains (partials 2t and 2t+1)
         float2 p = make_float2(0.f, 0.f);
+        {
+            uint32_t *res_w = res_sh + t;
 #pragma unroll 5
-        for (uint32_t k = 0; k < k_iters; ++k) {
-            const uint32_t w = 128u * k + t;  // 32-bit word = feature pair 256k + 2t
-            if (2u * w < a.cols) {
-                uint32_t m = res_sh[w];
-                if (kAdd) {
-                    const uint32_t h = hid_sh[w];
-                    const float2 sum = __fadd2_rn(make_float2(bf16_lo(m), bf16_hi(m)), make_float2(bf16_lo(h), bf16_hi(h)));
-                    m = pack_bf16x2(sum.x, sum.y);  // bf16(bf16(res) + bf16(add)): the inputs are BF16 already
-                    res_sh[w] = m;
+            for (uint32_t k = 0; k < k_iters; ++k) {
+                if (kFull || 256u * k + 2u * t < a.cols) {
+                    uint32_t m = res_w[128u * k];
+                    if (kAdd) {
+                        m = add_bf16x2(m, hid_sh[128u * k]);  // bf16(bf16(res) + bf16(add))
+                        res_w[128u * k] = m;
+                    }
+                    const float2 v = make_float2(bf16_lo(m), bf16_hi(m));
+                    p = __ffma2_rn(v, v, p);
                 }
-                const float2 v = make_float2(bf16_lo(m), bf16_hi(m));
-                p = __ffma2_rn(v, v, p);
             }
         }
         reinterpret_cast<float2 *>(my_partials)[t] = p;
@@ -191,20 +199,24 @@ add_rmsnorm_stream_kernel(const norm_args a) {
             bulk_store(a.residual + base, res_sh, row_bytes);
             bulk_commit();
         }
-        // reference tree over the 256 partials: lane l takes 8l..8l+7, butterfly 16,8,4 lanes
-        // (= strides 128,64,32), 2,1 lanes (= 16,8), then strides 4,2,1 inside the lane
-        float s[8];
-        {
-            const float4 lo = reinterpret_cast<const float4 *>(my_partials)[2u * lane];
-            const float4 hi = reinterpret_cast<const float4 *>(my_partials)[2u * lane + 1u];
-            s[0] = lo.x; s[1] = lo.y; s[2] = lo.z; s[3] = lo.w; s[4] = hi.x; s[5] = hi.y; s[6] = hi.z; s[7] = hi.w;
-        }
+        // Reference tree over the 256 partials c: strides 128,64,32 then 16,8,4,2,1.  With lane l
+        // holding c = 8l + e, strides 128..8 are the lane butterfly 16,8,4,2,1 applied to each e
+        // separately; warp w of the team does e = 2w and 2w+1, then the four results meet in
+        // shared memory for strides 4,2,1 (e+4, e+2, e+1).
+        float s0 = my_partials[8u * lane + 2u * warp_in_team], s1 = my_partials[8u * lane + 2u * warp_in_team + 1u];
 #pragma unroll
         for (uint32_t off = 16u; off != 0u; off >>= 1u) {
-#pragma unroll
-            for (int e = 0; e < 8; ++e) s[e] = __fadd_rn(s[e], __shfl_xor_sync(0xffffffffu, s[e], off));
+            s0 = __fadd_rn(s0, __shfl_xor_sync(0xffffffffu, s0, off));
+            s1 = __fadd_rn(s1, __shfl_xor_sync(0xffffffffu, s1, off));
         }
-        const float t0 = __fadd_rn(s[0], s[4]), t1 = __fadd_rn(s[1], s[5]), t2 = __fadd_rn(s[2], s[6]), t3 = __fadd_rn(s[3], s[7]);
+        team_barrier(team);  // everyone has read the partials
+        if (lane == 0u) {
+            my_partials[2u * warp_in_team] = s0;
+            my_partials[2u * warp_in_team + 1u] = s1;
+        }
+        team_barrier(team);
+        const float4 lo = reinterpret_cast<const float4 *>(my_partials)[0], hi = reinterpret_cast<const float4 *>(my_partials)[1];
+        const float t0 = __fadd_rn(lo.x, hi.x), t1 = __fadd_rn(lo.y, hi.y), t2 = __fadd_rn(lo.z, hi.z), t3 = __fadd_rn(lo.w, hi.w);
         const float total = __fadd_rn(__fadd_rn(t0, t2), __fadd_rn(t1, t3));
         const float inverse = rsqrtf(__fadd_rn(__fdiv_rn(total, count), a.eps));
         const float2 inv2 = make_float2(inverse, inverse);
@@ -223,9 +235,9 @@ add_rmsnorm_stream_kernel(const norm_args a) {
         }
         bool needs_exact = false;
         const uint4 *row_sh = reinterpret_cast<const uint4 *>(res_sh);
-        norm_quant_sweep<false>(a, row_sh, gamma_sh, lut, inv2, base, c_iters, t, scale_ptr, scale_step, &needs_exact);
+        norm_quant_sweep<false, kFull>(a, row_sh, gamma_sh, lut, inv2, base, c_iters, t, scale_ptr, scale_step, &needs_exact);
         if (a.codes && (!lut_safe || __any_sync(0xffffffffu, needs_exact))) {
-            norm_quant_sweep<true>(a, row_sh, gamma_sh, lut, inv2, base, c_iters, t, scale_ptr, scale_step, &needs_exact);
+            norm_quant_sweep<true, kFull>(a, row_sh, gamma_sh, lut, inv2, base, c_iters, t, scale_ptr, scale_step, &needs_exact);
         }
         // the whole team is done with the slot: refill it with the row that comes spt rows later
         team_barrier(team);
@@ -323,17 +335,23 @@ size_t stream_fixed_bytes(uint32_t cols, uint32_t teams) {
            (size_t)teams * kMaxSlotsPerTeam * sizeof(uint64_t);
 }
 
-template <bool kAdd>
-void launch_stream(const norm_args &a, uint32_t teams, size_t smem, cudaStream_t stream) {
+template <bool kAdd, bool kFull>
+void launch_stream_impl(const norm_args &a, uint32_t teams, size_t smem, cudaStream_t stream) {
     static bool configured[64] = {};  // the attribute is per device; one process may drive several
     int dev = 0;
     cudaGetDevice(&dev);
     if (dev >= 0 && dev < 64 && !configured[dev]) {
-        cudaFuncSetAttribute(add_rmsnorm_stream_kernel<kAdd>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmemBudget);
+        cudaFuncSetAttribute(add_rmsnorm_stream_kernel<kAdd, kFull>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmemBudget);
         configured[dev] = true;
     }
     const uint32_t ctas = a.rows < kSmCount ? a.rows : kSmCount;
-    add_rmsnorm_stream_kernel<kAdd><<<ctas, teams * kTeamThreads, smem, stream>>>(a);
+    add_rmsnorm_stream_kernel<kAdd, kFull><<<ctas, teams * kTeamThreads, smem, stream>>>(a);
+}
+
+template <bool kAdd>
+void launch_stream(const norm_args &a, uint32_t teams, size_t smem, cudaStream_t stream) {
+    if (a.cols % 1024u == 0u) launch_stream_impl<kAdd, true>(a, teams, smem, stream);
+    else launch_stream_impl<kAdd, false>(a, teams, smem, stream);
 }
 
 }  // namespace

@@ -21,11 +21,6 @@ __device__ __forceinline__ void unpack8(const uint4 &v, float (&x)[8]) {
     x[6] = bf16_lo(v.w); x[7] = bf16_hi(v.w);
 }
 
-__device__ __forceinline__ float absmax8(const float (&x)[8]) {
-    const float a = fmaxf(fmaxf(fabsf(x[0]), fabsf(x[1])), fmaxf(fabsf(x[2]), fabsf(x[3])));
-    const float b = fmaxf(fmaxf(fabsf(x[4]), fabsf(x[5])), fmaxf(fabsf(x[6]), fabsf(x[7])));
-    return fmaxf(a, b);
-}
 
 // Every warp streams one contiguous range of chunks (ranges differ by at most
 // one 128-byte step, so all warps of the persistent grid finish together).
@@ -55,23 +50,23 @@ nvfp4_quantize_bf16_kernel(const uint4 *__restrict__ in, uint32_t total_chunks, 
             nxt[j] = c < last ? ld_stream(in + c) : make_uint4(0u, 0u, 0u, 0u);
         }
         uint32_t packed[kUnroll], scale_byte[kUnroll];
-        float mx[kUnroll];
         bool needs_exact = false;
 #pragma unroll
         for (uint32_t j = 0; j < kUnroll; ++j) {
             float x[8];
             unpack8(v[j], x);
-            float m = absmax8(x);
-            m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, 1));
-            mx[j] = fmaxf(m, 0.0f);  // an all-NaN block has maximum 0, as a running fmaxf from 0 gives
-            packed[j] = nvfp4_quantize8_fast(x, mx[j], G, lut, &scale_byte[j], &needs_exact);
+            float m = absmax8_nan(x);
+            m = max_nan(m, __shfl_xor_sync(0xffffffffu, m, 1));
+            packed[j] = nvfp4_quantize8_fast(x, m, G, lut, &scale_byte[j], &needs_exact);
         }
         if (!lut_safe || __any_sync(0xffffffffu, needs_exact)) {
-#pragma unroll 1
+#pragma unroll
             for (uint32_t j = 0; j < kUnroll; ++j) {
                 float x[8];
                 unpack8(v[j], x);
-                packed[j] = nvfp4_quantize8_exact(x[0], x[1], x[2], x[3], x[4], x[5], x[6], x[7], mx[j], G);
+                float m = absmax8_drop_nan(x);  // an all-NaN block has maximum 0, as a running fmaxf from 0 gives
+                m = fmaxf(fmaxf(m, __shfl_xor_sync(0xffffffffu, m, 1)), 0.0f);
+                packed[j] = nvfp4_quantize8_exact(x[0], x[1], x[2], x[3], x[4], x[5], x[6], x[7], m, G, &scale_byte[j]);
             }
         }
 #pragma unroll

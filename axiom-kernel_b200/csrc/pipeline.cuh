@@ -108,46 +108,82 @@ __device__ __forceinline__ bool build_scale_lut(scale_lut_entry *lut, float G) {
     return __syncthreads_and(safe) != 0;
 }
 
+// max(|a|, |b|) that PROPAGATES NaN (fmaxf drops it).  The straight-line quantizer
+// uses it so that a block holding a NaN is recognised (its maximum is NaN) and
+// handed to the exact path, which applies the reference's fmaxf semantics.
+__device__ __forceinline__ float absmax_nan(float a, float b) {
+    float d;
+    asm("{\n\t.reg .f32 x, y;\n\tabs.f32 x, %1;\n\tabs.f32 y, %2;\n\tmax.NaN.f32 %0, x, y;\n\t}" : "=f"(d) : "f"(a), "f"(b));
+    return d;
+}
+__device__ __forceinline__ float max_nan(float a, float b) {
+    float d;
+    asm("max.NaN.f32 %0, %1, %2;" : "=f"(d) : "f"(a), "f"(b));
+    return d;
+}
+__device__ __forceinline__ float absmax8_nan(const float (&x)[8]) {
+    return max_nan(max_nan(absmax_nan(x[0], x[1]), absmax_nan(x[2], x[3])),
+                   max_nan(absmax_nan(x[4], x[5]), absmax_nan(x[6], x[7])));
+}
+
 // 8 values (half a block) -> 4 code bytes, straight-line code (no branch, so an
-// unrolled caller can interleave several chunks).  max_abs is the block maximum;
-// *scale_byte receives the E4M3 code to store for the block.  The quotients use
-// div_by_shared(); when that is not exact for this block (divisor or quotient
-// outside the safe range) *needs_exact is raised and the caller must redo the
-// chunk with nvfp4_quantize8_exact() — this happens only for saturated block
-// scales or extreme global scales.
+// unrolled caller can interleave several chunks).  max_abs is the block maximum
+// from absmax8_nan() (+ the partner lane); *scale_byte receives the E4M3 code to
+// store for the block.  Quotients: with nr = -1/d (correctly rounded),
+//   t = RN(x * nr);  e = fma(d, t, x) = x - d*q0 exactly;  nq = fma(e, nr, t) = -RN(x/d)
+// — the residual-corrected quotient, negated so that signed zeros survive (a
+// positive-form last step would turn -0 into +0); the eight sign bits are flipped
+// back on the packed nibbles with one XOR.  When the sequence is not exact for
+// this block (divisor or quotient outside the safe range, NaN or infinity in the
+// block) *needs_exact is raised and the caller must redo the chunk with
+// nvfp4_quantize8_exact(): saturated block scales or extreme global scales only.
 __device__ __forceinline__ uint32_t nvfp4_quantize8_fast(const float (&x)[8], float max_abs, float G,
                                                          const scale_lut_entry *lut, uint32_t *scale_byte,
                                                          bool *needs_exact) {
     const uint32_t raw = cvt_e4m3x2(__fmul_rn(__fmul_rn(max_abs, 1.0f / 6.0f), G), 0.0f) & 0x7fu;
-    *scale_byte = raw == 0u ? 0x20u : raw;  // 0x7f cannot occur: the maximum is never NaN
+    *scale_byte = raw == 0u ? 0x20u : raw;
     const scale_lut_entry e = lut[raw];
-    *needs_exact = *needs_exact || !(__fmul_rn(max_abs, e.r) <= 1.0e30f);
-    const float2 r2 = make_float2(e.r, e.r);
-    const float2 nd2 = make_float2(-e.d, -e.d);
+    *needs_exact = *needs_exact || !(__fmul_rn(max_abs, e.r) <= 1.0e30f);  // also true for a NaN maximum
+    const float2 nr2 = make_float2(-e.r, -e.r);
+    const float2 d2 = make_float2(e.d, e.d);
     uint32_t b[4];
 #pragma unroll
     for (int i = 0; i < 4; ++i) {
         const float2 v = make_float2(x[2 * i], x[2 * i + 1]);
-        const float2 q0 = __fmul2_rn(v, r2);
-        const float2 err = __ffma2_rn(nd2, q0, v);
-        float2 q = __ffma2_rn(err, r2, q0);
-        q.x = __uint_as_float((__float_as_uint(q.x) & 0x7fffffffu) | (__float_as_uint(v.x) & 0x80000000u));
-        q.y = __uint_as_float((__float_as_uint(q.y) & 0x7fffffffu) | (__float_as_uint(v.y) & 0x80000000u));
-        b[i] = cvt_e2m1x2(q.x, q.y);
+        const float2 t = __fmul2_rn(v, nr2);
+        const float2 err = __ffma2_rn(d2, t, v);
+        const float2 nq = __ffma2_rn(err, nr2, t);
+        b[i] = cvt_e2m1x2(nq.x, nq.y);
     }
-    return __byte_perm(__byte_perm(b[0], b[1], 0x0040), __byte_perm(b[2], b[3], 0x0040), 0x5410);
+    return __byte_perm(__byte_perm(b[0], b[1], 0x0040), __byte_perm(b[2], b[3], 0x0040), 0x5410) ^ 0x88888888u;
 }
 
-// Same result through IEEE divisions; used on the rare chunks the fast path flags.
+// Same result through IEEE divisions; max_abs must come from fmaxf (NaN-dropping) reductions.
 static __device__ __noinline__ uint32_t nvfp4_quantize8_exact(float x0, float x1, float x2, float x3, float x4,
-                                                              float x5, float x6, float x7, float max_abs, float G) {
+                                                              float x5, float x6, float x7, float max_abs, float G,
+                                                              uint32_t *scale_byte) {
     const uint32_t code = encode_block_scale(__fmul_rn(__fmul_rn(max_abs, 1.0f / 6.0f), G));
+    *scale_byte = code;
     const float d = __fdiv_rn(e4m3_to_f32(code), G);
     const uint32_t b0 = cvt_e2m1x2(__fdiv_rn(x0, d), __fdiv_rn(x1, d)) & 0xffu;
     const uint32_t b1 = cvt_e2m1x2(__fdiv_rn(x2, d), __fdiv_rn(x3, d)) & 0xffu;
     const uint32_t b2 = cvt_e2m1x2(__fdiv_rn(x4, d), __fdiv_rn(x5, d)) & 0xffu;
     const uint32_t b3 = cvt_e2m1x2(__fdiv_rn(x6, d), __fdiv_rn(x7, d)) & 0xffu;
     return b0 | (b1 << 8) | (b2 << 16) | (b3 << 24);
+}
+
+__device__ __forceinline__ float absmax8_drop_nan(const float (&x)[8]) {
+    return fmaxf(fmaxf(fmaxf(fabsf(x[0]), fabsf(x[1])), fmaxf(fabsf(x[2]), fabsf(x[3]))),
+                 fmaxf(fmaxf(fabsf(x[4]), fabsf(x[5])), fmaxf(fabsf(x[6]), fabsf(x[7]))));
+}
+
+// bf16x2 + bf16x2, correctly rounded.  Equal to bf16(f32(a) + f32(b)) for every pair of finite
+// inputs: when the exponents are close the F32 sum is exact, when they are far apart the
+// smaller addend is below a quarter of a BF16 ulp of the larger, so no double rounding exists.
+__device__ __forceinline__ uint32_t add_bf16x2(uint32_t a, uint32_t b) {
+    uint32_t d;
+    asm("add.rn.bf16x2 %0, %1, %2;" : "=r"(d) : "r"(a), "r"(b));
+    return d;
 }
 
 #endif  // __CUDACC__

@@ -11,14 +11,17 @@
 //   out[p+half] = bf16(fma(n[p], s,   n[p+half]*c))
 //   dims >= rope_dim: bf16(n)
 //
-// One CTA per token.  A lane owns 8 consecutive dims (one 16-byte chunk) of one
-// head; head_dim/8 adjacent lanes form a head.  Three phases separated by CTA
-// barriers keep the expensive scalar work out of the 16x-replicated lane code:
-//   1. load chunks, FP64 sum of squares per head (shuffle tree) -> shared
-//   2. one thread per head: inv; one thread per (pair, cos|sin): table row
-//   3. normalise, exchange with the partner lane, rotate, round, store
-// The frequency table is an input: it is evaluated once per model on the
-// device (yarn_inv_freq_kernel) instead of powf/logf per thread per call.
+// One CTA per token.  A lane owns BOTH members of four NeoX pairs: dims 4l..4l+3 and
+// rope_dim/2 + 4l.. of one head (two 8-byte accesses; a warp still reads whole 128-byte
+// lines), so the rotation needs no lane exchange, no select and no divergent branch.
+// Lanes past the rotary dims carry 8 pass-through dims.  head_dim/8 adjacent lanes form a
+// head.  Three phases separated by CTA barriers keep the scalar work out of the replicated
+// lane code:
+//   1. load, FP64 sum of squares per head (shuffle tree) -> shared
+//   2. one thread per head: inv; one thread per (pair, cos|sin): table row (cos, sin, -sin)
+//   3. normalise, rotate, round, store (packed F32x2 arithmetic)
+// The frequency table is an input: it is evaluated once per model on the device
+// (yarn_inv_freq_kernel) instead of powf/logf per thread per call.
 #include "pipeline.cuh"
 #include "runtime.hpp"
 
@@ -26,12 +29,6 @@ namespace axb {
 
 namespace {
 
-__device__ __forceinline__ void unpack8(const uint4 &v, float (&x)[8]) {
-    x[0] = bf16_lo(v.x); x[1] = bf16_hi(v.x);
-    x[2] = bf16_lo(v.y); x[3] = bf16_hi(v.y);
-    x[4] = bf16_lo(v.z); x[5] = bf16_hi(v.z);
-    x[6] = bf16_lo(v.w); x[7] = bf16_hi(v.w);
-}
 
 constexpr uint32_t kMaxHeads = 512u;
 constexpr uint32_t kMaxHeadDim = 256u;
@@ -54,41 +51,61 @@ struct qk_dev_args {
     uint32_t block_tokens, n_layers, layer, pool_stride, tbl_stride, n_blocks;
 };
 
-// LPH = lanes per head (head_dim / 8); NPT = chunks per thread.
+__device__ __forceinline__ uint2 ld_stream8(const void *p) {
+    uint2 v;
+    asm volatile("ld.global.nc.L1::no_allocate.v2.u32 {%0,%1}, [%2];" : "=r"(v.x), "=r"(v.y) : "l"(p));
+    return v;
+}
+
+// LPH = lanes per head (head_dim / 8); NPT = (head, lane) work items per thread.
 template <int LPH, int NPT>
-__global__ void __launch_bounds__(512)
+__global__ void __launch_bounds__(512, NPT <= 4 ? 2 : 1)
 qk_norm_rope_paged_kernel(const qk_dev_args a) {
     __shared__ double ss_sh[kMaxHeads];
     __shared__ float inv_sh[kMaxHeads];
-    __shared__ float cos_sh[kMaxHeadDim / 2];
-    __shared__ float sin_sh[kMaxHeadDim / 2];
-    __shared__ float gq_sh[kMaxHeadDim];
-    __shared__ float gk_sh[kMaxHeadDim];
-    __shared__ unsigned long long kv_base_sh;  // chunk index into the pools, ~0 = no cache write
+    __shared__ __align__(16) float cos_sh[kMaxHeadDim / 2];
+    __shared__ __align__(16) float sin_sh[kMaxHeadDim / 2];
+    __shared__ __align__(16) float nsin_sh[kMaxHeadDim / 2];
+    __shared__ __align__(16) float gq_sh[kMaxHeadDim];
+    __shared__ __align__(16) float gk_sh[kMaxHeadDim];
+    __shared__ unsigned long long kv_base_sh;  // 8-byte unit index into the pools, ~0 = no cache write
     constexpr uint32_t D = LPH * 8u;
 
     const uint32_t tid = threadIdx.x;
     const uint32_t heads = a.q_heads + a.k_heads;
-    const uint32_t total_chunks = heads * LPH;
     const uint32_t half = a.rope_dim >> 1;
+    const uint32_t rot_lanes = a.rope_dim >> 3;  // lanes of a head that carry rotary pairs
 
     for (uint32_t i = tid; i < D; i += blockDim.x) {
         gq_sh[i] = a.q_heads ? __uint_as_float((uint32_t)a.q_gamma[i] << 16) : 0.0f;
         gk_sh[i] = a.k_heads ? __uint_as_float((uint32_t)a.k_gamma[i] << 16) : 0.0f;
     }
 
+    // Work item n of this thread is (head tid/LPH + n*blockDim/LPH, lane tid%LPH): blockDim is a
+    // multiple of 32 and LPH divides 32, so the lane geometry is the same for every item.
+    const uint32_t l = tid % LPH;
+    const uint32_t head0 = tid / LPH, head_step = blockDim.x / LPH;
+    const bool rotary = l < rot_lanes;
+    const uint32_t off_a = rotary ? 4u * l : a.rope_dim + 8u * (l - rot_lanes);
+    const uint32_t off_b = rotary ? half + 4u * l : off_a + 4u;
+    const uint32_t q_elems = a.q_heads * D;
+
     for (uint32_t t = blockIdx.x; t < a.tokens; t += gridDim.x) {
-        const uint4 *q_row = a.q + (uint64_t)t * a.q_heads * LPH;
-        const uint4 *k_row = a.k + (uint64_t)t * a.k_heads * LPH;
-        const uint32_t q_chunks = a.q_heads * LPH;
+        uint16_t *q_row = reinterpret_cast<uint16_t *>(a.q) + (uint64_t)t * q_elems;
+        const uint16_t *k_row = reinterpret_cast<const uint16_t *>(a.k) + (uint64_t)t * a.k_heads * D;
 
         // ---- phase 1: loads and per-head FP64 sum of squares
-        uint4 x[NPT];
+        uint2 xa[NPT], xb[NPT];
 #pragma unroll
         for (int n = 0; n < NPT; ++n) {
-            const uint32_t j = tid + blockDim.x * n;
-            x[n] = make_uint4(0u, 0u, 0u, 0u);
-            if (j < total_chunks) x[n] = j < q_chunks ? ld_stream(q_row + j) : ld_stream(k_row + (j - q_chunks));
+            xa[n] = make_uint2(0u, 0u);
+            xb[n] = make_uint2(0u, 0u);
+            if ((head0 + head_step * n < heads)) {
+                const bool is_k = (head0 + head_step * n) >= a.q_heads;
+                const uint16_t *row = is_k ? k_row + ((head0 + head_step * n) - a.q_heads) * D : q_row + (head0 + head_step * n) * D;
+                xa[n] = ld_stream8(row + off_a);
+                xb[n] = ld_stream8(row + off_b);
+            }
         }
         const uint32_t pos = a.positions[t];
         if (tid == 0u) {
@@ -106,7 +123,7 @@ qk_norm_rope_paged_kernel(const qk_dev_args a) {
                 }
                 if (ok) {
                     base = ((((uint64_t)pb * a.n_layers + a.layer) * a.block_tokens + pos % a.block_tokens) *
-                            a.pool_stride) >> 3;
+                            a.pool_stride) >> 2;
                 } else if (a.status_word) {
                     atomicCAS(a.status_word, AXIOM_STATUS_WORD_OK, AXIOM_STATUS_WORD_BAD_ADDRESS);
                 }
@@ -115,8 +132,8 @@ qk_norm_rope_paged_kernel(const qk_dev_args a) {
         }
 #pragma unroll
         for (int n = 0; n < NPT; ++n) {
-            float f[8];
-            unpack8(x[n], f);
+            const float f[8] = {bf16_lo(xa[n].x), bf16_hi(xa[n].x), bf16_lo(xa[n].y), bf16_hi(xa[n].y),
+                                bf16_lo(xb[n].x), bf16_hi(xb[n].x), bf16_lo(xb[n].y), bf16_hi(xb[n].y)};
             double s = 0.0;
 #pragma unroll
             for (int i = 0; i < 8; ++i) {
@@ -125,8 +142,7 @@ qk_norm_rope_paged_kernel(const qk_dev_args a) {
             }
 #pragma unroll
             for (int off = LPH / 2; off != 0; off >>= 1) s += __shfl_xor_sync(0xffffffffu, s, off);
-            const uint32_t j = tid + blockDim.x * n;
-            if (j < total_chunks && (j % LPH) == 0u) ss_sh[j / LPH] = s;
+            if ((head0 + head_step * n < heads) && l == 0u) ss_sh[head0 + head_step * n] = s;
         }
         __syncthreads();
 
@@ -138,8 +154,13 @@ qk_norm_rope_paged_kernel(const qk_dev_args a) {
                 const uint32_t idx = e - heads;
                 const uint32_t p = idx < half ? idx : idx - half;
                 const float angle = __fmul_rn((float)pos, a.inv_freq[p]);
-                if (idx < half) cos_sh[p] = __fmul_rn(cosf(angle), a.mscale);
-                else sin_sh[p] = __fmul_rn(sinf(angle), a.mscale);
+                if (idx < half) {
+                    cos_sh[p] = __fmul_rn(cosf(angle), a.mscale);
+                } else {
+                    const float sv = __fmul_rn(sinf(angle), a.mscale);
+                    sin_sh[p] = sv;
+                    nsin_sh[p] = -sv;
+                }
             }
         }
         __syncthreads();
@@ -148,54 +169,58 @@ qk_norm_rope_paged_kernel(const qk_dev_args a) {
         const unsigned long long kv_base = kv_base_sh;
 #pragma unroll
         for (int n = 0; n < NPT; ++n) {
-            const uint32_t j = tid + blockDim.x * n;
-            const bool ok = j < total_chunks;
-            const uint32_t head = ok ? j / LPH : 0u;
-            const uint32_t l = j % LPH;
-            const uint32_t e0 = l * 8u;
-            const bool is_k = head >= a.q_heads;
+            const bool is_k = (head0 + head_step * n) >= a.q_heads;
             const float *gamma = is_k ? gk_sh : gq_sh;
-            const float inv = inv_sh[head];
-            float f[8], nv[8], pv[8];
-            unpack8(x[n], f);
-#pragma unroll
-            for (int i = 0; i < 8; ++i) nv[i] = __fmul_rn(__fmul_rn(f[i], inv), gamma[e0 + i]);
-            const uint32_t partner = half >> 3;  // lane distance of the NeoX pair; 0 when nothing rotates
-#pragma unroll
-            for (int i = 0; i < 8; ++i) pv[i] = __shfl_xor_sync(0xffffffffu, nv[i], partner);
-            float o[8];
-            if (e0 < half) {
-#pragma unroll
-                for (int i = 0; i < 8; ++i) {
-                    const float c = cos_sh[e0 + i], s = sin_sh[e0 + i];
-                    o[i] = __fmaf_rn(nv[i], c, -__fmul_rn(pv[i], s));
-                }
-            } else if (e0 < a.rope_dim) {
-#pragma unroll
-                for (int i = 0; i < 8; ++i) {
-                    const float c = cos_sh[e0 - half + i], s = sin_sh[e0 - half + i];
-                    o[i] = __fmaf_rn(pv[i], s, __fmul_rn(nv[i], c));
-                }
-            } else {
-#pragma unroll
-                for (int i = 0; i < 8; ++i) o[i] = nv[i];
+            const float inv = inv_sh[(head0 + head_step * n)];
+            const float2 inv2 = make_float2(inv, inv);
+            const float4 ga = *reinterpret_cast<const float4 *>(gamma + off_a);
+            const float4 gb = *reinterpret_cast<const float4 *>(gamma + off_b);
+            // n = (x * inv) * gamma
+            const float2 a0 = __fmul2_rn(__fmul2_rn(make_float2(bf16_lo(xa[n].x), bf16_hi(xa[n].x)), inv2), make_float2(ga.x, ga.y));
+            const float2 a1 = __fmul2_rn(__fmul2_rn(make_float2(bf16_lo(xa[n].y), bf16_hi(xa[n].y)), inv2), make_float2(ga.z, ga.w));
+            const float2 b0 = __fmul2_rn(__fmul2_rn(make_float2(bf16_lo(xb[n].x), bf16_hi(xb[n].x)), inv2), make_float2(gb.x, gb.y));
+            const float2 b1 = __fmul2_rn(__fmul2_rn(make_float2(bf16_lo(xb[n].y), bf16_hi(xb[n].y)), inv2), make_float2(gb.z, gb.w));
+            float2 oa0 = a0, oa1 = a1, ob0 = b0, ob1 = b1;
+            if (rotary) {
+                // out[p] = fma(first, c, -(second*s)); out[p+half] = fma(first, s, second*c)
+                const uint32_t p0 = off_a;
+                const float4 c = *reinterpret_cast<const float4 *>(cos_sh + p0);
+                const float4 s = *reinterpret_cast<const float4 *>(sin_sh + p0);
+                const float4 ns = *reinterpret_cast<const float4 *>(nsin_sh + p0);
+                const float2 c0 = make_float2(c.x, c.y), c1 = make_float2(c.z, c.w);
+                const float2 s0 = make_float2(s.x, s.y), s1 = make_float2(s.z, s.w);
+                oa0 = __ffma2_rn(a0, c0, __fmul2_rn(b0, make_float2(ns.x, ns.y)));
+                oa1 = __ffma2_rn(a1, c1, __fmul2_rn(b1, make_float2(ns.z, ns.w)));
+                ob0 = __ffma2_rn(a0, s0, __fmul2_rn(b0, c0));
+                ob1 = __ffma2_rn(a1, s1, __fmul2_rn(b1, c1));
             }
-            const uint4 packed = make_uint4(pack_bf16x2(o[0], o[1]), pack_bf16x2(o[2], o[3]),
-                                            pack_bf16x2(o[4], o[5]), pack_bf16x2(o[6], o[7]));
-            if (ok) {
+            const uint2 pa = make_uint2(pack_bf16x2(oa0.x, oa0.y), pack_bf16x2(oa1.x, oa1.y));
+            const uint2 pb = make_uint2(pack_bf16x2(ob0.x, ob0.y), pack_bf16x2(ob1.x, ob1.y));
+            if ((head0 + head_step * n < heads)) {
                 if (!is_k) {
-                    st_stream(a.q + (uint64_t)t * q_chunks + j, packed);
+                    uint16_t *dst = q_row + (head0 + head_step * n) * D;
+                    st_stream(dst + off_a, pa);
+                    st_stream(dst + off_b, pb);
                 } else {
-                    const uint32_t kj = j - q_chunks;  // chunk inside the token's K row
-                    if (kv_base != ~0ull) st_stream(a.k_pool + kv_base + kj, packed);
-                    if (a.k_out) st_stream(a.k_out + (uint64_t)t * a.k_heads * LPH + kj, packed);
+                    const uint32_t kelem = ((head0 + head_step * n) - a.q_heads) * D;  // element inside the token's K row
+                    if (kv_base != ~0ull) {
+                        uint2 *dst = reinterpret_cast<uint2 *>(a.k_pool) + kv_base;
+                        st_stream(dst + ((kelem + off_a) >> 2), pa);
+                        st_stream(dst + ((kelem + off_b) >> 2), pb);
+                    }
+                    if (a.k_out) {
+                        uint16_t *dst = reinterpret_cast<uint16_t *>(a.k_out) + (uint64_t)t * a.k_heads * D + kelem;
+                        st_stream(dst + off_a, pa);
+                        st_stream(dst + off_b, pb);
+                    }
                 }
             }
         }
         // V rides along unchanged (BF16 in, BF16 cache)
         if (a.v && a.v_pool && kv_base != ~0ull) {
             const uint4 *v_row = a.v + (uint64_t)t * a.k_heads * LPH;
-            for (uint32_t j = tid; j < a.k_heads * LPH; j += blockDim.x) st_stream(a.v_pool + kv_base + j, ld_stream(v_row + j));
+            uint4 *dst = reinterpret_cast<uint4 *>(reinterpret_cast<uint2 *>(a.v_pool) + kv_base);
+            for (uint32_t j = tid; j < a.k_heads * LPH; j += blockDim.x) st_stream(dst + j, ld_stream(v_row + j));
         }
         __syncthreads();  // shared tables are rewritten by the next token
     }
@@ -224,15 +249,24 @@ __global__ void yarn_inv_freq_kernel(float *out, uint32_t rope_dim, float theta,
 
 template <int LPH>
 void launch_qk(const qk_dev_args &a, cudaStream_t stream) {
-    const uint32_t total_chunks = (a.q_heads + a.k_heads) * LPH;
+    const uint32_t items = (a.q_heads + a.k_heads) * LPH;
     const uint32_t grid = a.tokens;
-    if (total_chunks <= 2048u) {
-        uint32_t threads = ((total_chunks + 3u) / 4u + 31u) & ~31u;
-        if (threads < 64u) threads = 64u;
-        qk_norm_rope_paged_kernel<LPH, 4><<<grid, threads, 0, stream>>>(a);
-    } else {
-        const uint32_t threads = ((total_chunks + 7u) / 8u + 31u) & ~31u;
-        qk_norm_rope_paged_kernel<LPH, 8><<<grid, threads, 0, stream>>>(a);
+    // items per thread: the count that wastes the fewest lanes, ties to the larger CTA
+    uint32_t best_npt = 4u, best_threads = 0u, best_waste = ~0u;
+    for (uint32_t npt = 2u; npt <= 8u; npt *= 2u) {
+        for (uint32_t v = npt; v <= npt + (npt == 2u ? 1u : 0u); ++v) {  // 2, 3, 4, 8
+            const uint32_t threads = ((items + v - 1u) / v + 31u) & ~31u;
+            if (threads > 512u || threads < 32u) continue;
+            const uint32_t waste = threads * v - items;
+            if (waste < best_waste) { best_waste = waste; best_npt = v; best_threads = threads; }
+        }
+    }
+    if (best_threads == 0u) { best_npt = 8u; best_threads = 512u; }
+    switch (best_npt) {
+    case 2: qk_norm_rope_paged_kernel<LPH, 2><<<grid, best_threads, 0, stream>>>(a); break;
+    case 3: qk_norm_rope_paged_kernel<LPH, 3><<<grid, best_threads, 0, stream>>>(a); break;
+    case 4: qk_norm_rope_paged_kernel<LPH, 4><<<grid, best_threads, 0, stream>>>(a); break;
+    default: qk_norm_rope_paged_kernel<LPH, 8><<<grid, best_threads, 0, stream>>>(a); break;
     }
 }
 

@@ -169,14 +169,15 @@ swiglu_nvfp4_kernel(const uint4 *__restrict__ in, uint32_t rows, uint32_t chunks
             unpack8(u[j], uv);
 #pragma unroll
             for (int i = 0; i < 8; ++i) y[i] = silu_mul(gv[i], uv[i]);
-            float m = absmax8(y);
-            m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, 1));
-            m = fmaxf(m, 0.0f);
+            float m = absmax8_nan(y);
+            m = max_nan(m, __shfl_xor_sync(0xffffffffu, m, 1));
             uint32_t scale_code;
             bool needs_exact = false;
             uint32_t packed = nvfp4_quantize8_fast(y, m, G, lut, &scale_code, &needs_exact);
             if (!lut_safe || __any_sync(0xffffffffu, needs_exact)) {
-                packed = nvfp4_quantize8_exact(y[0], y[1], y[2], y[3], y[4], y[5], y[6], y[7], m, G);
+                m = absmax8(y);
+                m = fmaxf(fmaxf(m, __shfl_xor_sync(0xffffffffu, m, 1)), 0.0f);
+                packed = nvfp4_quantize8_exact(y[0], y[1], y[2], y[3], y[4], y[5], y[6], y[7], m, G, &scale_code);
             }
             if (c < total) {
                 st_stream(codes + c, packed);

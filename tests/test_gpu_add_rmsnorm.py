@@ -122,3 +122,27 @@ def test_no_bounded_wait_ran_out(axk, cuda_device):
     hidden, residual, gamma = wl.add_rmsnorm_inputs_np(2048, 5120)
     run(axk, hidden, residual, gamma, 100.0)
     assert axk.lib().axiom_b200_pipeline_faults(0) == 0
+
+
+def test_residual_add_over_all_exponents(axk, cuda_device):
+    """Random finite BF16 bit patterns (every exponent, both signs, denormals): the merged residual is
+    bf16(f32(a) + f32(b)) bit for bit, in the pipelined kernel (packed BF16 add) and in the CTA kernel."""
+    from gpu_util import dev, host, sync
+    import torch
+
+    rng = np.random.default_rng(99)
+    for rows in (512, 40):
+        a = rng.integers(0, 65536, (rows, 5120)).astype(np.uint16)
+        b = rng.integers(0, 65536, (rows, 5120)).astype(np.uint16)
+        for arr in (a, b):
+            arr[(arr & 0x7F80) == 0x7F80] &= 0x807F       # no inf / NaN patterns: make them denormals
+        b[:, ::7] = a[:, ::7] ^ 0x8000                     # exact cancellation
+        b[:, 1::7] = ((a[:, 1::7].astype(np.int32) + rng.integers(-3, 4, a[:, 1::7].shape)) & 0xFFFF).astype(np.uint16)
+        b[(b & 0x7F80) == 0x7F80] &= 0x807F
+        gamma = wl.to_bf16_bits(np.ones(5120, np.float32))
+        r = dev(b)
+        norm = torch.zeros((rows, 5120), dtype=torch.int16, device="cuda")
+        hd, gd = dev(a), dev(gamma)
+        assert axk.add_rmsnorm_nvfp4(0, hd, r, gd, 1e-6, rows, 5120, 1.0, norm, None, None, 0) == axk.AXIOM_OK
+        sync()
+        assert np.array_equal(host(r, np.uint16).reshape(rows, 5120), ol.add_bf16(a, b))
