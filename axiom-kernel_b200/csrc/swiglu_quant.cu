@@ -9,8 +9,15 @@
 //       (src/axiom_qwen38_nvfp4_mlp.cu:229-317)
 //
 // The FP8 flavour needs the whole row before it can scale it: one CTA owns one
-// row, every thread keeps its share of y in registers across the row-max
-// reduction, so gate|up is read once and only the codes are written.
+// row at a time, every thread keeps its share of y in registers across the
+// row-max reduction, so gate|up is read once and only the codes are written.
+//
+// silu(g) = g / (1 + expf(-g)) depends on the BF16 gate alone, so the throughput
+// kernels tabulate it once per CTA in shared memory — 47 binades x 128 mantissas
+// x 2 signs, filled by the very expression the direct path evaluates, hence
+// bit-identical — and replace expf + an IEEE division per element by one
+// shared-memory load.  Gates outside the table (|g| < 2^-40, |g| >= 128, NaN,
+// infinity) take the direct expression.
 #include "pipeline.cuh"
 #include "runtime.hpp"
 
@@ -25,32 +32,85 @@ __device__ __forceinline__ void unpack8(const uint4 &v, float (&x)[8]) {
     x[6] = bf16_lo(v.w); x[7] = bf16_hi(v.w);
 }
 
-__device__ __forceinline__ float silu_mul(float g, float u) {
-    return __fmul_rn(__fdiv_rn(g, __fadd_rn(1.0f, expf(-g))), u);
+__device__ __forceinline__ float silu(float g) { return __fdiv_rn(g, __fadd_rn(1.0f, expf(-g))); }
+__device__ __forceinline__ float silu_mul(float g, float u) { return __fmul_rn(silu(g), u); }
+
+// ---- shared-memory silu table -------------------------------------------------------------
+constexpr uint32_t kSiluExpLo = 87u;    // 2^-40
+constexpr uint32_t kSiluExpHi = 133u;   // up to (not including) 2^7
+constexpr uint32_t kSiluFirst = kSiluExpLo << 7;                       // first tabulated BF16 magnitude
+constexpr uint32_t kSiluCount = (kSiluExpHi - kSiluExpLo + 1u) << 7;   // magnitudes per sign
+constexpr uint32_t kSiluTableBytes = 2u * kSiluCount * sizeof(float);
+
+__device__ __forceinline__ void build_silu_table(float *table) {
+    for (uint32_t i = threadIdx.x; i < 2u * kSiluCount; i += blockDim.x) {
+        const uint32_t sign = i >= kSiluCount ? 1u : 0u;
+        const uint32_t bits = (sign << 15) | (kSiluFirst + (i - sign * kSiluCount));
+        table[i] = silu(__uint_as_float(bits << 16));
+    }
+    __syncthreads();
 }
 
-__device__ __forceinline__ float absmax8(const float (&x)[8]) {
-    const float a = fmaxf(fmaxf(fabsf(x[0]), fabsf(x[1])), fmaxf(fabsf(x[2]), fabsf(x[3])));
-    const float b = fmaxf(fmaxf(fabsf(x[4]), fabsf(x[5])), fmaxf(fabsf(x[6]), fabsf(x[7])));
-    return fmaxf(a, b);
+// bits16: one BF16 pattern in the low half.  Out-of-table patterns read entry 0 and raise *outside.
+__device__ __forceinline__ float silu_lookup(const float *table, uint32_t bits16, bool *outside) {
+    const uint32_t rel = (bits16 & 0x7fffu) - kSiluFirst;
+    const bool in = rel < kSiluCount;
+    *outside = *outside || !in;
+    return table[(in ? rel : 0u) + (bits16 >> 15) * kSiluCount];
 }
 
-// Maximum over the CTA; every thread receives it.  fmaxf drops NaN operands,
-// the final clamp makes an all-NaN row give 0 as a running fmaxf from 0 does.
+// y[0..7] = silu(gate) * up for one 16-byte chunk of each
+template <bool kTable>
+__device__ __forceinline__ void swiglu8(const float *table, const uint4 &g, const uint4 &u, float (&y)[8]) {
+    float uv[8];
+    unpack8(u, uv);
+    if (kTable) {
+        const uint32_t w[4] = {g.x, g.y, g.z, g.w};
+        bool outside = false;
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            const float2 s = make_float2(silu_lookup(table, w[i] & 0xffffu, &outside), silu_lookup(table, w[i] >> 16, &outside));
+            const float2 p = __fmul2_rn(s, make_float2(uv[2 * i], uv[2 * i + 1]));
+            y[2 * i] = p.x;
+            y[2 * i + 1] = p.y;
+        }
+        if (outside) {  // rare: a gate beyond the table in this chunk
+            float gv[8];
+            unpack8(g, gv);
+#pragma unroll
+            for (int i = 0; i < 8; ++i) y[i] = silu_mul(gv[i], uv[i]);
+        }
+    } else {
+        float gv[8];
+        unpack8(g, gv);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) y[i] = silu_mul(gv[i], uv[i]);
+    }
+}
+
+// Maximum over the CTA; every thread receives it.  kNan: NaN-propagating (a NaN anywhere in the
+// row gives NaN), otherwise fmaxf semantics with the clamp that makes an all-NaN row give 0.
+template <bool kNan>
 __device__ __forceinline__ float cta_max(float m, float *warp_max) {
     const uint32_t lane = threadIdx.x & 31u, warp = threadIdx.x >> 5, warps = (blockDim.x + 31u) >> 5;
 #pragma unroll
-    for (uint32_t off = 16u; off != 0u; off >>= 1u) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, off));
+    for (uint32_t off = 16u; off != 0u; off >>= 1u) {
+        const float o = __shfl_xor_sync(0xffffffffu, m, off);
+        m = kNan ? max_nan(m, o) : fmaxf(m, o);
+    }
     if (lane == 0u) warp_max[warp] = m;
     __syncthreads();
     float all = lane < warps ? warp_max[lane] : 0.0f;
 #pragma unroll
-    for (uint32_t off = 16u; off != 0u; off >>= 1u) all = fmaxf(all, __shfl_xor_sync(0xffffffffu, all, off));
-    __syncthreads();  // warp_max is reused by the next row
-    return fmaxf(all, 0.0f);
+    for (uint32_t off = 16u; off != 0u; off >>= 1u) {
+        const float o = __shfl_xor_sync(0xffffffffu, all, off);
+        all = kNan ? max_nan(all, o) : fmaxf(all, o);
+    }
+    __syncthreads();  // warp_max is reused
+    return kNan ? all : fmaxf(all, 0.0f);
 }
 
-enum class row_op { swiglu, plain_finite_only };
+enum class row_op { swiglu, swiglu_table, plain_finite_only };
 
 // CPT = 16-byte chunks (8 values) per thread; blockDim.x * CPT >= width / 8.
 constexpr uint32_t kMaxRowThreads = 576u;
@@ -59,14 +119,18 @@ template <int CPT, row_op kOp>
 __global__ void __launch_bounds__(kMaxRowThreads, CPT <= 4 ? 2 : 1)
 fp8_rows_kernel(const uint4 *__restrict__ in, uint32_t rows, uint32_t chunks, uint32_t in_chunks_per_row,
                 uint2 *__restrict__ codes, float *__restrict__ scales, uint32_t *__restrict__ status_word) {
+    extern __shared__ __align__(16) float silu_table[];
     __shared__ float warp_max[32];
+    constexpr bool kSwiglu = kOp != row_op::plain_finite_only;
+    constexpr bool kTable = kOp == row_op::swiglu_table;
     const uint32_t tid = threadIdx.x;
+    if (kTable) build_silu_table(silu_table);
     for (uint32_t row = blockIdx.x; row < rows; row += gridDim.x) {
         const uint4 *gate = in + (uint64_t)row * in_chunks_per_row;
         float y[CPT][8];
-        float m = 0.0f;
+        float m = 0.0f;       // NaN-propagating maximum (swiglu) / finite-only maximum (plain)
         bool nonfinite = false;
-        if (kOp == row_op::swiglu) {
+        if (kSwiglu) {
             const uint4 *up = gate + chunks;
             uint4 g[CPT], u[CPT];
 #pragma unroll
@@ -78,12 +142,8 @@ fp8_rows_kernel(const uint4 *__restrict__ in, uint32_t rows, uint32_t chunks, ui
             }
 #pragma unroll
             for (int k = 0; k < CPT; ++k) {
-                float gv[8], uv[8];
-                unpack8(g[k], gv);
-                unpack8(u[k], uv);
-#pragma unroll
-                for (int i = 0; i < 8; ++i) y[k][i] = silu_mul(gv[i], uv[i]);
-                m = fmaxf(m, absmax8(y[k]));
+                swiglu8<kTable>(silu_table, g[k], u[k], y[k]);
+                m = max_nan(m, absmax8_nan(y[k]));
             }
         } else {
             uint4 g[CPT];
@@ -104,30 +164,56 @@ fp8_rows_kernel(const uint4 *__restrict__ in, uint32_t rows, uint32_t chunks, ui
                 }
             }
         }
-        m = cta_max(m, warp_max);
+        m = kSwiglu ? cta_max<true>(m, warp_max) : cta_max<false>(m, warp_max);
+        if (kSwiglu && !(m == m)) {
+            // a NaN somewhere in the row: the reference's maximum drops it
+            float d = 0.0f;
+#pragma unroll
+            for (int k = 0; k < CPT; ++k) d = fmaxf(d, absmax8_drop_nan(y[k]));
+            m = cta_max<false>(d, warp_max);
+            nonfinite = true;
+        }
         float scale = m == 0.0f ? 1.0f : __fdiv_rn(m, 448.0f);
-        if (kOp == row_op::swiglu) {
+        if (kSwiglu) {
             if (!isfinite(scale) || scale <= 0.0f) scale = 1.0f;
         } else if (nonfinite && status_word) {
             atomicCAS(status_word, AXIOM_STATUS_WORD_OK, AXIOM_STATUS_WORD_NONFINITE);
         }
         if (tid == 0u) scales[row] = scale;
         const float r = __frcp_rn(scale);
-        const bool safe = divisor_is_safe(scale, r, m) && !nonfinite;
+        const bool safe = divisor_is_safe(scale, r, m) && !nonfinite;  // uniform over the CTA
         uint2 *out = codes + (uint64_t)row * chunks;
+        if (safe) {
+            // negated residual-corrected quotients (signed zeros survive), signs flipped back on the codes
+            const float2 nr2 = make_float2(-r, -r), d2 = make_float2(scale, scale);
 #pragma unroll
-        for (int k = 0; k < CPT; ++k) {
-            const uint32_t q = tid + blockDim.x * k;
-            uint32_t w[2];
+            for (int k = 0; k < CPT; ++k) {
+                const uint32_t q = tid + blockDim.x * k;
+                uint32_t c[4];
 #pragma unroll
-            for (int h = 0; h < 2; ++h) {
-                const float a0 = div_exact_or_shared(y[k][4 * h + 0], scale, r, safe);
-                const float a1 = div_exact_or_shared(y[k][4 * h + 1], scale, r, safe);
-                const float a2 = div_exact_or_shared(y[k][4 * h + 2], scale, r, safe);
-                const float a3 = div_exact_or_shared(y[k][4 * h + 3], scale, r, safe);
-                w[h] = cvt_e4m3x2(a0, a1) | (cvt_e4m3x2(a2, a3) << 16);
+                for (int i = 0; i < 4; ++i) {
+                    const float2 v = make_float2(y[k][2 * i], y[k][2 * i + 1]);
+                    const float2 t = __fmul2_rn(v, nr2);
+                    const float2 nq = __ffma2_rn(__ffma2_rn(d2, t, v), nr2, t);
+                    c[i] = cvt_e4m3x2(nq.x, nq.y);
+                }
+                if (q < chunks) {
+                    st_stream(out + q, make_uint2(__byte_perm(c[0], c[1], 0x5410) ^ 0x80808080u,
+                                                  __byte_perm(c[2], c[3], 0x5410) ^ 0x80808080u));
+                }
             }
-            if (q < chunks) st_stream(out + q, make_uint2(w[0], w[1]));
+        } else {
+#pragma unroll
+            for (int k = 0; k < CPT; ++k) {
+                const uint32_t q = tid + blockDim.x * k;
+                uint32_t w[2];
+#pragma unroll
+                for (int h = 0; h < 2; ++h) {
+                    w[h] = cvt_e4m3x2(__fdiv_rn(y[k][4 * h + 0], scale), __fdiv_rn(y[k][4 * h + 1], scale)) |
+                           (cvt_e4m3x2(__fdiv_rn(y[k][4 * h + 2], scale), __fdiv_rn(y[k][4 * h + 3], scale)) << 16);
+                }
+                if (q < chunks) st_stream(out + q, make_uint2(w[0], w[1]));
+            }
         }
     }
 }
@@ -137,11 +223,14 @@ fp8_rows_kernel(const uint4 *__restrict__ in, uint32_t rows, uint32_t chunks, ui
 constexpr uint32_t kNvThreads = 256u;
 constexpr uint32_t kNvUnroll = 2u;
 
+template <bool kTable>
 __global__ void __launch_bounds__(kNvThreads)
 swiglu_nvfp4_kernel(const uint4 *__restrict__ in, uint32_t rows, uint32_t chunks, float G,
                     uint32_t *__restrict__ codes, uint8_t *__restrict__ scales, uint32_t layout,
                     uint32_t groups, uint32_t inner_tiles) {
+    extern __shared__ __align__(16) float silu_table[];
     __shared__ scale_lut_entry lut[128];
+    if (kTable) build_silu_table(silu_table);
     const bool lut_safe = build_scale_lut(lut, G);
     const uint32_t lane = threadIdx.x & 31u;
     const uint32_t warp = (blockIdx.x * kNvThreads + threadIdx.x) >> 5;
@@ -164,18 +253,15 @@ swiglu_nvfp4_kernel(const uint4 *__restrict__ in, uint32_t rows, uint32_t chunks
 #pragma unroll
         for (uint32_t j = 0; j < kNvUnroll; ++j) {
             const uint64_t c = tile * kTile + j * 32u + lane;
-            float gv[8], uv[8], y[8];
-            unpack8(g[j], gv);
-            unpack8(u[j], uv);
-#pragma unroll
-            for (int i = 0; i < 8; ++i) y[i] = silu_mul(gv[i], uv[i]);
+            float y[8];
+            swiglu8<kTable>(silu_table, g[j], u[j], y);
             float m = absmax8_nan(y);
             m = max_nan(m, __shfl_xor_sync(0xffffffffu, m, 1));
             uint32_t scale_code;
             bool needs_exact = false;
             uint32_t packed = nvfp4_quantize8_fast(y, m, G, lut, &scale_code, &needs_exact);
             if (!lut_safe || __any_sync(0xffffffffu, needs_exact)) {
-                m = absmax8(y);
+                m = absmax8_drop_nan(y);
                 m = fmaxf(fmaxf(m, __shfl_xor_sync(0xffffffffu, m, 1)), 0.0f);
                 packed = nvfp4_quantize8_exact(y[0], y[1], y[2], y[3], y[4], y[5], y[6], y[7], m, G, &scale_code);
             }
@@ -219,18 +305,25 @@ int launch_fp8_rows(const void *in, uint32_t rows, uint32_t width, uint32_t in_c
     const uint32_t chunks = width / 8u;
     const row_shape s = pick_row_shape(chunks);
     if (s.threads == 0u) return AXIOM_ERR_INVALID_ARGUMENT;
-    const uint32_t ctas = rows < kSmCount * 16u ? rows : kSmCount * 16u;
+    constexpr bool kTable = kOp == row_op::swiglu_table;
+    const size_t smem = kTable ? kSiluTableBytes : 0u;
+    // table flavour: persistent CTAs (the table is built once per CTA), two per SM
+    const uint32_t cap = kTable ? kSmCount * 2u : kSmCount * 16u;
+    const uint32_t ctas = rows < cap ? rows : cap;
     const uint4 *src = (const uint4 *)in;
     uint2 *dst = (uint2 *)codes;
     switch (s.cpt) {
-    case 1: fp8_rows_kernel<1, kOp><<<ctas, s.threads, 0, stream>>>(src, rows, chunks, in_chunks_per_row, dst, scales, status_word); break;
-    case 2: fp8_rows_kernel<2, kOp><<<ctas, s.threads, 0, stream>>>(src, rows, chunks, in_chunks_per_row, dst, scales, status_word); break;
-    case 4: fp8_rows_kernel<4, kOp><<<ctas, s.threads, 0, stream>>>(src, rows, chunks, in_chunks_per_row, dst, scales, status_word); break;
-    default: fp8_rows_kernel<8, kOp><<<ctas, s.threads, 0, stream>>>(src, rows, chunks, in_chunks_per_row, dst, scales, status_word); break;
+    case 1: fp8_rows_kernel<1, kOp><<<ctas, s.threads, smem, stream>>>(src, rows, chunks, in_chunks_per_row, dst, scales, status_word); break;
+    case 2: fp8_rows_kernel<2, kOp><<<ctas, s.threads, smem, stream>>>(src, rows, chunks, in_chunks_per_row, dst, scales, status_word); break;
+    case 4: fp8_rows_kernel<4, kOp><<<ctas, s.threads, smem, stream>>>(src, rows, chunks, in_chunks_per_row, dst, scales, status_word); break;
+    default: fp8_rows_kernel<8, kOp><<<ctas, s.threads, smem, stream>>>(src, rows, chunks, in_chunks_per_row, dst, scales, status_word); break;
     }
     note_launch();
     return AXIOM_OK;
 }
+
+// rows at or above which building the 47 KB silu table per CTA pays for itself
+constexpr uint32_t kTableMinRows = 2u * kSmCount;
 
 }  // namespace
 
@@ -238,6 +331,9 @@ unsigned int swiglu_fault_word() { return read_and_clear_pipeline_fault(); }
 
 int launch_swiglu_fp8_bf16(const void *gate_up, uint32_t rows, uint32_t width, uint8_t *codes, float *scales,
                            cudaStream_t stream) {
+    if (rows >= kTableMinRows) {
+        return launch_fp8_rows<row_op::swiglu_table>(gate_up, rows, width, width / 4u, codes, scales, nullptr, stream);
+    }
     return launch_fp8_rows<row_op::swiglu>(gate_up, rows, width, width / 4u, codes, scales, nullptr, stream);
 }
 
@@ -254,8 +350,21 @@ int launch_swiglu_nvfp4_bf16(const void *gate_up, uint32_t rows, uint32_t width,
     const uint32_t tiles = (total + 32u * kNvUnroll - 1u) / (32u * kNvUnroll);
     uint32_t blocks = (tiles + kNvThreads / 32u - 1u) / (kNvThreads / 32u);
     if (blocks > kSmCount * 16u) blocks = kSmCount * 16u;
-    swiglu_nvfp4_kernel<<<blocks, kNvThreads, 0, stream>>>((const uint4 *)gate_up, rows, chunks, G, (uint32_t *)codes,
-                                                            scales, layout, groups, (groups + 3u) / 4u);
+    if (rows >= kTableMinRows) {
+        static bool configured[64] = {};
+        int dev = 0;
+        cudaGetDevice(&dev);
+        if (dev >= 0 && dev < 64 && !configured[dev]) {
+            cudaFuncSetAttribute(swiglu_nvfp4_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSiluTableBytes);
+            configured[dev] = true;
+        }
+        if (blocks > kSmCount * 4u) blocks = kSmCount * 4u;  // persistent: the table is built once per CTA
+        swiglu_nvfp4_kernel<true><<<blocks, kNvThreads, kSiluTableBytes, stream>>>(
+                (const uint4 *)gate_up, rows, chunks, G, (uint32_t *)codes, scales, layout, groups, (groups + 3u) / 4u);
+    } else {
+        swiglu_nvfp4_kernel<false><<<blocks, kNvThreads, 0, stream>>>(
+                (const uint4 *)gate_up, rows, chunks, G, (uint32_t *)codes, scales, layout, groups, (groups + 3u) / 4u);
+    }
     note_launch();
     return AXIOM_OK;
 }
