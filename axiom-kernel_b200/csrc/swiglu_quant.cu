@@ -36,53 +36,61 @@ __device__ __forceinline__ float silu(float g) { return __fdiv_rn(g, __fadd_rn(1
 __device__ __forceinline__ float silu_mul(float g, float u) { return __fmul_rn(silu(g), u); }
 
 // ---- shared-memory silu table -------------------------------------------------------------
-constexpr uint32_t kSiluExpLo = 87u;    // 2^-40
-constexpr uint32_t kSiluExpHi = 133u;   // up to (not including) 2^7
-constexpr uint32_t kSiluFirst = kSiluExpLo << 7;                       // first tabulated BF16 magnitude
-constexpr uint32_t kSiluCount = (kSiluExpHi - kSiluExpLo + 1u) << 7;   // magnitudes per sign
-constexpr uint32_t kSiluTableBytes = 2u * kSiluCount * sizeof(float);
+// 64 binades (2^-57 .. 2^7) x 128 mantissas x 2 signs = 16384 floats.  Byte offset of a BF16
+// pattern b: (((b & 0x7fff) - first) & 0x1fff) * 4 + (b & 0x8000) — every offset is inside the
+// table, patterns outside the tabulated range alias into it and are caught by the range test.
+constexpr uint32_t kSiluExpLo = 70u;                                  // 2^-57
+constexpr uint32_t kSiluFirst = kSiluExpLo << 7;                      // first tabulated magnitude
+constexpr uint32_t kSiluEnd = (kSiluExpLo + 64u) << 7;                // one past the last
+constexpr uint32_t kSiluTableBytes = 2u * 8192u * sizeof(float);
 
 __device__ __forceinline__ void build_silu_table(float *table) {
-    for (uint32_t i = threadIdx.x; i < 2u * kSiluCount; i += blockDim.x) {
-        const uint32_t sign = i >= kSiluCount ? 1u : 0u;
-        const uint32_t bits = (sign << 15) | (kSiluFirst + (i - sign * kSiluCount));
+    for (uint32_t i = threadIdx.x; i < 16384u; i += blockDim.x) {
+        const uint32_t bits = ((i >> 13) << 15) | (kSiluFirst + (i & 8191u));
         table[i] = silu(__uint_as_float(bits << 16));
     }
     __syncthreads();
 }
 
-// bits16: one BF16 pattern in the low half.  Out-of-table patterns read entry 0 and raise *outside.
-__device__ __forceinline__ float silu_lookup(const float *table, uint32_t bits16, bool *outside) {
-    const uint32_t rel = (bits16 & 0x7fffu) - kSiluFirst;
-    const bool in = rel < kSiluCount;
-    *outside = *outside || !in;
-    return table[(in ? rel : 0u) + (bits16 >> 15) * kSiluCount];
+// silu of the two BF16 gates packed in w, read from the table (garbage for out-of-range gates).
+__device__ __forceinline__ float2 silu_lookup2(const float *table, uint32_t w) {
+    const char *base = reinterpret_cast<const char *>(table);
+    const uint32_t dlo = (w << 2) - 4u * kSiluFirst;
+    const uint32_t dhi = (w >> 14) - 4u * kSiluFirst;
+    const uint32_t olo = ((w & 0x8000u) | (dlo & 0x7ffcu));
+    const uint32_t ohi = (((w >> 16) & 0x8000u) | (dhi & 0x7ffcu));
+    return make_float2(*reinterpret_cast<const float *>(base + olo), *reinterpret_cast<const float *>(base + ohi));
+}
+
+// Bit 15 / 31 of the result is set when the low / high gate of w lies outside the table
+// (|g| < 2^-57, |g| >= 128, NaN, infinity).  Halves never carry into each other.
+__device__ __forceinline__ uint32_t silu_outside2(uint32_t w) {
+    const uint32_t m2 = w & 0x7fff7fffu;
+    const uint32_t above = m2 + (0x8000u - kSiluEnd) * 0x00010001u;        // bit 15 set: magnitude >= end
+    const uint32_t below = (m2 | 0x80008000u) - kSiluFirst * 0x00010001u;  // bit 15 clear: magnitude < first
+    return (above | ~below) & 0x80008000u;
 }
 
 // y[0..7] = silu(gate) * up for one 16-byte chunk of each
 template <bool kTable>
 __device__ __forceinline__ void swiglu8(const float *table, const uint4 &g, const uint4 &u, float (&y)[8]) {
-    float uv[8];
-    unpack8(u, uv);
     if (kTable) {
-        const uint32_t w[4] = {g.x, g.y, g.z, g.w};
-        bool outside = false;
-#pragma unroll
-        for (int i = 0; i < 4; ++i) {
-            const float2 s = make_float2(silu_lookup(table, w[i] & 0xffffu, &outside), silu_lookup(table, w[i] >> 16, &outside));
-            const float2 p = __fmul2_rn(s, make_float2(uv[2 * i], uv[2 * i + 1]));
-            y[2 * i] = p.x;
-            y[2 * i + 1] = p.y;
-        }
-        if (outside) {  // rare: a gate beyond the table in this chunk
-            float gv[8];
+        const float2 p0 = __fmul2_rn(silu_lookup2(table, g.x), make_float2(bf16_lo(u.x), bf16_hi(u.x)));
+        const float2 p1 = __fmul2_rn(silu_lookup2(table, g.y), make_float2(bf16_lo(u.y), bf16_hi(u.y)));
+        const float2 p2 = __fmul2_rn(silu_lookup2(table, g.z), make_float2(bf16_lo(u.z), bf16_hi(u.z)));
+        const float2 p3 = __fmul2_rn(silu_lookup2(table, g.w), make_float2(bf16_lo(u.w), bf16_hi(u.w)));
+        y[0] = p0.x; y[1] = p0.y; y[2] = p1.x; y[3] = p1.y; y[4] = p2.x; y[5] = p2.y; y[6] = p3.x; y[7] = p3.y;
+        if (silu_outside2(g.x) | silu_outside2(g.y) | silu_outside2(g.z) | silu_outside2(g.w)) {
+            float gv[8], uv[8];  // rare: a gate beyond the table in this chunk
             unpack8(g, gv);
+            unpack8(u, uv);
 #pragma unroll
             for (int i = 0; i < 8; ++i) y[i] = silu_mul(gv[i], uv[i]);
         }
     } else {
-        float gv[8];
+        float gv[8], uv[8];
         unpack8(g, gv);
+        unpack8(u, uv);
 #pragma unroll
         for (int i = 0; i < 8; ++i) y[i] = silu_mul(gv[i], uv[i]);
     }
@@ -220,39 +228,45 @@ fp8_rows_kernel(const uint4 *__restrict__ in, uint32_t rows, uint32_t chunks, ui
 
 // SwiGLU -> NVFP4: no row-wide dependency; lanes own one chunk of gate and the
 // matching chunk of up, lane pairs form a 16-value block.
-constexpr uint32_t kNvThreads = 256u;
-constexpr uint32_t kNvUnroll = 2u;
+constexpr uint32_t kNvThreads = 512u;
+constexpr uint32_t kNvUnroll = 2u;  // warp tiles in flight per iteration
 
+// A warp tile is 32 consecutive chunks of one row (column group `col` of `col_groups`); a warp
+// takes tiles warp, warp + W, ... and advances (row, col) incrementally, so no division runs
+// inside the loop.  step_rows = W / col_groups and step_cols = W % col_groups come from the host.
 template <bool kTable>
 __global__ void __launch_bounds__(kNvThreads)
-swiglu_nvfp4_kernel(const uint4 *__restrict__ in, uint32_t rows, uint32_t chunks, float G,
-                    uint32_t *__restrict__ codes, uint8_t *__restrict__ scales, uint32_t layout,
-                    uint32_t groups, uint32_t inner_tiles) {
+swiglu_nvfp4_kernel(const uint4 *__restrict__ in, uint32_t rows, uint32_t chunks, uint32_t col_groups,
+                    uint32_t step_rows, uint32_t step_cols, float G, uint32_t *__restrict__ codes,
+                    uint8_t *__restrict__ scales, uint32_t layout, uint32_t groups, uint32_t inner_tiles) {
     extern __shared__ __align__(16) float silu_table[];
     __shared__ scale_lut_entry lut[128];
     if (kTable) build_silu_table(silu_table);
     const bool lut_safe = build_scale_lut(lut, G);
     const uint32_t lane = threadIdx.x & 31u;
     const uint32_t warp = (blockIdx.x * kNvThreads + threadIdx.x) >> 5;
-    const uint32_t warps = (gridDim.x * kNvThreads) >> 5;
-    const uint32_t total = rows * chunks;
-    constexpr uint32_t kTile = 32u * kNvUnroll;
-    for (uint64_t tile = warp; tile * kTile < total; tile += warps) {
+    uint32_t row = warp / col_groups, col = warp % col_groups;
+    while (row < rows) {
+        uint32_t rws[kNvUnroll], qs[kNvUnroll];
+        bool oks[kNvUnroll];
         uint4 g[kNvUnroll], u[kNvUnroll];
-        uint32_t row[kNvUnroll], q[kNvUnroll];
 #pragma unroll
         for (uint32_t j = 0; j < kNvUnroll; ++j) {
-            const uint64_t c = tile * kTile + j * 32u + lane;
-            const bool ok = c < total;
-            row[j] = ok ? (uint32_t)(c / chunks) : 0u;
-            q[j] = ok ? (uint32_t)c - row[j] * chunks : 0u;
-            const uint4 *gate = in + (uint64_t)row[j] * 2u * chunks + q[j];
-            g[j] = ok ? ld_stream(gate) : make_uint4(0u, 0u, 0u, 0u);
-            u[j] = ok ? ld_stream(gate + chunks) : make_uint4(0u, 0u, 0u, 0u);
+            rws[j] = row;
+            qs[j] = col * 32u + lane;
+            oks[j] = row < rows && qs[j] < chunks;
+            const uint4 *gate = in + (uint64_t)row * 2u * chunks + qs[j];
+            g[j] = oks[j] ? ld_stream(gate) : make_uint4(0u, 0u, 0u, 0u);
+            u[j] = oks[j] ? ld_stream(gate + chunks) : make_uint4(0u, 0u, 0u, 0u);
+            row += step_rows;
+            col += step_cols;
+            if (col >= col_groups) {
+                col -= col_groups;
+                ++row;
+            }
         }
 #pragma unroll
         for (uint32_t j = 0; j < kNvUnroll; ++j) {
-            const uint64_t c = tile * kTile + j * 32u + lane;
             float y[8];
             swiglu8<kTable>(silu_table, g[j], u[j], y);
             float m = absmax8_nan(y);
@@ -265,10 +279,10 @@ swiglu_nvfp4_kernel(const uint4 *__restrict__ in, uint32_t rows, uint32_t chunks
                 m = fmaxf(fmaxf(m, __shfl_xor_sync(0xffffffffu, m, 1)), 0.0f);
                 packed = nvfp4_quantize8_exact(y[0], y[1], y[2], y[3], y[4], y[5], y[6], y[7], m, G, &scale_code);
             }
-            if (c < total) {
-                st_stream(codes + c, packed);
+            if (oks[j]) {
+                st_stream(codes + (uint64_t)rws[j] * chunks + qs[j], packed);
                 if ((lane & 1u) == 0u) {
-                    scales[scale_offset(row[j], q[j] >> 1, groups, inner_tiles, layout)] = (uint8_t)scale_code;
+                    scales[scale_offset(rws[j], qs[j] >> 1, groups, inner_tiles, layout)] = (uint8_t)scale_code;
                 }
             }
         }
@@ -312,6 +326,18 @@ int launch_fp8_rows(const void *in, uint32_t rows, uint32_t width, uint32_t in_c
     const uint32_t ctas = rows < cap ? rows : cap;
     const uint4 *src = (const uint4 *)in;
     uint2 *dst = (uint2 *)codes;
+    if (kTable) {
+        static bool configured[64] = {};
+        int dev = 0;
+        cudaGetDevice(&dev);
+        if (dev >= 0 && dev < 64 && !configured[dev]) {
+            cudaFuncSetAttribute(fp8_rows_kernel<1, kOp>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSiluTableBytes);
+            cudaFuncSetAttribute(fp8_rows_kernel<2, kOp>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSiluTableBytes);
+            cudaFuncSetAttribute(fp8_rows_kernel<4, kOp>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSiluTableBytes);
+            cudaFuncSetAttribute(fp8_rows_kernel<8, kOp>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSiluTableBytes);
+            configured[dev] = true;
+        }
+    }
     switch (s.cpt) {
     case 1: fp8_rows_kernel<1, kOp><<<ctas, s.threads, smem, stream>>>(src, rows, chunks, in_chunks_per_row, dst, scales, status_word); break;
     case 2: fp8_rows_kernel<2, kOp><<<ctas, s.threads, smem, stream>>>(src, rows, chunks, in_chunks_per_row, dst, scales, status_word); break;
@@ -346,11 +372,17 @@ int launch_swiglu_nvfp4_bf16(const void *gate_up, uint32_t rows, uint32_t width,
                              uint8_t *scales, uint32_t layout, cudaStream_t stream) {
     const uint32_t chunks = width / 8u;
     const uint32_t groups = width / kGroup;
-    const uint32_t total = rows * chunks;
-    const uint32_t tiles = (total + 32u * kNvUnroll - 1u) / (32u * kNvUnroll);
-    uint32_t blocks = (tiles + kNvThreads / 32u - 1u) / (kNvThreads / 32u);
-    if (blocks > kSmCount * 16u) blocks = kSmCount * 16u;
-    if (rows >= kTableMinRows) {
+    const uint32_t col_groups = (chunks + 31u) / 32u;
+    const uint64_t tiles = (uint64_t)rows * col_groups;
+    const uint32_t warps_per_block = kNvThreads / 32u;
+    const bool table = rows >= kTableMinRows;
+    // table flavour: persistent CTAs (the table is built once per CTA), two 512-thread CTAs with 64 KB each per SM
+    const uint64_t cap = table ? kSmCount * 2u : kSmCount * 8u;
+    uint64_t blocks = (tiles + warps_per_block - 1u) / warps_per_block;
+    if (blocks > cap) blocks = cap;
+    const uint32_t W = (uint32_t)blocks * warps_per_block;
+    const uint4 *src = (const uint4 *)gate_up;
+    if (table) {
         static bool configured[64] = {};
         int dev = 0;
         cudaGetDevice(&dev);
@@ -358,12 +390,13 @@ int launch_swiglu_nvfp4_bf16(const void *gate_up, uint32_t rows, uint32_t width,
             cudaFuncSetAttribute(swiglu_nvfp4_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSiluTableBytes);
             configured[dev] = true;
         }
-        if (blocks > kSmCount * 4u) blocks = kSmCount * 4u;  // persistent: the table is built once per CTA
-        swiglu_nvfp4_kernel<true><<<blocks, kNvThreads, kSiluTableBytes, stream>>>(
-                (const uint4 *)gate_up, rows, chunks, G, (uint32_t *)codes, scales, layout, groups, (groups + 3u) / 4u);
+        swiglu_nvfp4_kernel<true><<<(uint32_t)blocks, kNvThreads, kSiluTableBytes, stream>>>(
+                src, rows, chunks, col_groups, W / col_groups, W % col_groups, G, (uint32_t *)codes, scales, layout, groups,
+                (groups + 3u) / 4u);
     } else {
-        swiglu_nvfp4_kernel<false><<<blocks, kNvThreads, 0, stream>>>(
-                (const uint4 *)gate_up, rows, chunks, G, (uint32_t *)codes, scales, layout, groups, (groups + 3u) / 4u);
+        swiglu_nvfp4_kernel<false><<<(uint32_t)blocks, kNvThreads, 0, stream>>>(
+                src, rows, chunks, col_groups, W / col_groups, W % col_groups, G, (uint32_t *)codes, scales, layout, groups,
+                (groups + 3u) / 4u);
     }
     note_launch();
     return AXIOM_OK;
