@@ -77,6 +77,8 @@ __device__ __forceinline__ void bulk_store(void *dst_global, const void *src_sha
 __device__ __forceinline__ void bulk_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
 // Returns once every committed bulk store of this thread has finished READING shared memory.
 __device__ __forceinline__ void bulk_wait_read_all() { asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory"); }
+// Returns once all but the most recent committed bulk store of this thread have finished reading.
+__device__ __forceinline__ void bulk_wait_read_but_one() { asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory"); }
 // Orders this thread's earlier generic-proxy shared-memory writes before later async-proxy accesses.
 __device__ __forceinline__ void fence_async_shared() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
 
@@ -87,9 +89,9 @@ __device__ __forceinline__ void fence_async_shared() { asm volatile("fence.proxy
 // per-block work is one shared-memory load instead of a decode, a division
 // and a reciprocal.
 // ---------------------------------------------------------------------------
-struct scale_lut_entry {
+struct __align__(8) scale_lut_entry {
+    float nr;  // -1/d: correctly rounded reciprocal, negated for the quotient sequence
     float d;
-    float r;
 };
 
 // Called by all threads of the CTA; returns (through __syncthreads_and) whether
@@ -101,8 +103,9 @@ __device__ __forceinline__ bool build_scale_lut(scale_lut_entry *lut, float G) {
         if (code == 0u) code = 0x20u;
         if (code == 0x7fu) code = 0x7eu;
         const float d = __fdiv_rn(e4m3_to_f32(code), G);
+        const float r = __frcp_rn(d);
         lut[c].d = d;
-        lut[c].r = __frcp_rn(d);
+        lut[c].nr = -r;
         safe = safe && d >= 1.0e-25f && d <= 1.0e30f;
     }
     return __syncthreads_and(safe) != 0;
@@ -142,10 +145,10 @@ __device__ __forceinline__ uint32_t nvfp4_quantize8_fast(const float (&x)[8], fl
                                                          bool *needs_exact) {
     const uint32_t raw = cvt_e4m3x2(__fmul_rn(__fmul_rn(max_abs, 1.0f / 6.0f), G), 0.0f) & 0x7fu;
     *scale_byte = raw == 0u ? 0x20u : raw;
-    const scale_lut_entry e = lut[raw];
-    *needs_exact = *needs_exact || !(__fmul_rn(max_abs, e.r) <= 1.0e30f);  // also true for a NaN maximum
-    const float2 nr2 = make_float2(-e.r, -e.r);
-    const float2 d2 = make_float2(e.d, e.d);
+    const float2 e = *reinterpret_cast<const float2 *>(lut + raw);
+    *needs_exact = *needs_exact || !(__fmul_rn(max_abs, e.x) >= -1.0e30f);  // also true for a NaN maximum
+    const float2 nr2 = make_float2(e.x, e.x);
+    const float2 d2 = make_float2(e.y, e.y);
     uint32_t b[4];
 #pragma unroll
     for (int i = 0; i < 4; ++i) {

@@ -58,7 +58,9 @@ __device__ __forceinline__ uint2 ld_stream8(const void *p) {
 }
 
 // LPH = lanes per head (head_dim / 8); NPT = (head, lane) work items per thread.
-template <int LPH, int NPT>
+// kFast: every thread's NPT items exist and every lane carries rotary pairs (full-head
+// rotation), which removes the bounds predicates and the pass-through branch.
+template <int LPH, int NPT, bool kFast>
 __global__ void __launch_bounds__(512, NPT <= 4 ? 2 : 1)
 qk_norm_rope_paged_kernel(const qk_dev_args a) {
     __shared__ double ss_sh[kMaxHeads];
@@ -68,7 +70,7 @@ qk_norm_rope_paged_kernel(const qk_dev_args a) {
     __shared__ __align__(16) float nsin_sh[kMaxHeadDim / 2];
     __shared__ __align__(16) float gq_sh[kMaxHeadDim];
     __shared__ __align__(16) float gk_sh[kMaxHeadDim];
-    __shared__ unsigned long long kv_base_sh;  // 8-byte unit index into the pools, ~0 = no cache write
+    __shared__ unsigned long long kv_base_sh;  // element index into the pools, ~0 = no cache write
     constexpr uint32_t D = LPH * 8u;
 
     const uint32_t tid = threadIdx.x;
@@ -82,27 +84,36 @@ qk_norm_rope_paged_kernel(const qk_dev_args a) {
     }
 
     // Work item n of this thread is (head tid/LPH + n*blockDim/LPH, lane tid%LPH): blockDim is a
-    // multiple of 32 and LPH divides 32, so the lane geometry is the same for every item.
+    // multiple of 32 and LPH divides 32, so the lane geometry is the same for every item and
+    // everything below is fixed across tokens.
     const uint32_t l = tid % LPH;
     const uint32_t head0 = tid / LPH, head_step = blockDim.x / LPH;
-    const bool rotary = l < rot_lanes;
+    const bool rotary = kFast || l < rot_lanes;
     const uint32_t off_a = rotary ? 4u * l : a.rope_dim + 8u * (l - rot_lanes);
     const uint32_t off_b = rotary ? half + 4u * l : off_a + 4u;
-    const uint32_t q_elems = a.q_heads * D;
+    const uint32_t q_elems = a.q_heads * D, k_elems = a.k_heads * D;
+    // element offset of item n inside the token's Q row (heads < q_heads) or K row
+    uint32_t item_off[NPT];
+#pragma unroll
+    for (int n = 0; n < NPT; ++n) {
+        const uint32_t h = head0 + head_step * n;
+        item_off[n] = (h < a.q_heads ? h : h - a.q_heads) * D;
+    }
+    __syncthreads();
 
     for (uint32_t t = blockIdx.x; t < a.tokens; t += gridDim.x) {
         uint16_t *q_row = reinterpret_cast<uint16_t *>(a.q) + (uint64_t)t * q_elems;
-        const uint16_t *k_row = reinterpret_cast<const uint16_t *>(a.k) + (uint64_t)t * a.k_heads * D;
+        const uint16_t *k_row = reinterpret_cast<const uint16_t *>(a.k) + (uint64_t)t * k_elems;
 
         // ---- phase 1: loads and per-head FP64 sum of squares
         uint2 xa[NPT], xb[NPT];
 #pragma unroll
         for (int n = 0; n < NPT; ++n) {
+            const uint32_t h = head0 + head_step * n;
             xa[n] = make_uint2(0u, 0u);
             xb[n] = make_uint2(0u, 0u);
-            if ((head0 + head_step * n < heads)) {
-                const bool is_k = (head0 + head_step * n) >= a.q_heads;
-                const uint16_t *row = is_k ? k_row + ((head0 + head_step * n) - a.q_heads) * D : q_row + (head0 + head_step * n) * D;
+            if (kFast || h < heads) {
+                const uint16_t *row = (h < a.q_heads ? q_row : k_row) + item_off[n];
                 xa[n] = ld_stream8(row + off_a);
                 xb[n] = ld_stream8(row + off_b);
             }
@@ -122,8 +133,7 @@ qk_norm_rope_paged_kernel(const qk_dev_args a) {
                     ok = pb >= 0 && (uint32_t)pb < a.n_blocks;
                 }
                 if (ok) {
-                    base = ((((uint64_t)pb * a.n_layers + a.layer) * a.block_tokens + pos % a.block_tokens) *
-                            a.pool_stride) >> 2;
+                    base = (((uint64_t)pb * a.n_layers + a.layer) * a.block_tokens + pos % a.block_tokens) * a.pool_stride;
                 } else if (a.status_word) {
                     atomicCAS(a.status_word, AXIOM_STATUS_WORD_OK, AXIOM_STATUS_WORD_BAD_ADDRESS);
                 }
@@ -142,7 +152,8 @@ qk_norm_rope_paged_kernel(const qk_dev_args a) {
             }
 #pragma unroll
             for (int off = LPH / 2; off != 0; off >>= 1) s += __shfl_xor_sync(0xffffffffu, s, off);
-            if ((head0 + head_step * n < heads) && l == 0u) ss_sh[head0 + head_step * n] = s;
+            const uint32_t h = head0 + head_step * n;
+            if (l == 0u && (kFast || h < heads)) ss_sh[h] = s;
         }
         __syncthreads();
 
@@ -167,11 +178,21 @@ qk_norm_rope_paged_kernel(const qk_dev_args a) {
 
         // ---- phase 3: normalise, rotate, round, store
         const unsigned long long kv_base = kv_base_sh;
+        float4 c = make_float4(0.f, 0.f, 0.f, 0.f), sn = c, ns = c;
+        if (rotary) {
+            c = *reinterpret_cast<const float4 *>(cos_sh + off_a);
+            sn = *reinterpret_cast<const float4 *>(sin_sh + off_a);
+            ns = *reinterpret_cast<const float4 *>(nsin_sh + off_a);
+        }
+        const float2 c0 = make_float2(c.x, c.y), c1 = make_float2(c.z, c.w);
+        const float2 s0 = make_float2(sn.x, sn.y), s1 = make_float2(sn.z, sn.w);
+        const float2 n0 = make_float2(ns.x, ns.y), n1 = make_float2(ns.z, ns.w);
 #pragma unroll
         for (int n = 0; n < NPT; ++n) {
-            const bool is_k = (head0 + head_step * n) >= a.q_heads;
+            const uint32_t h = head0 + head_step * n;
+            const bool is_k = h >= a.q_heads;
             const float *gamma = is_k ? gk_sh : gq_sh;
-            const float inv = inv_sh[(head0 + head_step * n)];
+            const float inv = inv_sh[(kFast || h < heads) ? h : 0u];
             const float2 inv2 = make_float2(inv, inv);
             const float4 ga = *reinterpret_cast<const float4 *>(gamma + off_a);
             const float4 gb = *reinterpret_cast<const float4 *>(gamma + off_b);
@@ -183,33 +204,26 @@ qk_norm_rope_paged_kernel(const qk_dev_args a) {
             float2 oa0 = a0, oa1 = a1, ob0 = b0, ob1 = b1;
             if (rotary) {
                 // out[p] = fma(first, c, -(second*s)); out[p+half] = fma(first, s, second*c)
-                const uint32_t p0 = off_a;
-                const float4 c = *reinterpret_cast<const float4 *>(cos_sh + p0);
-                const float4 s = *reinterpret_cast<const float4 *>(sin_sh + p0);
-                const float4 ns = *reinterpret_cast<const float4 *>(nsin_sh + p0);
-                const float2 c0 = make_float2(c.x, c.y), c1 = make_float2(c.z, c.w);
-                const float2 s0 = make_float2(s.x, s.y), s1 = make_float2(s.z, s.w);
-                oa0 = __ffma2_rn(a0, c0, __fmul2_rn(b0, make_float2(ns.x, ns.y)));
-                oa1 = __ffma2_rn(a1, c1, __fmul2_rn(b1, make_float2(ns.z, ns.w)));
+                oa0 = __ffma2_rn(a0, c0, __fmul2_rn(b0, n0));
+                oa1 = __ffma2_rn(a1, c1, __fmul2_rn(b1, n1));
                 ob0 = __ffma2_rn(a0, s0, __fmul2_rn(b0, c0));
                 ob1 = __ffma2_rn(a1, s1, __fmul2_rn(b1, c1));
             }
             const uint2 pa = make_uint2(pack_bf16x2(oa0.x, oa0.y), pack_bf16x2(oa1.x, oa1.y));
             const uint2 pb = make_uint2(pack_bf16x2(ob0.x, ob0.y), pack_bf16x2(ob1.x, ob1.y));
-            if ((head0 + head_step * n < heads)) {
+            if (kFast || h < heads) {
                 if (!is_k) {
-                    uint16_t *dst = q_row + (head0 + head_step * n) * D;
+                    uint16_t *dst = q_row + item_off[n];
                     st_stream(dst + off_a, pa);
                     st_stream(dst + off_b, pb);
                 } else {
-                    const uint32_t kelem = ((head0 + head_step * n) - a.q_heads) * D;  // element inside the token's K row
                     if (kv_base != ~0ull) {
-                        uint2 *dst = reinterpret_cast<uint2 *>(a.k_pool) + kv_base;
-                        st_stream(dst + ((kelem + off_a) >> 2), pa);
-                        st_stream(dst + ((kelem + off_b) >> 2), pb);
+                        uint16_t *dst = reinterpret_cast<uint16_t *>(a.k_pool) + kv_base + item_off[n];
+                        st_stream(dst + off_a, pa);
+                        st_stream(dst + off_b, pb);
                     }
                     if (a.k_out) {
-                        uint16_t *dst = reinterpret_cast<uint16_t *>(a.k_out) + (uint64_t)t * a.k_heads * D + kelem;
+                        uint16_t *dst = reinterpret_cast<uint16_t *>(a.k_out) + (uint64_t)t * k_elems + item_off[n];
                         st_stream(dst + off_a, pa);
                         st_stream(dst + off_b, pb);
                     }
@@ -219,7 +233,7 @@ qk_norm_rope_paged_kernel(const qk_dev_args a) {
         // V rides along unchanged (BF16 in, BF16 cache)
         if (a.v && a.v_pool && kv_base != ~0ull) {
             const uint4 *v_row = a.v + (uint64_t)t * a.k_heads * LPH;
-            uint4 *dst = reinterpret_cast<uint4 *>(reinterpret_cast<uint2 *>(a.v_pool) + kv_base);
+            uint4 *dst = reinterpret_cast<uint4 *>(reinterpret_cast<uint16_t *>(a.v_pool) + kv_base);
             for (uint32_t j = tid; j < a.k_heads * LPH; j += blockDim.x) st_stream(dst + j, ld_stream(v_row + j));
         }
         __syncthreads();  // shared tables are rewritten by the next token
@@ -262,12 +276,19 @@ void launch_qk(const qk_dev_args &a, cudaStream_t stream) {
         }
     }
     if (best_threads == 0u) { best_npt = 8u; best_threads = 512u; }
+    const bool fast = best_waste == 0u && a.rope_dim == a.head_dim;
+#define AXB_QK_LAUNCH(NPT)                                                                              \
+    do {                                                                                                 \
+        if (fast) qk_norm_rope_paged_kernel<LPH, NPT, true><<<grid, best_threads, 0, stream>>>(a);       \
+        else qk_norm_rope_paged_kernel<LPH, NPT, false><<<grid, best_threads, 0, stream>>>(a);           \
+    } while (0)
     switch (best_npt) {
-    case 2: qk_norm_rope_paged_kernel<LPH, 2><<<grid, best_threads, 0, stream>>>(a); break;
-    case 3: qk_norm_rope_paged_kernel<LPH, 3><<<grid, best_threads, 0, stream>>>(a); break;
-    case 4: qk_norm_rope_paged_kernel<LPH, 4><<<grid, best_threads, 0, stream>>>(a); break;
-    default: qk_norm_rope_paged_kernel<LPH, 8><<<grid, best_threads, 0, stream>>>(a); break;
+    case 2: AXB_QK_LAUNCH(2); break;
+    case 3: AXB_QK_LAUNCH(3); break;
+    case 4: AXB_QK_LAUNCH(4); break;
+    default: AXB_QK_LAUNCH(8); break;
     }
+#undef AXB_QK_LAUNCH
 }
 
 bool is_pow2(uint32_t v) { return v && !(v & (v - 1u)); }
