@@ -11,15 +11,15 @@
 //   out[p+half] = bf16(fma(n[p], s,   n[p+half]*c))
 //   dims >= rope_dim: bf16(n)
 //
-// One CTA per token.  A lane owns BOTH members of four NeoX pairs: dims 4l..4l+3 and
-// rope_dim/2 + 4l.. of one head (two 8-byte accesses; a warp still reads whole 128-byte
-// lines), so the rotation needs no lane exchange, no select and no divergent branch.
-// Lanes past the rotary dims carry 8 pass-through dims.  head_dim/8 adjacent lanes form a
-// head.  Three phases separated by CTA barriers keep the scalar work out of the replicated
-// lane code:
-//   1. load, FP64 sum of squares per head (shuffle tree) -> shared
-//   2. one thread per head: inv; one thread per (pair, cos|sin): table row (cos, sin, -sin)
-//   3. normalise, rotate, round, store (packed F32x2 arithmetic)
+// A lane owns BOTH members of four NeoX pairs: dims 4l..4l+3 and rope_dim/2 + 4l.. of one
+// head (two 8-byte accesses; a warp still covers whole 128-byte lines), so the rotation needs
+// no lane exchange, no select and no divergent branch.  Lanes past the rotary dims carry 8
+// pass-through dims.  head_dim/8 adjacent lanes form a head, so a head never leaves its warp:
+// the FP64 sum is a shuffle butterfly and every lane derives the head's factor itself.  The
+// only cross-thread data is the token's rotary table (cos, sin, -sin per pair; sincosf gives
+// bit-for-bit the values of separate sinf and cosf calls for every non-negative float —
+// checked exhaustively on the device).  Two kernels share this arithmetic: one CTA per token
+// for short batches, and a persistent bulk-copy pipeline for long ones.
 // The frequency table is an input: it is evaluated once per model on the device
 // (yarn_inv_freq_kernel) instead of powf/logf per thread per call.
 #include "pipeline.cuh"
@@ -57,14 +57,110 @@ __device__ __forceinline__ uint2 ld_stream8(const void *p) {
     return v;
 }
 
-// LPH = lanes per head (head_dim / 8); NPT = (head, lane) work items per thread.
-// kFast: every thread's NPT items exist and every lane carries rotary pairs (full-head
-// rotation), which removes the bounds predicates and the pass-through branch.
+
+// (float)(1.0 / sqrt(v)), v = ss / D + eps, without the FP64 square root and division on the
+// common path.  y0 = rsqrt.approx(float(v)) is within 2^-22 of 1/sqrt(v); one Newton step in
+// FP64, y = y0 + (y0/2)(1 - v*y0^2), brings that to 1.5 * 2^-44.  The reference value (a
+// correctly rounded FP64 sqrt, then a correctly rounded division: within 2^-52 of the true
+// quotient) and y therefore both lie in [y(1 - 2^-41), y(1 + 2^-41)]; when the two ends of that
+// interval round to the same float, every value inside does, and that float is the answer.
+// Otherwise (about one value in 2^17), or when float(v) leaves the range where the
+// approximation is specified for normal numbers, the plain expression is evaluated.
+__device__ __forceinline__ float inv_rms_from_sum(double ss, double inv_d, double eps) {
+    const double v = __fma_rn(ss, inv_d, eps);  // ss / D is exact (D is a power of two)
+    const float vf = (float)v;
+    float y0;
+    asm("rsqrt.approx.ftz.f32 %0, %1;" : "=f"(y0) : "f"(vf));
+    const double y0d = (double)y0;
+    const double r = __fma_rn(-__dmul_rn(v, y0d), y0d, 1.0);
+    const double y = __fma_rn(__dmul_rn(0.5, y0d), r, y0d);
+    const float lo = (float)__dmul_rn(y, 1.0 - 0x1p-41), hi = (float)__dmul_rn(y, 1.0 + 0x1p-41);
+    if (lo == hi && vf > 1.0e-30f && vf < 1.0e30f) return lo;
+    return (float)(1.0 / sqrt(v));
+}
+
+// One row of the rotary table: c = cosf(angle) * mscale, s = sinf(angle) * mscale with
+// angle = (float)pos * inv_freq.  sincosf() shares the argument reduction between the two.
+__device__ __forceinline__ void rope_table_entry(uint32_t pos, float inv_freq, float mscale, float *c, float *s) {
+    const float angle = __fmul_rn((float)pos, inv_freq);
+    float sv, cv;
+    sincosf(angle, &sv, &cv);
+    *c = __fmul_rn(cv, mscale);
+    *s = __fmul_rn(sv, mscale);
+}
+
+// Rotary factors of one lane: four (cos, sin, -sin) triples as packed pairs.
+struct rot_regs {
+    float2 c0, c1, s0, s1, n0, n1;
+};
+
+__device__ __forceinline__ rot_regs load_rot(const float *cos_t, const float *sin_t, const float *nsin_t, uint32_t off,
+                                             bool rotary) {
+    float4 c = make_float4(0.f, 0.f, 0.f, 0.f), sn = c, ns = c;
+    if (rotary) {
+        c = *reinterpret_cast<const float4 *>(cos_t + off);
+        sn = *reinterpret_cast<const float4 *>(sin_t + off);
+        ns = *reinterpret_cast<const float4 *>(nsin_t + off);
+    }
+    rot_regs r;
+    r.c0 = make_float2(c.x, c.y); r.c1 = make_float2(c.z, c.w);
+    r.s0 = make_float2(sn.x, sn.y); r.s1 = make_float2(sn.z, sn.w);
+    r.n0 = make_float2(ns.x, ns.y); r.n1 = make_float2(ns.z, ns.w);
+    return r;
+}
+
+// One work item: eight dims of one head held by one lane (xa = dims off_a.., xb = dims off_b..).
+// Sums the squares in FP64 across the LPH lanes of the head (xor butterfly: every lane ends with
+// the total; FP64 sums of BF16 squares are exact unless the row spans more than ~2^18 in
+// magnitude, so the order of the additions is immaterial), derives the head's factor in every
+// lane — the same instructions a single lane would cost, and no shared-memory round trip or
+// barrier — then normalises, rotates and packs.
+template <int LPH>
+__device__ __forceinline__ void qk_item(uint2 xa, uint2 xb, const float4 ga, const float4 gb, const rot_regs &r,
+                                        bool rotary, double inv_d, double eps, uint2 *out_a, uint2 *out_b) {
+    const float2 fa0 = make_float2(bf16_lo(xa.x), bf16_hi(xa.x)), fa1 = make_float2(bf16_lo(xa.y), bf16_hi(xa.y));
+    const float2 fb0 = make_float2(bf16_lo(xb.x), bf16_hi(xb.x)), fb1 = make_float2(bf16_lo(xb.y), bf16_hi(xb.y));
+    double s = 0.0, s_hi = 0.0;
+    {
+        const double d0 = (double)fa0.x, d1 = (double)fa0.y, d2 = (double)fa1.x, d3 = (double)fa1.y;
+        const double e0 = (double)fb0.x, e1 = (double)fb0.y, e2 = (double)fb1.x, e3 = (double)fb1.y;
+        s = __fma_rn(d0, d0, s); s_hi = __fma_rn(e0, e0, s_hi);
+        s = __fma_rn(d1, d1, s); s_hi = __fma_rn(e1, e1, s_hi);
+        s = __fma_rn(d2, d2, s); s_hi = __fma_rn(e2, e2, s_hi);
+        s = __fma_rn(d3, d3, s); s_hi = __fma_rn(e3, e3, s_hi);
+        s += s_hi;
+    }
+#pragma unroll
+    for (int off = LPH / 2; off != 0; off >>= 1) s += __shfl_xor_sync(0xffffffffu, s, off);
+    const float inv = inv_rms_from_sum(s, inv_d, eps);
+    const float2 inv2 = make_float2(inv, inv);
+    // n = (x * inv) * gamma
+    const float2 a0 = __fmul2_rn(__fmul2_rn(fa0, inv2), make_float2(ga.x, ga.y));
+    const float2 a1 = __fmul2_rn(__fmul2_rn(fa1, inv2), make_float2(ga.z, ga.w));
+    const float2 b0 = __fmul2_rn(__fmul2_rn(fb0, inv2), make_float2(gb.x, gb.y));
+    const float2 b1 = __fmul2_rn(__fmul2_rn(fb1, inv2), make_float2(gb.z, gb.w));
+    float2 oa0 = a0, oa1 = a1, ob0 = b0, ob1 = b1;
+    if (rotary) {
+        // out[p] = fma(first, c, -(second*s)); out[p+half] = fma(first, s, second*c)
+        oa0 = __ffma2_rn(a0, r.c0, __fmul2_rn(b0, r.n0));
+        oa1 = __ffma2_rn(a1, r.c1, __fmul2_rn(b1, r.n1));
+        ob0 = __ffma2_rn(a0, r.s0, __fmul2_rn(b0, r.c0));
+        ob1 = __ffma2_rn(a1, r.s1, __fmul2_rn(b1, r.c1));
+    }
+    *out_a = make_uint2(pack_bf16x2(oa0.x, oa0.y), pack_bf16x2(oa1.x, oa1.y));
+    *out_b = make_uint2(pack_bf16x2(ob0.x, ob0.y), pack_bf16x2(ob1.x, ob1.y));
+}
+
+// ---------------------------------------------------------------------------
+// Per-token flavour (few tokens: lowest latency).  One CTA per token, LPH = lanes per head
+// (head_dim / 8), NPT = (head, lane) work items per thread.  kFast: every thread's NPT items
+// exist and every lane carries rotary pairs, which removes the bounds predicates and the
+// pass-through branch.  One CTA barrier: the rotary table (threads below rope_dim/2) and the
+// cache address (thread 0) are produced while the Q/K loads are in flight.
+// ---------------------------------------------------------------------------
 template <int LPH, int NPT, bool kFast>
-__global__ void __launch_bounds__(512, NPT <= 4 ? 2 : 1)
+__global__ void __launch_bounds__(512, 1)
 qk_norm_rope_paged_kernel(const qk_dev_args a) {
-    __shared__ double ss_sh[kMaxHeads];
-    __shared__ float inv_sh[kMaxHeads];
     __shared__ __align__(16) float cos_sh[kMaxHeadDim / 2];
     __shared__ __align__(16) float sin_sh[kMaxHeadDim / 2];
     __shared__ __align__(16) float nsin_sh[kMaxHeadDim / 2];
@@ -84,28 +180,19 @@ qk_norm_rope_paged_kernel(const qk_dev_args a) {
     }
 
     // Work item n of this thread is (head tid/LPH + n*blockDim/LPH, lane tid%LPH): blockDim is a
-    // multiple of 32 and LPH divides 32, so the lane geometry is the same for every item and
-    // everything below is fixed across tokens.
+    // multiple of 32 and LPH divides 32, so the lane geometry is the same for every item.
     const uint32_t l = tid % LPH;
     const uint32_t head0 = tid / LPH, head_step = blockDim.x / LPH;
     const bool rotary = kFast || l < rot_lanes;
     const uint32_t off_a = rotary ? 4u * l : a.rope_dim + 8u * (l - rot_lanes);
     const uint32_t off_b = rotary ? half + 4u * l : off_a + 4u;
     const uint32_t q_elems = a.q_heads * D, k_elems = a.k_heads * D;
-    // element offset of item n inside the token's Q row (heads < q_heads) or K row
-    uint32_t item_off[NPT];
-#pragma unroll
-    for (int n = 0; n < NPT; ++n) {
-        const uint32_t h = head0 + head_step * n;
-        item_off[n] = (h < a.q_heads ? h : h - a.q_heads) * D;
-    }
-    __syncthreads();
+    const double inv_d = 1.0 / (double)D, eps = (double)a.eps;
 
     for (uint32_t t = blockIdx.x; t < a.tokens; t += gridDim.x) {
         uint16_t *q_row = reinterpret_cast<uint16_t *>(a.q) + (uint64_t)t * q_elems;
         const uint16_t *k_row = reinterpret_cast<const uint16_t *>(a.k) + (uint64_t)t * k_elems;
 
-        // ---- phase 1: loads and per-head FP64 sum of squares
         uint2 xa[NPT], xb[NPT];
 #pragma unroll
         for (int n = 0; n < NPT; ++n) {
@@ -113,13 +200,27 @@ qk_norm_rope_paged_kernel(const qk_dev_args a) {
             xa[n] = make_uint2(0u, 0u);
             xb[n] = make_uint2(0u, 0u);
             if (kFast || h < heads) {
-                const uint16_t *row = (h < a.q_heads ? q_row : k_row) + item_off[n];
+                const uint16_t *row = h < a.q_heads ? q_row + h * D : k_row + (h - a.q_heads) * D;
                 xa[n] = ld_stream8(row + off_a);
                 xb[n] = ld_stream8(row + off_b);
             }
         }
         const uint32_t pos = a.positions[t];
-        if (tid == 0u) {
+        if (tid < half) {
+            float cv, sv;
+            rope_table_entry(pos, a.inv_freq[tid], a.mscale, &cv, &sv);
+            cos_sh[tid] = cv;
+            sin_sh[tid] = sv;
+            nsin_sh[tid] = -sv;
+        }
+        for (uint32_t p = tid + blockDim.x; p < half; p += blockDim.x) {  // CTAs narrower than the table
+            float cv, sv;
+            rope_table_entry(pos, a.inv_freq[p], a.mscale, &cv, &sv);
+            cos_sh[p] = cv;
+            sin_sh[p] = sv;
+            nsin_sh[p] = -sv;
+        }
+        if (tid == blockDim.x - 1u) {
             unsigned long long base = ~0ull;
             if (a.k_pool) {
                 uint32_t lb = pos / a.block_tokens;
@@ -140,90 +241,33 @@ qk_norm_rope_paged_kernel(const qk_dev_args a) {
             }
             kv_base_sh = base;
         }
-#pragma unroll
-        for (int n = 0; n < NPT; ++n) {
-            const float f[8] = {bf16_lo(xa[n].x), bf16_hi(xa[n].x), bf16_lo(xa[n].y), bf16_hi(xa[n].y),
-                                bf16_lo(xb[n].x), bf16_hi(xb[n].x), bf16_lo(xb[n].y), bf16_hi(xb[n].y)};
-            double s = 0.0;
-#pragma unroll
-            for (int i = 0; i < 8; ++i) {
-                const double d = (double)f[i];
-                s = __fma_rn(d, d, s);
-            }
-#pragma unroll
-            for (int off = LPH / 2; off != 0; off >>= 1) s += __shfl_xor_sync(0xffffffffu, s, off);
-            const uint32_t h = head0 + head_step * n;
-            if (l == 0u && (kFast || h < heads)) ss_sh[h] = s;
-        }
         __syncthreads();
 
-        // ---- phase 2: one thread per head / per table entry
-        for (uint32_t e = tid; e < heads + a.rope_dim; e += blockDim.x) {
-            if (e < heads) {
-                inv_sh[e] = (float)(1.0 / sqrt(ss_sh[e] / (double)D + (double)a.eps));
-            } else {
-                const uint32_t idx = e - heads;
-                const uint32_t p = idx < half ? idx : idx - half;
-                const float angle = __fmul_rn((float)pos, a.inv_freq[p]);
-                if (idx < half) {
-                    cos_sh[p] = __fmul_rn(cosf(angle), a.mscale);
-                } else {
-                    const float sv = __fmul_rn(sinf(angle), a.mscale);
-                    sin_sh[p] = sv;
-                    nsin_sh[p] = -sv;
-                }
-            }
-        }
-        __syncthreads();
-
-        // ---- phase 3: normalise, rotate, round, store
         const unsigned long long kv_base = kv_base_sh;
-        float4 c = make_float4(0.f, 0.f, 0.f, 0.f), sn = c, ns = c;
-        if (rotary) {
-            c = *reinterpret_cast<const float4 *>(cos_sh + off_a);
-            sn = *reinterpret_cast<const float4 *>(sin_sh + off_a);
-            ns = *reinterpret_cast<const float4 *>(nsin_sh + off_a);
-        }
-        const float2 c0 = make_float2(c.x, c.y), c1 = make_float2(c.z, c.w);
-        const float2 s0 = make_float2(sn.x, sn.y), s1 = make_float2(sn.z, sn.w);
-        const float2 n0 = make_float2(ns.x, ns.y), n1 = make_float2(ns.z, ns.w);
+        const rot_regs r = load_rot(cos_sh, sin_sh, nsin_sh, off_a, rotary);
 #pragma unroll
         for (int n = 0; n < NPT; ++n) {
             const uint32_t h = head0 + head_step * n;
             const bool is_k = h >= a.q_heads;
             const float *gamma = is_k ? gk_sh : gq_sh;
-            const float inv = inv_sh[(kFast || h < heads) ? h : 0u];
-            const float2 inv2 = make_float2(inv, inv);
             const float4 ga = *reinterpret_cast<const float4 *>(gamma + off_a);
             const float4 gb = *reinterpret_cast<const float4 *>(gamma + off_b);
-            // n = (x * inv) * gamma
-            const float2 a0 = __fmul2_rn(__fmul2_rn(make_float2(bf16_lo(xa[n].x), bf16_hi(xa[n].x)), inv2), make_float2(ga.x, ga.y));
-            const float2 a1 = __fmul2_rn(__fmul2_rn(make_float2(bf16_lo(xa[n].y), bf16_hi(xa[n].y)), inv2), make_float2(ga.z, ga.w));
-            const float2 b0 = __fmul2_rn(__fmul2_rn(make_float2(bf16_lo(xb[n].x), bf16_hi(xb[n].x)), inv2), make_float2(gb.x, gb.y));
-            const float2 b1 = __fmul2_rn(__fmul2_rn(make_float2(bf16_lo(xb[n].y), bf16_hi(xb[n].y)), inv2), make_float2(gb.z, gb.w));
-            float2 oa0 = a0, oa1 = a1, ob0 = b0, ob1 = b1;
-            if (rotary) {
-                // out[p] = fma(first, c, -(second*s)); out[p+half] = fma(first, s, second*c)
-                oa0 = __ffma2_rn(a0, c0, __fmul2_rn(b0, n0));
-                oa1 = __ffma2_rn(a1, c1, __fmul2_rn(b1, n1));
-                ob0 = __ffma2_rn(a0, s0, __fmul2_rn(b0, c0));
-                ob1 = __ffma2_rn(a1, s1, __fmul2_rn(b1, c1));
-            }
-            const uint2 pa = make_uint2(pack_bf16x2(oa0.x, oa0.y), pack_bf16x2(oa1.x, oa1.y));
-            const uint2 pb = make_uint2(pack_bf16x2(ob0.x, ob0.y), pack_bf16x2(ob1.x, ob1.y));
+            uint2 pa, pb;
+            qk_item<LPH>(xa[n], xb[n], ga, gb, r, rotary, inv_d, eps, &pa, &pb);
             if (kFast || h < heads) {
                 if (!is_k) {
-                    uint16_t *dst = q_row + item_off[n];
+                    uint16_t *dst = q_row + h * D;
                     st_stream(dst + off_a, pa);
                     st_stream(dst + off_b, pb);
                 } else {
+                    const uint32_t off = (h - a.q_heads) * D;
                     if (kv_base != ~0ull) {
-                        uint16_t *dst = reinterpret_cast<uint16_t *>(a.k_pool) + kv_base + item_off[n];
+                        uint16_t *dst = reinterpret_cast<uint16_t *>(a.k_pool) + kv_base + off;
                         st_stream(dst + off_a, pa);
                         st_stream(dst + off_b, pb);
                     }
                     if (a.k_out) {
-                        uint16_t *dst = reinterpret_cast<uint16_t *>(a.k_out) + (uint64_t)t * k_elems + item_off[n];
+                        uint16_t *dst = reinterpret_cast<uint16_t *>(a.k_out) + (uint64_t)t * k_elems + off;
                         st_stream(dst + off_a, pa);
                         st_stream(dst + off_b, pb);
                     }
@@ -236,8 +280,190 @@ qk_norm_rope_paged_kernel(const qk_dev_args a) {
             uint4 *dst = reinterpret_cast<uint4 *>(reinterpret_cast<uint16_t *>(a.v_pool) + kv_base);
             for (uint32_t j = tid; j < a.k_heads * LPH; j += blockDim.x) st_stream(dst + j, ld_stream(v_row + j));
         }
-        __syncthreads();  // shared tables are rewritten by the next token
+        __syncthreads();  // the shared tables are rewritten for the next token
     }
+}
+
+// ---------------------------------------------------------------------------
+// Streaming flavour for many tokens: a persistent CTA per SM made of independent teams.
+// A team owns `slots` shared-memory token slots laid out [Q heads | K heads | V heads]; its
+// thread 0 keeps bulk loads of the next tokens in flight, the team normalises and rotates the
+// slot IN PLACE, and thread 0 sends the finished slot out with bulk stores (Q row back in
+// place, K row to its cache page and/or k_out, V row to its cache page) — the data path has
+// no per-thread global access at all.  Slot (i-1) is refilled at the end of token i, once its
+// stores have finished reading shared memory (one store group may stay pending), so loads run
+// `slots - 1` tokens ahead.  One team barrier per token: the rotary table of token i+1 is
+// written (double-buffered) at the top of iteration i, before the wait for token i's data;
+// positions and block-table entries are fetched two and one iterations ahead into registers,
+// which keeps the dependent pos -> table -> address chain off the critical path.
+// ---------------------------------------------------------------------------
+constexpr uint32_t kQkMaxSlots = 4u;
+constexpr uint32_t kQkStreamThreads = 768u;  // 24 warps: leaves 80 registers per thread
+
+struct qk_stream_geom {
+    uint32_t team_threads, teams, slots, slot_bytes;
+};
+
+// floats of one team's table area: two buffers of three D/2 tables
+__host__ __device__ inline uint32_t qk_team_words(uint32_t D) { return (D / 2u) * 6u; }
+
+__device__ __forceinline__ void team_sync(uint32_t team, uint32_t threads) {
+    asm volatile("bar.sync %0, %1;" ::"r"(team + 1u), "r"(threads) : "memory");
+}
+
+template <int LPH, int NPT, bool kFullRot>
+__global__ void __launch_bounds__(kQkStreamThreads, 1)
+qk_norm_rope_stream_kernel(const qk_dev_args a, const qk_stream_geom g) {
+    extern __shared__ __align__(128) uint8_t smem[];
+    constexpr uint32_t D = LPH * 8u;
+    const uint32_t half = a.rope_dim >> 1;
+    const uint32_t rot_lanes = a.rope_dim >> 3;
+    const uint32_t q_bytes = a.q_heads * D * 2u, k_bytes = a.k_heads * D * 2u;
+    const bool has_v = a.v != nullptr && a.v_pool != nullptr;
+
+    // [teams][slots][slot_bytes] | gq[D] gk[D] | per team: 2 x (cos, sin, -sin)[D/2] | barriers
+    float *gq_sh = reinterpret_cast<float *>(smem + (size_t)g.teams * g.slots * g.slot_bytes);
+    float *gk_sh = gq_sh + D;
+    float *team_area = gk_sh + D;
+    const uint32_t tid = threadIdx.x, team = tid / g.team_threads, t = tid % g.team_threads;
+    float *tables = team_area + (size_t)team * qk_team_words(D);
+    uint64_t *bars = reinterpret_cast<uint64_t *>(team_area + (size_t)g.teams * qk_team_words(D)) + team * kQkMaxSlots;
+    uint8_t *my_slots = smem + (size_t)team * g.slots * g.slot_bytes;
+
+    for (uint32_t i = tid; i < D; i += blockDim.x) {
+        gq_sh[i] = a.q_heads ? __uint_as_float((uint32_t)a.q_gamma[i] << 16) : 0.0f;
+        gk_sh[i] = a.k_heads ? __uint_as_float((uint32_t)a.k_gamma[i] << 16) : 0.0f;
+    }
+    if (t == 0u) {
+        for (uint32_t j = 0; j < g.slots; ++j) mbar_init(bars + j, 1u);
+        mbar_init_fence();
+    }
+    __syncthreads();
+
+    const uint32_t l = t % LPH;
+    const uint32_t head0 = t / LPH, head_step = g.team_threads / LPH;
+    const bool rotary = kFullRot || l < rot_lanes;
+    const uint32_t off_a = rotary ? 4u * l : a.rope_dim + 8u * (l - rot_lanes);
+    const uint32_t off_b = rotary ? half + 4u * l : off_a + 4u;
+    const double inv_d = 1.0 / (double)D, eps = (double)a.eps;
+    // byte offset of this thread's first item inside a slot, and the step to its next item
+    const uint32_t item0 = (head0 * D + off_a) * 2u, item_step = head_step * D * 2u, b_delta = (off_b - off_a) * 2u;
+
+    // tokens of this CTA: blockIdx.x + n * gridDim.x; this team takes n = team + teams * i
+    const uint32_t cta_tokens = a.tokens > blockIdx.x ? (a.tokens - blockIdx.x + gridDim.x - 1u) / gridDim.x : 0u;
+    const uint32_t my_tokens = team < cta_tokens ? (cta_tokens - team + g.teams - 1u) / g.teams : 0u;
+    auto token_of = [&](uint32_t i) { return blockIdx.x + (team + g.teams * i) * gridDim.x; };
+
+    auto issue = [&](uint32_t i) {  // thread 0 of the team
+        const uint64_t tok = token_of(i);
+        const uint32_t j = i % g.slots;
+        uint8_t *slot = my_slots + (size_t)j * g.slot_bytes;
+        mbar_arrive_expect_tx(bars + j, q_bytes + k_bytes + (has_v ? k_bytes : 0u));
+        if (q_bytes) bulk_load(slot, reinterpret_cast<const uint8_t *>(a.q) + tok * q_bytes, q_bytes, bars + j);
+        if (k_bytes) bulk_load(slot + q_bytes, reinterpret_cast<const uint8_t *>(a.k) + tok * k_bytes, k_bytes, bars + j);
+        if (has_v) bulk_load(slot + q_bytes + k_bytes, reinterpret_cast<const uint8_t *>(a.v) + tok * k_bytes, k_bytes, bars + j);
+    };
+    if (t == 0u) {
+        for (uint32_t i = 0; i + 1u < g.slots && i < my_tokens; ++i) issue(i);
+    }
+
+    // table entry that maps a position's logical cache block (thread 0 only; ~0 when the
+    // position lies outside the table)
+    auto table_index = [&](uint32_t pos, uint32_t tok) -> uint64_t {
+        uint32_t lb = pos / a.block_tokens;
+        if (a.flags & AXIOM_QK_FLAG_RING) lb %= a.tbl_stride;
+        else if (lb >= a.tbl_stride) return ~0ull;
+        const uint64_t trow = (a.flags & AXIOM_QK_FLAG_PER_TOKEN_TABLE) ? tok : 0u;
+        return trow * a.tbl_stride + lb;
+    };
+    auto write_table = [&](uint32_t buffer, uint32_t pos) {  // threads below rope_dim/2 (any team size)
+        float *cos_t = tables + buffer * (D / 2u) * 3u, *sin_t = cos_t + D / 2u, *nsin_t = sin_t + D / 2u;
+        for (uint32_t p = t; p < half; p += g.team_threads) {
+            float cv, sv;
+            rope_table_entry(pos, a.inv_freq[p], a.mscale, &cv, &sv);
+            cos_t[p] = cv;
+            sin_t[p] = sv;
+            nsin_t[p] = -sv;
+        }
+    };
+    const bool paged = a.k_pool != nullptr && t == 0u;
+    uint32_t pos_cur = my_tokens > 0u ? a.positions[token_of(0u)] : 0u;
+    uint32_t pos_n1 = my_tokens > 1u ? a.positions[token_of(1u)] : 0u;
+    int32_t pb_cur = -1;  // physical block of the current token, -1 = none
+    if (paged && my_tokens > 0u) {
+        const uint64_t idx = table_index(pos_cur, token_of(0u));
+        if (idx != ~0ull) pb_cur = a.block_tables[idx];
+    }
+    if (my_tokens > 0u) write_table(0u, pos_cur);
+    team_sync(team, g.team_threads);
+
+    bool faulted = false;
+    for (uint32_t i = 0; i < my_tokens; ++i) {
+        const uint32_t j = i % g.slots;
+        const uint32_t tok = token_of(i);
+        // fetch ahead: position of token i+2, table entry and rotary table of token i+1
+        const uint32_t pos_n2 = i + 2u < my_tokens ? a.positions[token_of(i + 2u)] : 0u;
+        int32_t pb_n1 = -1;
+        if (paged && i + 1u < my_tokens) {
+            const uint64_t idx = table_index(pos_n1, token_of(i + 1u));
+            if (idx != ~0ull) pb_n1 = a.block_tables[idx];
+        }
+        if (i + 1u < my_tokens) write_table((i + 1u) & 1u, pos_n1);
+
+        uint8_t *slot = my_slots + (size_t)j * g.slot_bytes;
+        // A wait that ran out raises the fault word; the team carries on (on whatever the slot
+        // holds) so that its barriers stay matched, and stops waiting and storing.
+        if (!faulted && !mbar_wait(bars + j, (i / g.slots) & 1u)) faulted = true;
+
+        const float *cos_t = tables + (i & 1u) * (D / 2u) * 3u;
+        const rot_regs r = load_rot(cos_t, cos_t + D / 2u, cos_t + D, off_a, rotary);
+        uint8_t *item = slot + item0;
+        uint32_t h = head0;
+#pragma unroll
+        for (int n = 0; n < NPT; ++n) {
+            const float *gamma = h >= a.q_heads ? gk_sh : gq_sh;
+            uint2 *pa_ptr = reinterpret_cast<uint2 *>(item);
+            uint2 *pb_ptr = reinterpret_cast<uint2 *>(item + b_delta);
+            const float4 ga = *reinterpret_cast<const float4 *>(gamma + off_a);
+            const float4 gb = *reinterpret_cast<const float4 *>(gamma + off_b);
+            uint2 pa, pb;
+            qk_item<LPH>(*pa_ptr, *pb_ptr, ga, gb, r, rotary, inv_d, eps, &pa, &pb);
+            *pa_ptr = pa;
+            *pb_ptr = pb;
+            item += item_step;
+            h += head_step;
+        }
+        fence_async_shared();
+        team_sync(team, g.team_threads);
+
+        if (t == 0u && !faulted) {
+            const uint8_t *src = slot;
+            if (q_bytes) bulk_store(reinterpret_cast<uint8_t *>(a.q) + (uint64_t)tok * q_bytes, src, q_bytes);
+            if (k_bytes && a.k_out) bulk_store(reinterpret_cast<uint8_t *>(a.k_out) + (uint64_t)tok * k_bytes, src + q_bytes, k_bytes);
+            if (a.k_pool) {
+                if (pb_cur >= 0 && (uint32_t)pb_cur < a.n_blocks) {
+                    const uint64_t base = ((((uint64_t)pb_cur * a.n_layers + a.layer) * a.block_tokens +
+                                            pos_cur % a.block_tokens) * a.pool_stride) * 2u;
+                    if (k_bytes) bulk_store(reinterpret_cast<uint8_t *>(a.k_pool) + base, src + q_bytes, k_bytes);
+                    if (has_v) bulk_store(reinterpret_cast<uint8_t *>(a.v_pool) + base, src + q_bytes + k_bytes, k_bytes);
+                } else if (a.status_word) {
+                    atomicCAS(a.status_word, AXIOM_STATUS_WORD_OK, AXIOM_STATUS_WORD_BAD_ADDRESS);
+                }
+            }
+            bulk_commit();
+            // refill the slot of the PREVIOUS token (slot of token i + slots - 1): its stores are
+            // the older group, so only they have to be done reading.
+            const uint32_t nxt = i + g.slots - 1u;
+            if (nxt < my_tokens) {
+                bulk_wait_read_but_one();
+                issue(nxt);
+            }
+        }
+        pos_cur = pos_n1;
+        pos_n1 = pos_n2;
+        pb_cur = pb_n1;
+    }
+    if (t == 0u) bulk_wait_read_all();
 }
 
 // Frequency table.  The correction range (floor/ceil of the two YaRN
@@ -291,6 +517,78 @@ void launch_qk(const qk_dev_args &a, cudaStream_t stream) {
 #undef AXB_QK_LAUNCH
 }
 
+constexpr size_t kQkSmemBudget = 227u * 1024u;
+
+size_t qk_stream_smem(const qk_dev_args &a, const qk_stream_geom &g) {
+    return (size_t)g.teams * g.slots * g.slot_bytes + 2u * a.head_dim * sizeof(float) +
+           (size_t)g.teams * qk_team_words(a.head_dim) * sizeof(float) +
+           (size_t)g.teams * kQkMaxSlots * sizeof(uint64_t);
+}
+
+// Picks the team shape of the streaming kernel; false when the problem does not fit it
+// (work items do not divide evenly into whole warps, or fewer than three slots fit).
+template <int LPH>
+bool launch_qk_stream(const qk_dev_args &a, cudaStream_t stream) {
+    const uint32_t items = (a.q_heads + a.k_heads) * LPH;
+    const bool has_v = a.v != nullptr && a.v_pool != nullptr;
+    qk_stream_geom best{};
+    uint32_t best_npt = 0u, best_score = 0u;
+    static const uint32_t kNpt[] = {2u, 3u, 4u, 6u, 8u};
+    for (uint32_t npt : kNpt) {
+        if (items % npt) continue;
+        qk_stream_geom g{};
+        g.team_threads = items / npt;
+        if (g.team_threads % 32u || g.team_threads > 512u || g.team_threads < 64u) continue;
+        g.slot_bytes = ((a.q_heads + a.k_heads) + (has_v ? a.k_heads : 0u)) * a.head_dim * 2u;
+        g.slots = 3u;
+        g.teams = kQkStreamThreads / g.team_threads;
+        while (g.teams != 0u && qk_stream_smem(a, g) > kQkSmemBudget) --g.teams;
+        if (g.teams == 0u) continue;
+        while (g.slots < kQkMaxSlots) {
+            qk_stream_geom wider = g;
+            ++wider.slots;
+            if (qk_stream_smem(a, wider) > kQkSmemBudget) break;
+            g = wider;
+        }
+        // most resident threads first, then the shape with more independent teams
+        const uint32_t score = g.teams * g.team_threads * 16u + g.teams;
+        if (score > best_score) { best_score = score; best = g; best_npt = npt; }
+    }
+    if (best_npt == 0u || best.teams == 0u) return false;
+    const size_t smem = qk_stream_smem(a, best);
+    const uint32_t ctas = std::min<uint32_t>(kSmCount, (a.tokens + best.teams - 1u) / best.teams);
+    const bool full = a.rope_dim == a.head_dim;
+#define AXB_QK_STREAM(NPT)                                                                               \
+    do {                                                                                                 \
+        if (full) {                                                                                      \
+            auto kern = qk_norm_rope_stream_kernel<LPH, NPT, true>;                                      \
+            cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kQkSmemBudget); \
+            kern<<<ctas, best.teams * best.team_threads, smem, stream>>>(a, best);                       \
+        } else {                                                                                         \
+            auto kern = qk_norm_rope_stream_kernel<LPH, NPT, false>;                                     \
+            cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kQkSmemBudget); \
+            kern<<<ctas, best.teams * best.team_threads, smem, stream>>>(a, best);                       \
+        }                                                                                                \
+    } while (0)
+    switch (best_npt) {
+    case 2: AXB_QK_STREAM(2); break;
+    case 3: AXB_QK_STREAM(3); break;
+    case 4: AXB_QK_STREAM(4); break;
+    case 6: AXB_QK_STREAM(6); break;
+    case 8: AXB_QK_STREAM(8); break;
+    default: return false;
+    }
+#undef AXB_QK_STREAM
+    return true;
+}
+
+template <int LPH>
+void launch_qk_any(const qk_dev_args &a, cudaStream_t stream) {
+    // The per-token kernel has the shortest latency; the streaming kernel the highest throughput.
+    if (a.tokens >= 2u * kSmCount && launch_qk_stream<LPH>(a, stream)) return;
+    launch_qk<LPH>(a, stream);
+}
+
 bool is_pow2(uint32_t v) { return v && !(v & (v - 1u)); }
 
 }  // namespace
@@ -316,9 +614,9 @@ int launch_qk_norm_rope_paged_bf16(const axiom_qk_rope_args *p, cudaStream_t str
     a.block_tokens = p->block_tokens; a.n_layers = p->n_layers; a.layer = p->layer;
     a.pool_stride = p->pool_stride; a.tbl_stride = p->tbl_stride; a.n_blocks = p->n_blocks;
     switch (p->head_dim) {
-    case 64: launch_qk<8>(a, stream); break;
-    case 128: launch_qk<16>(a, stream); break;
-    default: launch_qk<32>(a, stream); break;
+    case 64: launch_qk_any<8>(a, stream); break;
+    case 128: launch_qk_any<16>(a, stream); break;
+    default: launch_qk_any<32>(a, stream); break;
     }
     note_launch();
     return AXIOM_OK;

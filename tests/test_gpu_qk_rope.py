@@ -43,8 +43,12 @@ def run_case(axk, tokens, q_heads, k_heads, head_dim, rope_dim, *, n_blocks=64, 
     q, k, v, qg, kg, positions, table = wl.qk_inputs_np(tokens, q_heads, k_heads, head_dim, n_blocks, seed, max_base)
     if per_token:
         rng = np.random.default_rng(seed + 1)
-        table = np.stack([rng.permutation(n_blocks).astype(np.int32) for _ in range(tokens)])
-        positions = rng.integers(0, n_blocks * block_tokens, tokens).astype(np.uint32)
+        if tokens <= 64:
+            table = np.stack([rng.permutation(n_blocks).astype(np.int32) for _ in range(tokens)])
+            positions = rng.integers(0, n_blocks * block_tokens, tokens).astype(np.uint32)
+        else:  # many tokens: one permutation in every row and distinct positions, so no two tokens share a cell
+            table = np.tile(rng.permutation(n_blocks).astype(np.int32), (tokens, 1))
+            positions = rng.permutation(n_blocks * block_tokens)[:tokens].astype(np.uint32)
     inv_freq = ol.yarn_inv_freq(theta, factor, ctx, 32.0, 1.0, rope_dim) if rope_dim else np.zeros(1, np.float32)
     mscale = float(ol.o().axo_yarn_mscale(factor))
     kv_dim = k_heads * head_dim
@@ -130,6 +134,55 @@ def test_pool_stride_padding_layers_and_no_v(axk, cuda_device):
 
 def test_per_token_tables_decode_batch(axk, cuda_device):
     run_case(axk, 64, 64, 8, 128, 128, per_token=True, n_blocks=128)
+
+
+@pytest.mark.parametrize("q_heads,k_heads,head_dim,rope_dim", [(64, 8, 128, 128), (24, 4, 256, 64), (40, 8, 128, 128),
+                                                                (6, 2, 64, 32), (16, 2, 128, 0), (5, 1, 64, 64)])
+def test_streaming_kernel_geometries(axk, cuda_device, q_heads, k_heads, head_dim, rope_dim):
+    """Token counts of two or more per SM take the persistent streaming kernel (or, for shapes it does not
+    cover, the per-token kernel): 148 * 4 + 5 tokens leave the teams ragged tails."""
+    run_case(axk, 597, q_heads, k_heads, head_dim, rope_dim, n_blocks=1024, n_layers=2, layer=1, theta=1e7,
+             ctx=262144.0, max_base=4000)
+
+
+def test_streaming_kernel_variants(axk, cuda_device):
+    run_case(axk, 400, 8, 2, 128, 128, n_layers=3, layer=2, pool_pad=64, n_blocks=64, max_base=300)
+    run_case(axk, 400, 8, 2, 128, 128, with_v=False, n_blocks=64, max_base=300)
+    run_case(axk, 333, 64, 8, 128, 128, per_token=True, n_blocks=128)
+    run_case(axk, 300, 16, 4, 128, 128, ring=False, n_blocks=16, max_base=100)  # half the tokens fall off the table
+
+
+def test_streaming_and_per_token_kernels_agree_bitwise(axk, cuda_device):
+    """The same 2048 tokens once in one call (streaming kernel) and once in calls of 128 (per-token kernel)."""
+    import torch
+    from gpu_util import dev, sync
+
+    tokens = 2048
+    q, k, v, qg, kg, positions, table = wl.qk_inputs_np(tokens, 64, 8, 128, 4096, seed=11)
+    inv_freq = ol.yarn_inv_freq(1e6, 4.0, 32768.0, 32.0, 1.0, 128)
+    mscale = float(ol.o().axo_yarn_mscale(4.0))
+    qgd, kgd, fd, td = dev(qg), dev(kg), dev(inv_freq), dev(table)
+    results = []
+    for step in (tokens, 128):
+        qd, kd, vd, pd = dev(q).view(-1), dev(k).view(-1), dev(v).view(-1), dev(positions)
+        kp = torch.full((4096 * 16 * 1024,), -1, dtype=torch.int16, device="cuda")
+        vp = torch.full((4096 * 16 * 1024,), -1, dtype=torch.int16, device="cuda")
+        ko = torch.zeros(tokens * 1024, dtype=torch.int16, device="cuda")
+        status = torch.zeros(1, dtype=torch.int32, device="cuda")
+        for lo in range(0, tokens, step):
+            args = axk.make_qk_args(tokens=step, q_heads=64, k_heads=8, head_dim=128, rope_dim=128,
+                                    flags=axk.QK_FLAG_RING, eps=1e-6, mscale=mscale, block_tokens=16, n_layers=1,
+                                    layer=0, pool_stride=1024, tbl_stride=4096, n_blocks=4096,
+                                    q=qd[lo * 8192:], k=kd[lo * 1024:], v=vd[lo * 1024:], q_gamma=qgd, k_gamma=kgd,
+                                    inv_freq=fd, positions=pd[lo:], block_tables=td, k_pool=kp, v_pool=vp,
+                                    k_out=ko[lo * 1024:], status_word=status)
+            assert axk.qk_norm_rope_paged(0, args) == axk.AXIOM_OK
+        sync()
+        assert int(status.item()) == 0
+        results.append([x.cpu().numpy() for x in (qd, kp, vp, ko)])
+    for a, b in zip(*results):
+        assert np.array_equal(a, b)
+    assert axk.lib().axiom_b200_pipeline_faults(0) == 0
 
 
 def test_out_of_range_addresses_raise_status_and_skip(axk, cuda_device):
