@@ -39,6 +39,8 @@ if str(ROOT) not in sys.path:
 ROWS = 8192
 COLS = 5120
 NSETS = 4  # rotating buffer sets so no step finds its inputs in L2 (126 MB)
+# DRAM bytes of one headline launch from the committed ncu capture (read 167.8 MB + write 53.2 MB)
+NCU_DRAM_BYTES_PER_LAUNCH = 167_837_000 + 53_243_000
 METRIC = "fused_add_rmsnorm_nvfp4_tokens_per_s"
 UNIT = "tokens/s"
 
@@ -183,6 +185,7 @@ def main():
 
     axk = importlib.import_module("axiom-kernel_b200")
     wl = importlib.import_module("axiom-kernel_b200.workloads")
+    sharding = importlib.import_module("axiom-kernel_b200.sharding")
     lib = axk.lib()  # raises if the CUDA library is missing: there is no fallback
 
     world = int(os.environ.get("WORLD_SIZE", "1"))
@@ -233,8 +236,6 @@ def main():
 
     def step(i):
         s = sets[i % NSETS]
-        if i % (8 * NSETS) < NSETS and i >= NSETS:
-            pass
         rc = axk.add_rmsnorm_nvfp4(local, s["hidden"], s["residual"], s["gamma"], wl.EPS, ROWS, COLS, G, None,
                                    s["codes"], s["scales"], 0, stream)
         if rc:
@@ -256,9 +257,7 @@ def main():
     launches = int(lib.axiom_b200_kernel_launch_count()) - launches0
     clocks = sampler.stop() if rank == 0 else None
     if dist:
-        t = torch.tensor([ms], dtype=torch.float64, device=device)
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        ms = float(t.item())
+        ms = sharding.max_over_ranks(dist, ms, device)  # a multi-GPU step takes as long as its slowest rank
         dist.barrier()
     value = world * ROWS / (ms * 1e-3)
     algo = bytes_add_rmsnorm_nvfp4(ROWS, COLS)
@@ -273,7 +272,11 @@ def main():
                                                                f"of {algo / 1e6:.0f} MB",
                    "partition": "token rows, no collective"},
         "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
-                     "traffic": None, "peak_kind": peak_kind, "kernel": "add_rmsnorm_warp_rows_kernel<20,true>",
+                     "traffic": NCU_DRAM_BYTES_PER_LAUNCH if (ROWS, COLS) == (8192, 5120) else None,
+                     "traffic_note": "dram__bytes_read.sum + dram__bytes_write.sum of one ncu capture of this launch "
+                                     "(profiles/add_rmsnorm_nvfp4_8192x5120.md); the write part is below the algorithmic "
+                                     "write bytes because lines still dirty in the 126 MB L2 at kernel end are not counted",
+                     "peak_kind": peak_kind, "kernel": "add_rmsnorm_stream_kernel<true,true>",
                      "algorithmic_bytes_per_launch": algo},
         "gpu_launches": launches,
         "clocks": clocks,
@@ -307,9 +310,7 @@ def main():
         torch.cuda.synchronize()
         e2e_ms = (time.perf_counter() - t0) / e2e_steps * 1e3
         if dist:
-            t = torch.tensor([e2e_ms], dtype=torch.float64, device=device)
-            dist.all_reduce(t, op=dist.ReduceOp.MAX)
-            e2e_ms = float(t.item())
+            e2e_ms = sharding.max_over_ranks(dist, e2e_ms, device)
         line["e2e"] = {"value": world * ROWS / (e2e_ms * 1e-3), "unit": UNIT,
                        "h2d_bytes_per_step": 2 * ROWS * COLS * 2 + COLS * 2,
                        "d2h_bytes_per_step": ROWS * COLS * 2 + ROWS * COLS // 2 + ROWS * COLS // 16,
