@@ -6,8 +6,8 @@
 // summation order: 256 partial sums over features (c + 256*k) accumulated with
 // fmaf in k order, then the tree 128/64/32/16/8/4/2/1.
 //
-// Throughput kernel (add_rmsnorm_stream_kernel): persistent CTAs, one per SM,
-// made of independent 4-warp teams.  A team owns two (or more) shared-memory
+// One kernel for every row count (add_rmsnorm_stream_kernel): persistent CTAs, one per SM,
+// made of independent 4-warp teams (as many teams as the busiest CTA has rows, at most five).  A team owns two (or more) shared-memory
 // slots; its first thread fills a slot with one row (hidden | residual) through
 // 1-D bulk copies that complete on the slot's mbarrier, and refills it the
 // moment the team has finished with it, so the next row is always in flight
@@ -19,9 +19,6 @@
 // merged row is written back into the slot (it is BF16-valued by construction),
 // leaves for HBM as one bulk store, and sweep 2 (normalise + quantize) re-reads
 // it in 16-byte chunks, lane pairs forming the 16-value NVFP4 blocks.
-//
-// Latency kernel (add_rmsnorm_cta_rows_kernel): one 256-thread CTA per row for
-// small token counts, the reference's own thread/feature assignment.
 #include "pipeline.cuh"
 #include "runtime.hpp"
 
@@ -165,9 +162,12 @@ add_rmsnorm_stream_kernel(const norm_args a) {
     }
     const bool lut_safe = build_scale_lut(lut, a.codes ? a.G : 1.0f);  // contains the CTA barrier
 
+    bool faulted = false;
     for (uint32_t i = 0; i < my_rows; ++i) {
         const uint32_t j = i % spt;
-        if (!mbar_wait(my_bars + j, (i / spt) & 1u)) break;
+        // A wait that ran out raises the fault word; the team carries on (on whatever the slot
+        // holds) so that its barriers stay matched, and stops waiting.
+        if (!faulted && !mbar_wait(my_bars + j, (i / spt) & 1u)) faulted = true;
         const uint32_t row = blockIdx.x + (team + teams * i) * gridDim.x;
         const uint64_t base = (uint64_t)row * a.chunks_per_row;
         uint8_t *slot = my_slots + (size_t)j * slot_bytes;
@@ -249,82 +249,117 @@ add_rmsnorm_stream_kernel(const norm_args a) {
     if (kAdd && t == 0u) bulk_wait_read_all();
 }
 
-// One CTA per row, thread t owns features t + 256*k, merged row kept in shared memory as BF16.
-constexpr uint32_t kCtaThreads = 256u;
+// ---------------------------------------------------------------------------
+// Few rows (decode shapes): one CTA per row with one thread per 16-byte chunk, so a row costs
+// one global round trip: every thread loads its chunk of hidden, residual and gamma at once,
+// merges, stores the residual chunk and parks the merged chunk in shared memory; 128 threads
+// then run the reference's 256 fmaf chains from shared memory (20 dependent FMAs each at 5120
+// columns), one warp runs the reference tree, and every thread normalises and quantizes the
+// chunk it still holds in registers.
+// ---------------------------------------------------------------------------
+constexpr uint32_t kWideMaxChunksPerThread = 2u;  // 16384 columns = 2048 chunks over 1024 threads
 
-__global__ void __launch_bounds__(kCtaThreads)
-add_rmsnorm_cta_rows_kernel(const norm_args a) {
-    extern __shared__ __align__(16) uint8_t smem_raw[];
-    uint16_t *merged = reinterpret_cast<uint16_t *>(smem_raw);  // [cols]
-    __shared__ float sums[kCtaThreads];
-    const uint32_t tid = threadIdx.x;
-    const uint16_t *hidden = reinterpret_cast<const uint16_t *>(a.hidden);
-    uint16_t *residual = reinterpret_cast<uint16_t *>(a.residual);
-    const uint16_t *gamma = a.gamma;
-    uint16_t *norm_out = reinterpret_cast<uint16_t *>(a.norm_out);
-    uint8_t *codes = reinterpret_cast<uint8_t *>(a.codes);
+template <bool kAdd>
+__global__ void __launch_bounds__(1024, 1)
+add_rmsnorm_wide_row_kernel(const norm_args a) {
+    extern __shared__ __align__(16) uint8_t smem[];
+    uint4 *merged_sh = reinterpret_cast<uint4 *>(smem);  // [chunks_per_row]
+    __shared__ scale_lut_entry lut[128];
+    __shared__ __align__(16) float partials[256];
+    __shared__ float total_sh;
+    const uint32_t tid = threadIdx.x, lane = tid & 31u;
+    const uint4 *gamma16 = reinterpret_cast<const uint4 *>(a.gamma);
 
     for (uint32_t row = blockIdx.x; row < a.rows; row += gridDim.x) {
-        const uint64_t base = (uint64_t)row * a.cols;
-        float sum = 0.0f;
-        for (uint32_t f = tid; f < a.cols; f += kCtaThreads) {
-            uint16_t bits = residual[base + f];
-            float r = __uint_as_float((uint32_t)bits << 16);
-            if (hidden) {
-                r = __fadd_rn(r, __uint_as_float((uint32_t)hidden[base + f] << 16));
-                bits = (uint16_t)(pack_bf16x2(r, 0.0f) & 0xffffu);
-                r = __uint_as_float((uint32_t)bits << 16);
-                residual[base + f] = bits;
+        const uint64_t base = (uint64_t)row * a.chunks_per_row;
+        uint4 m[kWideMaxChunksPerThread], gam[kWideMaxChunksPerThread];
+#pragma unroll
+        for (uint32_t c = 0; c < kWideMaxChunksPerThread; ++c) {
+            const uint32_t q = tid + c * blockDim.x;
+            m[c] = make_uint4(0u, 0u, 0u, 0u);
+            gam[c] = m[c];
+            if (q < a.chunks_per_row) {
+                m[c] = ld_stream(a.residual + base + q);
+                uint4 h = make_uint4(0u, 0u, 0u, 0u);
+                if (kAdd) h = ld_stream(a.hidden + base + q);
+                gam[c] = gamma16[q];
+                if (kAdd) {
+                    m[c].x = add_bf16x2(m[c].x, h.x); m[c].y = add_bf16x2(m[c].y, h.y);
+                    m[c].z = add_bf16x2(m[c].z, h.z); m[c].w = add_bf16x2(m[c].w, h.w);
+                    st_stream(a.residual + base + q, m[c]);
+                }
+                merged_sh[q] = m[c];
             }
-            merged[f] = bits;
-            sum = __fmaf_rn(r, r, sum);
         }
-        sums[tid] = sum;
+        const bool lut_safe = build_scale_lut(lut, a.codes ? a.G : 1.0f);  // CTA barrier inside: merged_sh is complete
+
+        // partial sums 2t, 2t+1: features 256k + 2t, 2t+1 in k order (the reference's chains)
+        if (tid < 128u) {
+            const uint32_t *words = reinterpret_cast<const uint32_t *>(merged_sh) + tid;
+            float2 p = make_float2(0.f, 0.f);
+            const uint32_t k_iters = (a.cols + 255u) / 256u;
+            for (uint32_t k = 0; k < k_iters; ++k) {
+                if (256u * k + 2u * tid < a.cols) {
+                    const uint32_t w = words[128u * k];
+                    const float2 v = make_float2(bf16_lo(w), bf16_hi(w));
+                    p = __ffma2_rn(v, v, p);
+                }
+            }
+            reinterpret_cast<float2 *>(partials)[tid] = p;
+        }
         __syncthreads();
-        for (uint32_t stride = kCtaThreads / 2u; stride >= 32u; stride >>= 1u) {
-            if (tid < stride) sums[tid] = __fadd_rn(sums[tid], sums[tid + stride]);
-            __syncthreads();
-        }
         if (tid < 32u) {
-            float total = sums[tid];
+            // strides 128, 64, 32 through shared memory, then 16..1 as a butterfly (same additions)
+            float v = __fadd_rn(__fadd_rn(__fadd_rn(partials[lane], partials[lane + 128u]),
+                                          __fadd_rn(partials[lane + 64u], partials[lane + 192u])),
+                                __fadd_rn(__fadd_rn(partials[lane + 32u], partials[lane + 160u]),
+                                          __fadd_rn(partials[lane + 96u], partials[lane + 224u])));
 #pragma unroll
-            for (uint32_t stride = 16u; stride != 0u; stride >>= 1u) {
-                total = __fadd_rn(total, __shfl_xor_sync(0xffffffffu, total, stride));
-            }
-            if (tid == 0u) sums[0] = total;
+            for (uint32_t off = 16u; off != 0u; off >>= 1u) v = __fadd_rn(v, __shfl_xor_sync(0xffffffffu, v, off));
+            if (lane == 0u) total_sh = v;
         }
         __syncthreads();
-        const float inverse = rsqrtf(__fadd_rn(__fdiv_rn(sums[0], (float)a.cols), a.eps));
-        // cols % 16 == 0, so all 16 lanes of a block are in range together
-        for (uint32_t f0 = 0; f0 < a.cols; f0 += kCtaThreads) {
-            const uint32_t f = f0 + tid;
-            const bool ok = f < a.cols;
-            float n = 0.0f;
-            if (ok) {
-                const float r = __uint_as_float((uint32_t)merged[f] << 16);
-                const float w = __uint_as_float((uint32_t)gamma[f] << 16);
-                const uint16_t bits = (uint16_t)(pack_bf16x2(__fmul_rn(__fmul_rn(r, inverse), w), 0.0f) & 0xffffu);
-                if (norm_out) norm_out[base + f] = bits;
-                n = __uint_as_float((uint32_t)bits << 16);
-            }
-            if (codes) {
-                float mx = fabsf(n);
+        const float inverse = rsqrtf(__fadd_rn(__fdiv_rn(total_sh, (float)a.cols), a.eps));
+        const float2 inv2 = make_float2(inverse, inverse);
+
 #pragma unroll
-                for (uint32_t off = 8u; off != 0u; off >>= 1u) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, off));
-                mx = fmaxf(mx, 0.0f);
-                const uint32_t scale_code = encode_block_scale(__fmul_rn(__fmul_rn(mx, 1.0f / 6.0f), a.G));
-                const float d = __fdiv_rn(e4m3_to_f32(scale_code), a.G);
-                const float qv = __fdiv_rn(n, d);
-                const float next = __shfl_down_sync(0xffffffffu, qv, 1);
-                if (ok && (tid & 1u) == 0u) {
-                    codes[(base + f) >> 1] = (uint8_t)(cvt_e2m1x2(qv, next) & 0xffu);
-                    if ((tid & 15u) == 0u) {
-                        a.scales[scale_offset(row, f >> 4, a.groups, a.inner_tiles, a.layout)] = (uint8_t)scale_code;
+        for (uint32_t c = 0; c < kWideMaxChunksPerThread; ++c) {
+            const uint32_t q = tid + c * blockDim.x;
+            if (c * blockDim.x >= a.chunks_per_row) break;  // uniform: no thread has a chunk in this round
+            const bool ok = q < a.chunks_per_row;
+            const float2 y0 = __fmul2_rn(__fmul2_rn(make_float2(bf16_lo(m[c].x), bf16_hi(m[c].x)), inv2),
+                                         make_float2(bf16_lo(gam[c].x), bf16_hi(gam[c].x)));
+            const float2 y1 = __fmul2_rn(__fmul2_rn(make_float2(bf16_lo(m[c].y), bf16_hi(m[c].y)), inv2),
+                                         make_float2(bf16_lo(gam[c].y), bf16_hi(gam[c].y)));
+            const float2 y2 = __fmul2_rn(__fmul2_rn(make_float2(bf16_lo(m[c].z), bf16_hi(m[c].z)), inv2),
+                                         make_float2(bf16_lo(gam[c].z), bf16_hi(gam[c].z)));
+            const float2 y3 = __fmul2_rn(__fmul2_rn(make_float2(bf16_lo(m[c].w), bf16_hi(m[c].w)), inv2),
+                                         make_float2(bf16_lo(gam[c].w), bf16_hi(gam[c].w)));
+            const uint4 nrm = make_uint4(pack_bf16x2(y0.x, y0.y), pack_bf16x2(y1.x, y1.y), pack_bf16x2(y2.x, y2.y),
+                                         pack_bf16x2(y3.x, y3.y));
+            if (a.norm_out && ok) st_stream(a.norm_out + base + q, nrm);
+            if (a.codes) {
+                float y[8];
+                unpack8(nrm, y);  // the quantizer sees the BF16-rounded values
+                float mx = absmax8_nan(y);
+                mx = max_nan(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
+                uint32_t scale_byte;
+                bool needs_exact = false;
+                uint32_t packed = nvfp4_quantize8_fast(y, mx, a.G, lut, &scale_byte, &needs_exact);
+                if (!lut_safe || __any_sync(0xffffffffu, needs_exact)) {
+                    mx = absmax8_drop_nan(y);
+                    mx = fmaxf(fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 1)), 0.0f);
+                    packed = nvfp4_quantize8_exact(y[0], y[1], y[2], y[3], y[4], y[5], y[6], y[7], mx, a.G, &scale_byte);
+                }
+                if (ok) {
+                    st_stream(a.codes + base + q, packed);
+                    if ((q & 1u) == 0u) {
+                        a.scales[scale_offset(row, q >> 1, a.groups, a.inner_tiles, a.layout)] = (uint8_t)scale_byte;
                     }
                 }
             }
         }
-        __syncthreads();
+        __syncthreads();  // merged_sh, partials and total_sh are rewritten for the next row
     }
 }
 
@@ -387,18 +422,23 @@ int launch_add_rmsnorm_nvfp4_bf16(const void *hidden, void *residual, const void
         spt = (uint32_t)((kSmemBudget - stream_fixed_bytes(cols, teams)) / (teams * slot_bytes));
         if (spt > kMaxSlotsPerTeam) spt = kMaxSlotsPerTeam;
     }
-    // Few rows: latency matters, spread each row over a whole CTA.  Rows too
-    // wide for two double-buffered teams take that kernel as well.
-    const bool use_cta = rows < 2u * kSmCount || teams < 2u;
-    if (use_cta) {
-        uint32_t ctas = rows < kSmCount * 8u ? rows : kSmCount * 8u;
-        add_rmsnorm_cta_rows_kernel<<<ctas, kCtaThreads, (size_t)cols * sizeof(uint16_t), stream>>>(a);
-    } else {
-        a.ring_slots = spt;
-        const size_t smem = stream_fixed_bytes(cols, teams) + (size_t)teams * spt * slot_bytes;
-        if (hidden) launch_stream<true>(a, teams, smem, stream);
-        else launch_stream<false>(a, teams, smem, stream);
+    // The widest row the entry points accept (16384 columns) still fits one team with two slots.
+    if (teams == 0u || spt < 2u) return AXIOM_ERR_INVALID_ARGUMENT;
+    // Few rows: latency matters more than streaming; one wide CTA per row.
+    if (rows < 2u * kSmCount) {
+        uint32_t threads = (a.chunks_per_row + 31u) & ~31u;
+        if (threads > 1024u) threads = 1024u;
+        if (threads < 128u) threads = 128u;  // the 256 partial sums are produced by the first 128 threads
+        const size_t row_smem = (size_t)a.chunks_per_row * sizeof(uint4);
+        if (hidden) add_rmsnorm_wide_row_kernel<true><<<rows, threads, row_smem, stream>>>(a);
+        else add_rmsnorm_wide_row_kernel<false><<<rows, threads, row_smem, stream>>>(a);
+        note_launch();
+        return AXIOM_OK;
     }
+    a.ring_slots = spt;
+    const size_t smem = stream_fixed_bytes(cols, teams) + (size_t)teams * spt * slot_bytes;
+    if (hidden) launch_stream<true>(a, teams, smem, stream);
+    else launch_stream<false>(a, teams, smem, stream);
     note_launch();
     return AXIOM_OK;
 }

@@ -12,12 +12,15 @@
 // row at a time, every thread keeps its share of y in registers across the
 // row-max reduction, so gate|up is read once and only the codes are written.
 //
-// silu(g) = g / (1 + expf(-g)) depends on the BF16 gate alone, so the throughput
-// kernels tabulate it once per CTA in shared memory — 47 binades x 128 mantissas
-// x 2 signs, filled by the very expression the direct path evaluates, hence
-// bit-identical — and replace expf + an IEEE division per element by one
-// shared-memory load.  Gates outside the table (|g| < 2^-40, |g| >= 128, NaN,
-// infinity) take the direct expression.
+// silu(g) = g / (1 + expf(-g)) depends on the BF16 gate alone, so it is tabulated
+// — 64 binades x 128 mantissas x 2 signs, filled by the very expression the direct
+// path evaluates, hence bit-identical — and the hot loop replaces expf + an IEEE
+// division per element by one shared-memory load.  Gates outside the table
+// (|g| < 2^-57, |g| >= 128, NaN, infinity) take the direct expression.  The table
+// does not depend on any input: it is filled once per device into a 64 KB device
+// array and every CTA copies it into shared memory (16-byte loads, L2 hits); a
+// call that arrives during stream capture before that one-time fill lets each CTA
+// fill its own copy instead.
 #include "pipeline.cuh"
 #include "runtime.hpp"
 
@@ -44,10 +47,29 @@ constexpr uint32_t kSiluFirst = kSiluExpLo << 7;                      // first t
 constexpr uint32_t kSiluEnd = (kSiluExpLo + 64u) << 7;                // one past the last
 constexpr uint32_t kSiluTableBytes = 2u * 8192u * sizeof(float);
 
-__device__ __forceinline__ void build_silu_table(float *table) {
-    for (uint32_t i = threadIdx.x; i < 16384u; i += blockDim.x) {
-        const uint32_t bits = ((i >> 13) << 15) | (kSiluFirst + (i & 8191u));
-        table[i] = silu(__uint_as_float(bits << 16));
+constexpr uint32_t kSiluEntries = 16384u;
+
+__device__ __forceinline__ float silu_table_entry(uint32_t i) {
+    const uint32_t bits = ((i >> 13) << 15) | (kSiluFirst + (i & 8191u));
+    return silu(__uint_as_float(bits << 16));
+}
+
+// The per-device copy of the table (filled once by silu_table_fill_kernel) and its host-side state.
+static __device__ __align__(256) float g_silu_table[kSiluEntries];
+
+__global__ void silu_table_fill_kernel(float *table) {
+    const uint32_t i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < kSiluEntries) table[i] = silu_table_entry(i);
+}
+
+// Shared-memory table of a CTA: copied from the device table, or computed here when there is none yet.
+__device__ __forceinline__ void build_silu_table(float *table, const float *device_table) {
+    if (device_table) {
+        const uint4 *src = reinterpret_cast<const uint4 *>(device_table);
+        uint4 *dst = reinterpret_cast<uint4 *>(table);
+        for (uint32_t i = threadIdx.x; i < kSiluEntries / 4u; i += blockDim.x) dst[i] = __ldg(src + i);
+    } else {
+        for (uint32_t i = threadIdx.x; i < kSiluEntries; i += blockDim.x) table[i] = silu_table_entry(i);
     }
     __syncthreads();
 }
@@ -126,13 +148,14 @@ constexpr uint32_t kMaxRowThreads = 576u;
 template <int CPT, row_op kOp>
 __global__ void __launch_bounds__(kMaxRowThreads, CPT <= 4 ? 2 : 1)
 fp8_rows_kernel(const uint4 *__restrict__ in, uint32_t rows, uint32_t chunks, uint32_t in_chunks_per_row,
-                uint2 *__restrict__ codes, float *__restrict__ scales, uint32_t *__restrict__ status_word) {
+                uint2 *__restrict__ codes, float *__restrict__ scales, uint32_t *__restrict__ status_word,
+                const float *__restrict__ device_table) {
     extern __shared__ __align__(16) float silu_table[];
     __shared__ float warp_max[32];
     constexpr bool kSwiglu = kOp != row_op::plain_finite_only;
     constexpr bool kTable = kOp == row_op::swiglu_table;
     const uint32_t tid = threadIdx.x;
-    if (kTable) build_silu_table(silu_table);
+    if (kTable) build_silu_table(silu_table, device_table);
     for (uint32_t row = blockIdx.x; row < rows; row += gridDim.x) {
         const uint4 *gate = in + (uint64_t)row * in_chunks_per_row;
         float y[CPT][8];
@@ -238,10 +261,11 @@ template <bool kTable>
 __global__ void __launch_bounds__(kNvThreads)
 swiglu_nvfp4_kernel(const uint4 *__restrict__ in, uint32_t rows, uint32_t chunks, uint32_t col_groups,
                     uint32_t step_rows, uint32_t step_cols, float G, uint32_t *__restrict__ codes,
-                    uint8_t *__restrict__ scales, uint32_t layout, uint32_t groups, uint32_t inner_tiles) {
+                    uint8_t *__restrict__ scales, uint32_t layout, uint32_t groups, uint32_t inner_tiles,
+                    const float *__restrict__ device_table) {
     extern __shared__ __align__(16) float silu_table[];
     __shared__ scale_lut_entry lut[128];
-    if (kTable) build_silu_table(silu_table);
+    if (kTable) build_silu_table(silu_table, device_table);
     const bool lut_safe = build_scale_lut(lut, G);
     const uint32_t lane = threadIdx.x & 31u;
     const uint32_t warp = (blockIdx.x * kNvThreads + threadIdx.x) >> 5;
@@ -313,6 +337,36 @@ row_shape pick_row_shape(uint32_t chunks) {
     return best;
 }
 
+// Device address of the per-device silu table, filling it on the first call for that device:
+// one small kernel on `stream` and one synchronisation of that stream, so that calls on any
+// other stream may use the table afterwards.  Returns nullptr (each CTA then fills its own
+// shared-memory copy) when the table is not ready and cannot be made ready here: `stream` is
+// being captured (a synchronisation would invalidate the capture), or the driver refused.
+const float *device_silu_table(cudaStream_t stream) {
+    static const float *ready[64] = {};
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return nullptr;
+    if (ready[dev]) return ready[dev];
+    cudaStreamCaptureStatus capture = cudaStreamCaptureStatusNone;
+    if (cudaStreamIsCapturing(stream, &capture) != cudaSuccess || capture != cudaStreamCaptureStatusNone) {
+        cudaGetLastError();
+        return nullptr;
+    }
+    float *table = nullptr;
+    if (cudaGetSymbolAddress((void **)&table, g_silu_table) != cudaSuccess || !table) {
+        cudaGetLastError();
+        return nullptr;
+    }
+    silu_table_fill_kernel<<<kSiluEntries / 256u, 256, 0, stream>>>(table);
+    if (cudaGetLastError() != cudaSuccess || cudaStreamSynchronize(stream) != cudaSuccess) {
+        cudaGetLastError();
+        return nullptr;
+    }
+    note_launch();
+    ready[dev] = table;
+    return table;
+}
+
 template <row_op kOp>
 int launch_fp8_rows(const void *in, uint32_t rows, uint32_t width, uint32_t in_chunks_per_row, uint8_t *codes,
                     float *scales, uint32_t *status_word, cudaStream_t stream) {
@@ -321,6 +375,7 @@ int launch_fp8_rows(const void *in, uint32_t rows, uint32_t width, uint32_t in_c
     if (s.threads == 0u) return AXIOM_ERR_INVALID_ARGUMENT;
     constexpr bool kTable = kOp == row_op::swiglu_table;
     const size_t smem = kTable ? kSiluTableBytes : 0u;
+    const float *device_table = kTable ? device_silu_table(stream) : nullptr;
     // table flavour: persistent CTAs (the table is built once per CTA), two per SM
     const uint32_t cap = kTable ? kSmCount * 2u : kSmCount * 16u;
     const uint32_t ctas = rows < cap ? rows : cap;
@@ -339,17 +394,19 @@ int launch_fp8_rows(const void *in, uint32_t rows, uint32_t width, uint32_t in_c
         }
     }
     switch (s.cpt) {
-    case 1: fp8_rows_kernel<1, kOp><<<ctas, s.threads, smem, stream>>>(src, rows, chunks, in_chunks_per_row, dst, scales, status_word); break;
-    case 2: fp8_rows_kernel<2, kOp><<<ctas, s.threads, smem, stream>>>(src, rows, chunks, in_chunks_per_row, dst, scales, status_word); break;
-    case 4: fp8_rows_kernel<4, kOp><<<ctas, s.threads, smem, stream>>>(src, rows, chunks, in_chunks_per_row, dst, scales, status_word); break;
-    default: fp8_rows_kernel<8, kOp><<<ctas, s.threads, smem, stream>>>(src, rows, chunks, in_chunks_per_row, dst, scales, status_word); break;
+    case 1: fp8_rows_kernel<1, kOp><<<ctas, s.threads, smem, stream>>>(src, rows, chunks, in_chunks_per_row, dst, scales, status_word, device_table); break;
+    case 2: fp8_rows_kernel<2, kOp><<<ctas, s.threads, smem, stream>>>(src, rows, chunks, in_chunks_per_row, dst, scales, status_word, device_table); break;
+    case 4: fp8_rows_kernel<4, kOp><<<ctas, s.threads, smem, stream>>>(src, rows, chunks, in_chunks_per_row, dst, scales, status_word, device_table); break;
+    default: fp8_rows_kernel<8, kOp><<<ctas, s.threads, smem, stream>>>(src, rows, chunks, in_chunks_per_row, dst, scales, status_word, device_table); break;
     }
     note_launch();
     return AXIOM_OK;
 }
 
-// rows at or above which building the 47 KB silu table per CTA pays for itself
+// rows at or above which a 64 KB shared-memory silu table per CTA pays for itself: when every
+// CTA fills its own, and when it only copies the device table
 constexpr uint32_t kTableMinRows = 2u * kSmCount;
+constexpr uint32_t kCopiedTableMinRows = 96u;
 
 }  // namespace
 
@@ -375,7 +432,8 @@ int launch_swiglu_nvfp4_bf16(const void *gate_up, uint32_t rows, uint32_t width,
     const uint32_t col_groups = (chunks + 31u) / 32u;
     const uint64_t tiles = (uint64_t)rows * col_groups;
     const uint32_t warps_per_block = kNvThreads / 32u;
-    const bool table = rows >= kTableMinRows;
+    const float *device_table = rows >= kCopiedTableMinRows ? device_silu_table(stream) : nullptr;
+    const bool table = rows >= kTableMinRows || device_table != nullptr;
     // table flavour: persistent CTAs (the table is built once per CTA), two 512-thread CTAs with 64 KB each per SM
     const uint64_t cap = table ? kSmCount * 2u : kSmCount * 8u;
     uint64_t blocks = (tiles + warps_per_block - 1u) / warps_per_block;
@@ -392,11 +450,11 @@ int launch_swiglu_nvfp4_bf16(const void *gate_up, uint32_t rows, uint32_t width,
         }
         swiglu_nvfp4_kernel<true><<<(uint32_t)blocks, kNvThreads, kSiluTableBytes, stream>>>(
                 src, rows, chunks, col_groups, W / col_groups, W % col_groups, G, (uint32_t *)codes, scales, layout, groups,
-                (groups + 3u) / 4u);
+                (groups + 3u) / 4u, device_table);
     } else {
         swiglu_nvfp4_kernel<false><<<(uint32_t)blocks, kNvThreads, 0, stream>>>(
                 src, rows, chunks, col_groups, W / col_groups, W % col_groups, G, (uint32_t *)codes, scales, layout, groups,
-                (groups + 3u) / 4u);
+                (groups + 3u) / 4u, nullptr);
     }
     note_launch();
     return AXIOM_OK;

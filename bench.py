@@ -455,13 +455,21 @@ def bench_chain(torch, axk, wl, local, device, stream, timed, peak):
                                 k_gamma=kg, inv_freq=inv_freq, positions=pos, block_tables=tab, k_pool=pool,
                                 status_word=status)
 
+        stages = {
+            "gather": lambda _i, s=stream: axk.embedding_gather(local, table, wl.VOCAB, wl.HIDDEN, ids, m, hidden, status, s),
+            "add_rmsnorm_nvfp4": lambda _i, s=stream: axk.add_rmsnorm_nvfp4(local, hidden, residual, gamma, wl.EPS, m,
+                                                                             wl.HIDDEN, 90.0, None, codes, scales, 0, s),
+            "qk_norm_rope_paged_kv": lambda _i, s=stream: axk.qk_norm_rope_paged(local, args, s),
+            "swiglu_nvfp4": lambda _i, s=stream: axk.swiglu_nvfp4(local, gu, m, wl.FFN, 40.0, mc, msc, 0, s),
+        }
+
         def run_chain(_i, s=stream):
-            axk.embedding_gather(local, table, wl.VOCAB, wl.HIDDEN, ids, m, hidden, status, s)
-            axk.add_rmsnorm_nvfp4(local, hidden, residual, gamma, wl.EPS, m, wl.HIDDEN, 90.0, None, codes, scales, 0, s)
-            axk.qk_norm_rope_paged(local, args, s)
-            axk.swiglu_nvfp4(local, gu, m, wl.FFN, 40.0, mc, msc, 0, s)
+            for fn in stages.values():
+                fn(_i, s)
 
         eager_us = timed(run_chain, n=200) * 1e3
+        # each stage alone, back to back on the stream (the larger of its duration and the launch rate)
+        stage_us = {name: timed(fn, n=200) * 1e3 for name, fn in stages.items()}
         graph = torch.cuda.CUDAGraph()
         with torch.cuda.graph(graph, stream=stream):
             run_chain(0, torch.cuda.current_stream())
@@ -477,7 +485,7 @@ def bench_chain(torch, axk, wl, local, device, stream, timed, peak):
         graph_us = start.elapsed_time(end) / 200 * 1e3
         algo = m * (wl.HIDDEN * 2 * 2 + (3 * wl.HIDDEN * 2 + wl.HIDDEN // 2 + wl.HIDDEN // 16) +
                     (2 * 64 * 128 * 2 + 2 * 8 * 128 * 2 + 4) + (2 * wl.FFN * 2 + wl.FFN // 2 + wl.FFN // 16)) + wl.HIDDEN * 2
-        chain[str(m)] = {"eager_us": eager_us, "graph_us": graph_us, "algorithmic_bytes": algo,
+        chain[str(m)] = {"eager_us": eager_us, "graph_us": graph_us, "stage_us": stage_us, "algorithmic_bytes": algo,
                          "frac_of_peak_graph": algo / (graph_us * 1e-6) / 1e9 / peak}
         del graph
     return chain

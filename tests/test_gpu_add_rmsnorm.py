@@ -66,14 +66,14 @@ def check_against_oracle(axk, rows, cols, layout=0, with_add=True):
 
 
 @pytest.mark.parametrize("rows", [1, 2, 7, 8, 9, 64])
-@pytest.mark.parametrize("cols", [5120, 1024, 48, 8192])
-def test_cta_per_row_kernel(axk, cuda_device, rows, cols):
+@pytest.mark.parametrize("cols", [5120, 1024, 48, 8192, 16384])
+def test_wide_row_kernel(axk, cuda_device, rows, cols):
     check_against_oracle(axk, rows, cols)
 
 
 @pytest.mark.parametrize("rows,cols", [(300, 5120), (333, 1024), (512, 2048), (297, 4096), (301, 7168), (299, 8192),
                                         (310, 48), (305, 3072), (320, 6144)])
-def test_warp_per_row_kernel(axk, cuda_device, rows, cols):
+def test_streaming_kernel(axk, cuda_device, rows, cols):
     check_against_oracle(axk, rows, cols)
 
 

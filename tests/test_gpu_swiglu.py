@@ -128,6 +128,38 @@ def test_swiglu_nvfp4(axk, cuda_device, rows, width, layout):
     assert np.mean(codes.payload().reshape(rows, width // 2) != want_codes) < 2e-3
 
 
+def test_swiglu_flavours_agree_bitwise(axk, cuda_device):
+    """Few rows evaluate silu directly, more rows read it from the tabulated copy (device table copied into
+    shared memory, or filled per CTA): the same 600 rows in calls of 8, of 40 and at once must give the same
+    bytes — the table holds the direct expression's bits.  Includes gates outside the table's range."""
+    import torch
+    from gpu_util import dev, sync
+
+    rows, width = 600, 2048
+    gu = wl.swiglu_input_np(rows, width, seed=21)
+    rng = np.random.default_rng(5)
+    specials = wl.to_bf16_bits(np.array([0.0, -0.0, 1e-30, -1e-30, 200.0, -200.0, np.inf, -np.inf, np.nan, 127.9, 2.0 ** -57,
+                                         2.0 ** -58], np.float32))
+    idx = rng.integers(0, rows * width, 4000)
+    gu[idx // width, idx % width] = specials[rng.integers(0, specials.size, idx.size)]  # gate half of the rows
+    x = dev(gu)
+    outs = []
+    for step in (8, 40, rows):
+        c4 = torch.zeros((rows, width // 2), dtype=torch.uint8, device="cuda")
+        s4 = torch.zeros((rows, width // 16), dtype=torch.uint8, device="cuda")
+        c8 = torch.zeros((rows, width), dtype=torch.uint8, device="cuda")
+        s8 = torch.zeros((rows,), dtype=torch.float32, device="cuda")
+        for lo in range(0, rows, step):
+            n = min(step, rows - lo)
+            assert axk.swiglu_nvfp4(0, x[lo:], n, width, 37.0, c4[lo:], s4[lo:], 0) == axk.AXIOM_OK
+            assert axk.swiglu_fp8(0, x[lo:], n, width, c8[lo:], s8[lo:]) == axk.AXIOM_OK
+        sync()
+        outs.append([t.cpu().numpy() for t in (c4, s4, c8)] + [s8.cpu().numpy().view(np.uint32)])
+    for other in outs[1:]:
+        for a, b in zip(outs[0], other):
+            assert np.array_equal(a, b)
+
+
 def test_config4_full_size_sample(axk, cuda_device):
     """T = 16384 is exercised at full width; the oracle checks a 512-row slab of it."""
     check_swiglu_fp8(axk, 512, 17408, seed=4)
