@@ -130,11 +130,13 @@ add_rmsnorm_stream_kernel(const norm_args a) {
     uint64_t *my_bars = bars + team * kMaxSlotsPerTeam;
     uint8_t *my_slots = smem + (size_t)team * spt * slot_bytes;
     float *my_partials = partials + team * 256u;
+    allow_dependents();
     if (t == 0u) {
         for (uint32_t j = 0; j < spt; ++j) mbar_init(my_bars + j, 1u);
         mbar_init_fence();
     }
     team_barrier(team);
+    dependency_wait();
 
     // rows of this CTA: blockIdx.x + n * gridDim.x; this team takes n = team + teams * i
     const uint32_t cta_rows = blockIdx.x < a.rows ? (a.rows - blockIdx.x + gridDim.x - 1u) / gridDim.x : 0u;
@@ -269,6 +271,8 @@ add_rmsnorm_wide_row_kernel(const norm_args a) {
     __shared__ float total_sh;
     const uint32_t tid = threadIdx.x, lane = tid & 31u;
     const uint4 *gamma16 = reinterpret_cast<const uint4 *>(a.gamma);
+    allow_dependents();
+    dependency_wait();
 
     for (uint32_t row = blockIdx.x; row < a.rows; row += gridDim.x) {
         const uint64_t base = (uint64_t)row * a.chunks_per_row;
@@ -380,7 +384,7 @@ void launch_stream_impl(const norm_args &a, uint32_t teams, size_t smem, cudaStr
         configured[dev] = true;
     }
     const uint32_t ctas = a.rows < kSmCount ? a.rows : kSmCount;
-    add_rmsnorm_stream_kernel<kAdd, kFull><<<ctas, teams * kTeamThreads, smem, stream>>>(a);
+    launch_chained(add_rmsnorm_stream_kernel<kAdd, kFull>, dim3(ctas), dim3(teams * kTeamThreads), smem, stream, a);
 }
 
 template <bool kAdd>
@@ -430,8 +434,8 @@ int launch_add_rmsnorm_nvfp4_bf16(const void *hidden, void *residual, const void
         if (threads > 1024u) threads = 1024u;
         if (threads < 128u) threads = 128u;  // the 256 partial sums are produced by the first 128 threads
         const size_t row_smem = (size_t)a.chunks_per_row * sizeof(uint4);
-        if (hidden) add_rmsnorm_wide_row_kernel<true><<<rows, threads, row_smem, stream>>>(a);
-        else add_rmsnorm_wide_row_kernel<false><<<rows, threads, row_smem, stream>>>(a);
+        if (hidden) launch_chained(add_rmsnorm_wide_row_kernel<true>, dim3(rows), dim3(threads), row_smem, stream, a);
+        else launch_chained(add_rmsnorm_wide_row_kernel<false>, dim3(rows), dim3(threads), row_smem, stream, a);
         note_launch();
         return AXIOM_OK;
     }

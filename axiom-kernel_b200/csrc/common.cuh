@@ -54,6 +54,39 @@ struct buffer_impl;
 
 #ifdef __CUDACC__
 
+// ---- programmatic dependent launch ---------------------------------------------------------
+// Every kernel of the fused chain is launched with programmatic stream serialisation allowed:
+// the next kernel on the stream may be scheduled while this one still runs, executes whatever
+// does not depend on earlier work (shared-memory set-up, tables computed from scalar arguments)
+// and then blocks in dependency_wait() until all earlier kernels have completed and their
+// writes are visible.  At decode shapes, where a layer is a chain of few-microsecond kernels,
+// this takes the launch latency of each kernel off the critical path; it also works inside
+// CUDA graph capture (the edges become programmatic).  Rules the kernels follow:
+//   * dependency_wait() comes before the first access to any caller-visible global memory
+//     (reads AND writes) and is executed on every path, so completion of kernel N implies
+//     completion of every kernel before it;
+//   * allow_dependents() is called at the top: the hardware starts the dependents only once
+//     every CTA of this grid has started or finished, so they never take resources this grid
+//     still needs.
+__device__ __forceinline__ void dependency_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void allow_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
+template <typename... KArgs, typename... Args>
+inline cudaError_t launch_chained(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
+                                  Args &&...args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
+}
+
 __device__ __forceinline__ float bf16_lo(uint32_t packed) { return __uint_as_float(packed << 16); }
 __device__ __forceinline__ float bf16_hi(uint32_t packed) { return __uint_as_float(packed & 0xffff0000u); }
 

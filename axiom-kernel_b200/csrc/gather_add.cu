@@ -14,6 +14,8 @@ __global__ void __launch_bounds__(kThreads)
 embedding_gather_bf16_kernel(const uint4 *__restrict__ table, uint32_t vocab, uint32_t chunks_per_row,
                              const uint32_t *__restrict__ ids, uint32_t tokens, uint4 *__restrict__ out,
                              uint32_t *__restrict__ status_word) {
+    allow_dependents();
+    dependency_wait();
     const uint64_t total = (uint64_t)tokens * chunks_per_row;
     for (uint64_t c = (uint64_t)blockIdx.x * kThreads + threadIdx.x; c < total; c += (uint64_t)gridDim.x * kThreads) {
         const uint32_t token = (uint32_t)(c / chunks_per_row);
@@ -32,6 +34,8 @@ embedding_gather_bf16_kernel(const uint4 *__restrict__ table, uint32_t vocab, ui
 __global__ void __launch_bounds__(kThreads)
 add_bf16_kernel(const uint4 *__restrict__ a, const uint4 *__restrict__ b, uint4 *__restrict__ out, uint64_t chunks,
                 const uint16_t *a_tail, const uint16_t *b_tail, uint16_t *out_tail, uint32_t tail) {
+    allow_dependents();
+    dependency_wait();
     for (uint64_t c = (uint64_t)blockIdx.x * kThreads + threadIdx.x; c < chunks; c += (uint64_t)gridDim.x * kThreads) {
         const uint4 x = ld_stream(a + c), y = ld_stream(b + c);
         uint4 r;
@@ -60,7 +64,7 @@ uint32_t grid_for(uint64_t work_items) {
 int launch_embedding_gather_bf16(const void *table, uint32_t vocab, uint32_t hidden, const uint32_t *ids,
                                  uint32_t tokens, void *out, uint32_t *status_word, cudaStream_t stream) {
     const uint32_t chunks_per_row = hidden / 8u;
-    embedding_gather_bf16_kernel<<<grid_for((uint64_t)tokens * chunks_per_row), kThreads, 0, stream>>>(
+    launch_chained(embedding_gather_bf16_kernel, dim3(grid_for((uint64_t)tokens * chunks_per_row)), dim3(kThreads), 0, stream, 
             (const uint4 *)table, vocab, chunks_per_row, ids, tokens, (uint4 *)out, status_word);
     note_launch();
     return AXIOM_OK;
@@ -69,7 +73,7 @@ int launch_embedding_gather_bf16(const void *table, uint32_t vocab, uint32_t hid
 int launch_add_bf16(const void *a, const void *b, void *out, uint64_t count, cudaStream_t stream) {
     const uint64_t chunks = count / 8u;
     const uint32_t tail = (uint32_t)(count - chunks * 8u);
-    add_bf16_kernel<<<grid_for(chunks), kThreads, 0, stream>>>(
+    launch_chained(add_bf16_kernel, dim3(grid_for(chunks)), dim3(kThreads), 0, stream, 
             (const uint4 *)a, (const uint4 *)b, (uint4 *)out, chunks, (const uint16_t *)a + chunks * 8u,
             (const uint16_t *)b + chunks * 8u, (uint16_t *)out + chunks * 8u, tail);
     note_launch();

@@ -34,6 +34,8 @@ nvfp4_quantize_bf16_kernel(const uint4 *__restrict__ in, uint32_t total_chunks, 
     const uint64_t first = (uint64_t)warp * chunks_per_warp;
     const uint64_t last = first + chunks_per_warp < total_chunks ? first + chunks_per_warp : total_chunks;
     constexpr uint32_t kTile = 32u * kUnroll;
+    allow_dependents();
+    dependency_wait();
     // the first tile is requested before the CTA builds its scale table
     uint4 v[kUnroll];
 #pragma unroll
@@ -138,7 +140,7 @@ int launch_nvfp4_quantize_bf16(const void *input, uint32_t rows, uint32_t cols, 
     const uint32_t warps = blocks * warps_per_block;
     uint32_t per_warp = (total + warps - 1u) / warps;
     per_warp = (per_warp + 7u) & ~7u;  // ranges start on 128-byte boundaries and never split a block
-    nvfp4_quantize_bf16_kernel<<<blocks, kThreads, 0, stream>>>(
+    launch_chained(nvfp4_quantize_bf16_kernel, dim3(blocks), dim3(kThreads), 0, stream, 
             (const uint4 *)input, total, per_warp, chunks_per_row, G, (uint32_t *)codes, scales, layout, groups,
             (groups + 3u) / 4u);
     note_launch();

@@ -173,6 +173,8 @@ qk_norm_rope_paged_kernel(const qk_dev_args a) {
     const uint32_t heads = a.q_heads + a.k_heads;
     const uint32_t half = a.rope_dim >> 1;
     const uint32_t rot_lanes = a.rope_dim >> 3;  // lanes of a head that carry rotary pairs
+    allow_dependents();
+    dependency_wait();
 
     for (uint32_t i = tid; i < D; i += blockDim.x) {
         gq_sh[i] = a.q_heads ? __uint_as_float((uint32_t)a.q_gamma[i] << 16) : 0.0f;
@@ -329,6 +331,8 @@ qk_norm_rope_stream_kernel(const qk_dev_args a, const qk_stream_geom g) {
     float *tables = team_area + (size_t)team * qk_team_words(D);
     uint64_t *bars = reinterpret_cast<uint64_t *>(team_area + (size_t)g.teams * qk_team_words(D)) + team * kQkMaxSlots;
     uint8_t *my_slots = smem + (size_t)team * g.slots * g.slot_bytes;
+    allow_dependents();
+    dependency_wait();
 
     for (uint32_t i = tid; i < D; i += blockDim.x) {
         gq_sh[i] = a.q_heads ? __uint_as_float((uint32_t)a.q_gamma[i] << 16) : 0.0f;
@@ -505,8 +509,8 @@ void launch_qk(const qk_dev_args &a, cudaStream_t stream) {
     const bool fast = best_waste == 0u && a.rope_dim == a.head_dim;
 #define AXB_QK_LAUNCH(NPT)                                                                              \
     do {                                                                                                 \
-        if (fast) qk_norm_rope_paged_kernel<LPH, NPT, true><<<grid, best_threads, 0, stream>>>(a);       \
-        else qk_norm_rope_paged_kernel<LPH, NPT, false><<<grid, best_threads, 0, stream>>>(a);           \
+        if (fast) launch_chained(qk_norm_rope_paged_kernel<LPH, NPT, true>, dim3(grid), dim3(best_threads), 0, stream, a);       \
+        else launch_chained(qk_norm_rope_paged_kernel<LPH, NPT, false>, dim3(grid), dim3(best_threads), 0, stream, a);           \
     } while (0)
     switch (best_npt) {
     case 2: AXB_QK_LAUNCH(2); break;
@@ -563,11 +567,11 @@ bool launch_qk_stream(const qk_dev_args &a, cudaStream_t stream) {
         if (full) {                                                                                      \
             auto kern = qk_norm_rope_stream_kernel<LPH, NPT, true>;                                      \
             cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kQkSmemBudget); \
-            kern<<<ctas, best.teams * best.team_threads, smem, stream>>>(a, best);                       \
+            launch_chained(kern, dim3(ctas), dim3(best.teams * best.team_threads), smem, stream, a, best);                       \
         } else {                                                                                         \
             auto kern = qk_norm_rope_stream_kernel<LPH, NPT, false>;                                     \
             cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kQkSmemBudget); \
-            kern<<<ctas, best.teams * best.team_threads, smem, stream>>>(a, best);                       \
+            launch_chained(kern, dim3(ctas), dim3(best.teams * best.team_threads), smem, stream, a, best);                       \
         }                                                                                                \
     } while (0)
     switch (best_npt) {

@@ -155,7 +155,9 @@ fp8_rows_kernel(const uint4 *__restrict__ in, uint32_t rows, uint32_t chunks, ui
     constexpr bool kSwiglu = kOp != row_op::plain_finite_only;
     constexpr bool kTable = kOp == row_op::swiglu_table;
     const uint32_t tid = threadIdx.x;
-    if (kTable) build_silu_table(silu_table, device_table);
+    allow_dependents();
+    if (kTable) build_silu_table(silu_table, device_table);  // the device table never changes once filled
+    dependency_wait();
     for (uint32_t row = blockIdx.x; row < rows; row += gridDim.x) {
         const uint4 *gate = in + (uint64_t)row * in_chunks_per_row;
         float y[CPT][8];
@@ -265,8 +267,10 @@ swiglu_nvfp4_kernel(const uint4 *__restrict__ in, uint32_t rows, uint32_t chunks
                     const float *__restrict__ device_table) {
     extern __shared__ __align__(16) float silu_table[];
     __shared__ scale_lut_entry lut[128];
-    if (kTable) build_silu_table(silu_table, device_table);
+    allow_dependents();
+    if (kTable) build_silu_table(silu_table, device_table);  // the device table never changes once filled
     const bool lut_safe = build_scale_lut(lut, G);
+    dependency_wait();
     const uint32_t lane = threadIdx.x & 31u;
     const uint32_t warp = (blockIdx.x * kNvThreads + threadIdx.x) >> 5;
     uint32_t row = warp / col_groups, col = warp % col_groups;
@@ -394,10 +398,10 @@ int launch_fp8_rows(const void *in, uint32_t rows, uint32_t width, uint32_t in_c
         }
     }
     switch (s.cpt) {
-    case 1: fp8_rows_kernel<1, kOp><<<ctas, s.threads, smem, stream>>>(src, rows, chunks, in_chunks_per_row, dst, scales, status_word, device_table); break;
-    case 2: fp8_rows_kernel<2, kOp><<<ctas, s.threads, smem, stream>>>(src, rows, chunks, in_chunks_per_row, dst, scales, status_word, device_table); break;
-    case 4: fp8_rows_kernel<4, kOp><<<ctas, s.threads, smem, stream>>>(src, rows, chunks, in_chunks_per_row, dst, scales, status_word, device_table); break;
-    default: fp8_rows_kernel<8, kOp><<<ctas, s.threads, smem, stream>>>(src, rows, chunks, in_chunks_per_row, dst, scales, status_word, device_table); break;
+    case 1: launch_chained(fp8_rows_kernel<1, kOp>, dim3(ctas), dim3(s.threads), smem, stream, src, rows, chunks, in_chunks_per_row, dst, scales, status_word, device_table); break;
+    case 2: launch_chained(fp8_rows_kernel<2, kOp>, dim3(ctas), dim3(s.threads), smem, stream, src, rows, chunks, in_chunks_per_row, dst, scales, status_word, device_table); break;
+    case 4: launch_chained(fp8_rows_kernel<4, kOp>, dim3(ctas), dim3(s.threads), smem, stream, src, rows, chunks, in_chunks_per_row, dst, scales, status_word, device_table); break;
+    default: launch_chained(fp8_rows_kernel<8, kOp>, dim3(ctas), dim3(s.threads), smem, stream, src, rows, chunks, in_chunks_per_row, dst, scales, status_word, device_table); break;
     }
     note_launch();
     return AXIOM_OK;
@@ -448,11 +452,11 @@ int launch_swiglu_nvfp4_bf16(const void *gate_up, uint32_t rows, uint32_t width,
             cudaFuncSetAttribute(swiglu_nvfp4_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSiluTableBytes);
             configured[dev] = true;
         }
-        swiglu_nvfp4_kernel<true><<<(uint32_t)blocks, kNvThreads, kSiluTableBytes, stream>>>(
+        launch_chained(swiglu_nvfp4_kernel<true>, dim3((uint32_t)blocks), dim3(kNvThreads), kSiluTableBytes, stream, 
                 src, rows, chunks, col_groups, W / col_groups, W % col_groups, G, (uint32_t *)codes, scales, layout, groups,
                 (groups + 3u) / 4u, device_table);
     } else {
-        swiglu_nvfp4_kernel<false><<<(uint32_t)blocks, kNvThreads, 0, stream>>>(
+        launch_chained(swiglu_nvfp4_kernel<false>, dim3((uint32_t)blocks), dim3(kNvThreads), 0, stream, 
                 src, rows, chunks, col_groups, W / col_groups, W % col_groups, G, (uint32_t *)codes, scales, layout, groups,
                 (groups + 3u) / 4u, nullptr);
     }
