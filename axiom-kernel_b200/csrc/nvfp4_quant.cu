@@ -22,71 +22,117 @@ __device__ __forceinline__ void unpack8(const uint4 &v, float (&x)[8]) {
 }
 
 
-// Every warp streams one contiguous range of chunks (ranges differ by at most
-// one 128-byte step, so all warps of the persistent grid finish together).
-__global__ void __launch_bounds__(kThreads)
-nvfp4_quantize_bf16_kernel(const uint4 *__restrict__ in, uint32_t total_chunks, uint32_t chunks_per_warp,
-                           uint32_t chunks_per_row, float G, uint32_t *__restrict__ codes,
-                           uint8_t *__restrict__ scales, uint32_t layout, uint32_t groups, uint32_t inner_tiles) {
-    __shared__ scale_lut_entry lut[128];
-    const uint32_t lane = threadIdx.x & 31u;
-    const uint32_t warp = (blockIdx.x * kThreads + threadIdx.x) >> 5;
-    const uint64_t first = (uint64_t)warp * chunks_per_warp;
-    const uint64_t last = first + chunks_per_warp < total_chunks ? first + chunks_per_warp : total_chunks;
-    constexpr uint32_t kTile = 32u * kUnroll;
-    allow_dependents();
-    dependency_wait();
-    // the first tile is requested before the CTA builds its scale table
-    uint4 v[kUnroll];
+// Quantizes the kUnroll chunks a lane holds for one warp tile (lane pairs form the 16-value blocks).
+__device__ __forceinline__ void quantize_tile(const uint4 (&v)[kUnroll], float G, const scale_lut_entry *lut,
+                                              bool lut_safe, uint32_t (&packed)[kUnroll],
+                                              uint32_t (&scale_byte)[kUnroll]) {
+    bool needs_exact = false;
 #pragma unroll
     for (uint32_t j = 0; j < kUnroll; ++j) {
-        const uint64_t c = first + j * 32u + lane;
-        v[j] = c < last ? ld_stream(in + c) : make_uint4(0u, 0u, 0u, 0u);
+        float x[8];
+        unpack8(v[j], x);
+        float m = absmax8_nan(x);
+        m = max_nan(m, __shfl_xor_sync(0xffffffffu, m, 1));
+        packed[j] = nvfp4_quantize8_fast(x, m, G, lut, &scale_byte[j], &needs_exact);
     }
-    const bool lut_safe = build_scale_lut(lut, G);
-    for (uint64_t tile = first; tile < last; tile += kTile) {
-        uint4 nxt[kUnroll];
-#pragma unroll
-        for (uint32_t j = 0; j < kUnroll; ++j) {  // software pipeline: next tile in flight during this one
-            const uint64_t c = tile + kTile + j * 32u + lane;
-            nxt[j] = c < last ? ld_stream(in + c) : make_uint4(0u, 0u, 0u, 0u);
-        }
-        uint32_t packed[kUnroll], scale_byte[kUnroll];
-        bool needs_exact = false;
+    if (!lut_safe || __any_sync(0xffffffffu, needs_exact)) {
 #pragma unroll
         for (uint32_t j = 0; j < kUnroll; ++j) {
             float x[8];
             unpack8(v[j], x);
-            float m = absmax8_nan(x);
-            m = max_nan(m, __shfl_xor_sync(0xffffffffu, m, 1));
-            packed[j] = nvfp4_quantize8_fast(x, m, G, lut, &scale_byte[j], &needs_exact);
+            float m = absmax8_drop_nan(x);  // an all-NaN block has maximum 0, as a running fmaxf from 0 gives
+            m = fmaxf(fmaxf(m, __shfl_xor_sync(0xffffffffu, m, 1)), 0.0f);
+            packed[j] = nvfp4_quantize8_exact(x[0], x[1], x[2], x[3], x[4], x[5], x[6], x[7], m, G, &scale_byte[j]);
         }
-        if (!lut_safe || __any_sync(0xffffffffu, needs_exact)) {
+    }
+}
+
+// Every warp streams one contiguous range of chunks (ranges differ by at most one 128-byte
+// step, so all warps of the persistent grid finish together).  A warp tile is kUnroll x 32
+// chunks; full tiles run without a single bounds predicate and with addresses that are a
+// per-lane pointer plus a compile-time offset, the ragged last tile of a range takes the
+// predicated copy of the same code.  The next tile's loads are issued before the current
+// tile is converted.  kTiled: block scales go to the 128 x 4 tiled plane, whose (row, group)
+// coordinates a lane tracks incrementally (one division per warp, none per chunk).
+template <bool kTiled>
+__global__ void __launch_bounds__(kThreads)
+nvfp4_quantize_bf16_kernel(const uint4 *__restrict__ in, uint32_t total_chunks, uint32_t chunks_per_warp,
+                           uint32_t chunks_per_row, float G, uint32_t *__restrict__ codes,
+                           uint8_t *__restrict__ scales, uint32_t groups, uint32_t inner_tiles) {
+    __shared__ scale_lut_entry lut[128];
+    constexpr uint32_t kTile = 32u * kUnroll;
+    const uint32_t lane = threadIdx.x & 31u;
+    const uint32_t warp = (blockIdx.x * kThreads + threadIdx.x) >> 5;
+    allow_dependents();
+    const bool lut_safe = build_scale_lut(lut, G);  // depends on the scalar argument only
+    dependency_wait();
+    const uint64_t first64 = (uint64_t)warp * chunks_per_warp;
+    if (first64 >= total_chunks) return;
+    const uint32_t first = (uint32_t)first64;
+    const uint32_t count = total_chunks - first < chunks_per_warp ? total_chunks - first : chunks_per_warp;
+
+    const uint4 *src = in + first + lane;
+    uint32_t *dst = codes + first + lane;
+    uint8_t *sc = scales + ((first + lane) >> 1);          // canonical plane: block index = chunk / 2
+    uint32_t row = 0u, col = 0u;                            // tiled plane: this lane's chunk as (row, chunk in row)
+    if (kTiled) {
+        row = (first + lane) / chunks_per_row;
+        col = (first + lane) - row * chunks_per_row;
+    }
+    auto store_scale = [&](uint32_t j, uint32_t byte) {
+        if (!kTiled) {
+            sc[j * 16u] = (uint8_t)byte;
+        } else {
+            // position of chunk (col + 32 j) of this row, carried into the next rows
+            uint32_t r = row, c = col + 32u * j;
+            while (c >= chunks_per_row) { c -= chunks_per_row; ++r; }
+            scales[scale_offset(r, c >> 1, groups, inner_tiles, AXIOM_SCALE_LAYOUT_TILED)] = (uint8_t)byte;
+        }
+    };
+    auto advance = [&]() {
+        src += kTile; dst += kTile; sc += kTile / 2u;
+        if (kTiled) {
+            col += kTile;
+            while (col >= chunks_per_row) { col -= chunks_per_row; ++row; }
+        }
+    };
+
+    const uint32_t full_tiles = count / kTile;
+    uint4 v[kUnroll];
+    if (full_tiles) {
 #pragma unroll
-            for (uint32_t j = 0; j < kUnroll; ++j) {
-                float x[8];
-                unpack8(v[j], x);
-                float m = absmax8_drop_nan(x);  // an all-NaN block has maximum 0, as a running fmaxf from 0 gives
-                m = fmaxf(fmaxf(m, __shfl_xor_sync(0xffffffffu, m, 1)), 0.0f);
-                packed[j] = nvfp4_quantize8_exact(x[0], x[1], x[2], x[3], x[4], x[5], x[6], x[7], m, G, &scale_byte[j]);
-            }
+        for (uint32_t j = 0; j < kUnroll; ++j) v[j] = ld_stream(src + 32u * j);
+    }
+    for (uint32_t t = 0; t < full_tiles; ++t) {
+        uint4 nxt[kUnroll];
+        if (t + 1u < full_tiles) {
+#pragma unroll
+            for (uint32_t j = 0; j < kUnroll; ++j) nxt[j] = ld_stream(src + kTile + 32u * j);
         }
+        uint32_t packed[kUnroll], scale_byte[kUnroll];
+        quantize_tile(v, G, lut, lut_safe, packed, scale_byte);
 #pragma unroll
         for (uint32_t j = 0; j < kUnroll; ++j) {
-            const uint64_t c = tile + j * 32u + lane;
-            if (c < last) {
-                st_stream(codes + c, packed[j]);
-                if ((lane & 1u) == 0u) {
-                    uint64_t off = c >> 1;
-                    if (layout != AXIOM_SCALE_LAYOUT_CANONICAL) {
-                        const uint32_t row = (uint32_t)(c / chunks_per_row);
-                        const uint32_t group = ((uint32_t)c - row * chunks_per_row) >> 1;
-                        off = scale_offset(row, group, groups, inner_tiles, layout);
-                    }
-                    scales[off] = (uint8_t)scale_byte[j];
-                }
-            }
+            st_stream(dst + 32u * j, packed[j]);
+            if ((lane & 1u) == 0u) store_scale(j, scale_byte[j]);
             v[j] = nxt[j];
+        }
+        advance();
+    }
+    const uint32_t rest = count - full_tiles * kTile;  // < kTile chunks, a whole number of blocks
+    if (rest) {
+#pragma unroll
+        for (uint32_t j = 0; j < kUnroll; ++j) {
+            v[j] = 32u * j + lane < rest ? ld_stream(src + 32u * j) : make_uint4(0u, 0u, 0u, 0u);
+        }
+        uint32_t packed[kUnroll], scale_byte[kUnroll];
+        quantize_tile(v, G, lut, lut_safe, packed, scale_byte);
+#pragma unroll
+        for (uint32_t j = 0; j < kUnroll; ++j) {
+            if (32u * j + lane < rest) {
+                st_stream(dst + 32u * j, packed[j]);
+                if ((lane & 1u) == 0u) store_scale(j, scale_byte[j]);
+            }
         }
     }
 }
@@ -132,17 +178,22 @@ int launch_nvfp4_quantize_bf16(const void *input, uint32_t rows, uint32_t cols, 
     const uint32_t total = rows * chunks_per_row;
     const uint32_t groups = cols / kGroup;
     const uint32_t warps_per_block = kThreads / 32u;
-    // persistent grid: 6 CTAs of 256 threads per SM, or fewer when there is little to do
-    uint32_t blocks = kSmCount * 6u;
+    // persistent grid: the 3 CTAs of 256 threads per SM that are resident at 80 registers (one wave), or
+    // fewer when there is little to do
+    uint32_t blocks = kSmCount * 3u;
     const uint32_t min_chunks_per_warp = 32u * kUnroll;
     const uint32_t needed = (total + min_chunks_per_warp * warps_per_block - 1u) / (min_chunks_per_warp * warps_per_block);
     if (blocks > needed) blocks = needed;
     const uint32_t warps = blocks * warps_per_block;
     uint32_t per_warp = (total + warps - 1u) / warps;
     per_warp = (per_warp + 7u) & ~7u;  // ranges start on 128-byte boundaries and never split a block
-    launch_chained(nvfp4_quantize_bf16_kernel, dim3(blocks), dim3(kThreads), 0, stream, 
-            (const uint4 *)input, total, per_warp, chunks_per_row, G, (uint32_t *)codes, scales, layout, groups,
-            (groups + 3u) / 4u);
+    if (layout == AXIOM_SCALE_LAYOUT_TILED) {
+        launch_chained(nvfp4_quantize_bf16_kernel<true>, dim3(blocks), dim3(kThreads), 0, stream, (const uint4 *)input,
+                       total, per_warp, chunks_per_row, G, (uint32_t *)codes, scales, groups, (groups + 3u) / 4u);
+    } else {
+        launch_chained(nvfp4_quantize_bf16_kernel<false>, dim3(blocks), dim3(kThreads), 0, stream, (const uint4 *)input,
+                       total, per_warp, chunks_per_row, G, (uint32_t *)codes, scales, groups, (groups + 3u) / 4u);
+    }
     note_launch();
     return AXIOM_OK;
 }
