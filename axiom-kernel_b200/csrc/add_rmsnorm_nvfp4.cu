@@ -145,13 +145,26 @@ add_rmsnorm_stream_kernel(const norm_args a) {
     const uint32_t k_iters = (a.cols + 255u) / 256u;                      // sweep 1: feature pairs 256k + 2t
     const uint32_t c_iters = (a.chunks_per_row + kTeamThreads - 1u) / kTeamThreads;  // sweep 2: chunks t + 128k
 
-    auto issue = [&](uint32_t i) {  // thread 0 of the team: start loading the team's i-th row into its slot
+    // A row arrives in two bulk copies that complete on the slot's mbarrier.  The addend half of a
+    // slot is dead as soon as sweep 1 has merged it into the residual half, so the NEXT row's
+    // addend is requested right then (announced with expect_tx only) and only its residual has
+    // to wait until sweep 2 and the bulk store of the merged row are done with the other half.
+    auto issue_addend = [&](uint32_t i) {  // thread 0 of the team
         const uint64_t row = blockIdx.x + (uint64_t)(team + teams * i) * gridDim.x;
         const uint32_t j = i % spt;
-        uint8_t *slot = my_slots + (size_t)j * slot_bytes;
-        mbar_arrive_expect_tx(my_bars + j, slot_bytes);
-        if (kAdd) bulk_load(slot, a.hidden + row * a.chunks_per_row, row_bytes, my_bars + j);
-        bulk_load(slot + (kAdd ? row_bytes : 0u), a.residual + row * a.chunks_per_row, row_bytes, my_bars + j);
+        mbar_expect_tx(my_bars + j, row_bytes);
+        bulk_load(my_slots + (size_t)j * slot_bytes, a.hidden + row * a.chunks_per_row, row_bytes, my_bars + j);
+    };
+    auto issue_residual = [&](uint32_t i) {
+        const uint64_t row = blockIdx.x + (uint64_t)(team + teams * i) * gridDim.x;
+        const uint32_t j = i % spt;
+        mbar_arrive_expect_tx(my_bars + j, row_bytes);
+        bulk_load(my_slots + (size_t)j * slot_bytes + (kAdd ? row_bytes : 0u), a.residual + row * a.chunks_per_row, row_bytes,
+                  my_bars + j);
+    };
+    auto issue = [&](uint32_t i) {
+        if (kAdd) issue_addend(i);
+        issue_residual(i);
     };
     // the first rows are already on their way while the CTA prepares gamma and the scale table
     if (t == 0u) {
@@ -200,6 +213,7 @@ add_rmsnorm_stream_kernel(const norm_args a) {
             // the merged row leaves as one bulk store; the slot stays in use until it has been read
             bulk_store(a.residual + base, res_sh, row_bytes);
             bulk_commit();
+            if (i + spt < my_rows) issue_addend(i + spt);  // every thread is past its reads of the addend half
         }
         // Reference tree over the 256 partials c: strides 128,64,32 then 16,8,4,2,1.  With lane l
         // holding c = 8l + e, strides 128..8 are the lane butterfly 16,8,4,2,1 applied to each e
@@ -245,7 +259,7 @@ add_rmsnorm_stream_kernel(const norm_args a) {
         team_barrier(team);
         if (t == 0u) {
             if (kAdd) bulk_wait_read_all();
-            if (i + spt < my_rows) issue(i + spt);
+            if (i + spt < my_rows) issue_residual(i + spt);
         }
     }
     if (kAdd && t == 0u) bulk_wait_read_all();
@@ -416,18 +430,26 @@ int launch_add_rmsnorm_nvfp4_bf16(const void *hidden, void *residual, const void
     a.groups = cols / kGroup;
     a.inner_tiles = (a.groups + 3u) / 4u;
 
-    // Stream kernel shape: as many 4-warp teams as double-buffered slots fit beside the
-    // F32 gamma copy (5 teams x 2 slots of 20 KB at 5120 columns with an addend).
+    // Stream kernel shape.  The kernel is bound by instruction issue, not by memory, so resident
+    // warps count for more than prefetch depth: eight teams with one slot each (while a team
+    // waits for its next row the other seven compute) beat five double-buffered teams at 5120
+    // columns (53.5 us against 56.0 us for 8192 rows).  Narrow rows get both: up to eight
+    // teams and as many slots per team as fit.
     const size_t slot_bytes = (size_t)cols * 2u * (hidden ? 2u : 1u);
-    uint32_t teams = kMaxTeams;
-    while (teams != 0u && stream_fixed_bytes(cols, teams) + (size_t)teams * 2u * slot_bytes > kSmemBudget) --teams;
+    auto teams_that_fit = [&](uint32_t slots) {
+        uint32_t t = kMaxTeams;
+        while (t != 0u && stream_fixed_bytes(cols, t) + (size_t)t * slots * slot_bytes > kSmemBudget) --t;
+        return t;
+    };
+    const uint32_t single = teams_that_fit(1u), dual = teams_that_fit(2u);
+    uint32_t teams = single >= dual + 2u ? single : dual;
     uint32_t spt = 0u;
     if (teams != 0u) {
         spt = (uint32_t)((kSmemBudget - stream_fixed_bytes(cols, teams)) / (teams * slot_bytes));
         if (spt > kMaxSlotsPerTeam) spt = kMaxSlotsPerTeam;
     }
-    // The widest row the entry points accept (16384 columns) still fits one team with two slots.
-    if (teams == 0u || spt < 2u) return AXIOM_ERR_INVALID_ARGUMENT;
+    // The widest row the entry points accept (16384 columns) still fits one team with one slot.
+    if (teams == 0u || spt == 0u) return AXIOM_ERR_INVALID_ARGUMENT;
     // Few rows: latency matters more than streaming; one wide CTA per row.
     if (rows < 2u * kSmCount) {
         uint32_t threads = (a.chunks_per_row + 31u) & ~31u;
