@@ -288,11 +288,11 @@ qk_norm_rope_paged_kernel(const qk_dev_args a) {
 
 // ---------------------------------------------------------------------------
 // Streaming flavour for many tokens: a persistent CTA per SM made of independent teams.
-// A team owns `slots` shared-memory token slots laid out [Q heads | K heads | V heads]; its
+// A team owns `slots` shared-memory token slots laid out [Q heads | K heads]; its
 // thread 0 keeps bulk loads of the next tokens in flight, the team normalises and rotates the
 // slot IN PLACE, and thread 0 sends the finished slot out with bulk stores (Q row back in
-// place, K row to its cache page and/or k_out, V row to its cache page) — the data path has
-// no per-thread global access at all.  Slot (i-1) is refilled at the end of token i, once its
+// place, K row to its cache page and/or k_out); V, a 2 KB copy per token, is moved by the team's
+// first threads with 16-byte accesses.  Slot (i-1) is refilled at the end of token i, once its
 // stores have finished reading shared memory (one store group may stay pending), so loads run
 // `slots - 1` tokens ahead.  One team barrier per token: the rotary table of token i+1 is
 // written (double-buffered) at the top of iteration i, before the wait for token i's data;
@@ -300,14 +300,15 @@ qk_norm_rope_paged_kernel(const qk_dev_args a) {
 // which keeps the dependent pos -> table -> address chain off the critical path.
 // ---------------------------------------------------------------------------
 constexpr uint32_t kQkMaxSlots = 4u;
+constexpr uint32_t kQkVRegs = 2u;  // 16-byte V chunks a thread carries across the token's barrier
 constexpr uint32_t kQkStreamThreads = 768u;  // 24 warps: leaves 80 registers per thread
 
 struct qk_stream_geom {
     uint32_t team_threads, teams, slots, slot_bytes;
 };
 
-// floats of one team's table area: two buffers of three D/2 tables
-__host__ __device__ inline uint32_t qk_team_words(uint32_t D) { return (D / 2u) * 6u; }
+// floats of one team's table area: two buffers of three D/2 tables, two 64-bit cache addresses
+__host__ __device__ inline uint32_t qk_team_words(uint32_t D) { return (D / 2u) * 6u + 4u; }
 
 __device__ __forceinline__ void team_sync(uint32_t team, uint32_t threads) {
     asm volatile("bar.sync %0, %1;" ::"r"(team + 1u), "r"(threads) : "memory");
@@ -322,6 +323,7 @@ qk_norm_rope_stream_kernel(const qk_dev_args a, const qk_stream_geom g) {
     const uint32_t rot_lanes = a.rope_dim >> 3;
     const uint32_t q_bytes = a.q_heads * D * 2u, k_bytes = a.k_heads * D * 2u;
     const bool has_v = a.v != nullptr && a.v_pool != nullptr;
+    const uint32_t v_chunks = a.k_heads * LPH;  // 16-byte chunks of a V row
 
     // [teams][slots][slot_bytes] | gq[D] gk[D] | per team: 2 x (cos, sin, -sin)[D/2] | barriers
     float *gq_sh = reinterpret_cast<float *>(smem + (size_t)g.teams * g.slots * g.slot_bytes);
@@ -329,6 +331,7 @@ qk_norm_rope_stream_kernel(const qk_dev_args a, const qk_stream_geom g) {
     float *team_area = gk_sh + D;
     const uint32_t tid = threadIdx.x, team = tid / g.team_threads, t = tid % g.team_threads;
     float *tables = team_area + (size_t)team * qk_team_words(D);
+    unsigned long long *v_base_sh = reinterpret_cast<unsigned long long *>(tables + (D / 2u) * 6u);  // [2], ~0 = none
     uint64_t *bars = reinterpret_cast<uint64_t *>(team_area + (size_t)g.teams * qk_team_words(D)) + team * kQkMaxSlots;
     uint8_t *my_slots = smem + (size_t)team * g.slots * g.slot_bytes;
     allow_dependents();
@@ -344,6 +347,7 @@ qk_norm_rope_stream_kernel(const qk_dev_args a, const qk_stream_geom g) {
     }
     __syncthreads();
 
+    const bool v_in_regs = v_chunks <= kQkVRegs * g.team_threads;
     const uint32_t l = t % LPH;
     const uint32_t head0 = t / LPH, head_step = g.team_threads / LPH;
     const bool rotary = kFullRot || l < rot_lanes;
@@ -362,13 +366,15 @@ qk_norm_rope_stream_kernel(const qk_dev_args a, const qk_stream_geom g) {
         const uint64_t tok = token_of(i);
         const uint32_t j = i % g.slots;
         uint8_t *slot = my_slots + (size_t)j * g.slot_bytes;
-        mbar_arrive_expect_tx(bars + j, q_bytes + k_bytes + (has_v ? k_bytes : 0u));
+        mbar_arrive_expect_tx(bars + j, q_bytes + k_bytes);
         if (q_bytes) bulk_load(slot, reinterpret_cast<const uint8_t *>(a.q) + tok * q_bytes, q_bytes, bars + j);
         if (k_bytes) bulk_load(slot + q_bytes, reinterpret_cast<const uint8_t *>(a.k) + tok * k_bytes, k_bytes, bars + j);
-        if (has_v) bulk_load(slot + q_bytes + k_bytes, reinterpret_cast<const uint8_t *>(a.v) + tok * k_bytes, k_bytes, bars + j);
     };
+    // With two or more slots the refill lags one token behind (see below) and slots - 1 tokens
+    // are requested up front; a single slot is refilled as soon as its own stores have drained.
+    const uint32_t ahead = g.slots > 1u ? g.slots - 1u : 1u;
     if (t == 0u) {
-        for (uint32_t i = 0; i + 1u < g.slots && i < my_tokens; ++i) issue(i);
+        for (uint32_t i = 0; i < ahead && i < my_tokens; ++i) issue(i);
     }
 
     // table entry that maps a position's logical cache block (thread 0 only; ~0 when the
@@ -413,6 +419,24 @@ qk_norm_rope_stream_kernel(const qk_dev_args a, const qk_stream_geom g) {
             if (idx != ~0ull) pb_n1 = a.block_tables[idx];
         }
         if (i + 1u < my_tokens) write_table((i + 1u) & 1u, pos_n1);
+        // V is a plain copy into the token's cache row: too small to deserve slot space.  The
+        // team's first threads read it now and write it after the barrier, when thread 0 has
+        // published the row's address.
+        uint4 v_reg[kQkVRegs];
+        if (has_v) {
+            if (t == 0u) {
+                v_base_sh[i & 1u] = (pb_cur >= 0 && (uint32_t)pb_cur < a.n_blocks)
+                        ? (((uint64_t)pb_cur * a.n_layers + a.layer) * a.block_tokens + pos_cur % a.block_tokens) * a.pool_stride
+                        : ~0ull;
+            }
+            if (v_in_regs) {
+#pragma unroll
+                for (uint32_t c = 0; c < kQkVRegs; ++c) {
+                    const uint32_t q = t + c * g.team_threads;
+                    if (q < v_chunks) v_reg[c] = ld_stream(a.v + (uint64_t)tok * v_chunks + q);
+                }
+            }
+        }
 
         uint8_t *slot = my_slots + (size_t)j * g.slot_bytes;
         // A wait that ran out raises the fault word; the team carries on (on whatever the slot
@@ -440,6 +464,23 @@ qk_norm_rope_stream_kernel(const qk_dev_args a, const qk_stream_geom g) {
         fence_async_shared();
         team_sync(team, g.team_threads);
 
+        if (has_v && !faulted) {
+            const unsigned long long v_base = v_base_sh[i & 1u];  // element index of the row in the pools
+            if (v_base != ~0ull) {
+                uint4 *dst = reinterpret_cast<uint4 *>(reinterpret_cast<uint16_t *>(a.v_pool) + v_base);
+                if (v_in_regs) {
+#pragma unroll
+                    for (uint32_t c = 0; c < kQkVRegs; ++c) {
+                        const uint32_t q = t + c * g.team_threads;
+                        if (q < v_chunks) st_stream(dst + q, v_reg[c]);
+                    }
+                } else {
+                    for (uint32_t q = t; q < v_chunks; q += g.team_threads) {
+                        st_stream(dst + q, ld_stream(a.v + (uint64_t)tok * v_chunks + q));
+                    }
+                }
+            }
+        }
         if (t == 0u && !faulted) {
             const uint8_t *src = slot;
             if (q_bytes) bulk_store(reinterpret_cast<uint8_t *>(a.q) + (uint64_t)tok * q_bytes, src, q_bytes);
@@ -449,7 +490,6 @@ qk_norm_rope_stream_kernel(const qk_dev_args a, const qk_stream_geom g) {
                     const uint64_t base = ((((uint64_t)pb_cur * a.n_layers + a.layer) * a.block_tokens +
                                             pos_cur % a.block_tokens) * a.pool_stride) * 2u;
                     if (k_bytes) bulk_store(reinterpret_cast<uint8_t *>(a.k_pool) + base, src + q_bytes, k_bytes);
-                    if (has_v) bulk_store(reinterpret_cast<uint8_t *>(a.v_pool) + base, src + q_bytes + k_bytes, k_bytes);
                 } else if (a.status_word) {
                     atomicCAS(a.status_word, AXIOM_STATUS_WORD_OK, AXIOM_STATUS_WORD_BAD_ADDRESS);
                 }
@@ -457,9 +497,10 @@ qk_norm_rope_stream_kernel(const qk_dev_args a, const qk_stream_geom g) {
             bulk_commit();
             // refill the slot of the PREVIOUS token (slot of token i + slots - 1): its stores are
             // the older group, so only they have to be done reading.
-            const uint32_t nxt = i + g.slots - 1u;
+            const uint32_t nxt = i + ahead;
             if (nxt < my_tokens) {
-                bulk_wait_read_but_one();
+                if (g.slots > 1u) bulk_wait_read_but_one();
+                else bulk_wait_read_all();
                 issue(nxt);
             }
         }
@@ -534,7 +575,6 @@ size_t qk_stream_smem(const qk_dev_args &a, const qk_stream_geom &g) {
 template <int LPH>
 bool launch_qk_stream(const qk_dev_args &a, cudaStream_t stream) {
     const uint32_t items = (a.q_heads + a.k_heads) * LPH;
-    const bool has_v = a.v != nullptr && a.v_pool != nullptr;
     qk_stream_geom best{};
     uint32_t best_npt = 0u, best_score = 0u;
     static const uint32_t kNpt[] = {2u, 3u, 4u, 6u, 8u};
@@ -543,7 +583,7 @@ bool launch_qk_stream(const qk_dev_args &a, cudaStream_t stream) {
         qk_stream_geom g{};
         g.team_threads = items / npt;
         if (g.team_threads % 32u || g.team_threads > 512u || g.team_threads < 64u) continue;
-        g.slot_bytes = ((a.q_heads + a.k_heads) + (has_v ? a.k_heads : 0u)) * a.head_dim * 2u;
+        g.slot_bytes = (a.q_heads + a.k_heads) * a.head_dim * 2u;
         g.slots = 3u;
         g.teams = kQkStreamThreads / g.team_threads;
         while (g.teams != 0u && qk_stream_smem(a, g) > kQkSmemBudget) --g.teams;
