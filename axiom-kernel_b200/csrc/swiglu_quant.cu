@@ -74,35 +74,38 @@ __device__ __forceinline__ void build_silu_table(float *table, const float *devi
     __syncthreads();
 }
 
-// silu of the two BF16 gates packed in w, read from the table (garbage for out-of-range gates).
-__device__ __forceinline__ float2 silu_lookup2(const float *table, uint32_t w) {
+// Table lookups for the two BF16 gates packed in w, with everything that can be done on both
+// halves at once done on the packed word.  m2 = magnitudes; below/above = m2 + (0x8000 - first)
+// and m2 + (0x8000 - end) per half: bit 15 of a half is set iff its magnitude is >= first / >= end,
+// and no half can carry into its neighbour (magnitudes are at most 0x7fff).  The low 13 bits of a
+// `below` half are the entry's index inside its sign plane; z puts the sign next to them (bit 13),
+// and the last shifts and masks turn each half of z into a byte offset, dropping the stray bits
+// the 3-input select lets through.  `outside` collects, in bits 15 and 31, whether any gate seen
+// so far lies outside the table (|g| < 2^-57, |g| >= 128, NaN, infinity).
+__device__ __forceinline__ float2 silu_lookup2(const float *table, uint32_t w, uint32_t *outside) {
     const char *base = reinterpret_cast<const char *>(table);
-    const uint32_t dlo = (w << 2) - 4u * kSiluFirst;
-    const uint32_t dhi = (w >> 14) - 4u * kSiluFirst;
-    const uint32_t olo = ((w & 0x8000u) | (dlo & 0x7ffcu));
-    const uint32_t ohi = (((w >> 16) & 0x8000u) | (dhi & 0x7ffcu));
-    return make_float2(*reinterpret_cast<const float *>(base + olo), *reinterpret_cast<const float *>(base + ohi));
-}
-
-// Bit 15 / 31 of the result is set when the low / high gate of w lies outside the table
-// (|g| < 2^-57, |g| >= 128, NaN, infinity).  Halves never carry into each other.
-__device__ __forceinline__ uint32_t silu_outside2(uint32_t w) {
     const uint32_t m2 = w & 0x7fff7fffu;
-    const uint32_t above = m2 + (0x8000u - kSiluEnd) * 0x00010001u;        // bit 15 set: magnitude >= end
-    const uint32_t below = (m2 | 0x80008000u) - kSiluFirst * 0x00010001u;  // bit 15 clear: magnitude < first
-    return (above | ~below) & 0x80008000u;
+    const uint32_t below = m2 + (0x8000u - kSiluFirst) * 0x00010001u;
+    const uint32_t above = m2 + (0x8000u - kSiluEnd) * 0x00010001u;
+    *outside |= above | ~below;
+    uint32_t z;
+    asm("lop3.b32 %0, %1, %2, 0x1fff1fff, 0xe4;" : "=r"(z) : "r"(below), "r"(w >> 2));  // (below & c) | ((w>>2) & ~c)
+    const uint32_t olo = (z << 2) & 0xfffcu;
+    const uint32_t ohi = (z >> 14) & 0xfffcu;
+    return make_float2(*reinterpret_cast<const float *>(base + olo), *reinterpret_cast<const float *>(base + ohi));
 }
 
 // y[0..7] = silu(gate) * up for one 16-byte chunk of each
 template <bool kTable>
 __device__ __forceinline__ void swiglu8(const float *table, const uint4 &g, const uint4 &u, float (&y)[8]) {
     if (kTable) {
-        const float2 p0 = __fmul2_rn(silu_lookup2(table, g.x), make_float2(bf16_lo(u.x), bf16_hi(u.x)));
-        const float2 p1 = __fmul2_rn(silu_lookup2(table, g.y), make_float2(bf16_lo(u.y), bf16_hi(u.y)));
-        const float2 p2 = __fmul2_rn(silu_lookup2(table, g.z), make_float2(bf16_lo(u.z), bf16_hi(u.z)));
-        const float2 p3 = __fmul2_rn(silu_lookup2(table, g.w), make_float2(bf16_lo(u.w), bf16_hi(u.w)));
+        uint32_t outside = 0u;
+        const float2 p0 = __fmul2_rn(silu_lookup2(table, g.x, &outside), make_float2(bf16_lo(u.x), bf16_hi(u.x)));
+        const float2 p1 = __fmul2_rn(silu_lookup2(table, g.y, &outside), make_float2(bf16_lo(u.y), bf16_hi(u.y)));
+        const float2 p2 = __fmul2_rn(silu_lookup2(table, g.z, &outside), make_float2(bf16_lo(u.z), bf16_hi(u.z)));
+        const float2 p3 = __fmul2_rn(silu_lookup2(table, g.w, &outside), make_float2(bf16_lo(u.w), bf16_hi(u.w)));
         y[0] = p0.x; y[1] = p0.y; y[2] = p1.x; y[3] = p1.y; y[4] = p2.x; y[5] = p2.y; y[6] = p3.x; y[7] = p3.y;
-        if (silu_outside2(g.x) | silu_outside2(g.y) | silu_outside2(g.z) | silu_outside2(g.w)) {
+        if (outside & 0x80008000u) {
             float gv[8], uv[8];  // rare: a gate beyond the table in this chunk
             unpack8(g, gv);
             unpack8(u, uv);
