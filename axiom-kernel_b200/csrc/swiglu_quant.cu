@@ -75,19 +75,21 @@ __device__ __forceinline__ void build_silu_table(float *table, const float *devi
 }
 
 // Table lookups for the two BF16 gates packed in w, with everything that can be done on both
-// halves at once done on the packed word.  m2 = magnitudes; below/above = m2 + (0x8000 - first)
-// and m2 + (0x8000 - end) per half: bit 15 of a half is set iff its magnitude is >= first / >= end,
-// and no half can carry into its neighbour (magnitudes are at most 0x7fff).  The low 13 bits of a
-// `below` half are the entry's index inside its sign plane; z puts the sign next to them (bit 13),
-// and the last shifts and masks turn each half of z into a byte offset, dropping the stray bits
-// the 3-input select lets through.  `outside` collects, in bits 15 and 31, whether any gate seen
-// so far lies outside the table (|g| < 2^-57, |g| >= 128, NaN, infinity).
+// halves at once done on the packed word.  below = magnitude + (0x8000 - first) per half (no half
+// can carry into its neighbour: magnitudes are at most 0x7fff).  For a magnitude inside the
+// table, below = 0x8000 + index with index < 0x2000; above the table the index reaches bit 13
+// or 14, and under it below falls into [0x8000 - first, 0x8000), whose bit 14 is set because
+// first < 0x4000 — so "bit 13 or 14 of a half of below" is exactly "this gate is outside the
+// table" (|g| < 2^-57, |g| >= 128, NaN, infinity), and `outside` just ORs the words together.
+// The low 13 bits of a `below` half are the entry's index inside its sign plane; z puts the sign
+// next to them (bit 13), and the last shifts and masks turn each half of z into a byte offset,
+// dropping the stray bits the 3-input select lets through.
+static_assert(kSiluFirst < 0x4000u && kSiluEnd == kSiluFirst + 0x2000u, "range test relies on the table window");
+
 __device__ __forceinline__ float2 silu_lookup2(const float *table, uint32_t w, uint32_t *outside) {
     const char *base = reinterpret_cast<const char *>(table);
-    const uint32_t m2 = w & 0x7fff7fffu;
-    const uint32_t below = m2 + (0x8000u - kSiluFirst) * 0x00010001u;
-    const uint32_t above = m2 + (0x8000u - kSiluEnd) * 0x00010001u;
-    *outside |= above | ~below;
+    const uint32_t below = (w & 0x7fff7fffu) + (0x8000u - kSiluFirst) * 0x00010001u;
+    *outside |= below;
     uint32_t z;
     asm("lop3.b32 %0, %1, %2, 0x1fff1fff, 0xe4;" : "=r"(z) : "r"(below), "r"(w >> 2));  // (below & c) | ((w>>2) & ~c)
     const uint32_t olo = (z << 2) & 0xfffcu;
@@ -105,7 +107,7 @@ __device__ __forceinline__ void swiglu8(const float *table, const uint4 &g, cons
         const float2 p2 = __fmul2_rn(silu_lookup2(table, g.z, &outside), make_float2(bf16_lo(u.z), bf16_hi(u.z)));
         const float2 p3 = __fmul2_rn(silu_lookup2(table, g.w, &outside), make_float2(bf16_lo(u.w), bf16_hi(u.w)));
         y[0] = p0.x; y[1] = p0.y; y[2] = p1.x; y[3] = p1.y; y[4] = p2.x; y[5] = p2.y; y[6] = p3.x; y[7] = p3.y;
-        if (outside & 0x80008000u) {
+        if (outside & 0x60006000u) {
             float gv[8], uv[8];  // rare: a gate beyond the table in this chunk
             unpack8(g, gv);
             unpack8(u, uv);
