@@ -126,6 +126,8 @@ SIGNATURES = {
     "axiom_nvfp4_scale_plane_bytes": (u64, [u32, u32, u32]),
     "axiom_nvfp4_scale_plane_offset": (u64, [u32, u32, u32, u32]),
     "axiom_b200_kernel_launch_count": (u64, []),
+    "axiom_b200_static_scratch_bytes": (u64, []),
+    "axiom_b200_nvfp4_quantize_bf16_host_static": (i32, [C.c_int, vp, u32, u32, f32, u32, vp, vp, vp]),
     "axiom_b200_pipeline_faults": (u32, [i32]),
 }
 

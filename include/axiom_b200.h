@@ -273,6 +273,22 @@ int axiom_runtime_swiglu_fp8_bf16(axiom_runtime *runtime, const void *gate_up_bf
 uint64_t axiom_nvfp4_scale_plane_bytes(uint32_t rows, uint32_t groups, uint32_t scale_layout);
 uint64_t axiom_nvfp4_scale_plane_offset(uint32_t row, uint32_t group, uint32_t groups, uint32_t scale_layout);
 
+/* Host-I/O NVFP4 quantize that performs no allocation of any kind.  NO COUNTERPART IN THE
+ * REFERENCE: it exists for callers that must not allocate while they run.  Same results as
+ * axiom_runtime_nvfp4_quantize_bf16 (which stages through buffers the runtime allocates on
+ * demand); here the staging of input, codes and scales is a fixed device array inside the
+ * library image, of axiom_b200_static_scratch_bytes() bytes (8 MiB) per device.
+ *   - A call whose input + codes + scale plane (each rounded up to 256 bytes) exceed that
+ *     size returns AXIOM_ERR_BUDGET and touches nothing.
+ *   - The first call on a device looks the array's address up (no allocation, no
+ *     synchronisation); make that call before any stream capture begins.  The call itself
+ *     ends with a synchronisation of `stream` and therefore cannot be captured.
+ *   - Every call on a device uses the same array: calls that overlap in time (other host
+ *     threads, other streams) corrupt each other.  Serialise them.
+ *   - out_scales_host receives axiom_nvfp4_scale_plane_bytes(rows, cols/16, scale_layout) bytes. */
+uint64_t axiom_b200_static_scratch_bytes(void);
+int axiom_b200_nvfp4_quantize_bf16_host_static(int device, const void *input_bf16_host, uint32_t rows, uint32_t cols, float global_scale, uint32_t scale_layout, uint8_t *out_codes_host, uint8_t *out_scales_host, void *stream);
+
 /* Number of kernel launches issued by this library in this process (bench bookkeeping). */
 uint64_t axiom_b200_kernel_launch_count(void);
 
