@@ -1,5 +1,5 @@
 // Asynchronous row pipeline primitives for sm_100a: mbarrier phases, 1-D bulk
-// copies (TMA engine, no tensor map, no multicast) between global and shared
+// copies (TMA engine, no tensor map, each copy serves one CTA) between global and shared
 // memory, and the shared-memory lookup table of NVFP4 block-scale divisors.
 //
 // Every wait is bounded: after kSpinLimit failed polls the waiter raises a
