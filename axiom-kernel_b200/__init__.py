@@ -32,6 +32,7 @@ SCALE_CANONICAL = 0
 SCALE_TILED = 1
 QK_FLAG_RING = 1
 QK_FLAG_PER_TOKEN_TABLE = 2
+QK_FLAG_CACHE_E4M3 = 4
 STATUS_WORD_OK = 0
 STATUS_WORD_BAD_ADDRESS = 1
 STATUS_WORD_NONFINITE = 4

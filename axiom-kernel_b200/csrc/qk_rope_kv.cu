@@ -151,6 +151,15 @@ __device__ __forceinline__ void qk_item(uint2 xa, uint2 xb, const float4 ga, con
     *out_b = make_uint2(pack_bf16x2(ob0.x, ob0.y), pack_bf16x2(ob1.x, ob1.y));
 }
 
+// BF16 -> E4M3 codes at scale 1 for the FP8 flavour of the cache (qwen38_kv_encode_e4m3fn_scale1,
+// src/axiom_qwen38_attention.cu:245-248: the saturating converter applied to the BF16-valued float).
+__device__ __forceinline__ uint32_t bf16x4_to_e4m3x4(const uint2 v) {
+    return __byte_perm(cvt_e4m3x2(bf16_lo(v.x), bf16_hi(v.x)), cvt_e4m3x2(bf16_lo(v.y), bf16_hi(v.y)), 0x5410);
+}
+__device__ __forceinline__ uint2 bf16x8_to_e4m3x8(const uint4 v) {
+    return make_uint2(bf16x4_to_e4m3x4(make_uint2(v.x, v.y)), bf16x4_to_e4m3x4(make_uint2(v.z, v.w)));
+}
+
 // ---------------------------------------------------------------------------
 // Per-token flavour (few tokens: lowest latency).  One CTA per token, LPH = lanes per head
 // (head_dim / 8), NPT = (head, lane) work items per thread.  kFast: every thread's NPT items
@@ -190,6 +199,7 @@ qk_norm_rope_paged_kernel(const qk_dev_args a) {
     const uint32_t off_b = rotary ? half + 4u * l : off_a + 4u;
     const uint32_t q_elems = a.q_heads * D, k_elems = a.k_heads * D;
     const double inv_d = 1.0 / (double)D, eps = (double)a.eps;
+    const bool fp8_cache = (a.flags & AXIOM_QK_FLAG_CACHE_E4M3) != 0u;
 
     for (uint32_t t = blockIdx.x; t < a.tokens; t += gridDim.x) {
         uint16_t *q_row = reinterpret_cast<uint16_t *>(a.q) + (uint64_t)t * q_elems;
@@ -264,9 +274,15 @@ qk_norm_rope_paged_kernel(const qk_dev_args a) {
                 } else {
                     const uint32_t off = (h - a.q_heads) * D;
                     if (kv_base != ~0ull) {
-                        uint16_t *dst = reinterpret_cast<uint16_t *>(a.k_pool) + kv_base + off;
-                        st_stream(dst + off_a, pa);
-                        st_stream(dst + off_b, pb);
+                        if (fp8_cache) {
+                            uint8_t *dst = reinterpret_cast<uint8_t *>(a.k_pool) + kv_base + off;
+                            st_stream(reinterpret_cast<uint32_t *>(dst + off_a), bf16x4_to_e4m3x4(pa));
+                            st_stream(reinterpret_cast<uint32_t *>(dst + off_b), bf16x4_to_e4m3x4(pb));
+                        } else {
+                            uint16_t *dst = reinterpret_cast<uint16_t *>(a.k_pool) + kv_base + off;
+                            st_stream(dst + off_a, pa);
+                            st_stream(dst + off_b, pb);
+                        }
                     }
                     if (a.k_out) {
                         uint16_t *dst = reinterpret_cast<uint16_t *>(a.k_out) + (uint64_t)t * k_elems + off;
@@ -276,11 +292,16 @@ qk_norm_rope_paged_kernel(const qk_dev_args a) {
                 }
             }
         }
-        // V rides along unchanged (BF16 in, BF16 cache)
+        // V rides along: a copy into a BF16 cache, a conversion into an E4M3 cache
         if (a.v && a.v_pool && kv_base != ~0ull) {
             const uint4 *v_row = a.v + (uint64_t)t * a.k_heads * LPH;
-            uint4 *dst = reinterpret_cast<uint4 *>(reinterpret_cast<uint16_t *>(a.v_pool) + kv_base);
-            for (uint32_t j = tid; j < a.k_heads * LPH; j += blockDim.x) st_stream(dst + j, ld_stream(v_row + j));
+            if (fp8_cache) {
+                uint2 *dst = reinterpret_cast<uint2 *>(reinterpret_cast<uint8_t *>(a.v_pool) + kv_base);
+                for (uint32_t j = tid; j < a.k_heads * LPH; j += blockDim.x) st_stream(dst + j, bf16x8_to_e4m3x8(ld_stream(v_row + j)));
+            } else {
+                uint4 *dst = reinterpret_cast<uint4 *>(reinterpret_cast<uint16_t *>(a.v_pool) + kv_base);
+                for (uint32_t j = tid; j < a.k_heads * LPH; j += blockDim.x) st_stream(dst + j, ld_stream(v_row + j));
+            }
         }
         __syncthreads();  // the shared tables are rewritten for the next token
     }
@@ -348,6 +369,7 @@ qk_norm_rope_stream_kernel(const qk_dev_args a, const qk_stream_geom g) {
     __syncthreads();
 
     const bool v_in_regs = v_chunks <= kQkVRegs * g.team_threads;
+    const bool fp8_cache = (a.flags & AXIOM_QK_FLAG_CACHE_E4M3) != 0u;
     const uint32_t l = t % LPH;
     const uint32_t head0 = t / LPH, head_step = g.team_threads / LPH;
     const bool rotary = kFullRot || l < rot_lanes;
@@ -423,13 +445,13 @@ qk_norm_rope_stream_kernel(const qk_dev_args a, const qk_stream_geom g) {
         // team's first threads read it now and write it after the barrier, when thread 0 has
         // published the row's address.
         uint4 v_reg[kQkVRegs];
-        if (has_v) {
+        if (has_v || fp8_cache) {
             if (t == 0u) {
                 v_base_sh[i & 1u] = (pb_cur >= 0 && (uint32_t)pb_cur < a.n_blocks)
                         ? (((uint64_t)pb_cur * a.n_layers + a.layer) * a.block_tokens + pos_cur % a.block_tokens) * a.pool_stride
                         : ~0ull;
             }
-            if (v_in_regs) {
+            if (has_v && v_in_regs) {
 #pragma unroll
                 for (uint32_t c = 0; c < kQkVRegs; ++c) {
                     const uint32_t q = t + c * g.team_threads;
@@ -464,21 +486,47 @@ qk_norm_rope_stream_kernel(const qk_dev_args a, const qk_stream_geom g) {
         fence_async_shared();
         team_sync(team, g.team_threads);
 
-        if (has_v && !faulted) {
+        if ((has_v || fp8_cache) && !faulted) {
             const unsigned long long v_base = v_base_sh[i & 1u];  // element index of the row in the pools
-            if (v_base != ~0ull) {
-                uint4 *dst = reinterpret_cast<uint4 *>(reinterpret_cast<uint16_t *>(a.v_pool) + v_base);
-                if (v_in_regs) {
+            if (v_base != ~0ull && has_v) {
+                if (fp8_cache) {
+                    uint2 *dst = reinterpret_cast<uint2 *>(reinterpret_cast<uint8_t *>(a.v_pool) + v_base);
+                    if (v_in_regs) {
 #pragma unroll
-                    for (uint32_t c = 0; c < kQkVRegs; ++c) {
-                        const uint32_t q = t + c * g.team_threads;
-                        if (q < v_chunks) st_stream(dst + q, v_reg[c]);
+                        for (uint32_t c = 0; c < kQkVRegs; ++c) {
+                            const uint32_t q = t + c * g.team_threads;
+                            if (q < v_chunks) st_stream(dst + q, bf16x8_to_e4m3x8(v_reg[c]));
+                        }
+                    } else {
+                        for (uint32_t q = t; q < v_chunks; q += g.team_threads) {
+                            st_stream(dst + q, bf16x8_to_e4m3x8(ld_stream(a.v + (uint64_t)tok * v_chunks + q)));
+                        }
                     }
                 } else {
-                    for (uint32_t q = t; q < v_chunks; q += g.team_threads) {
-                        st_stream(dst + q, ld_stream(a.v + (uint64_t)tok * v_chunks + q));
+                    uint4 *dst = reinterpret_cast<uint4 *>(reinterpret_cast<uint16_t *>(a.v_pool) + v_base);
+                    if (v_in_regs) {
+#pragma unroll
+                        for (uint32_t c = 0; c < kQkVRegs; ++c) {
+                            const uint32_t q = t + c * g.team_threads;
+                            if (q < v_chunks) st_stream(dst + q, v_reg[c]);
+                        }
+                    } else {
+                        for (uint32_t q = t; q < v_chunks; q += g.team_threads) {
+                            st_stream(dst + q, ld_stream(a.v + (uint64_t)tok * v_chunks + q));
+                        }
                     }
                 }
+            }
+            if (fp8_cache) {
+                // the rotated K row sits in the slot as BF16 (it leaves as such for k_out): its E4M3
+                // image for the cache is produced here, 8 values per thread
+                if (v_base != ~0ull && a.k_pool) {
+                    const uint4 *k_sh = reinterpret_cast<const uint4 *>(slot + q_bytes);
+                    uint2 *dst = reinterpret_cast<uint2 *>(reinterpret_cast<uint8_t *>(a.k_pool) + v_base);
+                    for (uint32_t q = t; q < v_chunks; q += g.team_threads) st_stream(dst + q, bf16x8_to_e4m3x8(k_sh[q]));
+                }
+                // with one or two slots thread 0 refills THIS slot below: everyone has to be done reading it
+                if (g.slots <= 2u) team_sync(team, g.team_threads);
             }
         }
         if (t == 0u && !faulted) {
@@ -489,7 +537,7 @@ qk_norm_rope_stream_kernel(const qk_dev_args a, const qk_stream_geom g) {
                 if (pb_cur >= 0 && (uint32_t)pb_cur < a.n_blocks) {
                     const uint64_t base = ((((uint64_t)pb_cur * a.n_layers + a.layer) * a.block_tokens +
                                             pos_cur % a.block_tokens) * a.pool_stride) * 2u;
-                    if (k_bytes) bulk_store(reinterpret_cast<uint8_t *>(a.k_pool) + base, src + q_bytes, k_bytes);
+                    if (k_bytes && !fp8_cache) bulk_store(reinterpret_cast<uint8_t *>(a.k_pool) + base, src + q_bytes, k_bytes);
                 } else if (a.status_word) {
                     atomicCAS(a.status_word, AXIOM_STATUS_WORD_OK, AXIOM_STATUS_WORD_BAD_ADDRESS);
                 }

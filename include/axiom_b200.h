@@ -218,6 +218,8 @@ float axiom_qwen38_fused_yarn_mscale(float factor);
  * k_out (optional) also receives rotated K contiguously. */
 #define AXIOM_QK_FLAG_RING 1u            /* logical block index wraps modulo tbl_stride */
 #define AXIOM_QK_FLAG_PER_TOKEN_TABLE 2u /* token t uses block-table row t (batched decode); else row 0 (one sequence) */
+#define AXIOM_QK_FLAG_CACHE_E4M3 4u      /* k_pool / v_pool hold E4M3 codes at scale 1 (one byte per element) instead of
+                                          * BF16: qwen38_kv_store_e4m3fn_scale1, src/axiom_qwen38_attention.cu:245-281 */
 typedef struct {
     uint32_t abi_version;     /* AXIOM_ABI_VERSION */
     uint32_t struct_size;     /* sizeof(axiom_qk_rope_args) */
@@ -243,7 +245,7 @@ typedef struct {
     const float *inv_freq;    /* [rope_dim/2] */
     const uint32_t *positions;/* [tokens] */
     const int32_t *block_tables;
-    void *k_pool_bf16;        /* optional; NULL = no cache write */
+    void *k_pool_bf16;        /* optional; NULL = no cache write.  BF16, or E4M3 bytes with AXIOM_QK_FLAG_CACHE_E4M3 */
     void *v_pool_bf16;        /* optional */
     void *k_out_bf16;         /* optional */
     uint32_t *status_word;    /* optional */

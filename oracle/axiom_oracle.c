@@ -624,6 +624,19 @@ int axo_qk_norm_rope_paged_bf16(const axo_qk_params *p, uint16_t *q, const uint1
     return AXO_OK;
 }
 
+/* E4M3 image of BF16 cache rows at scale 1: qwen38_kv_encode_e4m3fn_scale1
+ * (reference src/axiom_qwen38_attention.cu:245-248) applied to BF16-valued floats. */
+int axo_bf16_to_e4m3_scale1(const uint16_t *in, uint8_t *out, uint64_t count) {
+    if (!in || !out) return AXO_INVALID;
+    for (uint64_t i = 0; i < count; ++i) {
+        uint32_t bits = (uint32_t)in[i] << 16;
+        float f;
+        memcpy(&f, &bits, sizeof f);
+        out[i] = axo_e4m3_encode_satfinite(f);
+    }
+    return AXO_OK;
+}
+
 /* ------------------------------------------------------------------ */
 /* embedding gather                                                    */
 /* ------------------------------------------------------------------ */

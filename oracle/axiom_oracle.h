@@ -121,6 +121,9 @@ int axo_qk_norm_rope_paged_bf16(const axo_qk_params *p, uint16_t *q, const uint1
                                 uint16_t *k_pool, uint16_t *v_pool, uint16_t *k_out,
                                 uint32_t *status);
 
+/* E4M3 codes (scale 1, saturating) of BF16 values: the FP8 flavour of the KV cache */
+int axo_bf16_to_e4m3_scale1(const uint16_t *in, uint8_t *out, uint64_t count);
+
 /* ---- embedding gather ---- */
 int axo_embedding_gather_bf16(const uint16_t *table, uint32_t vocab, uint32_t hidden,
                               const uint32_t *ids, uint32_t tokens, uint16_t *out);

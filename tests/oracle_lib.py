@@ -244,6 +244,13 @@ def qk_norm_rope_paged(q_bits, k_bits, v_bits, q_gamma, k_gamma, inv_freq, posit
     return q_out, k_out, int(status[0])
 
 
+def bf16_to_e4m3_scale1(bits):
+    flat = np.ascontiguousarray(bits).reshape(-1)
+    out = np.empty(flat.size, np.uint8)
+    _ok(o().axo_bf16_to_e4m3_scale1(_p(flat), _p(out), C.c_uint64(flat.size)), "bf16_to_e4m3_scale1")
+    return out.reshape(bits.shape)
+
+
 def embedding_gather_bf16(table_bits, ids):
     vocab, hidden = table_bits.shape
     out = np.empty((ids.shape[0], hidden), np.uint16)

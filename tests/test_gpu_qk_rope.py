@@ -36,7 +36,7 @@ def tolerance(q_in, gamma, inv_freq, positions, rope_dim, mscale, eps=1e-6):
 
 def run_case(axk, tokens, q_heads, k_heads, head_dim, rope_dim, *, n_blocks=64, block_tokens=16, n_layers=2, layer=1,
              pool_pad=0, ring=True, per_token=False, with_v=True, theta=1e6, factor=4.0, ctx=32768.0, max_base=100000,
-             seed=3):
+             seed=3, fp8_cache=False):
     import torch
     from gpu_util import Guarded, dev, host, sync
 
@@ -54,13 +54,15 @@ def run_case(axk, tokens, q_heads, k_heads, head_dim, rope_dim, *, n_blocks=64, 
     kv_dim = k_heads * head_dim
     pool_stride = kv_dim + pool_pad
     pool_elems = n_blocks * n_layers * block_tokens * pool_stride
-    k_pool, v_pool = Guarded(pool_elems * 2), Guarded(pool_elems * 2)
+    cell = 1 if fp8_cache else 2  # bytes per cache element
+    k_pool, v_pool = Guarded(pool_elems * cell), Guarded(pool_elems * cell)
     k_out = Guarded(tokens * kv_dim * 2)
     qd, kd, vd = dev(q), dev(k), dev(v)
     # every device tensor is named: the argument struct only carries raw addresses
     qgd, kgd, fd, pd, td = dev(qg), dev(kg), dev(inv_freq), dev(positions), dev(table)
     status = torch.zeros(1, dtype=torch.int32, device="cuda")
-    flags = (axk.QK_FLAG_RING if ring else 0) | (axk.QK_FLAG_PER_TOKEN_TABLE if per_token else 0)
+    flags = ((axk.QK_FLAG_RING if ring else 0) | (axk.QK_FLAG_PER_TOKEN_TABLE if per_token else 0) |
+             (axk.QK_FLAG_CACHE_E4M3 if fp8_cache else 0))
     args = axk.make_qk_args(tokens=tokens, q_heads=q_heads, k_heads=k_heads, head_dim=head_dim, rope_dim=rope_dim,
                             flags=flags, eps=1e-6, mscale=mscale, block_tokens=block_tokens, n_layers=n_layers,
                             layer=layer, pool_stride=pool_stride, tbl_stride=table.shape[1], n_blocks=n_blocks,
@@ -93,7 +95,7 @@ def run_case(axk, tokens, q_heads, k_heads, head_dim, rope_dim, *, n_blocks=64, 
             assert np.array_equal(got[..., rope_dim:], want[..., rope_dim:])
 
     # paged scatter: exactly the oracle's cells were written, with this kernel's own K rows; V is a copy
-    got_kpool, got_vpool = k_pool.payload(np.uint16), v_pool.payload(np.uint16)
+    got_kpool, got_vpool = k_pool.payload(np.uint8 if fp8_cache else np.uint16), v_pool.payload(np.uint8 if fp8_cache else np.uint16)
     written = o_kpool != 0xFFFF
     expect_kpool = np.full(pool_elems, 0xFFFF, np.uint16)
     for t in range(tokens):
@@ -106,6 +108,16 @@ def run_case(axk, tokens, q_heads, k_heads, head_dim, rope_dim, *, n_blocks=64, 
             continue
         base = ((pb * n_layers + layer) * block_tokens + pos % block_tokens) * pool_stride
         expect_kpool[base:base + kv_dim] = got_k[t].reshape(-1)
+    if fp8_cache:
+        # E4M3 cache: every written cell is the saturating E4M3 code (scale 1) of the BF16 value, the rest keeps
+        # the guard pattern 0xFF
+        assert np.array_equal(got_kpool, np.where(written, ol.bf16_to_e4m3_scale1(expect_kpool), 0xFF).astype(np.uint8))
+        if with_v:
+            v_written = o_vpool != 0xFFFF
+            assert np.array_equal(got_vpool, np.where(v_written, ol.bf16_to_e4m3_scale1(o_vpool), 0xFF).astype(np.uint8))
+        else:
+            assert v_pool.untouched()
+        return got_q, got_k
     assert np.array_equal(got_kpool, expect_kpool)
     assert np.array_equal(got_kpool != 0xFFFF, written)
     if with_v:
@@ -150,6 +162,15 @@ def test_streaming_kernel_variants(axk, cuda_device):
     run_case(axk, 400, 8, 2, 128, 128, with_v=False, n_blocks=64, max_base=300)
     run_case(axk, 333, 64, 8, 128, 128, per_token=True, n_blocks=128)
     run_case(axk, 300, 16, 4, 128, 128, ring=False, n_blocks=16, max_base=100)  # half the tokens fall off the table
+
+
+@pytest.mark.parametrize("tokens", [9, 64, 333, 597])
+def test_e4m3_cache_flavour(axk, cuda_device, tokens):
+    """K and V go to an FP8 cache as E4M3 codes at scale 1; Q and k_out stay BF16."""
+    run_case(axk, tokens, 64, 8, 128, 128, n_blocks=1024, n_layers=1, layer=0, fp8_cache=True, max_base=4000)
+    run_case(axk, tokens, 24, 4, 256, 64, n_blocks=256, n_layers=2, layer=1, pool_pad=64, fp8_cache=True, max_base=900,
+             theta=1e7, ctx=262144.0)
+    run_case(axk, tokens, 8, 2, 128, 128, n_blocks=64, fp8_cache=True, with_v=False, max_base=300)
 
 
 def test_streaming_and_per_token_kernels_agree_bitwise(axk, cuda_device):

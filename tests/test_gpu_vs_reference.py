@@ -180,6 +180,23 @@ def test_yarn_table_and_qk_norm_rope_bit_exact(axk, cuda_device):
         assert np.array_equal(host(qd, np.uint16).reshape(q.shape), ref_q), base
         assert np.array_equal(host(k_out, np.uint16).reshape(k.shape), ref_k), base
         assert np.array_equal(ref_v, v)
+    # FP8 cache flavour against the reference's own E4M3 cache rows (positions 0..7 of one 8-token block)
+    q, k, v, qg, kg = rc.qk_inputs(seed=0)
+    ref_q, ref_k, ref_v, ref_kcache = rc.qk_temporal8(q, k, v, qg, kg, 0)
+    qd, kd, vd, qgd, kgd = dev(q), dev(k), dev(v), dev(qg), dev(kg)
+    k_cache = torch.zeros((8, 1024), dtype=torch.uint8, device="cuda")
+    v_cache = torch.zeros((8, 1024), dtype=torch.uint8, device="cuda")
+    table = dev(np.zeros((1, 1), np.int32))
+    positions = dev(np.arange(8, dtype=np.uint32))
+    args = axk.make_qk_args(tokens=8, q_heads=24, k_heads=4, head_dim=256, rope_dim=64, eps=1e-6, mscale=rc.REF_MSCALE,
+                            flags=axk.QK_FLAG_CACHE_E4M3, block_tokens=8, n_layers=1, layer=0, pool_stride=1024,
+                            tbl_stride=1, n_blocks=1, q=qd, k=kd, v=vd, q_gamma=qgd, k_gamma=kgd, inv_freq=inv,
+                            positions=positions, block_tables=table, k_pool=k_cache, v_pool=v_cache)
+    assert axk.qk_norm_rope_paged(0, args) == 0
+    sync()
+    assert np.array_equal(host(qd, np.uint16).reshape(q.shape), ref_q)
+    assert np.array_equal(k_cache.cpu().numpy(), ref_kcache)
+    assert np.array_equal(v_cache.cpu().numpy().reshape(-1), ol.bf16_to_e4m3_scale1(v).reshape(-1))
 
 
 def test_generic_f32_ops_bit_exact(axk, cuda_device):
