@@ -111,6 +111,7 @@ SIGNATURES = {
     "axiom_qwen38_fused_add_rmsnorm_nvfp4_bf16_device": (i32, [i32, vp, vp, vp, f32, u32, u32, f32, vp, vp, vp, u32, vp]),
     "axiom_qwen38_fused_swiglu_fp8_bf16_device": (i32, [i32, vp, u32, u32, vp, vp, vp]),
     "axiom_qwen38_fused_swiglu_nvfp4_bf16_device": (i32, [i32, vp, u32, u32, f32, vp, vp, u32, vp]),
+    "axiom_qwen38_fused_sigmoid_gate_nvfp4_bf16_device": (i32, [i32, vp, vp, u32, u32, f32, vp, vp, vp, u32, vp]),
     "axiom_qwen38_fused_fp8_quantize_bf16_device": (i32, [i32, vp, u32, u32, vp, vp, vp, vp]),
     "axiom_qwen38_fused_embedding_gather_bf16_device": (i32, [i32, vp, u32, u32, vp, u32, vp, vp, vp]),
     "axiom_qwen38_fused_yarn_inv_freq_device": (i32, [i32, C.POINTER(RopeConfig), vp, vp]),
@@ -206,6 +207,12 @@ def swiglu_fp8(device, gate_up, rows, width, codes, scales, stream=None):
 def swiglu_nvfp4(device, gate_up, rows, width, global_scale, codes, scales, layout=SCALE_CANONICAL, stream=None):
     return lib().axiom_qwen38_fused_swiglu_nvfp4_bf16_device(
         device, _ptr(gate_up), rows, width, global_scale, _ptr(codes), _ptr(scales), layout, _stream_handle(stream))
+
+
+def sigmoid_gate_nvfp4(device, attention, gate, rows, width, G, out_bf16, codes, scales, layout=SCALE_CANONICAL, stream=None):
+    return lib().axiom_qwen38_fused_sigmoid_gate_nvfp4_bf16_device(device, _ptr(attention), _ptr(gate), rows, width, G,
+                                                                   _ptr(out_bf16), _ptr(codes), _ptr(scales), layout,
+                                                                   _stream_handle(stream))
 
 
 def fp8_quantize(device, x_bf16, rows, cols, codes, scales, status_word=None, stream=None):

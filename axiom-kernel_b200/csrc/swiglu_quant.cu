@@ -37,6 +37,14 @@ __device__ __forceinline__ void unpack8(const uint4 &v, float (&x)[8]) {
 
 __device__ __forceinline__ float silu(float g) { return __fdiv_rn(g, __fadd_rn(1.0f, expf(-g))); }
 __device__ __forceinline__ float silu_mul(float g, float u) { return __fmul_rn(silu(g), u); }
+// 1.0f / (1.0f + expf(-g)): the output gate of the attention block
+// (qwen38_sigmoid_gate_kernel, src/axiom_qwen38_attention.cu:470-479)
+__device__ __forceinline__ float sigmoid(float g) { return __fdiv_rn(1.0f, __fadd_rn(1.0f, expf(-g))); }
+
+// The function of the BF16 gate that a table holds.
+enum class gate_fn { silu, sigmoid };
+template <gate_fn kFn>
+__device__ __forceinline__ float gate_value(float g) { return kFn == gate_fn::silu ? silu(g) : sigmoid(g); }
 
 // ---- shared-memory silu table -------------------------------------------------------------
 // 64 binades (2^-57 .. 2^7) x 128 mantissas x 2 signs = 16384 floats.  Byte offset of a BF16
@@ -49,27 +57,31 @@ constexpr uint32_t kSiluTableBytes = 2u * 8192u * sizeof(float);
 
 constexpr uint32_t kSiluEntries = 16384u;
 
-__device__ __forceinline__ float silu_table_entry(uint32_t i) {
+template <gate_fn kFn>
+__device__ __forceinline__ float gate_table_entry(uint32_t i) {
     const uint32_t bits = ((i >> 13) << 15) | (kSiluFirst + (i & 8191u));
-    return silu(__uint_as_float(bits << 16));
+    return gate_value<kFn>(__uint_as_float(bits << 16));
 }
 
-// The per-device copy of the table (filled once by silu_table_fill_kernel) and its host-side state.
+// The per-device copies of the tables (each filled once by gate_table_fill_kernel).
 static __device__ __align__(256) float g_silu_table[kSiluEntries];
+static __device__ __align__(256) float g_sigmoid_table[kSiluEntries];
 
-__global__ void silu_table_fill_kernel(float *table) {
+template <gate_fn kFn>
+__global__ void gate_table_fill_kernel(float *table) {
     const uint32_t i = blockIdx.x * blockDim.x + threadIdx.x;
-    if (i < kSiluEntries) table[i] = silu_table_entry(i);
+    if (i < kSiluEntries) table[i] = gate_table_entry<kFn>(i);
 }
 
 // Shared-memory table of a CTA: copied from the device table, or computed here when there is none yet.
+template <gate_fn kFn = gate_fn::silu>
 __device__ __forceinline__ void build_silu_table(float *table, const float *device_table) {
     if (device_table) {
         const uint4 *src = reinterpret_cast<const uint4 *>(device_table);
         uint4 *dst = reinterpret_cast<uint4 *>(table);
         for (uint32_t i = threadIdx.x; i < kSiluEntries / 4u; i += blockDim.x) dst[i] = __ldg(src + i);
     } else {
-        for (uint32_t i = threadIdx.x; i < kSiluEntries; i += blockDim.x) table[i] = silu_table_entry(i);
+        for (uint32_t i = threadIdx.x; i < kSiluEntries; i += blockDim.x) table[i] = gate_table_entry<kFn>(i);
     }
     __syncthreads();
 }
@@ -97,8 +109,8 @@ __device__ __forceinline__ float2 silu_lookup2(const float *table, uint32_t w, u
     return make_float2(*reinterpret_cast<const float *>(base + olo), *reinterpret_cast<const float *>(base + ohi));
 }
 
-// y[0..7] = silu(gate) * up for one 16-byte chunk of each
-template <bool kTable>
+// y[0..7] = f(gate) * other for one 16-byte chunk of each; f = silu (SwiGLU) or sigmoid (output gate)
+template <bool kTable, gate_fn kFn = gate_fn::silu>
 __device__ __forceinline__ void swiglu8(const float *table, const uint4 &g, const uint4 &u, float (&y)[8]) {
     if (kTable) {
         uint32_t outside = 0u;
@@ -112,14 +124,14 @@ __device__ __forceinline__ void swiglu8(const float *table, const uint4 &g, cons
             unpack8(g, gv);
             unpack8(u, uv);
 #pragma unroll
-            for (int i = 0; i < 8; ++i) y[i] = silu_mul(gv[i], uv[i]);
+            for (int i = 0; i < 8; ++i) y[i] = __fmul_rn(gate_value<kFn>(gv[i]), uv[i]);
         }
     } else {
         float gv[8], uv[8];
         unpack8(g, gv);
         unpack8(u, uv);
 #pragma unroll
-        for (int i = 0; i < 8; ++i) y[i] = silu_mul(gv[i], uv[i]);
+        for (int i = 0; i < 8; ++i) y[i] = __fmul_rn(gate_value<kFn>(gv[i]), uv[i]);
     }
 }
 
@@ -264,16 +276,23 @@ constexpr uint32_t kNvUnroll = 2u;  // warp tiles in flight per iteration
 // A warp tile is 32 consecutive chunks of one row (column group `col` of `col_groups`); a warp
 // takes tiles warp, warp + W, ... and advances (row, col) incrementally, so no division runs
 // inside the loop.  step_rows = W / col_groups and step_cols = W % col_groups come from the host.
-template <bool kTable>
+//
+// kFn = silu: y = silu(gate) * up, never rounded, rows of `in` are [gate | up].
+// kFn = sigmoid: y = bf16(attention * sigmoid(gate)) (qwen38_sigmoid_gate_kernel, src/axiom_qwen38_attention.cu:
+// 470-479: the product is rounded to BF16 before anything consumes it), `in` holds the gates and `other` the
+// attention output, both [rows x chunks]; y is optionally written out as BF16 as well.
+template <bool kTable, gate_fn kFn>
 __global__ void __launch_bounds__(kNvThreads)
-swiglu_nvfp4_kernel(const uint4 *__restrict__ in, uint32_t rows, uint32_t chunks, uint32_t col_groups,
-                    uint32_t step_rows, uint32_t step_cols, float G, uint32_t *__restrict__ codes,
+swiglu_nvfp4_kernel(const uint4 *__restrict__ in, const uint4 *__restrict__ other, uint32_t row_stride,
+                    uint32_t rows, uint32_t chunks, uint32_t col_groups,
+                    uint32_t step_rows, uint32_t step_cols, float G, uint4 *__restrict__ out_bf16,
+                    uint32_t *__restrict__ codes,
                     uint8_t *__restrict__ scales, uint32_t layout, uint32_t groups, uint32_t inner_tiles,
                     const float *__restrict__ device_table) {
     extern __shared__ __align__(16) float silu_table[];
     __shared__ scale_lut_entry lut[128];
     allow_dependents();
-    if (kTable) build_silu_table(silu_table, device_table);  // the device table never changes once filled
+    if (kTable) build_silu_table<kFn>(silu_table, device_table);  // the device table never changes once filled
     const bool lut_safe = build_scale_lut(lut, G);
     dependency_wait();
     const uint32_t lane = threadIdx.x & 31u;
@@ -288,9 +307,9 @@ swiglu_nvfp4_kernel(const uint4 *__restrict__ in, uint32_t rows, uint32_t chunks
             rws[j] = row;
             qs[j] = col * 32u + lane;
             oks[j] = row < rows && qs[j] < chunks;
-            const uint4 *gate = in + (uint64_t)row * 2u * chunks + qs[j];
-            g[j] = oks[j] ? ld_stream(gate) : make_uint4(0u, 0u, 0u, 0u);
-            u[j] = oks[j] ? ld_stream(gate + chunks) : make_uint4(0u, 0u, 0u, 0u);
+            const uint64_t at = (uint64_t)row * row_stride + qs[j];
+            g[j] = oks[j] ? ld_stream(in + at) : make_uint4(0u, 0u, 0u, 0u);
+            u[j] = oks[j] ? ld_stream(other + at) : make_uint4(0u, 0u, 0u, 0u);
             row += step_rows;
             col += step_cols;
             if (col >= col_groups) {
@@ -301,7 +320,14 @@ swiglu_nvfp4_kernel(const uint4 *__restrict__ in, uint32_t rows, uint32_t chunks
 #pragma unroll
         for (uint32_t j = 0; j < kNvUnroll; ++j) {
             float y[8];
-            swiglu8<kTable>(silu_table, g[j], u[j], y);
+            swiglu8<kTable, kFn>(silu_table, g[j], u[j], y);
+            if (kFn == gate_fn::sigmoid) {
+                // the gated value exists in BF16 only: round, optionally store, and quantize the rounded values
+                const uint4 r = make_uint4(pack_bf16x2(y[0], y[1]), pack_bf16x2(y[2], y[3]), pack_bf16x2(y[4], y[5]),
+                                           pack_bf16x2(y[6], y[7]));
+                if (out_bf16 && oks[j]) st_stream(out_bf16 + (uint64_t)rws[j] * chunks + qs[j], r);
+                unpack8(r, y);
+            }
             float m = absmax8_nan(y);
             m = max_nan(m, __shfl_xor_sync(0xffffffffu, m, 1));
             uint32_t scale_code;
@@ -312,7 +338,7 @@ swiglu_nvfp4_kernel(const uint4 *__restrict__ in, uint32_t rows, uint32_t chunks
                 m = fmaxf(fmaxf(m, __shfl_xor_sync(0xffffffffu, m, 1)), 0.0f);
                 packed = nvfp4_quantize8_exact(y[0], y[1], y[2], y[3], y[4], y[5], y[6], y[7], m, G, &scale_code);
             }
-            if (oks[j]) {
+            if (oks[j] && codes) {
                 st_stream(codes + (uint64_t)rws[j] * chunks + qs[j], packed);
                 if ((lane & 1u) == 0u) {
                     scales[scale_offset(rws[j], qs[j] >> 1, groups, inner_tiles, layout)] = (uint8_t)scale_code;
@@ -351,7 +377,8 @@ row_shape pick_row_shape(uint32_t chunks) {
 // other stream may use the table afterwards.  Returns nullptr (each CTA then fills its own
 // shared-memory copy) when the table is not ready and cannot be made ready here: `stream` is
 // being captured (a synchronisation would invalidate the capture), or the driver refused.
-const float *device_silu_table(cudaStream_t stream) {
+template <gate_fn kFn>
+const float *device_gate_table(cudaStream_t stream) {
     static const float *ready[64] = {};
     int dev = 0;
     if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return nullptr;
@@ -362,11 +389,13 @@ const float *device_silu_table(cudaStream_t stream) {
         return nullptr;
     }
     float *table = nullptr;
-    if (cudaGetSymbolAddress((void **)&table, g_silu_table) != cudaSuccess || !table) {
+    const cudaError_t found = kFn == gate_fn::silu ? cudaGetSymbolAddress((void **)&table, g_silu_table)
+                                                   : cudaGetSymbolAddress((void **)&table, g_sigmoid_table);
+    if (found != cudaSuccess || !table) {
         cudaGetLastError();
         return nullptr;
     }
-    silu_table_fill_kernel<<<kSiluEntries / 256u, 256, 0, stream>>>(table);
+    gate_table_fill_kernel<kFn><<<kSiluEntries / 256u, 256, 0, stream>>>(table);
     if (cudaGetLastError() != cudaSuccess || cudaStreamSynchronize(stream) != cudaSuccess) {
         cudaGetLastError();
         return nullptr;
@@ -375,6 +404,8 @@ const float *device_silu_table(cudaStream_t stream) {
     ready[dev] = table;
     return table;
 }
+
+const float *device_silu_table(cudaStream_t stream) { return device_gate_table<gate_fn::silu>(stream); }
 
 template <row_op kOp>
 int launch_fp8_rows(const void *in, uint32_t rows, uint32_t width, uint32_t in_chunks_per_row, uint8_t *codes,
@@ -434,39 +465,54 @@ int launch_fp8_quantize_bf16(const void *input, uint32_t rows, uint32_t cols, ui
     return launch_fp8_rows<row_op::plain_finite_only>(input, rows, cols, cols / 8u, codes, scales, status_word, stream);
 }
 
-int launch_swiglu_nvfp4_bf16(const void *gate_up, uint32_t rows, uint32_t width, float G, uint8_t *codes,
-                             uint8_t *scales, uint32_t layout, cudaStream_t stream) {
+// Shared launcher of the two gated NVFP4 ops.  `gate` / `other` are the two operand planes, row_stride their row
+// pitch in 16-byte chunks.
+template <gate_fn kFn>
+int launch_gated_nvfp4(const uint4 *gate, const uint4 *other, uint32_t row_stride, uint32_t rows, uint32_t width, float G,
+                       void *out_bf16, uint8_t *codes, uint8_t *scales, uint32_t layout, cudaStream_t stream) {
     const uint32_t chunks = width / 8u;
     const uint32_t groups = width / kGroup;
     const uint32_t col_groups = (chunks + 31u) / 32u;
     const uint64_t tiles = (uint64_t)rows * col_groups;
     const uint32_t warps_per_block = kNvThreads / 32u;
-    const float *device_table = rows >= kCopiedTableMinRows ? device_silu_table(stream) : nullptr;
+    const float *device_table = rows >= kCopiedTableMinRows ? device_gate_table<kFn>(stream) : nullptr;
     const bool table = rows >= kTableMinRows || device_table != nullptr;
     // table flavour: persistent CTAs (the table is built once per CTA), two 512-thread CTAs with 64 KB each per SM
     const uint64_t cap = table ? kSmCount * 2u : kSmCount * 8u;
     uint64_t blocks = (tiles + warps_per_block - 1u) / warps_per_block;
     if (blocks > cap) blocks = cap;
     const uint32_t W = (uint32_t)blocks * warps_per_block;
-    const uint4 *src = (const uint4 *)gate_up;
     if (table) {
         static bool configured[64] = {};
         int dev = 0;
         cudaGetDevice(&dev);
         if (dev >= 0 && dev < 64 && !configured[dev]) {
-            cudaFuncSetAttribute(swiglu_nvfp4_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSiluTableBytes);
+            cudaFuncSetAttribute(swiglu_nvfp4_kernel<true, kFn>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSiluTableBytes);
             configured[dev] = true;
         }
-        launch_chained(swiglu_nvfp4_kernel<true>, dim3((uint32_t)blocks), dim3(kNvThreads), kSiluTableBytes, stream, 
-                src, rows, chunks, col_groups, W / col_groups, W % col_groups, G, (uint32_t *)codes, scales, layout, groups,
-                (groups + 3u) / 4u, device_table);
+        launch_chained(swiglu_nvfp4_kernel<true, kFn>, dim3((uint32_t)blocks), dim3(kNvThreads), kSiluTableBytes, stream,
+                       gate, other, row_stride, rows, chunks, col_groups, W / col_groups, W % col_groups, G, (uint4 *)out_bf16,
+                       (uint32_t *)codes, scales, layout, groups, (groups + 3u) / 4u, device_table);
     } else {
-        launch_chained(swiglu_nvfp4_kernel<false>, dim3((uint32_t)blocks), dim3(kNvThreads), 0, stream, 
-                src, rows, chunks, col_groups, W / col_groups, W % col_groups, G, (uint32_t *)codes, scales, layout, groups,
-                (groups + 3u) / 4u, nullptr);
+        launch_chained(swiglu_nvfp4_kernel<false, kFn>, dim3((uint32_t)blocks), dim3(kNvThreads), 0, stream,
+                       gate, other, row_stride, rows, chunks, col_groups, W / col_groups, W % col_groups, G, (uint4 *)out_bf16,
+                       (uint32_t *)codes, scales, layout, groups, (groups + 3u) / 4u, nullptr);
     }
     note_launch();
     return AXIOM_OK;
+}
+
+int launch_swiglu_nvfp4_bf16(const void *gate_up, uint32_t rows, uint32_t width, float G, uint8_t *codes,
+                             uint8_t *scales, uint32_t layout, cudaStream_t stream) {
+    const uint4 *gate = (const uint4 *)gate_up;
+    return launch_gated_nvfp4<gate_fn::silu>(gate, gate + width / 8u, 2u * (width / 8u), rows, width, G, nullptr, codes,
+                                             scales, layout, stream);
+}
+
+int launch_sigmoid_gate_nvfp4_bf16(const void *attention, const void *gate, uint32_t rows, uint32_t width, float G,
+                                   void *out_bf16, uint8_t *codes, uint8_t *scales, uint32_t layout, cudaStream_t stream) {
+    return launch_gated_nvfp4<gate_fn::sigmoid>((const uint4 *)gate, (const uint4 *)attention, width / 8u, rows, width, G,
+                                                out_bf16, codes, scales, layout, stream);
 }
 
 }  // namespace axb
@@ -511,5 +557,24 @@ extern "C" int axiom_qwen38_fused_swiglu_nvfp4_bf16_device(
     if (rc != AXIOM_OK) return rc;
     launch_swiglu_nvfp4_bf16(gate_up_bf16, rows, width, global_scale, out_codes, out_scales, scale_layout,
                              (cudaStream_t)stream);
+    return launch_status();
+}
+
+extern "C" int axiom_qwen38_fused_sigmoid_gate_nvfp4_bf16_device(
+        int device, const void *attention_bf16, const void *gate_bf16, uint32_t rows, uint32_t width, float global_scale,
+        void *out_bf16, uint8_t *out_codes, uint8_t *out_scales, uint32_t scale_layout, void *stream) {
+    if (!attention_bf16 || !gate_bf16 || rows == 0u || width == 0u || (width % kGroup) != 0u ||
+        scale_layout > AXIOM_SCALE_LAYOUT_TILED || !aligned16(attention_bf16) || !aligned16(gate_bf16) ||
+        (uint64_t)rows * (width / 8u) > 0xffffffffull) {
+        return AXIOM_ERR_INVALID_ARGUMENT;
+    }
+    if ((out_codes == nullptr) != (out_scales == nullptr)) return AXIOM_ERR_INVALID_ARGUMENT;
+    if (!out_codes && !out_bf16) return AXIOM_ERR_INVALID_ARGUMENT;
+    if (out_codes && (!valid_scale(global_scale) || (reinterpret_cast<uintptr_t>(out_codes) & 3u))) return AXIOM_ERR_INVALID_ARGUMENT;
+    if (out_bf16 && !aligned16(out_bf16)) return AXIOM_ERR_INVALID_ARGUMENT;
+    int rc = select_device(device);
+    if (rc != AXIOM_OK) return rc;
+    launch_sigmoid_gate_nvfp4_bf16(attention_bf16, gate_bf16, rows, width, out_codes ? global_scale : 1.0f, out_bf16, out_codes,
+                                   out_scales, scale_layout, (cudaStream_t)stream);
     return launch_status();
 }

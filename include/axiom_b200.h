@@ -179,6 +179,11 @@ int axiom_qwen38_fused_swiglu_fp8_bf16_device(int device, const void *gate_up_bf
  * (src/axiom_qwen38_nvfp4_mlp.cu:229-317).  width % 16 == 0. */
 int axiom_qwen38_fused_swiglu_nvfp4_bf16_device(int device, const void *gate_up_bf16, uint32_t rows, uint32_t width, float global_scale, uint8_t *out_codes, uint8_t *out_scales, uint32_t scale_layout, void *stream);
 
+/* Replaces qwen38_sigmoid_gate_kernel (src/axiom_qwen38_attention.cu:470-479) and the activation quantizer of
+ * the output projection that follows it: y = bf16(attention * (1/(1+expf(-gate)))), optionally written to out_bf16,
+ * and/or quantized to NVFP4 (both code outputs or neither).  attention, gate, out: [rows x width] BF16. width % 16 == 0. */
+int axiom_qwen38_fused_sigmoid_gate_nvfp4_bf16_device(int device, const void *attention_bf16, const void *gate_bf16, uint32_t rows, uint32_t width, float global_scale, void *out_bf16, uint8_t *out_codes, uint8_t *out_scales, uint32_t scale_layout, void *stream);
+
 /* Replaces quantize_bf16_rows_e4m3_kernel (src/axiom_qwen38_mtp_compute.cu:239-278)
  * and, for BF16-valued input, quantize_columns_e4m3_kernel.  status_word
  * (optional, device) receives AXIOM_STATUS_WORD_NONFINITE via compare-and-swap. cols % 8 == 0. */

@@ -449,6 +449,39 @@ int axo_swiglu_nvfp4_bf16(const uint16_t *gate_up, uint32_t rows, uint32_t width
     return AXO_OK;
 }
 
+/* Output gate of the attention block followed by the o_proj activation quantizer:
+ * y = bf16(attention * (1.0f / (1.0f + expf(-gate)))) (qwen38_sigmoid_gate_kernel, reference
+ * src/axiom_qwen38_attention.cu:470-479), then the NVFP4 quantizer on the BF16 values.
+ * out_bf16, codes/scales optional (codes and scales together). */
+int axo_sigmoid_gate_nvfp4_bf16(const uint16_t *attention, const uint16_t *gate, uint32_t rows,
+                                uint32_t width, float global_scale, uint16_t *out_bf16,
+                                uint8_t *codes, uint8_t *scales) {
+    if (!attention || !gate || rows == 0u || width == 0u || (width % 16u) != 0u ||
+        ((codes == NULL) != (scales == NULL)) || (!codes && !out_bf16) ||
+        (codes && !valid_scale(global_scale))) {
+        return AXO_INVALID;
+    }
+    const uint32_t groups = width / 16u;
+    AXO_PARALLEL_FOR
+    for (int64_t r = 0; r < (int64_t)rows; ++r) {
+        float y[16];
+        for (uint32_t g = 0; g < groups; ++g) {
+            for (int i = 0; i < 16; ++i) {
+                const size_t at = (size_t)r * width + 16u * g + i;
+                const float sig = 1.0f / (1.0f + expf(-axo_bf16_to_f32(gate[at])));
+                const uint16_t bits = axo_f32_to_bf16(axo_bf16_to_f32(attention[at]) * sig);
+                if (out_bf16) out_bf16[at] = bits;
+                y[i] = axo_bf16_to_f32(bits);
+            }
+            if (codes) {
+                nvfp4_group(y, global_scale, codes + (size_t)r * (width / 2u) + 8u * g,
+                            scales + (size_t)r * groups + g);
+            }
+        }
+    }
+    return AXO_OK;
+}
+
 /* ------------------------------------------------------------------ */
 /* YaRN frequencies                                                    */
 /* ------------------------------------------------------------------ */

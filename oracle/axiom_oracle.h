@@ -121,6 +121,11 @@ int axo_qk_norm_rope_paged_bf16(const axo_qk_params *p, uint16_t *q, const uint1
                                 uint16_t *k_pool, uint16_t *v_pool, uint16_t *k_out,
                                 uint32_t *status);
 
+/* y = bf16(attention * sigmoid(gate)), optional BF16 copy, optional NVFP4 quantize of y */
+int axo_sigmoid_gate_nvfp4_bf16(const uint16_t *attention, const uint16_t *gate, uint32_t rows,
+                                uint32_t width, float global_scale, uint16_t *out_bf16,
+                                uint8_t *codes, uint8_t *scales);
+
 /* E4M3 codes (scale 1, saturating) of BF16 values: the FP8 flavour of the KV cache */
 int axo_bf16_to_e4m3_scale1(const uint16_t *in, uint8_t *out, uint64_t count);
 

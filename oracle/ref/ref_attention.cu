@@ -38,3 +38,10 @@ extern "C" int ref_qk_norm_partial_rope_cache8(float *q, float *k, const float *
             max_context, position, yarn != 0, nullptr);
     return ref_done();
 }
+
+// attention, gate, out: F32 [8][6144] holding BF16 values (the reference's fixed batch of 8 token columns)
+extern "C" int ref_sigmoid_gate8(const float *attention, const float *gate, float *out) {
+    const uint64_t count = static_cast<uint64_t>(kQDim) * kBatch;
+    qwen38_sigmoid_gate_kernel<<<static_cast<uint32_t>((count + kThreads - 1u) / kThreads), kThreads>>>(attention, gate, out);
+    return ref_done();
+}

@@ -244,6 +244,16 @@ def qk_norm_rope_paged(q_bits, k_bits, v_bits, q_gamma, k_gamma, inv_freq, posit
     return q_out, k_out, int(status[0])
 
 
+def sigmoid_gate_nvfp4_bf16(attention_bits, gate_bits, G):
+    rows, width = attention_bits.shape
+    out = np.empty_like(attention_bits)
+    codes = np.empty((rows, width // 2), np.uint8)
+    scales = np.empty((rows, width // 16), np.uint8)
+    _ok(o().axo_sigmoid_gate_nvfp4_bf16(_p(attention_bits), _p(gate_bits), rows, width, C.c_float(G), _p(out), _p(codes),
+                                        _p(scales)), "sigmoid_gate_nvfp4_bf16")
+    return out, codes, scales
+
+
 def bf16_to_e4m3_scale1(bits):
     flat = np.ascontiguousarray(bits).reshape(-1)
     out = np.empty(flat.size, np.uint8)

@@ -22,6 +22,7 @@ SIGNATURES = {
     "ref_yarn_inv_frequency": [vp],
     "ref_qk_norm_partial_rope_cache_temporal8": [vp, vp, vp, vp, vp, vp, vp, vp, vp, u32, u32, i32],
     "ref_qk_norm_partial_rope_cache8": [vp, vp, vp, vp, vp, vp, vp, vp, vp, u32, u32, u32, i32],
+    "ref_sigmoid_gate8": [vp, vp, vp],
     "ref_rmsnorm_f32": [vp, vp, vp, u32, f32, i32],
     "ref_rmsnorm_f32_dual": [vp, vp, vp, vp, vp, u32, f32],
     "ref_head_rmsnorm_f32": [vp, u32, u32, f32],

@@ -163,3 +163,42 @@ def test_swiglu_flavours_agree_bitwise(axk, cuda_device):
 def test_config4_full_size_sample(axk, cuda_device):
     """T = 16384 is exercised at full width; the oracle checks a 512-row slab of it."""
     check_swiglu_fp8(axk, 512, 17408, seed=4)
+
+
+@pytest.mark.parametrize("rows,width,layout", [(1, 6144, 0), (8, 8192, 1), (3, 16, 0), (120, 6144, 1), (400, 2048, 0)])
+def test_sigmoid_gate_nvfp4(axk, cuda_device, rows, width, layout):
+    """y = bf16(attention * sigmoid(gate)) and its NVFP4 image vs the oracle: y within one BF16 ulp (device
+    expf), codes re-derived bit-exactly from the kernel's own y."""
+    import torch
+    from gpu_util import Guarded, dev, sync
+
+    rng = np.random.default_rng(rows * 7 + width)
+    attn = wl.to_bf16_bits(rng.standard_normal((rows, width), dtype=np.float32))
+    gate = wl.to_bf16_bits(rng.standard_normal((rows, width), dtype=np.float32) * np.float32(2.0))
+    want_y, _, _ = ol.sigmoid_gate_nvfp4_bf16(attn, gate, 1.0)
+    G = wl.nvfp4_global_scale(float(np.abs(wl.from_bf16_bits(want_y)).max()))
+    a, g = dev(attn), dev(gate)
+    y = Guarded(rows * width * 2)
+    codes = Guarded(rows * width // 2)
+    nscale = int(axk.lib().axiom_nvfp4_scale_plane_bytes(rows, width // 16, layout))
+    scales = Guarded(nscale)
+    if layout == 1:
+        scales.raw[scales.pad:scales.pad + nscale] = 0
+    assert axk.sigmoid_gate_nvfp4(0, a, g, rows, width, G, y.ptr, codes.ptr, scales.ptr, layout) == axk.AXIOM_OK
+    sync()
+    assert y.guards_intact() and codes.guards_intact() and scales.guards_intact()
+    got_y = y.payload(np.uint16).reshape(rows, width)
+    diff = np.abs(wl.from_bf16_bits(got_y) - wl.from_bf16_bits(want_y))
+    assert np.all(diff <= ol.bf16_ulp(np.abs(wl.from_bf16_bits(want_y))) * np.float32(1.01))
+    assert np.mean(got_y != want_y) < 5e-3
+    # the codes are the quantizer's image of the kernel's own BF16 values, bit for bit
+    want_codes, want_scales = ol.nvfp4_quantize_bf16(got_y, G)
+    want_plane = want_scales.reshape(-1) if layout == 0 else ol.scales_to_tiled(want_scales)
+    assert np.array_equal(codes.payload().reshape(rows, width // 2), want_codes)
+    assert np.array_equal(scales.payload(), want_plane)
+    # BF16-only and codes-only calls
+    y2 = torch.zeros((rows, width), dtype=torch.int16, device="cuda")
+    assert axk.sigmoid_gate_nvfp4(0, a, g, rows, width, G, y2, None, None, layout) == axk.AXIOM_OK
+    sync()
+    assert np.array_equal(y2.cpu().numpy().view(np.uint16), got_y)
+    assert axk.sigmoid_gate_nvfp4(0, a, g, rows, width, G, None, None, None, layout) == axk.AXIOM_ERR_INVALID_ARGUMENT

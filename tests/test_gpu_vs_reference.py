@@ -199,6 +199,33 @@ def test_yarn_table_and_qk_norm_rope_bit_exact(axk, cuda_device):
     assert np.array_equal(v_cache.cpu().numpy().reshape(-1), ol.bf16_to_e4m3_scale1(v).reshape(-1))
 
 
+def test_sigmoid_gate_bit_exact(axk, cuda_device):
+    """qwen38_sigmoid_gate_kernel on its fixed [8 x 6144] batch: the BF16 output must match bit for bit, also when the
+    same rows go through the tabulated flavour (a call of 8 x 50 rows takes the table path)."""
+    import torch
+    from gpu_util import dev, sync
+
+    r = ref_lib.lib()
+    rng = np.random.default_rng(12)
+    rows, width = 8, 6144
+    attn = wl.to_bf16_bits(rng.standard_normal((rows, width), dtype=np.float32))
+    gate = wl.to_bf16_bits(rng.standard_normal((rows, width), dtype=np.float32) * np.float32(3.0))
+    gate.reshape(-1)[:8] = wl.to_bf16_bits(np.array([0.0, -0.0, 90.0, -90.0, 200.0, -200.0, 1e-30, np.inf], np.float32))
+    a32 = torch.from_numpy(wl.from_bf16_bits(attn)).cuda()
+    g32 = torch.from_numpy(wl.from_bf16_bits(gate)).cuda()
+    out32 = torch.zeros_like(a32)
+    assert r.ref_sigmoid_gate8(a32.data_ptr(), g32.data_ptr(), out32.data_ptr()) == 0
+    want = wl.to_bf16_bits(out32.cpu().numpy())
+    assert np.array_equal(wl.from_bf16_bits(want), out32.cpu().numpy())  # the reference output is BF16-valued
+    for reps in (1, 50):
+        a, g = dev(np.tile(attn, (reps, 1))), dev(np.tile(gate, (reps, 1)))
+        y = torch.zeros((rows * reps, width), dtype=torch.int16, device="cuda")
+        assert axk.sigmoid_gate_nvfp4(0, a, g, rows * reps, width, 1.0, y, None, None, 0) == axk.AXIOM_OK
+        sync()
+        got = y.cpu().numpy().view(np.uint16)
+        assert np.array_equal(got[:rows], want) and np.array_equal(got[-rows:], want)
+
+
 def test_generic_f32_ops_bit_exact(axk, cuda_device):
     import torch
 
