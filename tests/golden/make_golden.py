@@ -127,6 +127,17 @@ def main():
     assert r.ref_silu_mul_f32(at.data_ptr(), bt.data_ptr(), ot.data_ptr(), 1000, 3.0) == 0
     fx["g_silu_mul_clamp3"] = ot.cpu().numpy()
 
+    # sigmoid output gate on the reference's fixed [8 x 6144] batch
+    sg_rng = np.random.default_rng(12)
+    attn = wl.to_bf16_bits(sg_rng.standard_normal((8, 6144), dtype=np.float32))
+    gate = wl.to_bf16_bits(sg_rng.standard_normal((8, 6144), dtype=np.float32) * np.float32(3.0))
+    gate.reshape(-1)[:8] = wl.to_bf16_bits(np.array([0.0, -0.0, 90.0, -90.0, 200.0, -200.0, 1e-30, np.inf], np.float32))
+    a32 = torch.from_numpy(wl.from_bf16_bits(attn)).cuda()
+    g32 = torch.from_numpy(wl.from_bf16_bits(gate)).cuda()
+    o32 = torch.zeros_like(a32)
+    assert r.ref_sigmoid_gate8(a32.data_ptr(), g32.data_ptr(), o32.data_ptr()) == 0
+    fx["sg_attention"], fx["sg_gate"], fx["sg_out"] = attn, gate, wl.to_bf16_bits(o32.cpu().numpy())
+
     path = out_dir / "reference_b200.npz"
     np.savez_compressed(path, **fx)
     print(f"wrote {path} ({path.stat().st_size} bytes, {len(fx)} arrays) on {torch.cuda.get_device_name(0)}")

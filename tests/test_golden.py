@@ -85,6 +85,22 @@ def test_yarn_table_and_qk_norm_rope(fx):
             assert np.mean(got != want) < 0.01
 
 
+def test_e4m3_cache_rows_bit_exact(fx):
+    """The reference's E4M3 (scale 1) cache rows are the saturating codes of its own rotated BF16 K rows."""
+    for tag in ("lo", "hi"):
+        want = fx[f"k_{tag}_k_e4m3"].reshape(-1)
+        assert np.array_equal(ol.bf16_to_e4m3_scale1(fx[f"k_{tag}_k_out"]).reshape(-1), want)
+
+
+def test_sigmoid_gate(fx):
+    got, _, _ = ol.sigmoid_gate_nvfp4_bf16(fx["sg_attention"], fx["sg_gate"], 1.0)
+    a, b = wl.from_bf16_bits(got), wl.from_bf16_bits(fx["sg_out"])
+    assert np.array_equal(np.isnan(a), np.isnan(b))
+    ok = ~np.isnan(b)
+    assert np.all(np.abs(a[ok] - b[ok]) <= ol.bf16_ulp(np.abs(b[ok])) * np.float32(1.01))  # libm vs device expf
+    assert np.mean(got != fx["sg_out"]) < 2e-3
+
+
 def test_generic_f32_ops(fx):
     x, w = fx["g_x"], fx["g_w"]
     for tag, tol in (("plain", 1e-3), ("hp", 2e-6), ("b1", 1e-3)):                  # fast-math unit: reference tolerance 1e-3

@@ -112,3 +112,32 @@ def test_yarn_table_and_qk_norm_rope(axk, cuda_device, fx):
         sync()
         assert np.array_equal(host(qd, np.uint16).reshape(8, 24, 256), fx[f"k_{tag}_q_out"])
         assert np.array_equal(host(k_out, np.uint16).reshape(8, 4, 256), fx[f"k_{tag}_k_out"])
+
+
+def test_sigmoid_gate_and_e4m3_cache(axk, cuda_device, fx):
+    import torch
+    from gpu_util import dev, sync
+
+    a, g = dev(fx["sg_attention"]), dev(fx["sg_gate"])
+    y = torch.zeros(fx["sg_out"].shape, dtype=torch.int16, device="cuda")
+    assert axk.sigmoid_gate_nvfp4(0, a, g, 8, 6144, 1.0, y, None, None, 0) == 0
+    sync()
+    assert np.array_equal(y.cpu().numpy().view(np.uint16), fx["sg_out"])
+    # E4M3 cache rows of the reference for the "lo" q/k case (positions base..base+7 -> one 8-token block)
+    inv = dev(fx["y_inv_freq"])
+    qd, kd, qgd, kgd = dev(fx["k_lo_q"]), dev(fx["k_lo_k"]), dev(fx["k_lo_qg"]), dev(fx["k_lo_kg"])
+    base = int(fx["k_lo_base"])
+    positions = dev((base + np.arange(8)).astype(np.uint32))
+    table = dev(np.zeros((1, (base + 8) // 8 + 1), np.int32))
+    k_cache = torch.zeros((8, 1024), dtype=torch.uint8, device="cuda")
+    args = axk.make_qk_args(tokens=8, q_heads=24, k_heads=4, head_dim=256, rope_dim=64, eps=1e-6,
+                            mscale=float(np.float32(1.138629436111989)), flags=axk.QK_FLAG_CACHE_E4M3 | axk.QK_FLAG_RING,
+                            block_tokens=8, n_layers=1, layer=0, pool_stride=1024, tbl_stride=1, n_blocks=1, q=qd, k=kd,
+                            q_gamma=qgd, k_gamma=kgd, inv_freq=inv, positions=positions, block_tables=table, k_pool=k_cache)
+    assert axk.qk_norm_rope_paged(0, args) == 0
+    sync()
+    got = k_cache.cpu().numpy()
+    want = fx["k_lo_k_e4m3"]
+    # with an 8-token block and a one-entry ring, position p lands in row p % 8
+    rows = [(base + t) % 8 for t in range(8)]
+    assert np.array_equal(got[rows], want)
