@@ -322,7 +322,7 @@ qk_norm_rope_paged_kernel(const qk_dev_args a) {
 // ---------------------------------------------------------------------------
 constexpr uint32_t kQkMaxSlots = 4u;
 constexpr uint32_t kQkVRegs = 2u;  // 16-byte V chunks a thread carries across the token's barrier
-constexpr uint32_t kQkStreamThreads = 768u;  // 24 warps: leaves 80 registers per thread
+constexpr uint32_t kQkStreamThreads = 896u;  // 28 warps: leaves 72 registers per thread
 
 struct qk_stream_geom {
     uint32_t team_threads, teams, slots, slot_bytes;
@@ -346,11 +346,18 @@ qk_norm_rope_stream_kernel(const qk_dev_args a, const qk_stream_geom g) {
     const bool has_v = a.v != nullptr && a.v_pool != nullptr;
     const uint32_t v_chunks = a.k_heads * LPH;  // 16-byte chunks of a V row
 
-    // [teams][slots][slot_bytes] | gq[D] gk[D] | per team: 2 x (cos, sin, -sin)[D/2] | barriers
+    // [teams][slots][slot_bytes] | gq[D] gk[D] | per team: 2 x (cos, sin, -sin)[D/2], 2 cache addresses | barriers
     float *gq_sh = reinterpret_cast<float *>(smem + (size_t)g.teams * g.slots * g.slot_bytes);
     float *gk_sh = gq_sh + D;
     float *team_area = gk_sh + D;
     const uint32_t tid = threadIdx.x, team = tid / g.team_threads, t = tid % g.team_threads;
+    // The last warp of a team is its manager: it owns no work items.  Its first lane drives the
+    // bulk copies and the cache addressing, all its lanes compute the rotary tables.  Everything
+    // that is serial by nature therefore runs beside the arithmetic warps, which only ever wait
+    // for data and for each other.
+    const uint32_t workers = g.team_threads - 32u;
+    const bool manager = t >= workers;
+    const bool lead = t == workers;
     float *tables = team_area + (size_t)team * qk_team_words(D);
     unsigned long long *v_base_sh = reinterpret_cast<unsigned long long *>(tables + (D / 2u) * 6u);  // [2], ~0 = none
     uint64_t *bars = reinterpret_cast<uint64_t *>(team_area + (size_t)g.teams * qk_team_words(D)) + team * kQkMaxSlots;
@@ -362,107 +369,143 @@ qk_norm_rope_stream_kernel(const qk_dev_args a, const qk_stream_geom g) {
         gq_sh[i] = a.q_heads ? __uint_as_float((uint32_t)a.q_gamma[i] << 16) : 0.0f;
         gk_sh[i] = a.k_heads ? __uint_as_float((uint32_t)a.k_gamma[i] << 16) : 0.0f;
     }
-    if (t == 0u) {
+    if (lead) {
         for (uint32_t j = 0; j < g.slots; ++j) mbar_init(bars + j, 1u);
         mbar_init_fence();
     }
     __syncthreads();
 
-    const bool v_in_regs = v_chunks <= kQkVRegs * g.team_threads;
     const bool fp8_cache = (a.flags & AXIOM_QK_FLAG_CACHE_E4M3) != 0u;
+    // tokens of this CTA: blockIdx.x + n * gridDim.x; this team takes n = team + teams * i
+    const uint32_t cta_tokens = a.tokens > blockIdx.x ? (a.tokens - blockIdx.x + gridDim.x - 1u) / gridDim.x : 0u;
+    const uint32_t my_tokens = team < cta_tokens ? (cta_tokens - team + g.teams - 1u) / g.teams : 0u;
+    auto token_of = [&](uint32_t i) { return blockIdx.x + (team + g.teams * i) * gridDim.x; };
+    // With three or more slots the refill lags one token behind (the stores of the previous token
+    // are the older bulk group: only they have to be done reading) and slots - 1 tokens are
+    // requested up front; fewer slots are refilled as soon as their own stores have drained.
+    const uint32_t ahead = g.slots > 2u ? g.slots - 1u : g.slots;
+
+    if (manager) {
+        // ------------------------------------------------------------------ manager warp
+        const uint32_t ml = t - workers;  // lane
+        auto issue = [&](uint32_t i) {
+            const uint64_t tok = token_of(i);
+            const uint32_t j = i % g.slots;
+            uint8_t *slot = my_slots + (size_t)j * g.slot_bytes;
+            mbar_arrive_expect_tx(bars + j, q_bytes + k_bytes);
+            if (q_bytes) bulk_load(slot, reinterpret_cast<const uint8_t *>(a.q) + tok * q_bytes, q_bytes, bars + j);
+            if (k_bytes) bulk_load(slot + q_bytes, reinterpret_cast<const uint8_t *>(a.k) + tok * k_bytes, k_bytes, bars + j);
+        };
+        // table entry that maps a position's logical cache block (~0: outside the table)
+        auto table_index = [&](uint32_t pos, uint32_t tok) -> uint64_t {
+            uint32_t lb = pos / a.block_tokens;
+            if (a.flags & AXIOM_QK_FLAG_RING) lb %= a.tbl_stride;
+            else if (lb >= a.tbl_stride) return ~0ull;
+            const uint64_t trow = (a.flags & AXIOM_QK_FLAG_PER_TOKEN_TABLE) ? tok : 0u;
+            return trow * a.tbl_stride + lb;
+        };
+        auto write_table = [&](uint32_t buffer, uint32_t pos) {
+            float *cos_t = tables + buffer * (D / 2u) * 3u, *sin_t = cos_t + D / 2u, *nsin_t = sin_t + D / 2u;
+            for (uint32_t p = ml; p < half; p += 32u) {
+                float cv, sv;
+                rope_table_entry(pos, a.inv_freq[p], a.mscale, &cv, &sv);
+                cos_t[p] = cv;
+                sin_t[p] = sv;
+                nsin_t[p] = -sv;
+            }
+        };
+        if (lead) {
+            for (uint32_t i = 0; i < ahead && i < my_tokens; ++i) issue(i);
+        }
+        // positions run two tokens ahead and block-table entries one (dependent loads off the critical path)
+        const bool paged = a.k_pool != nullptr && lead;
+        uint32_t pos_cur = my_tokens > 0u ? a.positions[token_of(0u)] : 0u;
+        uint32_t pos_n1 = my_tokens > 1u ? a.positions[token_of(1u)] : 0u;
+        int32_t pb_cur = -1;  // physical block of the current token, -1 = none
+        if (paged && my_tokens > 0u) {
+            const uint64_t idx = table_index(pos_cur, token_of(0u));
+            if (idx != ~0ull) pb_cur = a.block_tables[idx];
+        }
+        if (my_tokens > 0u) write_table(0u, pos_cur);
+        team_sync(team, g.team_threads);
+
+        bool faulted = false;
+        for (uint32_t i = 0; i < my_tokens; ++i) {
+            const uint32_t j = i % g.slots;
+            const uint32_t tok = token_of(i);
+            const uint32_t pos_n2 = i + 2u < my_tokens ? a.positions[token_of(i + 2u)] : 0u;
+            int32_t pb_n1 = -1;
+            if (paged && i + 1u < my_tokens) {
+                const uint64_t idx = table_index(pos_n1, token_of(i + 1u));
+                if (idx != ~0ull) pb_n1 = a.block_tables[idx];
+            }
+            if (i + 1u < my_tokens) write_table((i + 1u) & 1u, pos_n1);
+            const bool in_pool = pb_cur >= 0 && (uint32_t)pb_cur < a.n_blocks;
+            const uint64_t row_index = (((uint64_t)(in_pool ? pb_cur : 0) * a.n_layers + a.layer) * a.block_tokens +
+                                        pos_cur % a.block_tokens) * a.pool_stride;  // element index in the pools
+            if (lead && (has_v || fp8_cache)) v_base_sh[i & 1u] = in_pool ? row_index : ~0ull;
+            uint8_t *slot = my_slots + (size_t)j * g.slot_bytes;
+            // A wait that ran out raises the fault word; the team carries on (on whatever the slot
+            // holds) so that its barriers stay matched, and stops waiting and storing.
+            if (!faulted && !mbar_wait(bars + j, (i / g.slots) & 1u)) faulted = true;
+            team_sync(team, g.team_threads);  // the workers have rewritten the slot
+            if (fp8_cache && g.slots <= 2u) team_sync(team, g.team_threads);  // ... and converted its K row (see the workers)
+
+            if (lead && !faulted) {
+                const uint8_t *src = slot;
+                if (q_bytes) bulk_store(reinterpret_cast<uint8_t *>(a.q) + (uint64_t)tok * q_bytes, src, q_bytes);
+                if (k_bytes && a.k_out) bulk_store(reinterpret_cast<uint8_t *>(a.k_out) + (uint64_t)tok * k_bytes, src + q_bytes, k_bytes);
+                if (a.k_pool) {
+                    if (in_pool) {
+                        if (k_bytes && !fp8_cache) bulk_store(reinterpret_cast<uint8_t *>(a.k_pool) + row_index * 2u, src + q_bytes, k_bytes);
+                    } else if (a.status_word) {
+                        atomicCAS(a.status_word, AXIOM_STATUS_WORD_OK, AXIOM_STATUS_WORD_BAD_ADDRESS);
+                    }
+                }
+                bulk_commit();
+                const uint32_t nxt = i + ahead;
+                if (nxt < my_tokens) {
+                    if (g.slots > 2u) bulk_wait_read_but_one();
+                    else bulk_wait_read_all();
+                    issue(nxt);
+                }
+            }
+            pos_cur = pos_n1;
+            pos_n1 = pos_n2;
+            pb_cur = pb_n1;
+        }
+        if (lead) bulk_wait_read_all();
+        return;
+    }
+
+    // ---------------------------------------------------------------------- worker warps
+    const bool v_in_regs = v_chunks <= kQkVRegs * workers;
     const uint32_t l = t % LPH;
-    const uint32_t head0 = t / LPH, head_step = g.team_threads / LPH;
+    const uint32_t head0 = t / LPH, head_step = workers / LPH;
     const bool rotary = kFullRot || l < rot_lanes;
     const uint32_t off_a = rotary ? 4u * l : a.rope_dim + 8u * (l - rot_lanes);
     const uint32_t off_b = rotary ? half + 4u * l : off_a + 4u;
     const double inv_d = 1.0 / (double)D, eps = (double)a.eps;
     // byte offset of this thread's first item inside a slot, and the step to its next item
     const uint32_t item0 = (head0 * D + off_a) * 2u, item_step = head_step * D * 2u, b_delta = (off_b - off_a) * 2u;
-
-    // tokens of this CTA: blockIdx.x + n * gridDim.x; this team takes n = team + teams * i
-    const uint32_t cta_tokens = a.tokens > blockIdx.x ? (a.tokens - blockIdx.x + gridDim.x - 1u) / gridDim.x : 0u;
-    const uint32_t my_tokens = team < cta_tokens ? (cta_tokens - team + g.teams - 1u) / g.teams : 0u;
-    auto token_of = [&](uint32_t i) { return blockIdx.x + (team + g.teams * i) * gridDim.x; };
-
-    auto issue = [&](uint32_t i) {  // thread 0 of the team
-        const uint64_t tok = token_of(i);
-        const uint32_t j = i % g.slots;
-        uint8_t *slot = my_slots + (size_t)j * g.slot_bytes;
-        mbar_arrive_expect_tx(bars + j, q_bytes + k_bytes);
-        if (q_bytes) bulk_load(slot, reinterpret_cast<const uint8_t *>(a.q) + tok * q_bytes, q_bytes, bars + j);
-        if (k_bytes) bulk_load(slot + q_bytes, reinterpret_cast<const uint8_t *>(a.k) + tok * k_bytes, k_bytes, bars + j);
-    };
-    // With two or more slots the refill lags one token behind (see below) and slots - 1 tokens
-    // are requested up front; a single slot is refilled as soon as its own stores have drained.
-    const uint32_t ahead = g.slots > 1u ? g.slots - 1u : 1u;
-    if (t == 0u) {
-        for (uint32_t i = 0; i < ahead && i < my_tokens; ++i) issue(i);
-    }
-
-    // table entry that maps a position's logical cache block (thread 0 only; ~0 when the
-    // position lies outside the table)
-    auto table_index = [&](uint32_t pos, uint32_t tok) -> uint64_t {
-        uint32_t lb = pos / a.block_tokens;
-        if (a.flags & AXIOM_QK_FLAG_RING) lb %= a.tbl_stride;
-        else if (lb >= a.tbl_stride) return ~0ull;
-        const uint64_t trow = (a.flags & AXIOM_QK_FLAG_PER_TOKEN_TABLE) ? tok : 0u;
-        return trow * a.tbl_stride + lb;
-    };
-    auto write_table = [&](uint32_t buffer, uint32_t pos) {  // threads below rope_dim/2 (any team size)
-        float *cos_t = tables + buffer * (D / 2u) * 3u, *sin_t = cos_t + D / 2u, *nsin_t = sin_t + D / 2u;
-        for (uint32_t p = t; p < half; p += g.team_threads) {
-            float cv, sv;
-            rope_table_entry(pos, a.inv_freq[p], a.mscale, &cv, &sv);
-            cos_t[p] = cv;
-            sin_t[p] = sv;
-            nsin_t[p] = -sv;
-        }
-    };
-    const bool paged = a.k_pool != nullptr && t == 0u;
-    uint32_t pos_cur = my_tokens > 0u ? a.positions[token_of(0u)] : 0u;
-    uint32_t pos_n1 = my_tokens > 1u ? a.positions[token_of(1u)] : 0u;
-    int32_t pb_cur = -1;  // physical block of the current token, -1 = none
-    if (paged && my_tokens > 0u) {
-        const uint64_t idx = table_index(pos_cur, token_of(0u));
-        if (idx != ~0ull) pb_cur = a.block_tables[idx];
-    }
-    if (my_tokens > 0u) write_table(0u, pos_cur);
-    team_sync(team, g.team_threads);
+    team_sync(team, g.team_threads);  // the first rotary table is there
 
     bool faulted = false;
     for (uint32_t i = 0; i < my_tokens; ++i) {
         const uint32_t j = i % g.slots;
         const uint32_t tok = token_of(i);
-        // fetch ahead: position of token i+2, table entry and rotary table of token i+1
-        const uint32_t pos_n2 = i + 2u < my_tokens ? a.positions[token_of(i + 2u)] : 0u;
-        int32_t pb_n1 = -1;
-        if (paged && i + 1u < my_tokens) {
-            const uint64_t idx = table_index(pos_n1, token_of(i + 1u));
-            if (idx != ~0ull) pb_n1 = a.block_tables[idx];
-        }
-        if (i + 1u < my_tokens) write_table((i + 1u) & 1u, pos_n1);
         // V is a plain copy into the token's cache row: too small to deserve slot space.  The
-        // team's first threads read it now and write it after the barrier, when thread 0 has
+        // team's first threads read it now and write it after the barrier, when the manager has
         // published the row's address.
         uint4 v_reg[kQkVRegs];
-        if (has_v || fp8_cache) {
-            if (t == 0u) {
-                v_base_sh[i & 1u] = (pb_cur >= 0 && (uint32_t)pb_cur < a.n_blocks)
-                        ? (((uint64_t)pb_cur * a.n_layers + a.layer) * a.block_tokens + pos_cur % a.block_tokens) * a.pool_stride
-                        : ~0ull;
-            }
-            if (has_v && v_in_regs) {
+        if (has_v && v_in_regs) {
 #pragma unroll
-                for (uint32_t c = 0; c < kQkVRegs; ++c) {
-                    const uint32_t q = t + c * g.team_threads;
-                    if (q < v_chunks) v_reg[c] = ld_stream(a.v + (uint64_t)tok * v_chunks + q);
-                }
+            for (uint32_t c = 0; c < kQkVRegs; ++c) {
+                const uint32_t q = t + c * workers;
+                if (q < v_chunks) v_reg[c] = ld_stream(a.v + (uint64_t)tok * v_chunks + q);
             }
         }
-
         uint8_t *slot = my_slots + (size_t)j * g.slot_bytes;
-        // A wait that ran out raises the fault word; the team carries on (on whatever the slot
-        // holds) so that its barriers stay matched, and stops waiting and storing.
         if (!faulted && !mbar_wait(bars + j, (i / g.slots) & 1u)) faulted = true;
 
         const float *cos_t = tables + (i & 1u) * (D / 2u) * 3u;
@@ -494,11 +537,11 @@ qk_norm_rope_stream_kernel(const qk_dev_args a, const qk_stream_geom g) {
                     if (v_in_regs) {
 #pragma unroll
                         for (uint32_t c = 0; c < kQkVRegs; ++c) {
-                            const uint32_t q = t + c * g.team_threads;
+                            const uint32_t q = t + c * workers;
                             if (q < v_chunks) st_stream(dst + q, bf16x8_to_e4m3x8(v_reg[c]));
                         }
                     } else {
-                        for (uint32_t q = t; q < v_chunks; q += g.team_threads) {
+                        for (uint32_t q = t; q < v_chunks; q += workers) {
                             st_stream(dst + q, bf16x8_to_e4m3x8(ld_stream(a.v + (uint64_t)tok * v_chunks + q)));
                         }
                     }
@@ -507,56 +550,27 @@ qk_norm_rope_stream_kernel(const qk_dev_args a, const qk_stream_geom g) {
                     if (v_in_regs) {
 #pragma unroll
                         for (uint32_t c = 0; c < kQkVRegs; ++c) {
-                            const uint32_t q = t + c * g.team_threads;
+                            const uint32_t q = t + c * workers;
                             if (q < v_chunks) st_stream(dst + q, v_reg[c]);
                         }
                     } else {
-                        for (uint32_t q = t; q < v_chunks; q += g.team_threads) {
+                        for (uint32_t q = t; q < v_chunks; q += workers) {
                             st_stream(dst + q, ld_stream(a.v + (uint64_t)tok * v_chunks + q));
                         }
                     }
                 }
             }
-            if (fp8_cache) {
+            if (fp8_cache && v_base != ~0ull && a.k_pool) {
                 // the rotated K row sits in the slot as BF16 (it leaves as such for k_out): its E4M3
                 // image for the cache is produced here, 8 values per thread
-                if (v_base != ~0ull && a.k_pool) {
-                    const uint4 *k_sh = reinterpret_cast<const uint4 *>(slot + q_bytes);
-                    uint2 *dst = reinterpret_cast<uint2 *>(reinterpret_cast<uint8_t *>(a.k_pool) + v_base);
-                    for (uint32_t q = t; q < v_chunks; q += g.team_threads) st_stream(dst + q, bf16x8_to_e4m3x8(k_sh[q]));
-                }
-                // with one or two slots thread 0 refills THIS slot below: everyone has to be done reading it
-                if (g.slots <= 2u) team_sync(team, g.team_threads);
+                const uint4 *k_sh = reinterpret_cast<const uint4 *>(slot + q_bytes);
+                uint2 *dst = reinterpret_cast<uint2 *>(reinterpret_cast<uint8_t *>(a.k_pool) + v_base);
+                for (uint32_t q = t; q < v_chunks; q += workers) st_stream(dst + q, bf16x8_to_e4m3x8(k_sh[q]));
             }
         }
-        if (t == 0u && !faulted) {
-            const uint8_t *src = slot;
-            if (q_bytes) bulk_store(reinterpret_cast<uint8_t *>(a.q) + (uint64_t)tok * q_bytes, src, q_bytes);
-            if (k_bytes && a.k_out) bulk_store(reinterpret_cast<uint8_t *>(a.k_out) + (uint64_t)tok * k_bytes, src + q_bytes, k_bytes);
-            if (a.k_pool) {
-                if (pb_cur >= 0 && (uint32_t)pb_cur < a.n_blocks) {
-                    const uint64_t base = ((((uint64_t)pb_cur * a.n_layers + a.layer) * a.block_tokens +
-                                            pos_cur % a.block_tokens) * a.pool_stride) * 2u;
-                    if (k_bytes && !fp8_cache) bulk_store(reinterpret_cast<uint8_t *>(a.k_pool) + base, src + q_bytes, k_bytes);
-                } else if (a.status_word) {
-                    atomicCAS(a.status_word, AXIOM_STATUS_WORD_OK, AXIOM_STATUS_WORD_BAD_ADDRESS);
-                }
-            }
-            bulk_commit();
-            // refill the slot of the PREVIOUS token (slot of token i + slots - 1): its stores are
-            // the older group, so only they have to be done reading.
-            const uint32_t nxt = i + ahead;
-            if (nxt < my_tokens) {
-                if (g.slots > 1u) bulk_wait_read_but_one();
-                else bulk_wait_read_all();
-                issue(nxt);
-            }
-        }
-        pos_cur = pos_n1;
-        pos_n1 = pos_n2;
-        pb_cur = pb_n1;
+        // with one or two slots the manager refills THIS slot next: everyone has to be done reading it
+        if (fp8_cache && g.slots <= 2u) team_sync(team, g.team_threads);
     }
-    if (t == 0u) bulk_wait_read_all();
 }
 
 // Frequency table.  The correction range (floor/ceil of the two YaRN
@@ -629,8 +643,9 @@ bool launch_qk_stream(const qk_dev_args &a, cudaStream_t stream) {
     for (uint32_t npt : kNpt) {
         if (items % npt) continue;
         qk_stream_geom g{};
-        g.team_threads = items / npt;
-        if (g.team_threads % 32u || g.team_threads > 512u || g.team_threads < 64u) continue;
+        const uint32_t workers = items / npt;
+        if (workers % 32u || workers > 512u || workers < 64u) continue;
+        g.team_threads = workers + 32u;  // plus the manager warp
         g.slot_bytes = (a.q_heads + a.k_heads) * a.head_dim * 2u;
         g.slots = 3u;
         g.teams = kQkStreamThreads / g.team_threads;
