@@ -309,16 +309,17 @@ qk_norm_rope_paged_kernel(const qk_dev_args a) {
 
 // ---------------------------------------------------------------------------
 // Streaming flavour for many tokens: a persistent CTA per SM made of independent teams.
-// A team owns `slots` shared-memory token slots laid out [Q heads | K heads]; its
-// thread 0 keeps bulk loads of the next tokens in flight, the team normalises and rotates the
-// slot IN PLACE, and thread 0 sends the finished slot out with bulk stores (Q row back in
-// place, K row to its cache page and/or k_out); V, a 2 KB copy per token, is moved by the team's
-// first threads with 16-byte accesses.  Slot (i-1) is refilled at the end of token i, once its
-// stores have finished reading shared memory (one store group may stay pending), so loads run
-// `slots - 1` tokens ahead.  One team barrier per token: the rotary table of token i+1 is
-// written (double-buffered) at the top of iteration i, before the wait for token i's data;
-// positions and block-table entries are fetched two and one iterations ahead into registers,
-// which keeps the dependent pos -> table -> address chain off the critical path.
+// A team is a set of worker warps plus one manager warp and owns `slots` shared-memory token
+// slots laid out [Q heads | K heads].  The manager's first lane keeps bulk loads of the next
+// tokens in flight and sends finished slots out with bulk stores (Q row back in place, K row
+// to its cache page and/or k_out); its lanes also compute the rotary table of the next token
+// (double-buffered) and fetch positions and block-table entries two and one tokens ahead, so
+// the dependent pos -> table -> address chain and every single-threaded instruction sequence
+// run beside the arithmetic instead of in front of it.  The workers normalise and rotate the
+// slot IN PLACE and meet the manager at one team barrier per token; V, a 2 KB copy per token,
+// is moved by the first workers with 16-byte accesses.  With three or more slots, slot (i-1)
+// is refilled at the end of token i, once its stores have finished reading shared memory (one
+// store group may stay pending), so loads run `slots - 1` tokens ahead.
 // ---------------------------------------------------------------------------
 constexpr uint32_t kQkMaxSlots = 4u;
 constexpr uint32_t kQkVRegs = 2u;  // 16-byte V chunks a thread carries across the token's barrier
@@ -639,7 +640,7 @@ bool launch_qk_stream(const qk_dev_args &a, cudaStream_t stream) {
     const uint32_t items = (a.q_heads + a.k_heads) * LPH;
     qk_stream_geom best{};
     uint32_t best_npt = 0u, best_score = 0u;
-    static const uint32_t kNpt[] = {2u, 3u, 4u, 6u, 8u};
+    static const uint32_t kNpt[] = {2u, 3u, 4u, 6u, 8u, 9u};
     for (uint32_t npt : kNpt) {
         if (items % npt) continue;
         qk_stream_geom g{};
@@ -683,6 +684,7 @@ bool launch_qk_stream(const qk_dev_args &a, cudaStream_t stream) {
     case 4: AXB_QK_STREAM(4); break;
     case 6: AXB_QK_STREAM(6); break;
     case 8: AXB_QK_STREAM(8); break;
+    case 9: AXB_QK_STREAM(9); break;
     default: return false;
     }
 #undef AXB_QK_STREAM
