@@ -49,6 +49,11 @@ struct norm_args {
     uint32_t groups;
     uint32_t inner_tiles;
     uint32_t ring_slots;    // stream kernel: shared-memory slots per warp
+    // wide-row kernel only: the addend of row r is row token_ids[r] of an embedding table
+    const uint4 *table;     // may be null
+    const uint32_t *token_ids;
+    uint32_t vocab;
+    uint32_t *status_word;  // may be null
 };
 
 // Second sweep over one row held in shared memory as BF16: n = bf16((r * inv) * gamma), optional
@@ -290,6 +295,13 @@ add_rmsnorm_wide_row_kernel(const norm_args a) {
 
     for (uint32_t row = blockIdx.x; row < a.rows; row += gridDim.x) {
         const uint64_t base = (uint64_t)row * a.chunks_per_row;
+        uint32_t token_id = 0u;
+        if (kAdd && a.table) {
+            token_id = a.token_ids[row];
+            if (token_id >= a.vocab && tid == 0u && a.status_word) {
+                atomicCAS(a.status_word, AXIOM_STATUS_WORD_OK, AXIOM_STATUS_WORD_BAD_ADDRESS);
+            }
+        }
         uint4 m[kWideMaxChunksPerThread], gam[kWideMaxChunksPerThread];
 #pragma unroll
         for (uint32_t c = 0; c < kWideMaxChunksPerThread; ++c) {
@@ -299,7 +311,13 @@ add_rmsnorm_wide_row_kernel(const norm_args a) {
             if (q < a.chunks_per_row) {
                 m[c] = ld_stream(a.residual + base + q);
                 uint4 h = make_uint4(0u, 0u, 0u, 0u);
-                if (kAdd) h = ld_stream(a.hidden + base + q);
+                if (kAdd) {
+                    if (a.table) {  // gathered addend: id >= vocab gives a zero row and raises the status word
+                        if (token_id < a.vocab) h = ld_stream(a.table + (uint64_t)token_id * a.chunks_per_row + q);
+                    } else {
+                        h = ld_stream(a.hidden + base + q);
+                    }
+                }
                 gam[c] = gamma16[q];
                 if (kAdd) {
                     m[c].x = add_bf16x2(m[c].x, h.x); m[c].y = add_bf16x2(m[c].y, h.y);
@@ -411,6 +429,39 @@ void launch_stream(const norm_args &a, uint32_t teams, size_t smem, cudaStream_t
 
 unsigned int add_rmsnorm_fault_word() { return read_and_clear_pipeline_fault(); }
 
+int launch_gather_add_rmsnorm_nvfp4_bf16(const void *table, uint32_t vocab, const uint32_t *token_ids, void *residual,
+                                         const void *gamma, float eps, uint32_t rows, uint32_t cols, float G,
+                                         void *norm_out, uint8_t *codes, uint8_t *scales, uint32_t layout,
+                                         uint32_t *status_word, cudaStream_t stream) {
+    norm_args a{};
+    a.table = (const uint4 *)table;
+    a.token_ids = token_ids;
+    a.vocab = vocab;
+    a.status_word = status_word;
+    a.residual = (uint4 *)residual;
+    a.gamma = (const uint16_t *)gamma;
+    a.norm_out = (uint4 *)norm_out;
+    a.codes = (uint32_t *)codes;
+    a.scales = scales;
+    a.eps = eps;
+    a.G = G;
+    a.rows = rows;
+    a.cols = cols;
+    a.chunks_per_row = cols / 8u;
+    a.layout = layout;
+    a.groups = cols / kGroup;
+    a.inner_tiles = (a.groups + 3u) / 4u;
+    // one wide CTA per row at every row count: the gathered rows are scattered, there is nothing to stream
+    uint32_t threads = (a.chunks_per_row + 31u) & ~31u;
+    if (threads > 1024u) threads = 1024u;
+    if (threads < 128u) threads = 128u;
+    const uint32_t ctas = rows < kSmCount * 8u ? rows : kSmCount * 8u;
+    launch_chained(add_rmsnorm_wide_row_kernel<true>, dim3(ctas), dim3(threads), (size_t)a.chunks_per_row * sizeof(uint4),
+                   stream, a);
+    note_launch();
+    return AXIOM_OK;
+}
+
 int launch_add_rmsnorm_nvfp4_bf16(const void *hidden, void *residual, const void *gamma, float eps, uint32_t rows,
                                   uint32_t cols, float G, void *norm_out, uint8_t *codes, uint8_t *scales,
                                   uint32_t layout, cudaStream_t stream) {
@@ -492,5 +543,29 @@ extern "C" int axiom_qwen38_fused_add_rmsnorm_nvfp4_bf16_device(
     if (rc != AXIOM_OK) return rc;
     launch_add_rmsnorm_nvfp4_bf16(hidden_bf16, residual_bf16, gamma_bf16, eps, rows, cols, global_scale,
                                   norm_out_bf16, out_codes, out_scales, scale_layout, (cudaStream_t)stream);
+    return launch_status();
+}
+
+extern "C" int axiom_qwen38_fused_gather_add_rmsnorm_nvfp4_bf16_device(
+        int device, const void *table_bf16, uint32_t vocab, const uint32_t *token_ids, void *residual_bf16,
+        const void *gamma_bf16, float eps, uint32_t rows, uint32_t cols, float global_scale, void *norm_out_bf16,
+        uint8_t *out_codes, uint8_t *out_scales, uint32_t scale_layout, uint32_t *status_word, void *stream) {
+    if (!table_bf16 || !token_ids || vocab == 0u || !residual_bf16 || !gamma_bf16 || rows == 0u || cols == 0u ||
+        (cols % kGroup) != 0u || cols > 16384u || scale_layout > AXIOM_SCALE_LAYOUT_TILED || !(eps > 0.0f) ||
+        !std::isfinite(eps)) {
+        return AXIOM_ERR_INVALID_ARGUMENT;
+    }
+    if ((out_codes == nullptr) != (out_scales == nullptr)) return AXIOM_ERR_INVALID_ARGUMENT;
+    if (!out_codes && !norm_out_bf16) return AXIOM_ERR_INVALID_ARGUMENT;
+    if (out_codes && !valid_scale(global_scale)) return AXIOM_ERR_INVALID_ARGUMENT;
+    if (!aligned16(table_bf16) || !aligned16(residual_bf16) || !aligned16(gamma_bf16) || (norm_out_bf16 && !aligned16(norm_out_bf16)) ||
+        (out_codes && (reinterpret_cast<uintptr_t>(out_codes) & 3u))) {
+        return AXIOM_ERR_INVALID_ARGUMENT;
+    }
+    int rc = select_device(device);
+    if (rc != AXIOM_OK) return rc;
+    launch_gather_add_rmsnorm_nvfp4_bf16(table_bf16, vocab, token_ids, residual_bf16, gamma_bf16, eps, rows, cols,
+                                         out_codes ? global_scale : 1.0f, norm_out_bf16, out_codes, out_scales, scale_layout,
+                                         status_word, (cudaStream_t)stream);
     return launch_status();
 }

@@ -170,6 +170,12 @@ int axiom_qwen38_fused_add_bf16_device(int device, const void *a_bf16, const voi
  * cols % 16 == 0, cols <= 16384. */
 int axiom_qwen38_fused_add_rmsnorm_nvfp4_bf16_device(int device, const void *hidden_bf16, void *residual_bf16, const void *gamma_bf16, float eps, uint32_t rows, uint32_t cols, float global_scale, void *norm_out_bf16, uint8_t *out_codes, uint8_t *out_scales, uint32_t scale_layout, void *stream);
 
+/* The same with the addend gathered from an embedding table: residual[r] = bf16(residual[r] + table[token_ids[r]]),
+ * then norm and quantize as above — qwen38_embedding_gather_columns_kernel (src/axiom_qwen38_model.cu:321-341) fused
+ * into the first norm of the chain, so the gathered rows never make a round trip through HBM.  id >= vocab adds a
+ * zero row and raises AXIOM_STATUS_WORD_BAD_ADDRESS. */
+int axiom_qwen38_fused_gather_add_rmsnorm_nvfp4_bf16_device(int device, const void *table_bf16, uint32_t vocab, const uint32_t *token_ids, void *residual_bf16, const void *gamma_bf16, float eps, uint32_t rows, uint32_t cols, float global_scale, void *norm_out_bf16, uint8_t *out_codes, uint8_t *out_scales, uint32_t scale_layout, uint32_t *status_word, void *stream);
+
 /* Replaces silu_mul_batch_kernel + quantize_columns_e4m3_kernel
  * (src/axiom_qwen38_fp8_mlp.cu:16-21,111-128; src/axiom_qwen38_fp8.cu:64-94).
  * gate_up rows are [gate(width) | up(width)]; scales[row] = rowmax/448 (1 if 0). width % 8 == 0. */

@@ -68,3 +68,37 @@ def test_chain(axk, cuda_device, m):
     assert np.array_equal(cells[btab[0, lb], positions % 16], host(k_out, np.uint16).reshape(m, 1024))
     want_mc, want_ms = ol.swiglu_nvfp4_bf16(gu, G2)
     assert np.mean(host(mlp_codes, np.uint8) != want_mc) < 2e-3 and np.mean(host(mlp_scales, np.uint8) != want_ms) < 2e-3
+
+
+@pytest.mark.parametrize("m,cols", [(1, 5120), (8, 5120), (64, 1024), (300, 5120), (700, 2048)])
+def test_gather_fused_into_the_first_norm(axk, cuda_device, m, cols):
+    """gather + add + RMSNorm + NVFP4 in one launch gives the bytes of the two-launch sequence, including rows
+    whose token id is out of range (zero addend, status word raised)."""
+    import torch
+    from gpu_util import dev, host, sync
+
+    table, ids = wl.embedding_inputs_np(m, vocab=2048, hidden=cols)
+    bad = m >= 8
+    if bad:
+        ids[3] = 2048
+        ids[m - 1] = 0xFFFFFFFF
+    _, residual, gamma = wl.add_rmsnorm_inputs_np(m, cols)
+    G = 75.0
+    outs = []
+    for fused in (False, True):
+        t, i, r, g = dev(table), dev(ids), dev(residual), dev(gamma)
+        norm = torch.zeros((m, cols), dtype=torch.int16, device="cuda")
+        codes = torch.zeros((m, cols // 2), dtype=torch.uint8, device="cuda")
+        scales = torch.zeros((m, cols // 16), dtype=torch.uint8, device="cuda")
+        status = torch.zeros(1, dtype=torch.int32, device="cuda")
+        if fused:
+            assert axk.gather_add_rmsnorm_nvfp4(0, t, 2048, i, r, g, 1e-6, m, cols, G, norm, codes, scales, 0, status) == axk.AXIOM_OK
+        else:
+            hidden = torch.zeros((m, cols), dtype=torch.int16, device="cuda")
+            assert axk.embedding_gather(0, t, 2048, cols, i, m, hidden, status) == axk.AXIOM_OK
+            assert axk.add_rmsnorm_nvfp4(0, hidden, r, g, 1e-6, m, cols, G, norm, codes, scales, 0) == axk.AXIOM_OK
+        sync()
+        assert int(status.item()) == (axk.STATUS_WORD_BAD_ADDRESS if bad else 0)
+        outs.append([host(x, np.uint8) for x in (r, norm, codes, scales)])
+    for a, b in zip(*outs):
+        assert np.array_equal(a, b)
