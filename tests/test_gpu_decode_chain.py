@@ -102,3 +102,36 @@ def test_gather_fused_into_the_first_norm(axk, cuda_device, m, cols):
         outs.append([host(x, np.uint8) for x in (r, norm, codes, scales)])
     for a, b in zip(*outs):
         assert np.array_equal(a, b)
+
+
+def test_back_to_back_launches_respect_stream_order(axk, cuda_device):
+    """Every kernel may be scheduled before its predecessor on the stream has finished (programmatic dependent
+    launch) and must not touch memory before the dependency resolves.  Forty dependent launches — each adds the
+    previous result into the residual in place, alternating the streaming and the wide-row kernel, and quantizes
+    what the previous launch wrote — must give the bytes of forty synchronised launches."""
+    import torch
+    from gpu_util import dev, host, sync
+
+    rows, cols = 600, 5120
+    hidden, residual, gamma = wl.add_rmsnorm_inputs_np(rows, cols)
+    small = 40  # rows of the wide-row launches
+    results = []
+    for synchronise in (True, False):
+        h, r, g = dev(hidden), dev(residual), dev(gamma)
+        norm = torch.zeros((rows, cols), dtype=torch.int16, device="cuda")
+        codes = torch.zeros((rows, cols // 2), dtype=torch.uint8, device="cuda")
+        scales = torch.zeros((rows, cols // 16), dtype=torch.uint8, device="cuda")
+        q4 = torch.zeros((rows, cols // 2), dtype=torch.uint8, device="cuda")
+        s4 = torch.zeros((rows, cols // 16), dtype=torch.uint8, device="cuda")
+        for it in range(40):
+            n = rows if it % 2 == 0 else small
+            assert axk.add_rmsnorm_nvfp4(0, h, r, g, 1e-6, n, cols, 50.0, norm, codes, scales, 0) == axk.AXIOM_OK
+            # the next launch reads what this one wrote (norm) and the one after overwrites it again
+            assert axk.nvfp4_quantize(0, norm, n, cols, 50.0, q4, s4, 0) == axk.AXIOM_OK
+            assert axk.add_bf16(0, norm, h, h, n * cols) == axk.AXIOM_OK  # and feeds the addend of the next round
+            if synchronise:
+                sync()
+        sync()
+        results.append([host(x, np.uint8) for x in (h, r, norm, codes, scales, q4, s4)])
+    for a, b in zip(*results):
+        assert np.array_equal(a, b)
