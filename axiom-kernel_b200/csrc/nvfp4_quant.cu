@@ -79,21 +79,34 @@ nvfp4_quantize_bf16_kernel(const uint4 *__restrict__ in, uint32_t total_chunks, 
         row = (first + lane) / chunks_per_row;
         col = (first + lane) - row * chunks_per_row;
     }
+    uint64_t tile_off = 0u;  // tiled plane: offset of this lane's block (row, col / 2)
     auto store_scale = [&](uint32_t j, uint32_t byte) {
         if (!kTiled) {
             sc[j * 16u] = (uint8_t)byte;
         } else {
-            // position of chunk (col + 32 j) of this row, carried into the next rows
-            uint32_t r = row, c = col + 32u * j;
-            while (c >= chunks_per_row) { c -= chunks_per_row; ++r; }
-            scales[scale_offset(r, c >> 1, groups, inner_tiles, AXIOM_SCALE_LAYOUT_TILED)] = (uint8_t)byte;
+            const uint32_t c = col + 32u * j;
+            if (c < chunks_per_row) {
+                // same row: 32 chunks further is 16 blocks further = 4 tiles of 512 bytes further
+                scales[tile_off + j * 2048u] = (uint8_t)byte;
+            } else {
+                uint32_t r = row, cc = c;
+                while (cc >= chunks_per_row) { cc -= chunks_per_row; ++r; }
+                scales[scale_offset(r, cc >> 1, groups, inner_tiles, AXIOM_SCALE_LAYOUT_TILED)] = (uint8_t)byte;
+            }
         }
     };
+    auto locate = [&]() { tile_off = scale_offset(row, col >> 1, groups, inner_tiles, AXIOM_SCALE_LAYOUT_TILED); };
+    if (kTiled) locate();
     auto advance = [&]() {
         src += kTile; dst += kTile; sc += kTile / 2u;
         if (kTiled) {
             col += kTile;
-            while (col >= chunks_per_row) { col -= chunks_per_row; ++row; }
+            if (col < chunks_per_row) {
+                tile_off += (kTile / 32u) * 2048u;
+            } else {
+                while (col >= chunks_per_row) { col -= chunks_per_row; ++row; }
+                locate();
+            }
         }
     };
 

@@ -183,7 +183,7 @@ def main():
     ap.add_argument("--skip-e2e", action="store_true")
     ap.add_argument("--skip-cpu", action="store_true")
     ap.add_argument("--only", default=None,
-                    choices=["add_rmsnorm", "nvfp4_quantize", "qk", "swiglu_fp8", "swiglu_nvfp4", "chain"],
+                    choices=["add_rmsnorm", "add_rmsnorm_tiled", "nvfp4_quantize", "qk", "swiglu_fp8", "swiglu_nvfp4", "chain"],
                     help="run one configuration alone (profiling aid): device-timed, no e2e / CPU legs")
     ap.add_argument("--rows", type=int, default=0, help="with --only: override the token count")
     args = ap.parse_args()
@@ -392,6 +392,8 @@ def bench_other_ops(torch, axk, wl, local, device, stream, peak, only=None, rows
         out[name] = {"ms": ms, "gbs": gbs, "frac_of_peak": gbs / peak, "tokens_per_s": rows / (ms * 1e-3),
                      "algorithmic_bytes": algo, "note": note}
 
+    if only is None or only == "add_rmsnorm_tiled":
+        bench_add_rmsnorm_tiled(torch, axk, wl, local, device, stream, timed, report, rows_override or 8192)
     if want("nvfp4_quantize"):
         bench_nvfp4_quantize(torch, axk, wl, local, device, stream, timed, report, rows_override or 4096)
     if want("qk"):
@@ -401,6 +403,25 @@ def bench_other_ops(torch, axk, wl, local, device, stream, peak, only=None, rows
     if want("chain"):
         out["decode_chain"] = bench_chain(torch, axk, wl, local, device, stream, timed, peak)
     return out
+
+
+def bench_add_rmsnorm_tiled(torch, axk, wl, local, device, stream, timed, report, rows):
+    # config 2 with the block scales written straight into the cuBLASLt VEC16_UE4M3 tile layout (what the next GEMM reads)
+    cols = COLS
+    sets = []
+    for s in range(NSETS):
+        hidden, residual, gamma = wl.add_rmsnorm_inputs_torch(torch, device, rows, cols)
+        plane = int(axk.lib().axiom_nvfp4_scale_plane_bytes(rows, cols // 16, 1))
+        sets.append((hidden, residual, gamma, torch.empty((rows, cols // 2), dtype=torch.uint8, device=device),
+                     torch.zeros(plane, dtype=torch.uint8, device=device)))
+
+    def step(i):
+        h, r, g, c, s = sets[i % NSETS]
+        axk.add_rmsnorm_nvfp4(local, h, r, g, wl.EPS, rows, cols, 90.0, None, c, s, 1, stream)
+
+    ms = timed(step)
+    report("add_rmsnorm_nvfp4_tiled_scales", ms, bytes_add_rmsnorm_nvfp4(rows, cols), rows,
+           "config 2, block scales in the cuBLASLt tile layout")
 
 
 def bench_nvfp4_quantize(torch, axk, wl, local, device, stream, timed, report, rows):
