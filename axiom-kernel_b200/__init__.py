@@ -105,6 +105,9 @@ SIGNATURES = {
     "axiom_runtime_add_f32_device": (i32, [vp, *_BUF, *_BUF, *_BUF, u32]),
     "axiom_runtime_silu_mul_f32_device": (i32, [vp, *_BUF, *_BUF, *_BUF, u32]),
     "axiom_runtime_silu_mul_clamp_f32_device": (i32, [vp, *_BUF, *_BUF, *_BUF, u32, f32]),
+    "axiom_runtime_f16_embedding_streams_device": (i32, [vp, *_BUF, *_BUF, u32, u32, u32]),
+    "axiom_runtime_q8_0_embedding_gather_f32_device": (i32, [vp, *_BUF, *_BUF, u32, u32, u32]),
+    "axiom_runtime_q8_0_embedding_gather_token_f32_device": (i32, [vp, *_BUF, *_BUF, *_BUF, u32, u32]),
     "axiom_qwen38_nvfp4_quantize_reference_f32": (i32, [i32, vp, f32, vp, vp, u32, vp]),
     "axiom_qwen38_fused_nvfp4_quantize_bf16_device": (i32, [i32, vp, u32, u32, f32, vp, vp, u32, vp]),
     "axiom_qwen38_fused_add_bf16_device": (i32, [i32, vp, vp, vp, u64, vp]),

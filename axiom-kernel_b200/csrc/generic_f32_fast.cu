@@ -17,6 +17,8 @@
 // finish-after-launch convention.
 #include "runtime.hpp"
 
+#include <cuda_fp16.h>
+
 namespace axb {
 namespace {
 
@@ -312,6 +314,97 @@ extern "C" int axiom_runtime_kv_pool_store_paged_f32_device(axiom_runtime *rt, c
             cf(k_stage, k_stage_off), cf(v_stage, v_stage_off), mf(k_pool, k_pool_off), mf(v_pool, v_pool_off),
             (const int32_t *)at(tables, tbl_off), (const uint32_t *)at(pos, pos_off), tbl_stride, n_layers, layer,
             block_tokens, pool_stride, kv_dim);
+    note_launch();
+    return finish_after_launch(nullptr);
+}
+
+// ------------------------------------------------------------------------
+// Generic single-token embedding gathers (src/axiom_cuda.cu:2213-2256, 14458-14469; runtime
+// wrappers src/axiom_runtime.cpp:4656-4752).  Q8_0 rows are blocks of 34 bytes: a little-endian
+// F16 scale followed by 32 signed bytes; value = scale * q.  F16 rows are widened and replicated
+// into `streams` copies.  One 16-byte-free scalar path is enough: a row is a few KB.
+// ------------------------------------------------------------------------
+namespace axb {
+namespace {
+
+__device__ __forceinline__ float q8_0_value(const uint8_t *row, uint32_t idx) {
+    const uint8_t *blk = row + (uint64_t)(idx >> 5) * 34u;
+    const uint16_t bits = (uint16_t)blk[0] | ((uint16_t)blk[1] << 8);
+    const float d = __half2float(__ushort_as_half(bits));
+    return d * (float)((const int8_t *)(blk + 2u))[idx & 31u];
+}
+
+__global__ void q8_0_embedding_gather_kernel(const uint8_t *__restrict__ embedding, const uint32_t *__restrict__ token_ptr,
+                                             uint32_t token_value, float *__restrict__ out, uint32_t token_count,
+                                             uint32_t hidden) {
+    const uint32_t tok = token_ptr ? token_ptr[0] : token_value;
+    const uint32_t i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= hidden) return;
+    if (tok >= token_count) {
+        out[i] = 0.0f;
+        return;
+    }
+    out[i] = q8_0_value(embedding + (uint64_t)tok * (hidden / 32u) * 34u, i);
+}
+
+__global__ void f16_embedding_streams_kernel(const uint16_t *__restrict__ embedding, float *__restrict__ out, uint32_t token_id,
+                                             uint32_t hidden, uint32_t streams) {
+    const uint64_t idx = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (idx >= (uint64_t)hidden * streams) return;
+    out[idx] = __half2float(__ushort_as_half(embedding[(uint64_t)token_id * hidden + (uint32_t)(idx % hidden)]));
+}
+
+int q8_0_gather_entry(axiom_runtime *rt, const axiom_device_buffer *emb, uint64_t emb_off, const axiom_device_buffer *tok,
+                      uint64_t tok_off, uint32_t token_value, axiom_device_buffer *out, uint64_t out_off, uint32_t token_count,
+                      uint32_t hidden) {
+    if (rt->backend != AXIOM_BACKEND_CUDA) return AXIOM_ERR_UNSUPPORTED_BACKEND;
+    const uint64_t emb_bytes = (uint64_t)(hidden / 32u) * 34u * token_count;
+    if (!span_ok(emb, emb_off, emb_bytes) || !f32_span(out, out_off, hidden) || (tok && !span_ok(tok, tok_off, sizeof(uint32_t)))) {
+        return AXIOM_ERR_INVALID_ARGUMENT;
+    }
+    int rc = begin(rt);
+    if (rc != AXIOM_OK) return rc;
+    q8_0_embedding_gather_kernel<<<(hidden + 255u) / 256u, 256>>>(at(emb, emb_off), tok ? (const uint32_t *)at(tok, tok_off) : nullptr,
+                                                                 token_value, mf(out, out_off), token_count, hidden);
+    note_launch();
+    return finish_after_launch(nullptr);
+}
+
+}  // namespace
+}  // namespace axb
+
+extern "C" int axiom_runtime_q8_0_embedding_gather_f32_device(axiom_runtime *rt, const axiom_device_buffer *embedding_q8, uint64_t embedding_offset, axiom_device_buffer *out, uint64_t out_offset, uint32_t token_id, uint32_t token_count, uint32_t hidden) {
+    if (!rt || !embedding_q8 || !out || token_count == 0u || hidden == 0u || (hidden % 32u) != 0u || token_id >= token_count ||
+        !owned_by(rt, embedding_q8) || !owned_by(rt, out)) {
+        return AXIOM_ERR_INVALID_ARGUMENT;
+    }
+    return q8_0_gather_entry(rt, embedding_q8, embedding_offset, nullptr, 0u, token_id, out, out_offset, token_count, hidden);
+}
+
+extern "C" int axiom_runtime_q8_0_embedding_gather_token_f32_device(axiom_runtime *rt, const axiom_device_buffer *embedding_q8, uint64_t embedding_offset, const axiom_device_buffer *token_id, uint64_t token_id_offset, axiom_device_buffer *out, uint64_t out_offset, uint32_t token_count, uint32_t hidden) {
+    if (!rt || !embedding_q8 || !token_id || !out || token_count == 0u || hidden == 0u || (hidden % 32u) != 0u ||
+        !owned_by(rt, embedding_q8) || !owned_by(rt, token_id) || !owned_by(rt, out) || (token_id_offset & 3u)) {
+        return AXIOM_ERR_INVALID_ARGUMENT;
+    }
+    return q8_0_gather_entry(rt, embedding_q8, embedding_offset, token_id, token_id_offset, 0u, out, out_offset, token_count, hidden);
+}
+
+extern "C" int axiom_runtime_f16_embedding_streams_device(axiom_runtime *rt, const axiom_device_buffer *embedding_f16, uint64_t embedding_offset, axiom_device_buffer *out_streams, uint64_t out_offset, uint32_t token_id, uint32_t hidden, uint32_t streams) {
+    if (!rt || !embedding_f16 || !out_streams || hidden == 0u || streams == 0u || !owned_by(rt, embedding_f16) ||
+        !owned_by(rt, out_streams) || (embedding_offset & 1u)) {
+        return AXIOM_ERR_INVALID_ARGUMENT;
+    }
+    if (rt->backend != AXIOM_BACKEND_CUDA) return AXIOM_ERR_UNSUPPORTED_BACKEND;
+    uint64_t row_end = 0, out_count = 0;
+    if (!mul_ok((uint64_t)token_id + 1u, (uint64_t)hidden * sizeof(uint16_t), &row_end) || !mul_ok(hidden, streams, &out_count) ||
+        out_count > 0xffffffffull || !span_ok(embedding_f16, embedding_offset, row_end) ||
+        !f32_span(out_streams, out_offset, (uint32_t)out_count)) {
+        return AXIOM_ERR_INVALID_ARGUMENT;
+    }
+    int rc = begin(rt);
+    if (rc != AXIOM_OK) return rc;
+    f16_embedding_streams_kernel<<<(uint32_t)((out_count + 255u) / 256u), 256>>>((const uint16_t *)at(embedding_f16, embedding_offset),
+                                                                                mf(out_streams, out_offset), token_id, hidden, streams);
     note_launch();
     return finish_after_launch(nullptr);
 }

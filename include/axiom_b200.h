@@ -126,6 +126,13 @@ int axiom_runtime_silu_mul_f32_device(axiom_runtime *runtime, const axiom_device
 /* include/axiom/axiom.h:787-796 */
 int axiom_runtime_silu_mul_clamp_f32_device(axiom_runtime *runtime, const axiom_device_buffer *gate, uint64_t gate_offset, const axiom_device_buffer *up, uint64_t up_offset, axiom_device_buffer *out, uint64_t out_offset, uint32_t count, float clamp_abs);
 
+/* Generic single-token embedding gathers (include/axiom/axiom.h:839-866; kernels src/axiom_cuda.cu:2213-2256,
+ * 14458-14469).  Q8_0 rows: blocks of 34 bytes (little-endian F16 scale + 32 signed bytes), hidden % 32 == 0;
+ * token id >= token_count gives a zero row in the device-token flavour and is rejected in the immediate one. */
+int axiom_runtime_f16_embedding_streams_device(axiom_runtime *runtime, const axiom_device_buffer *embedding_f16, uint64_t embedding_offset, axiom_device_buffer *out_streams, uint64_t out_offset, uint32_t token_id, uint32_t hidden, uint32_t streams);
+int axiom_runtime_q8_0_embedding_gather_f32_device(axiom_runtime *runtime, const axiom_device_buffer *embedding_q8, uint64_t embedding_offset, axiom_device_buffer *out, uint64_t out_offset, uint32_t token_id, uint32_t token_count, uint32_t hidden);
+int axiom_runtime_q8_0_embedding_gather_token_f32_device(axiom_runtime *runtime, const axiom_device_buffer *embedding_q8, uint64_t embedding_offset, const axiom_device_buffer *token_id, uint64_t token_id_offset, axiom_device_buffer *out, uint64_t out_offset, uint32_t token_count, uint32_t hidden);
+
 /* include/axiom/qwen38_nvfp4.h:30-37 — the exported NVFP4 quantizer oracle:
  * one F32 row -> cols/2 packed E2M1 bytes + cols/16 E4M3 scales (canonical
  * order); synchronises its stream before returning

@@ -873,3 +873,57 @@ int axo_kv_pool_store_paged_f32(const float *k_stage, const float *v_stage, floa
     }
     return AXO_OK;
 }
+
+/* ------------------------------------------------------------------ */
+/* generic single-token embedding gathers                              */
+/* ------------------------------------------------------------------ */
+
+static float f16_bits_to_f32(uint16_t h) {
+    const uint32_t sign = (uint32_t)(h & 0x8000u) << 16;
+    uint32_t exp = (h >> 10) & 0x1fu, man = h & 0x3ffu, bits;
+    if (exp == 0u) {
+        if (man == 0u) {
+            bits = sign;
+        } else {  /* subnormal: renormalise */
+            int e = -1;
+            do { ++e; man <<= 1; } while (!(man & 0x400u));
+            bits = sign | ((uint32_t)(127 - 15 - e) << 23) | ((man & 0x3ffu) << 13);
+        }
+    } else if (exp == 31u) {
+        bits = sign | 0x7f800000u | (man << 13);
+    } else {
+        bits = sign | ((exp + 112u) << 23) | (man << 13);
+    }
+    float f;
+    memcpy(&f, &bits, sizeof f);
+    return f;
+}
+
+/* axiom_q8_0_embedding_gather_f32_kernel (reference src/axiom_cuda.cu:2213-2240): rows of
+ * hidden/32 blocks of 34 bytes, little-endian F16 scale then 32 signed bytes; a token id at
+ * or beyond token_count gives zeros. */
+int axo_q8_0_embedding_gather_f32(const uint8_t *embedding, uint32_t token_id, uint32_t token_count,
+                                  uint32_t hidden, float *out) {
+    if (!embedding || !out || hidden == 0u || (hidden % 32u) != 0u) return AXO_INVALID;
+    const uint8_t *row = embedding + (size_t)token_id * (hidden / 32u) * 34u;
+    for (uint32_t i = 0; i < hidden; ++i) {
+        if (token_id >= token_count) {
+            out[i] = 0.0f;
+            continue;
+        }
+        const uint8_t *blk = row + (size_t)(i >> 5) * 34u;
+        const float d = f16_bits_to_f32((uint16_t)(blk[0] | ((uint16_t)blk[1] << 8)));
+        out[i] = d * (float)((const int8_t *)(blk + 2))[i & 31u];
+    }
+    return AXO_OK;
+}
+
+/* axiom_f16_embedding_streams_device_kernel (reference src/axiom_cuda.cu:14458-14469) */
+int axo_f16_embedding_streams_f32(const uint16_t *embedding, uint32_t token_id, uint32_t hidden,
+                                  uint32_t streams, float *out) {
+    if (!embedding || !out || hidden == 0u || streams == 0u) return AXO_INVALID;
+    for (uint64_t idx = 0; idx < (uint64_t)hidden * streams; ++idx) {
+        out[idx] = f16_bits_to_f32(embedding[(size_t)token_id * hidden + (uint32_t)(idx % hidden)]);
+    }
+    return AXO_OK;
+}

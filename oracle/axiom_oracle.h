@@ -133,6 +133,12 @@ int axo_bf16_to_e4m3_scale1(const uint16_t *in, uint8_t *out, uint64_t count);
 int axo_embedding_gather_bf16(const uint16_t *table, uint32_t vocab, uint32_t hidden,
                               const uint32_t *ids, uint32_t tokens, uint16_t *out);
 
+/* ---- generic single-token embedding gathers (Q8_0 blocks / F16 rows) ---- */
+int axo_q8_0_embedding_gather_f32(const uint8_t *embedding, uint32_t token_id, uint32_t token_count,
+                                  uint32_t hidden, float *out);
+int axo_f16_embedding_streams_f32(const uint16_t *embedding, uint32_t token_id, uint32_t hidden,
+                                  uint32_t streams, float *out);
+
 /* ---- generic single-row F32 ops (runtime ABI semantics) ---- */
 int axo_rmsnorm_f32(const float *w, const float *x, float *out, uint32_t count, float eps);
 int axo_rmsnorm_f32_hp(const float *w, const float *x, float *out, uint32_t count, float eps);

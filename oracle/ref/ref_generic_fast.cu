@@ -43,3 +43,21 @@ extern "C" int ref_kv_pool_store_paged_f32(const float *k_stage, const float *v_
             k_stage, v_stage, kpool, vpool, tables, pos, tbl_stride, NL, L, BT, pool_stride, kv_dim);
     return ref_done();
 }
+
+extern "C" int ref_q8_0_embedding_gather_f32(const uint8_t *embedding, float *out, uint32_t token_id, uint32_t token_count,
+                                             uint32_t hidden) {
+    axiom_q8_0_embedding_gather_f32_kernel<<<(hidden + 255u) / 256u, 256>>>(embedding, out, token_id, token_count, hidden);
+    return ref_done();
+}
+
+extern "C" int ref_q8_0_embedding_gather_token_f32(const uint8_t *embedding, const uint32_t *token_id, float *out,
+                                                   uint32_t token_count, uint32_t hidden) {
+    axiom_q8_0_embedding_gather_token_f32_kernel<<<(hidden + 255u) / 256u, 256>>>(embedding, token_id, out, token_count, hidden);
+    return ref_done();
+}
+
+extern "C" int ref_f16_embedding_streams(const uint16_t *embedding, float *out, uint32_t token_id, uint32_t hidden, uint32_t streams) {
+    const uint64_t total = (uint64_t)hidden * streams;
+    axiom_f16_embedding_streams_device_kernel<<<(uint32_t)((total + 255u) / 256u), 256>>>(embedding, out, token_id, hidden, streams);
+    return ref_done();
+}

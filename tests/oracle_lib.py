@@ -268,6 +268,18 @@ def embedding_gather_bf16(table_bits, ids):
     return out
 
 
+def q8_0_embedding_gather_f32(embedding_bytes, token_id, token_count, hidden):
+    out = np.empty(hidden, np.float32)
+    _ok(o().axo_q8_0_embedding_gather_f32(_p(embedding_bytes), token_id, token_count, hidden, _p(out)), "q8_0 gather")
+    return out
+
+
+def f16_embedding_streams_f32(embedding_bits, token_id, hidden, streams):
+    out = np.empty(hidden * streams, np.float32)
+    _ok(o().axo_f16_embedding_streams_f32(_p(embedding_bits), token_id, hidden, streams, _p(out)), "f16 streams")
+    return out
+
+
 # ---- generic f32 ops ----
 
 def rmsnorm_f32(w, x, eps, variant="plain"):

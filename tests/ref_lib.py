@@ -23,6 +23,9 @@ SIGNATURES = {
     "ref_qk_norm_partial_rope_cache_temporal8": [vp, vp, vp, vp, vp, vp, vp, vp, vp, u32, u32, i32],
     "ref_qk_norm_partial_rope_cache8": [vp, vp, vp, vp, vp, vp, vp, vp, vp, u32, u32, u32, i32],
     "ref_sigmoid_gate8": [vp, vp, vp],
+    "ref_q8_0_embedding_gather_f32": [vp, vp, u32, u32, u32],
+    "ref_q8_0_embedding_gather_token_f32": [vp, vp, vp, u32, u32],
+    "ref_f16_embedding_streams": [vp, vp, u32, u32, u32],
     "ref_rmsnorm_f32": [vp, vp, vp, u32, f32, i32],
     "ref_rmsnorm_f32_dual": [vp, vp, vp, vp, vp, u32, f32],
     "ref_head_rmsnorm_f32": [vp, u32, u32, f32],

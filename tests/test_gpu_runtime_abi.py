@@ -280,6 +280,78 @@ def test_generic_f32_elementwise_and_paged_store(axk, rt):
         active, tbl, NL, NL, BT, stride, kv_dim) == axk.AXIOM_ERR_INVALID_ARGUMENT  # layer >= n_layers
 
 
+def make_q8_0_table(rng, tokens, hidden):
+    """Rows of hidden/32 blocks: little-endian F16 scale, then 32 signed bytes."""
+    blocks = tokens * hidden // 32
+    table = np.zeros((blocks, 34), np.uint8)
+    scales = (rng.standard_normal(blocks) * 0.01).astype(np.float16)
+    scales[::7] = np.float16(6e-8)  # F16 subnormals
+    table[:, :2] = scales.view(np.uint8).reshape(blocks, 2)
+    table[:, 2:] = rng.integers(-128, 128, (blocks, 32)).astype(np.int8).view(np.uint8)
+    return table.reshape(-1)
+
+
+def test_generic_embedding_gathers(axk, rt):
+    """axiom_runtime_{q8_0_embedding_gather[_token],f16_embedding_streams}_f32_device vs the oracle, bit for bit,
+    and vs the reference's kernels when its harness library is present."""
+    import ref_lib
+
+    lib = axk.lib()
+    rng = np.random.default_rng(7)
+    tokens, hidden = 50, 5120
+    table = make_q8_0_table(rng, tokens, hidden)
+    tb = buf_from(axk, rt, table)
+    ob = axk.DeviceBuffer(rt, hidden * 4 + 64)
+    got = np.empty(hidden, np.float32)
+    for tok in (0, 17, 49):
+        assert lib.axiom_runtime_q8_0_embedding_gather_f32_device(rt.handle, tb.handle, 0, ob.handle, 64, tok, tokens, hidden) == 0
+        full = np.empty(hidden + 16, np.float32); ob.download(full); got = full[16:]
+        want = ol.q8_0_embedding_gather_f32(table, tok, tokens, hidden)
+        assert np.array_equal(got.view(np.uint32), want.view(np.uint32))
+        idb = buf_from(axk, rt, np.array([tok], np.uint32))
+        assert lib.axiom_runtime_q8_0_embedding_gather_token_f32_device(rt.handle, tb.handle, 0, idb.handle, 0, ob.handle, 64,
+                                                                        tokens, hidden) == 0
+        ob.download(full)
+        assert np.array_equal(full[16:].view(np.uint32), want.view(np.uint32))
+    # device-side id beyond the table: zero row; immediate id beyond the table: rejected
+    idb = buf_from(axk, rt, np.array([tokens], np.uint32))
+    assert lib.axiom_runtime_q8_0_embedding_gather_token_f32_device(rt.handle, tb.handle, 0, idb.handle, 0, ob.handle, 64, tokens, hidden) == 0
+    ob.download(full)
+    assert not full[16:].any()
+    inv = axk.AXIOM_ERR_INVALID_ARGUMENT
+    assert lib.axiom_runtime_q8_0_embedding_gather_f32_device(rt.handle, tb.handle, 0, ob.handle, 64, tokens, tokens, hidden) == inv
+    assert lib.axiom_runtime_q8_0_embedding_gather_f32_device(rt.handle, tb.handle, 0, ob.handle, 64, 0, tokens, hidden + 8) == inv
+    assert lib.axiom_runtime_q8_0_embedding_gather_f32_device(rt.handle, tb.handle, 34, ob.handle, 64, 0, tokens, hidden) == inv  # span
+    # F16 rows replicated into streams
+    emb = rng.standard_normal((tokens, hidden)).astype(np.float16)
+    emb[3, :4] = np.array([0.0, -0.0, 6e-8, 65504.0], np.float16)
+    eb = buf_from(axk, rt, emb.view(np.uint16))
+    streams = 4
+    sb = axk.DeviceBuffer(rt, hidden * streams * 4)
+    out = np.empty(hidden * streams, np.float32)
+    for tok in (3, 49):
+        assert lib.axiom_runtime_f16_embedding_streams_device(rt.handle, eb.handle, 0, sb.handle, 0, tok, hidden, streams) == 0
+        sb.download(out)
+        want = ol.f16_embedding_streams_f32(emb.view(np.uint16).reshape(-1), tok, hidden, streams)
+        assert np.array_equal(out.view(np.uint32), want.view(np.uint32))
+        assert np.array_equal(out.reshape(streams, hidden)[2], emb[tok].astype(np.float32))
+    assert lib.axiom_runtime_f16_embedding_streams_device(rt.handle, eb.handle, 0, sb.handle, 0, tokens, hidden, streams) == inv
+    assert lib.axiom_runtime_f16_embedding_streams_device(rt.handle, eb.handle, 0, sb.handle, 0, 0, hidden, streams + 1) == inv
+    if ref_lib.available():
+        import torch
+
+        r = ref_lib.lib()
+        t_dev = torch.from_numpy(table).cuda()
+        o_dev = torch.zeros(hidden, dtype=torch.float32, device="cuda")
+        assert r.ref_q8_0_embedding_gather_f32(t_dev.data_ptr(), o_dev.data_ptr(), 17, tokens, hidden) == 0
+        assert np.array_equal(o_dev.cpu().numpy().view(np.uint32), ol.q8_0_embedding_gather_f32(table, 17, tokens, hidden).view(np.uint32))
+        e_dev = torch.from_numpy(emb.view(np.int16)).cuda()
+        s_dev = torch.zeros(hidden * streams, dtype=torch.float32, device="cuda")
+        assert r.ref_f16_embedding_streams(e_dev.data_ptr(), s_dev.data_ptr(), 3, hidden, streams) == 0
+        assert np.array_equal(s_dev.cpu().numpy().view(np.uint32),
+                              ol.f16_embedding_streams_f32(emb.view(np.uint16).reshape(-1), 3, hidden, streams).view(np.uint32))
+
+
 def test_launch_async_env_is_honoured(axk, rt):
     """With AXIOM_CUDA_LAUNCH_ASYNC=1 the generic ops return right after the launch; results are
     complete after an explicit synchronisation (src/axiom_cuda.cu:162-200 in the reference)."""
