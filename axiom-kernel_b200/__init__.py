@@ -77,6 +77,7 @@ _BUF = [vp, u64]  # (axiom_device_buffer*, byte offset)
 SIGNATURES = {
     "axiom_abi_version": (u32, []),
     "axiom_version": (C.c_char_p, []),
+    "axiom_abi_info_get": (i32, [vp]),
     "axiom_abi_check": (i32, [u32]),
     "axiom_status_string": (C.c_char_p, [i32]),
     "axiom_runtime_create": (i32, [C.POINTER(vp), C.POINTER(AxiomConfig)]),

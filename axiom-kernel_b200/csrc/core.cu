@@ -70,6 +70,19 @@ uint32_t axiom_abi_version(void) { return AXIOM_ABI_VERSION; }
 
 const char *axiom_version(void) { return "axiom-b200-fused 0.1.0 abi=1 cuda sm_100a"; }
 
+int axiom_abi_info_get(axiom_abi_info *out) {
+    if (!out || out->abi_version != AXIOM_ABI_VERSION) return AXIOM_ERR_INVALID_ARGUMENT;
+    std::memset(out, 0, sizeof(*out));
+    out->abi_version = AXIOM_ABI_VERSION;
+    out->header_abi_version = AXIOM_ABI_VERSION;
+    out->runtime_abi_version = AXIOM_ABI_VERSION;
+    out->struct_size = (uint32_t)sizeof(*out);
+    out->version = axiom_version();
+    out->backend = "cuda";
+    out->build_target = "sm_100a";
+    return AXIOM_OK;
+}
+
 int axiom_abi_check(uint32_t header_abi_version) {
     return header_abi_version == AXIOM_ABI_VERSION ? AXIOM_OK : AXIOM_ERR_INVALID_ARGUMENT;
 }

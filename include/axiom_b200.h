@@ -72,9 +72,22 @@ typedef struct {
     uint64_t flags;
 } axiom_config;
 
+/* include/axiom/axiom.h:366-375 */
+typedef struct {
+    uint32_t abi_version;          /* in: AXIOM_ABI_VERSION, else the call is rejected */
+    uint32_t header_abi_version;
+    uint32_t runtime_abi_version;
+    uint32_t struct_size;
+    const char *version;
+    const char *backend;           /* "cuda" */
+    const char *build_target;      /* "sm_100a" */
+    uint64_t flags;
+} axiom_abi_info;
+
 /* include/axiom/axiom.h:377-381 */
 uint32_t axiom_abi_version(void);
 const char *axiom_version(void);
+int axiom_abi_info_get(axiom_abi_info *out);
 int axiom_abi_check(uint32_t header_abi_version);
 const char *axiom_status_string(int status);
 

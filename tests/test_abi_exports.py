@@ -43,6 +43,19 @@ def test_identity_calls_need_no_device(axk):
     assert lib.axiom_abi_check(1) == axk.AXIOM_OK
     assert lib.axiom_abi_check(2) == axk.AXIOM_ERR_INVALID_ARGUMENT
     assert b"sm_100a" in lib.axiom_version()
+
+    class AbiInfo(C.Structure):
+        _fields_ = [("abi_version", C.c_uint32), ("header_abi_version", C.c_uint32), ("runtime_abi_version", C.c_uint32),
+                    ("struct_size", C.c_uint32), ("version", C.c_char_p), ("backend", C.c_char_p), ("build_target", C.c_char_p),
+                    ("flags", C.c_uint64)]
+
+    info = AbiInfo(abi_version=1)
+    assert lib.axiom_abi_info_get(C.byref(info)) == axk.AXIOM_OK
+    assert (info.header_abi_version, info.runtime_abi_version, info.struct_size) == (1, 1, C.sizeof(AbiInfo))
+    assert info.backend == b"cuda" and info.build_target == b"sm_100a" and info.version == lib.axiom_version()
+    stale = AbiInfo(abi_version=2)
+    assert lib.axiom_abi_info_get(C.byref(stale)) == axk.AXIOM_ERR_INVALID_ARGUMENT
+    assert lib.axiom_abi_info_get(None) == axk.AXIOM_ERR_INVALID_ARGUMENT
     assert axk.status_string(0) == "ok" and axk.status_string(1) == "invalid argument"
     assert axk.status_string(7) == "budget exceeded" and axk.status_string(99) == "unknown error"
     assert lib.axiom_nvfp4_scale_plane_bytes(4096, 320, axk.SCALE_TILED) == 32 * 80 * 512
