@@ -117,6 +117,7 @@ SIGNATURES = {
     "axiom_qwen38_fused_swiglu_fp8_bf16_device": (i32, [i32, vp, u32, u32, vp, vp, vp]),
     "axiom_qwen38_fused_swiglu_nvfp4_bf16_device": (i32, [i32, vp, u32, u32, f32, vp, vp, u32, vp]),
     "axiom_qwen38_fused_sigmoid_gate_nvfp4_bf16_device": (i32, [i32, vp, vp, u32, u32, f32, vp, vp, vp, u32, vp]),
+    "axiom_qwen38_fused_top1_f32_device": (i32, [i32, vp, u32, u32, vp, vp]),
     "axiom_qwen38_fused_fp8_quantize_bf16_device": (i32, [i32, vp, u32, u32, vp, vp, vp, vp]),
     "axiom_qwen38_fused_embedding_gather_bf16_device": (i32, [i32, vp, u32, u32, vp, u32, vp, vp, vp]),
     "axiom_qwen38_fused_yarn_inv_freq_device": (i32, [i32, C.POINTER(RopeConfig), vp, vp]),
@@ -225,6 +226,11 @@ def sigmoid_gate_nvfp4(device, attention, gate, rows, width, G, out_bf16, codes,
     return lib().axiom_qwen38_fused_sigmoid_gate_nvfp4_bf16_device(device, _ptr(attention), _ptr(gate), rows, width, G,
                                                                    _ptr(out_bf16), _ptr(codes), _ptr(scales), layout,
                                                                    _stream_handle(stream))
+
+
+def top1(device, logits, rows, vocab, results, stream=None):
+    """results: device buffer of rows x (float value, uint32 token_id, uint32 invalid)."""
+    return lib().axiom_qwen38_fused_top1_f32_device(device, _ptr(logits), rows, vocab, _ptr(results), _stream_handle(stream))
 
 
 def fp8_quantize(device, x_bf16, rows, cols, codes, scales, status_word=None, stream=None):

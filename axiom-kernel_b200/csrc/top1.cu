@@ -1,0 +1,126 @@
+// Greedy next-token selection: per row of logits the largest finite value, the smallest id
+// among equal values, and a flag that is raised when any logit of the row is not finite.
+//
+// Result rule of qwen38_top1_select / qwen38_top1_8_kernel (src/axiom_qwen38_model.cu:408-455,
+// 483-493): value > best, or value == best and id < best id; non-finite logits never win and
+// set `invalid`.  The rule is an order-independent reduction, so any partition of the row
+// gives the reference's result.  The reference's hierarchical path (stage 1 into a global
+// `partials` array, stage 2 over it, :510-600) becomes one launch: a thread-block cluster of
+// eight CTAs owns a row, every CTA reduces its eighth of the vocabulary with 16-byte loads, and
+// the eight partial results meet in the first CTA's shared memory over the cluster's
+// distributed shared memory — no global scratch, no second kernel.
+#include "runtime.hpp"
+
+#include <cooperative_groups.h>
+#include <math_constants.h>
+
+namespace cg = cooperative_groups;
+
+namespace axb {
+namespace {
+
+constexpr uint32_t kTop1Cluster = 8u;
+constexpr uint32_t kTop1Threads = 512u;
+
+struct top1_candidate {
+    float value;
+    uint32_t id;
+    uint32_t invalid;
+};
+
+__device__ __forceinline__ void top1_take(float value, uint32_t id, top1_candidate *best) {
+    if (value > best->value || (value == best->value && id < best->id)) {
+        best->value = value;
+        best->id = id;
+    }
+}
+
+__device__ __forceinline__ void top1_see(float value, uint32_t id, top1_candidate *best) {
+    if ((__float_as_uint(value) & 0x7f800000u) == 0x7f800000u) best->invalid = 1u;  // infinity or NaN
+    else top1_take(value, id, best);
+}
+
+__device__ __forceinline__ void top1_warp(top1_candidate *best) {
+#pragma unroll
+    for (uint32_t off = 16u; off != 0u; off >>= 1u) {
+        const float v = __shfl_xor_sync(0xffffffffu, best->value, off);
+        const uint32_t i = __shfl_xor_sync(0xffffffffu, best->id, off);
+        best->invalid |= __shfl_xor_sync(0xffffffffu, best->invalid, off);
+        top1_take(v, i, best);
+    }
+}
+
+__global__ void __cluster_dims__(kTop1Cluster, 1, 1) __launch_bounds__(kTop1Threads)
+top1_rows_kernel(const float *__restrict__ logits, uint32_t vocab, axiom_top1_result *__restrict__ results) {
+    __shared__ top1_candidate warp_best[kTop1Threads / 32u];
+    __shared__ top1_candidate cluster_best[kTop1Cluster];
+    cg::cluster_group cluster = cg::this_cluster();
+    const uint32_t part = cluster.block_rank();
+    const uint32_t row = blockIdx.x / kTop1Cluster;
+    const uint32_t tid = threadIdx.x, lane = tid & 31u, warp = tid >> 5;
+    allow_dependents();
+    dependency_wait();
+
+    // this CTA's slice of the row, in units of four logits when the row allows 16-byte loads
+    const float *row_logits = logits + (uint64_t)row * vocab;
+    top1_candidate best{-CUDART_INF_F, 0xffffffffu, 0u};
+    const bool vector = (vocab % 4u) == 0u && (reinterpret_cast<uintptr_t>(logits) & 15u) == 0u;
+    if (vector) {
+        const uint32_t quads = vocab / 4u;
+        const uint32_t per = (quads + kTop1Cluster - 1u) / kTop1Cluster;
+        const uint32_t lo = part * per, hi = lo + per < quads ? lo + per : quads;
+        const float4 *src = reinterpret_cast<const float4 *>(row_logits);
+        for (uint32_t q = lo + tid; q < hi; q += kTop1Threads) {
+            float4 v;
+            asm volatile("ld.global.nc.L1::no_allocate.v4.f32 {%0,%1,%2,%3}, [%4];"
+                         : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w) : "l"(src + q));
+            top1_see(v.x, 4u * q, &best);
+            top1_see(v.y, 4u * q + 1u, &best);
+            top1_see(v.z, 4u * q + 2u, &best);
+            top1_see(v.w, 4u * q + 3u, &best);
+        }
+    } else {
+        const uint32_t per = (vocab + kTop1Cluster - 1u) / kTop1Cluster;
+        const uint32_t lo = part * per, hi = lo + per < vocab ? lo + per : vocab;
+        for (uint32_t i = lo + tid; i < hi; i += kTop1Threads) top1_see(row_logits[i], i, &best);
+    }
+    top1_warp(&best);
+    if (lane == 0u) warp_best[warp] = best;
+    __syncthreads();
+    if (warp == 0u) {
+        best = lane < kTop1Threads / 32u ? warp_best[lane] : top1_candidate{-CUDART_INF_F, 0xffffffffu, 0u};
+        top1_warp(&best);
+        if (lane == 0u) {
+            // deposit this CTA's result in the first CTA's shared memory
+            top1_candidate *dst = cluster.map_shared_rank(cluster_best, 0);
+            dst[part] = best;
+        }
+    }
+    cluster.sync();
+    if (part == 0u && warp == 0u) {
+        best = lane < kTop1Cluster ? cluster_best[lane] : top1_candidate{-CUDART_INF_F, 0xffffffffu, 0u};
+        top1_warp(&best);
+        if (lane == 0u) {
+            results[row].value = best.value;
+            results[row].token_id = best.id;
+            results[row].invalid = best.invalid;
+        }
+    }
+}
+
+}  // namespace
+}  // namespace axb
+
+using namespace axb;
+
+extern "C" int axiom_qwen38_fused_top1_f32_device(int device, const float *logits, uint32_t rows, uint32_t vocab,
+                                                  axiom_top1_result *results, void *stream) {
+    if (!logits || !results || rows == 0u || vocab == 0u || rows > 65535u || (reinterpret_cast<uintptr_t>(logits) & 3u)) {
+        return AXIOM_ERR_INVALID_ARGUMENT;
+    }
+    int rc = select_device(device);
+    if (rc != AXIOM_OK) return rc;
+    launch_chained(top1_rows_kernel, dim3(rows * kTop1Cluster), dim3(kTop1Threads), 0, (cudaStream_t)stream, logits, vocab, results);
+    note_launch();
+    return launch_status();
+}

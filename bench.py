@@ -183,7 +183,8 @@ def main():
     ap.add_argument("--skip-e2e", action="store_true")
     ap.add_argument("--skip-cpu", action="store_true")
     ap.add_argument("--only", default=None,
-                    choices=["add_rmsnorm", "add_rmsnorm_tiled", "nvfp4_quantize", "qk", "swiglu_fp8", "swiglu_nvfp4", "chain"],
+                    choices=["add_rmsnorm", "add_rmsnorm_tiled", "nvfp4_quantize", "qk", "swiglu_fp8", "swiglu_nvfp4", "sigmoid_gate",
+                             "top1", "chain"],
                     help="run one configuration alone (profiling aid): device-timed, no e2e / CPU legs")
     ap.add_argument("--rows", type=int, default=0, help="with --only: override the token count")
     args = ap.parse_args()
@@ -400,6 +401,10 @@ def bench_other_ops(torch, axk, wl, local, device, stream, peak, only=None, rows
         bench_qk(torch, axk, wl, local, device, stream, timed, report, rows_override or 8192)
     if want("swiglu_fp8") or want("swiglu_nvfp4"):
         bench_swiglu(torch, axk, wl, local, device, stream, timed, report, rows_override or 16384, want)
+    if want("sigmoid_gate"):
+        bench_sigmoid_gate(torch, axk, wl, local, device, stream, timed, report, rows_override or 8192)
+    if want("top1"):
+        bench_top1(torch, axk, wl, local, device, stream, timed, report)
     if want("chain"):
         out["decode_chain"] = bench_chain(torch, axk, wl, local, device, stream, timed, peak)
     return out
@@ -472,6 +477,32 @@ def bench_swiglu(torch, axk, wl, local, device, stream, timed, report, T, want):
         s4 = torch.empty((T, W // 16), dtype=torch.uint8, device=device)
         ms = timed(lambda i: axk.swiglu_nvfp4(local, gu, T, W, 40.0, c4, s4, 0, stream), n=20)
         report("swiglu_nvfp4", ms, T * 2 * W * 2 + T * W // 2 + T * W // 16, T, "SwiGLU -> NVFP4 (down-projection input)")
+
+
+def bench_sigmoid_gate(torch, axk, wl, local, device, stream, timed, report, T):
+    # attention output gate + o_proj activation quantize: [T x 64*128] attention and gate planes, 2 rotating sets
+    W = 64 * 128
+    sets = []
+    for s in range(2):
+        g = torch.Generator(device=device).manual_seed(40 + s)
+        attn = torch.randn((T, W), generator=g, device=device, dtype=torch.float32).to(torch.bfloat16)
+        gate = (torch.randn((T, W), generator=g, device=device, dtype=torch.float32) * 2).to(torch.bfloat16)
+        sets.append((attn, gate, torch.empty((T, W // 2), dtype=torch.uint8, device=device),
+                     torch.empty((T, W // 16), dtype=torch.uint8, device=device)))
+    ms = timed(lambda i: axk.sigmoid_gate_nvfp4(local, sets[i % 2][0], sets[i % 2][1], T, W, 60.0, None, sets[i % 2][2],
+                                                sets[i % 2][3], 1, stream))
+    report("sigmoid_gate_nvfp4", ms, 2 * T * W * 2 + T * W // 2 + T * W // 16, T,
+           "attention * sigmoid(gate) -> NVFP4 with tiled scales (o_proj input), 64 heads x 128")
+
+
+def bench_top1(torch, axk, wl, local, device, stream, timed, report):
+    # greedy selection over F32 logits: the decode-step tail (8 rows) and a prefill-sized batch
+    for rows, vocab in ((8, 151936), (8, 248320), (256, 151936)):
+        logits = torch.randn((rows, vocab), device=device, dtype=torch.float32)
+        res = torch.empty((rows, 3), dtype=torch.int32, device=device)
+        ms = timed(lambda i: axk.top1(local, logits, rows, vocab, res, stream))
+        report(f"top1_{rows}x{vocab}", ms, rows * vocab * 4 + rows * 12, rows,
+               "one launch, 8-CTA clusters; logits stay in L2 between iterations at 8 rows (latency figure)")
 
 
 def bench_chain(torch, axk, wl, local, device, stream, timed, peak):

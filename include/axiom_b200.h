@@ -210,6 +210,18 @@ int axiom_qwen38_fused_swiglu_nvfp4_bf16_device(int device, const void *gate_up_
  * and/or quantized to NVFP4 (both code outputs or neither).  attention, gate, out: [rows x width] BF16. width % 16 == 0. */
 int axiom_qwen38_fused_sigmoid_gate_nvfp4_bf16_device(int device, const void *attention_bf16, const void *gate_bf16, uint32_t rows, uint32_t width, float global_scale, void *out_bf16, uint8_t *out_codes, uint8_t *out_scales, uint32_t scale_layout, void *stream);
 
+/* Greedy selection over rows of F32 logits.  Replaces qwen38_top1_8_kernel and the hierarchical pair
+ * qwen38_top1_8_stage1/stage2_kernel with its `partials` scratch (src/axiom_qwen38_model.cu:408-600):
+ * largest finite value, smallest id among equals, invalid = 1 if any logit of the row is not finite
+ * (token_id = 0xffffffff when none is finite).  Layout of axiom_qwen38_model_dspark_device_top1_result
+ * (include/axiom/qwen38_model.h:97-101).  logits: [rows x vocab], rows <= 65535. */
+typedef struct {
+    float value;
+    uint32_t token_id;
+    uint32_t invalid;
+} axiom_top1_result;
+int axiom_qwen38_fused_top1_f32_device(int device, const float *logits, uint32_t rows, uint32_t vocab, axiom_top1_result *results, void *stream);
+
 /* Replaces quantize_bf16_rows_e4m3_kernel (src/axiom_qwen38_mtp_compute.cu:239-278)
  * and, for BF16-valued input, quantize_columns_e4m3_kernel.  status_word
  * (optional, device) receives AXIOM_STATUS_WORD_NONFINITE via compare-and-swap. cols % 8 == 0. */

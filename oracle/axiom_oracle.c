@@ -927,3 +927,29 @@ int axo_f16_embedding_streams_f32(const uint16_t *embedding, uint32_t token_id, 
     }
     return AXO_OK;
 }
+
+/* ------------------------------------------------------------------ */
+/* greedy selection                                                    */
+/* ------------------------------------------------------------------ */
+
+/* qwen38_top1_8_kernel / qwen38_top1_select (reference src/axiom_qwen38_model.cu:408-455,
+ * 483-493): the largest finite logit of each row, the smallest id among equal values, and
+ * invalid = 1 when any logit of the row is not finite; id 0xffffffff when none is finite.
+ * out: rows x {float value, uint32 token_id, uint32 invalid} packed as three uint32 words. */
+int axo_top1_f32(const float *logits, uint32_t rows, uint32_t vocab, uint32_t *out) {
+    if (!logits || !out || rows == 0u || vocab == 0u) return AXO_INVALID;
+    AXO_PARALLEL_FOR
+    for (int64_t r = 0; r < (int64_t)rows; ++r) {
+        float best = -INFINITY;
+        uint32_t best_id = 0xffffffffu, invalid = 0u;
+        for (uint32_t i = 0; i < vocab; ++i) {
+            const float v = logits[(size_t)r * vocab + i];
+            if (!isfinite(v)) invalid = 1u;
+            else if (v > best || (v == best && i < best_id)) { best = v; best_id = i; }
+        }
+        memcpy(out + 3 * r, &best, sizeof best);
+        out[3 * r + 1] = best_id;
+        out[3 * r + 2] = invalid;
+    }
+    return AXO_OK;
+}

@@ -133,6 +133,9 @@ int axo_bf16_to_e4m3_scale1(const uint16_t *in, uint8_t *out, uint64_t count);
 int axo_embedding_gather_bf16(const uint16_t *table, uint32_t vocab, uint32_t hidden,
                               const uint32_t *ids, uint32_t tokens, uint16_t *out);
 
+/* ---- greedy selection: rows x {float value, uint32 id, uint32 invalid} ---- */
+int axo_top1_f32(const float *logits, uint32_t rows, uint32_t vocab, uint32_t *out);
+
 /* ---- generic single-token embedding gathers (Q8_0 blocks / F16 rows) ---- */
 int axo_q8_0_embedding_gather_f32(const uint8_t *embedding, uint32_t token_id, uint32_t token_count,
                                   uint32_t hidden, float *out);

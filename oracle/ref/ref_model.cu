@@ -38,3 +38,15 @@ extern "C" int ref_embedding_gather_columns(const uint16_t *embedding, const uin
     qwen38_embedding_gather_columns_kernel<<<columns, kThreads>>>(embedding, token_ids, out, columns);
     return ref_done();
 }
+
+// logits F32 [8][248320]; partials: 8 x 256 results of 12 bytes; results: 8 x 12 bytes.  hierarchical != 0 takes the
+// two-stage path, else the single-kernel one.
+extern "C" int ref_top1_8(const float *logits, void *partials, void *results, int hierarchical) {
+    if (hierarchical) {
+        qwen38_top1_8_stage1_kernel<<<dim3(kTop1Blocks, kBatch), kThreads>>>(logits, (qwen38_top1_result *)partials);
+        qwen38_top1_8_stage2_kernel<<<kBatch, kThreads>>>((const qwen38_top1_result *)partials, (qwen38_top1_result *)results);
+    } else {
+        qwen38_top1_8_kernel<<<kBatch, kThreads>>>(logits, (qwen38_top1_result *)results);
+    }
+    return ref_done();
+}

@@ -268,6 +268,13 @@ def embedding_gather_bf16(table_bits, ids):
     return out
 
 
+def top1_f32(logits):
+    rows, vocab = logits.shape
+    out = np.empty((rows, 3), np.uint32)
+    _ok(o().axo_top1_f32(_p(np.ascontiguousarray(logits)), rows, vocab, _p(out)), "top1")
+    return out
+
+
 def q8_0_embedding_gather_f32(embedding_bytes, token_id, token_count, hidden):
     out = np.empty(hidden, np.float32)
     _ok(o().axo_q8_0_embedding_gather_f32(_p(embedding_bytes), token_id, token_count, hidden, _p(out)), "q8_0 gather")

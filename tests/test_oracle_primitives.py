@@ -167,3 +167,29 @@ def test_yarn_frequencies_flavours_agree_and_ramp():
         assert np.isclose(dev[-1], plain[-1] / 4)  # low frequencies interpolated by the factor
         assert np.all(dev <= plain * (1 + 1e-6)) and np.all(dev >= plain / 4 * (1 - 1e-6))
     assert abs(ol.o().axo_yarn_mscale(4.0) - 1.138629436111989) < 1e-7  # include/axiom/qwen38_attention.h:29
+
+
+def test_top1_rule():
+    """Largest finite value, smallest id among equals, invalid flag (reference src/axiom_qwen38_model.cu:483-493)."""
+    x = np.array([[1.0, 5.0, 5.0, -2.0], [np.nan, -1.0, np.inf, -3.0], [np.nan, np.nan, np.nan, np.nan]], np.float32)
+    out = ol.top1_f32(x)
+    assert out[0, 1] == 1 and out[0, 2] == 0 and out[0, 0] == np.float32(5.0).view(np.uint32)
+    assert out[1, 1] == 1 and out[1, 2] == 1 and out[1, 0] == np.float32(-1.0).view(np.uint32)
+    assert out[2, 1] == 0xFFFFFFFF and out[2, 2] == 1 and out[2, 0] == np.float32(-np.inf).view(np.uint32)
+
+
+def test_q8_0_and_f16_gathers():
+    import struct
+
+    blk = bytearray(34 * 2)
+    blk[0:2] = struct.pack("<e", 0.5)
+    blk[2:34] = bytes((i - 16) & 0xFF for i in range(32))
+    blk[34:36] = struct.pack("<e", -2.0)
+    blk[36:68] = bytes([3] * 32)
+    table = np.frombuffer(bytes(blk), np.uint8)
+    got = ol.q8_0_embedding_gather_f32(table, 0, 1, 64)
+    assert np.array_equal(got[:32], 0.5 * (np.arange(32) - 16)) and np.array_equal(got[32:], np.full(32, -6.0, np.float32))
+    assert not ol.q8_0_embedding_gather_f32(table, 1, 1, 64).any()  # id beyond the table: zeros
+    h = np.array([0.0, 1.5, -65504.0, 6e-8], np.float16)
+    out = ol.f16_embedding_streams_f32(h.view(np.uint16), 0, 4, 3)
+    assert np.array_equal(out.reshape(3, 4), np.tile(h.astype(np.float32), (3, 1)))
