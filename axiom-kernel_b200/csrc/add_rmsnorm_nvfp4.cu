@@ -6,19 +6,22 @@
 // summation order: 256 partial sums over features (c + 256*k) accumulated with
 // fmaf in k order, then the tree 128/64/32/16/8/4/2/1.
 //
-// One kernel for every row count (add_rmsnorm_stream_kernel): persistent CTAs, one per SM,
-// made of independent 4-warp teams (as many teams as the busiest CTA has rows, at most five).  A team owns two (or more) shared-memory
-// slots; its first thread fills a slot with one row (hidden | residual) through
-// 1-D bulk copies that complete on the slot's mbarrier, and refills it the
-// moment the team has finished with it, so the next row is always in flight
-// while the current one is processed and no arithmetic warp issues a global
-// load.  Sweep 1 (merge + sum of squares) gives thread t the feature pairs
-// 256k + 2t, 2t+1: those are partial sums 2t and 2t+1 of the reference order,
-// so the fmaf chains run along k in registers; the 256 partials meet in shared
-// memory and every warp runs the reference tree as a shuffle butterfly.  The
-// merged row is written back into the slot (it is BF16-valued by construction),
-// leaves for HBM as one bulk store, and sweep 2 (normalise + quantize) re-reads
-// it in 16-byte chunks, lane pairs forming the 16-value NVFP4 blocks.
+// Streaming kernel (add_rmsnorm_stream_kernel, two rows per SM and more): persistent CTAs, one
+// per SM, made of up to eight independent 4-warp teams.  A team owns one shared-memory slot (more
+// when rows are narrow); its first thread fills the slot with one row (addend | residual) through
+// 1-D bulk copies that complete on the slot's mbarrier and no arithmetic warp issues a global
+// load.  The kernel is bound by instruction issue, so resident warps matter more than prefetch
+// depth: while a team waits for its next row the others compute, and the addend half of the next
+// row is requested as soon as sweep 1 has consumed the current one.  Sweep 1 (merge + sum of
+// squares) gives thread t the feature pairs 256k + 2t, 2t+1: those are partial sums 2t and 2t+1
+// of the reference order, so the fmaf chains run along k in registers; the 256 partials meet in
+// shared memory and every warp runs the reference tree as a shuffle butterfly.  The merged row is
+// written back into the slot (it is BF16-valued by construction), leaves for HBM as one bulk
+// store, and sweep 2 (normalise + quantize) re-reads it in 16-byte chunks, lane pairs forming the
+// 16-value NVFP4 blocks.
+//
+// Wide-row kernel (add_rmsnorm_wide_row_kernel, decode shapes and the gathered-addend flavour): one
+// CTA per row, one thread per 16-byte chunk, one global round trip per row.
 #include "pipeline.cuh"
 #include "runtime.hpp"
 
