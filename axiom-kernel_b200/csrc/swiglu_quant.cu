@@ -137,27 +137,23 @@ __device__ __forceinline__ void swiglu8(const float *table, const uint4 &g, cons
 
 // Maximum over the CTA; every thread receives it.  kNan: NaN-propagating (a NaN anywhere in the
 // row gives NaN), otherwise fmaxf semantics with the clamp that makes an all-NaN row give 0.
-// One CTA barrier per call: the per-warp staging alternates between two buffers (`phase`), so
-// the writes of the next call cannot overtake the reads of this one, and the buffer used now is
-// rewritten only after every thread has passed the next call's barrier.
 template <bool kNan>
-__device__ __forceinline__ float cta_max(float m, float (*warp_max)[32], uint32_t &phase) {
+__device__ __forceinline__ float cta_max(float m, float *warp_max) {
     const uint32_t lane = threadIdx.x & 31u, warp = threadIdx.x >> 5, warps = (blockDim.x + 31u) >> 5;
 #pragma unroll
     for (uint32_t off = 16u; off != 0u; off >>= 1u) {
         const float o = __shfl_xor_sync(0xffffffffu, m, off);
         m = kNan ? max_nan(m, o) : fmaxf(m, o);
     }
-    float *stage = warp_max[phase];
-    phase ^= 1u;
-    if (lane == 0u) stage[warp] = m;
+    if (lane == 0u) warp_max[warp] = m;
     __syncthreads();
-    float all = lane < warps ? stage[lane] : 0.0f;
+    float all = lane < warps ? warp_max[lane] : 0.0f;
 #pragma unroll
     for (uint32_t off = 16u; off != 0u; off >>= 1u) {
         const float o = __shfl_xor_sync(0xffffffffu, all, off);
         all = kNan ? max_nan(all, o) : fmaxf(all, o);
     }
+    __syncthreads();  // warp_max is reused; measured: alternating two staging buffers to drop this barrier is 4 % slower
     return kNan ? all : fmaxf(all, 0.0f);
 }
 
@@ -172,8 +168,7 @@ fp8_rows_kernel(const uint4 *__restrict__ in, uint32_t rows, uint32_t chunks, ui
                 uint2 *__restrict__ codes, float *__restrict__ scales, uint32_t *__restrict__ status_word,
                 const float *__restrict__ device_table) {
     extern __shared__ __align__(16) float silu_table[];
-    __shared__ float warp_max[2][32];
-    uint32_t max_phase = 0u;
+    __shared__ float warp_max[32];
     constexpr bool kSwiglu = kOp != row_op::plain_finite_only;
     constexpr bool kTable = kOp == row_op::swiglu_table;
     const uint32_t tid = threadIdx.x;
@@ -219,13 +214,13 @@ fp8_rows_kernel(const uint4 *__restrict__ in, uint32_t rows, uint32_t chunks, ui
                 }
             }
         }
-        m = kSwiglu ? cta_max<true>(m, warp_max, max_phase) : cta_max<false>(m, warp_max, max_phase);
+        m = kSwiglu ? cta_max<true>(m, warp_max) : cta_max<false>(m, warp_max);
         if (kSwiglu && !(m == m)) {
             // a NaN somewhere in the row: the reference's maximum drops it
             float d = 0.0f;
 #pragma unroll
             for (int k = 0; k < CPT; ++k) d = fmaxf(d, absmax8_drop_nan(y[k]));
-            m = cta_max<false>(d, warp_max, max_phase);
+            m = cta_max<false>(d, warp_max);
             nonfinite = true;
         }
         float scale = m == 0.0f ? 1.0f : __fdiv_rn(m, 448.0f);

@@ -70,14 +70,28 @@ top1_rows_kernel(const float *__restrict__ logits, uint32_t vocab, axiom_top1_re
         const uint32_t per = (quads + kTop1Cluster - 1u) / kTop1Cluster;
         const uint32_t lo = part * per, hi = lo + per < quads ? lo + per : quads;
         const float4 *src = reinterpret_cast<const float4 *>(row_logits);
-        for (uint32_t q = lo + tid; q < hi; q += kTop1Threads) {
-            float4 v;
-            asm volatile("ld.global.nc.L1::no_allocate.v4.f32 {%0,%1,%2,%3}, [%4];"
-                         : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w) : "l"(src + q));
-            top1_see(v.x, 4u * q, &best);
-            top1_see(v.y, 4u * q + 1u, &best);
-            top1_see(v.z, 4u * q + 2u, &best);
-            top1_see(v.w, 4u * q + 3u, &best);
+        constexpr uint32_t kBatch = 4u;  // loads in flight per thread
+        for (uint32_t q0 = lo + tid; q0 < hi; q0 += kBatch * kTop1Threads) {
+            float4 v[kBatch];
+#pragma unroll
+            for (uint32_t b = 0; b < kBatch; ++b) {
+                const uint32_t q = q0 + b * kTop1Threads;
+                v[b] = make_float4(-CUDART_INF_F, -CUDART_INF_F, -CUDART_INF_F, -CUDART_INF_F);
+                if (q < hi) {
+                    asm volatile("ld.global.nc.L1::no_allocate.v4.f32 {%0,%1,%2,%3}, [%4];"
+                                 : "=f"(v[b].x), "=f"(v[b].y), "=f"(v[b].z), "=f"(v[b].w) : "l"(src + q));
+                }
+            }
+#pragma unroll
+            for (uint32_t b = 0; b < kBatch; ++b) {
+                const uint32_t q = q0 + b * kTop1Threads;
+                if (q < hi) {
+                    top1_see(v[b].x, 4u * q, &best);
+                    top1_see(v[b].y, 4u * q + 1u, &best);
+                    top1_see(v[b].z, 4u * q + 2u, &best);
+                    top1_see(v[b].w, 4u * q + 3u, &best);
+                }
+            }
         }
     } else {
         const uint32_t per = (vocab + kTop1Cluster - 1u) / kTop1Cluster;
