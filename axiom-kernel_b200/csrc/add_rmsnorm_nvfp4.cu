@@ -57,6 +57,7 @@ struct norm_args {
     const uint32_t *token_ids;
     uint32_t vocab;
     uint32_t *status_word;  // may be null
+    uint4 *tap;             // may be null: second copy of the updated residual rows (layer tap)
 };
 
 // Second sweep over one row held in shared memory as BF16: n = bf16((r * inv) * gamma), optional
@@ -150,6 +151,7 @@ add_rmsnorm_stream_kernel(const norm_args a) {
     const uint32_t cta_rows = blockIdx.x < a.rows ? (a.rows - blockIdx.x + gridDim.x - 1u) / gridDim.x : 0u;
     const uint32_t my_rows = team < cta_rows ? (cta_rows - team + teams - 1u) / teams : 0u;
     const float count = (float)a.cols;
+    const bool stores = kAdd || a.tap != nullptr;  // rows leave shared memory through bulk stores
     const uint32_t k_iters = (a.cols + 255u) / 256u;                      // sweep 1: feature pairs 256k + 2t
     const uint32_t c_iters = (a.chunks_per_row + kTeamThreads - 1u) / kTeamThreads;  // sweep 2: chunks t + 128k
 
@@ -215,13 +217,14 @@ add_rmsnorm_stream_kernel(const norm_args a) {
             }
         }
         reinterpret_cast<float2 *>(my_partials)[t] = p;
-        if (kAdd) fence_async_shared();
+        if (stores) fence_async_shared();
         team_barrier(team);
-        if (kAdd && t == 0u) {
-            // the merged row leaves as one bulk store; the slot stays in use until it has been read
-            bulk_store(a.residual + base, res_sh, row_bytes);
+        if (stores && t == 0u) {
+            // the merged row leaves as one bulk store (two with a tap); the slot stays in use until it has been read
+            if (kAdd) bulk_store(a.residual + base, res_sh, row_bytes);
+            if (a.tap) bulk_store(a.tap + base, res_sh, row_bytes);
             bulk_commit();
-            if (i + spt < my_rows) issue_addend(i + spt);  // every thread is past its reads of the addend half
+            if (kAdd && i + spt < my_rows) issue_addend(i + spt);  // every thread is past its reads of the addend half
         }
         // Reference tree over the 256 partials c: strides 128,64,32 then 16,8,4,2,1.  With lane l
         // holding c = 8l + e, strides 128..8 are the lane butterfly 16,8,4,2,1 applied to each e
@@ -266,11 +269,11 @@ add_rmsnorm_stream_kernel(const norm_args a) {
         // the whole team is done with the slot: refill it with the row that comes spt rows later
         team_barrier(team);
         if (t == 0u) {
-            if (kAdd) bulk_wait_read_all();
+            if (stores) bulk_wait_read_all();
             if (i + spt < my_rows) issue_residual(i + spt);
         }
     }
-    if (kAdd && t == 0u) bulk_wait_read_all();
+    if (stores && t == 0u) bulk_wait_read_all();
 }
 
 // ---------------------------------------------------------------------------
@@ -327,6 +330,7 @@ add_rmsnorm_wide_row_kernel(const norm_args a) {
                     m[c].z = add_bf16x2(m[c].z, h.z); m[c].w = add_bf16x2(m[c].w, h.w);
                     st_stream(a.residual + base + q, m[c]);
                 }
+                if (a.tap) st_stream(a.tap + base + q, m[c]);
                 merged_sh[q] = m[c];
             }
         }
@@ -468,7 +472,15 @@ int launch_gather_add_rmsnorm_nvfp4_bf16(const void *table, uint32_t vocab, cons
 int launch_add_rmsnorm_nvfp4_bf16(const void *hidden, void *residual, const void *gamma, float eps, uint32_t rows,
                                   uint32_t cols, float G, void *norm_out, uint8_t *codes, uint8_t *scales,
                                   uint32_t layout, cudaStream_t stream) {
+    return launch_add_rmsnorm_tap_nvfp4_bf16(hidden, residual, gamma, eps, rows, cols, G, norm_out, codes, scales, layout,
+                                             nullptr, stream);
+}
+
+int launch_add_rmsnorm_tap_nvfp4_bf16(const void *hidden, void *residual, const void *gamma, float eps, uint32_t rows,
+                                      uint32_t cols, float G, void *norm_out, uint8_t *codes, uint8_t *scales,
+                                      uint32_t layout, void *tap, cudaStream_t stream) {
     norm_args a{};
+    a.tap = (uint4 *)tap;
     a.hidden = (const uint4 *)hidden;
     a.residual = (uint4 *)residual;
     a.gamma = (const uint16_t *)gamma;
@@ -570,5 +582,28 @@ extern "C" int axiom_qwen38_fused_gather_add_rmsnorm_nvfp4_bf16_device(
     launch_gather_add_rmsnorm_nvfp4_bf16(table_bf16, vocab, token_ids, residual_bf16, gamma_bf16, eps, rows, cols,
                                          out_codes ? global_scale : 1.0f, norm_out_bf16, out_codes, out_scales, scale_layout,
                                          status_word, (cudaStream_t)stream);
+    return launch_status();
+}
+
+extern "C" int axiom_qwen38_fused_add_rmsnorm_nvfp4_tap_bf16_device(
+        int device, const void *hidden_bf16, void *residual_bf16, const void *gamma_bf16, float eps, uint32_t rows,
+        uint32_t cols, float global_scale, void *norm_out_bf16, uint8_t *out_codes, uint8_t *out_scales,
+        uint32_t scale_layout, void *tap_out_bf16, void *stream) {
+    if (!tap_out_bf16 || !aligned16(tap_out_bf16) || tap_out_bf16 == residual_bf16) return AXIOM_ERR_INVALID_ARGUMENT;
+    if (!residual_bf16 || !gamma_bf16 || rows == 0u || cols == 0u || (cols % kGroup) != 0u || cols > 16384u ||
+        scale_layout > AXIOM_SCALE_LAYOUT_TILED || !(eps > 0.0f) || !std::isfinite(eps)) {
+        return AXIOM_ERR_INVALID_ARGUMENT;
+    }
+    if ((out_codes == nullptr) != (out_scales == nullptr)) return AXIOM_ERR_INVALID_ARGUMENT;
+    if (!out_codes && !norm_out_bf16) return AXIOM_ERR_INVALID_ARGUMENT;
+    if (out_codes && !valid_scale(global_scale)) return AXIOM_ERR_INVALID_ARGUMENT;
+    if ((hidden_bf16 && !aligned16(hidden_bf16)) || !aligned16(residual_bf16) || !aligned16(gamma_bf16) ||
+        (norm_out_bf16 && !aligned16(norm_out_bf16)) || (out_codes && (reinterpret_cast<uintptr_t>(out_codes) & 3u))) {
+        return AXIOM_ERR_INVALID_ARGUMENT;
+    }
+    int rc = select_device(device);
+    if (rc != AXIOM_OK) return rc;
+    launch_add_rmsnorm_tap_nvfp4_bf16(hidden_bf16, residual_bf16, gamma_bf16, eps, rows, cols, out_codes ? global_scale : 1.0f,
+                                      norm_out_bf16, out_codes, out_scales, scale_layout, tap_out_bf16, (cudaStream_t)stream);
     return launch_status();
 }

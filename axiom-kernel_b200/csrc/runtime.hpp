@@ -56,6 +56,9 @@ int launch_add_bf16(const void *a, const void *b, void *out, uint64_t count, cud
 int launch_add_rmsnorm_nvfp4_bf16(const void *hidden, void *residual, const void *gamma, float eps, uint32_t rows,
                                   uint32_t cols, float G, void *norm_out, uint8_t *codes, uint8_t *scales,
                                   uint32_t layout, cudaStream_t stream);
+int launch_add_rmsnorm_tap_nvfp4_bf16(const void *hidden, void *residual, const void *gamma, float eps, uint32_t rows,
+                                      uint32_t cols, float G, void *norm_out, uint8_t *codes, uint8_t *scales,
+                                      uint32_t layout, void *tap, cudaStream_t stream);
 int launch_swiglu_fp8_bf16(const void *gate_up, uint32_t rows, uint32_t width, uint8_t *codes, float *scales,
                            cudaStream_t stream);
 int launch_swiglu_nvfp4_bf16(const void *gate_up, uint32_t rows, uint32_t width, float G, uint8_t *codes,

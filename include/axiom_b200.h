@@ -190,6 +190,10 @@ int axiom_qwen38_fused_add_bf16_device(int device, const void *a_bf16, const voi
  * cols % 16 == 0, cols <= 16384. */
 int axiom_qwen38_fused_add_rmsnorm_nvfp4_bf16_device(int device, const void *hidden_bf16, void *residual_bf16, const void *gamma_bf16, float eps, uint32_t rows, uint32_t cols, float global_scale, void *norm_out_bf16, uint8_t *out_codes, uint8_t *out_scales, uint32_t scale_layout, void *stream);
 
+/* The same with a layer tap: tap_out_bf16 [rows x cols] receives a second copy of the updated residual rows
+ * (qwen38_capture_tap8_kernel, src/axiom_qwen38_model.cu:343-351, folded into the write of the residual). */
+int axiom_qwen38_fused_add_rmsnorm_nvfp4_tap_bf16_device(int device, const void *hidden_bf16, void *residual_bf16, const void *gamma_bf16, float eps, uint32_t rows, uint32_t cols, float global_scale, void *norm_out_bf16, uint8_t *out_codes, uint8_t *out_scales, uint32_t scale_layout, void *tap_out_bf16, void *stream);
+
 /* The same with the addend gathered from an embedding table: residual[r] = bf16(residual[r] + table[token_ids[r]]),
  * then norm and quantize as above — qwen38_embedding_gather_columns_kernel (src/axiom_qwen38_model.cu:321-341) fused
  * into the first norm of the chain, so the gathered rows never make a round trip through HBM.  id >= vocab adds a

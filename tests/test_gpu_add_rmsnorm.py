@@ -146,3 +146,35 @@ def test_residual_add_over_all_exponents(axk, cuda_device):
         assert axk.add_rmsnorm_nvfp4(0, hd, r, gd, 1e-6, rows, 5120, 1.0, norm, None, None, 0) == axk.AXIOM_OK
         sync()
         assert np.array_equal(host(r, np.uint16).reshape(rows, 5120), ol.add_bf16(a, b))
+
+
+@pytest.mark.parametrize("rows", [8, 600])
+@pytest.mark.parametrize("with_addend", [True, False])
+def test_layer_tap_is_a_copy_of_the_updated_residual(axk, cuda_device, rows, with_addend):
+    """The tap entry gives the plain entry's outputs plus a second copy of the residual rows as they leave
+    (both kernels, add and norm-only modes)."""
+    import torch
+    from gpu_util import dev, host, sync
+
+    cols = 5120
+    hidden, residual, gamma = wl.add_rmsnorm_inputs_np(rows, cols)
+    outs = []
+    for tap_entry in (False, True):
+        h, r, g = dev(hidden), dev(residual), dev(gamma)
+        norm = torch.zeros((rows, cols), dtype=torch.int16, device="cuda")
+        codes = torch.zeros((rows, cols // 2), dtype=torch.uint8, device="cuda")
+        scales = torch.zeros((rows, cols // 16), dtype=torch.uint8, device="cuda")
+        tap = torch.full((rows, cols), 0x5555, dtype=torch.int16, device="cuda")
+        addend = h if with_addend else None
+        if tap_entry:
+            assert axk.add_rmsnorm_nvfp4_tap(0, addend, r, g, 1e-6, rows, cols, 80.0, norm, codes, scales, 0, tap) == axk.AXIOM_OK
+        else:
+            assert axk.add_rmsnorm_nvfp4(0, addend, r, g, 1e-6, rows, cols, 80.0, norm, codes, scales, 0) == axk.AXIOM_OK
+        sync()
+        outs.append([host(x, np.uint8) for x in (r, norm, codes, scales)])
+        if tap_entry:
+            assert np.array_equal(host(tap, np.uint16), host(r, np.uint16))
+    for a, b in zip(*outs):
+        assert np.array_equal(a, b)
+    assert axk.add_rmsnorm_nvfp4_tap(0, None, dev(residual), dev(gamma), 1e-6, rows, cols, 80.0, None, None, None, 0,
+                                     None) == axk.AXIOM_ERR_INVALID_ARGUMENT
