@@ -366,16 +366,6 @@ qk_norm_rope_stream_kernel(const qk_dev_args a, const qk_stream_geom g) {
     allow_dependents();
     dependency_wait();
 
-    for (uint32_t i = tid; i < D; i += blockDim.x) {
-        gq_sh[i] = a.q_heads ? __uint_as_float((uint32_t)a.q_gamma[i] << 16) : 0.0f;
-        gk_sh[i] = a.k_heads ? __uint_as_float((uint32_t)a.k_gamma[i] << 16) : 0.0f;
-    }
-    if (lead) {
-        for (uint32_t j = 0; j < g.slots; ++j) mbar_init(bars + j, 1u);
-        mbar_init_fence();
-    }
-    __syncthreads();
-
     const bool fp8_cache = (a.flags & AXIOM_QK_FLAG_CACHE_E4M3) != 0u;
     // tokens of this CTA: blockIdx.x + n * gridDim.x; this team takes n = team + teams * i
     const uint32_t cta_tokens = a.tokens > blockIdx.x ? (a.tokens - blockIdx.x + gridDim.x - 1u) / gridDim.x : 0u;
@@ -385,18 +375,31 @@ qk_norm_rope_stream_kernel(const qk_dev_args a, const qk_stream_geom g) {
     // are the older bulk group: only they have to be done reading) and slots - 1 tokens are
     // requested up front; fewer slots are refilled as soon as their own stores have drained.
     const uint32_t ahead = g.slots > 2u ? g.slots - 1u : g.slots;
+    auto issue = [&](uint32_t i) {  // the manager's first lane
+        const uint64_t tok = token_of(i);
+        const uint32_t j = i % g.slots;
+        uint8_t *slot = my_slots + (size_t)j * g.slot_bytes;
+        mbar_arrive_expect_tx(bars + j, q_bytes + k_bytes);
+        if (q_bytes) bulk_load(slot, reinterpret_cast<const uint8_t *>(a.q) + tok * q_bytes, q_bytes, bars + j);
+        if (k_bytes) bulk_load(slot + q_bytes, reinterpret_cast<const uint8_t *>(a.k) + tok * k_bytes, k_bytes, bars + j);
+    };
+
+    // the first tokens are requested before anything else is set up: nobody else touches the
+    // barriers or the slots until the CTA barrier below
+    if (lead) {
+        for (uint32_t j = 0; j < g.slots; ++j) mbar_init(bars + j, 1u);
+        mbar_init_fence();
+        for (uint32_t i = 0; i < ahead && i < my_tokens; ++i) issue(i);
+    }
+    for (uint32_t i = tid; i < D; i += blockDim.x) {
+        gq_sh[i] = a.q_heads ? __uint_as_float((uint32_t)a.q_gamma[i] << 16) : 0.0f;
+        gk_sh[i] = a.k_heads ? __uint_as_float((uint32_t)a.k_gamma[i] << 16) : 0.0f;
+    }
+    __syncthreads();
 
     if (manager) {
         // ------------------------------------------------------------------ manager warp
         const uint32_t ml = t - workers;  // lane
-        auto issue = [&](uint32_t i) {
-            const uint64_t tok = token_of(i);
-            const uint32_t j = i % g.slots;
-            uint8_t *slot = my_slots + (size_t)j * g.slot_bytes;
-            mbar_arrive_expect_tx(bars + j, q_bytes + k_bytes);
-            if (q_bytes) bulk_load(slot, reinterpret_cast<const uint8_t *>(a.q) + tok * q_bytes, q_bytes, bars + j);
-            if (k_bytes) bulk_load(slot + q_bytes, reinterpret_cast<const uint8_t *>(a.k) + tok * k_bytes, k_bytes, bars + j);
-        };
         // table entry that maps a position's logical cache block (~0: outside the table)
         auto table_index = [&](uint32_t pos, uint32_t tok) -> uint64_t {
             uint32_t lb = pos / a.block_tokens;
@@ -415,9 +418,6 @@ qk_norm_rope_stream_kernel(const qk_dev_args a, const qk_stream_geom g) {
                 nsin_t[p] = -sv;
             }
         };
-        if (lead) {
-            for (uint32_t i = 0; i < ahead && i < my_tokens; ++i) issue(i);
-        }
         // positions run two tokens ahead and block-table entries one (dependent loads off the critical path)
         const bool paged = a.k_pool != nullptr && lead;
         uint32_t pos_cur = my_tokens > 0u ? a.positions[token_of(0u)] : 0u;
