@@ -113,6 +113,7 @@ SIGNATURES = {
     "axiom_qwen38_fused_nvfp4_quantize_bf16_device": (i32, [i32, vp, u32, u32, f32, vp, vp, u32, vp]),
     "axiom_qwen38_fused_add_bf16_device": (i32, [i32, vp, vp, vp, u64, vp]),
     "axiom_qwen38_fused_add_rmsnorm_nvfp4_bf16_device": (i32, [i32, vp, vp, vp, f32, u32, u32, f32, vp, vp, vp, u32, vp]),
+    "axiom_qwen38_fused_fp8_epilogue_add_rmsnorm_nvfp4_device": (i32, [i32, vp, vp, vp, vp, vp, f32, u32, u32, f32, vp, vp, vp, u32, vp]),
     "axiom_qwen38_fused_add_rmsnorm_nvfp4_tap_bf16_device": (i32, [i32, vp, vp, vp, f32, u32, u32, f32, vp, vp, vp, u32, vp, vp]),
     "axiom_qwen38_fused_gather_add_rmsnorm_nvfp4_bf16_device": (i32, [i32, vp, u32, vp, vp, vp, f32, u32, u32, f32, vp, vp, vp, u32, vp, vp]),
     "axiom_qwen38_fused_swiglu_fp8_bf16_device": (i32, [i32, vp, u32, u32, vp, vp, vp]),
@@ -214,6 +215,13 @@ def swiglu_fp8(device, gate_up, rows, width, codes, scales, stream=None):
 def swiglu_nvfp4(device, gate_up, rows, width, global_scale, codes, scales, layout=SCALE_CANONICAL, stream=None):
     return lib().axiom_qwen38_fused_swiglu_nvfp4_bf16_device(
         device, _ptr(gate_up), rows, width, global_scale, _ptr(codes), _ptr(scales), layout, _stream_handle(stream))
+
+
+def fp8_epilogue_add_rmsnorm_nvfp4(device, gemm_out, weight_scale, input_scale, residual, gamma, eps, rows, cols, global_scale,
+                                   norm_out, codes, scales, layout=SCALE_CANONICAL, stream=None):
+    return lib().axiom_qwen38_fused_fp8_epilogue_add_rmsnorm_nvfp4_device(
+        device, _ptr(gemm_out), _ptr(weight_scale), _ptr(input_scale), _ptr(residual), _ptr(gamma), eps, rows, cols,
+        global_scale, _ptr(norm_out), _ptr(codes), _ptr(scales), layout, _stream_handle(stream))
 
 
 def add_rmsnorm_nvfp4_tap(device, hidden, residual, gamma, eps, rows, cols, global_scale, norm_out, codes, scales, layout, tap,

@@ -58,7 +58,18 @@ struct norm_args {
     uint32_t vocab;
     uint32_t *status_word;  // may be null
     uint4 *tap;             // may be null: second copy of the updated residual rows (layer tap)
+    // scaled-F32 addend (kScaledF32): raw FP8-GEMM accumulators with their per-feature and per-token scales
+    const float *hidden_f32;        // [rows x cols]
+    const uint16_t *weight_scale;   // [cols] BF16
+    const float *input_scale;       // [rows]
 };
+
+// What is added to the residual before the norm.
+//   kBf16:      a BF16 tensor (or, in the wide-row kernel, rows gathered from a BF16 table)
+//   kScaledF32: bf16((raw * weight_scale[feature]) * input_scale[token]) of raw F32 accumulators — the FP8 GEMM's
+//               scale epilogue (fp8_group_row_scale_bf16_epilogue_kernel, src/axiom_qwen38_fp8.cu:250-262) evaluated
+//               in this kernel's prologue instead of in a pass of its own
+enum addend_kind : int { kNone = 0, kBf16 = 1, kScaledF32 = 2 };
 
 // Second sweep over one row held in shared memory as BF16: n = bf16((r * inv) * gamma), optional
 // BF16 copy out, NVFP4 quantize.  Thread t takes the 16-byte chunks t + 128k; lane pairs form
@@ -121,16 +132,19 @@ __device__ __forceinline__ void team_barrier(uint32_t team) {
 }
 
 // Shared memory: [teams x slots x slot_bytes][gamma F32, two planes][scale table][partials teams x 256][barriers]
-template <bool kAdd, bool kFull>
+template <int kAddend, bool kFull>
 __global__ void __launch_bounds__(kMaxTeams * kTeamThreads, 1)
 add_rmsnorm_stream_kernel(const norm_args a) {
     extern __shared__ __align__(128) uint8_t smem[];
+    constexpr bool kAdd = kAddend != kNone;
     const uint32_t teams = blockDim.x / kTeamThreads;
     const uint32_t spt = a.ring_slots;  // slots per team
     const uint32_t row_bytes = a.cols * 2u;
-    const uint32_t slot_bytes = kAdd ? 2u * row_bytes : row_bytes;
+    const uint32_t addend_bytes = kAddend == kScaledF32 ? 2u * row_bytes : kAddend == kBf16 ? row_bytes : 0u;
+    const uint32_t slot_bytes = addend_bytes + row_bytes;
     float *gamma_sh = reinterpret_cast<float *>(smem + (size_t)teams * spt * slot_bytes);
-    scale_lut_entry *lut = reinterpret_cast<scale_lut_entry *>(gamma_sh + a.cols);
+    float *wscale_sh = gamma_sh + a.cols;  // [cols] F32, kScaledF32 only
+    scale_lut_entry *lut = reinterpret_cast<scale_lut_entry *>(wscale_sh + (kAddend == kScaledF32 ? a.cols : 0u));
     float *partials = reinterpret_cast<float *>(lut + 128);                      // [teams][256]
     uint64_t *bars = reinterpret_cast<uint64_t *>(partials + teams * 256u);      // [teams][kMaxSlotsPerTeam]
 
@@ -162,14 +176,16 @@ add_rmsnorm_stream_kernel(const norm_args a) {
     auto issue_addend = [&](uint32_t i) {  // thread 0 of the team
         const uint64_t row = blockIdx.x + (uint64_t)(team + teams * i) * gridDim.x;
         const uint32_t j = i % spt;
-        mbar_expect_tx(my_bars + j, row_bytes);
-        bulk_load(my_slots + (size_t)j * slot_bytes, a.hidden + row * a.chunks_per_row, row_bytes, my_bars + j);
+        mbar_expect_tx(my_bars + j, addend_bytes);
+        const void *src = kAddend == kScaledF32 ? static_cast<const void *>(a.hidden_f32 + row * a.cols)
+                                                : static_cast<const void *>(a.hidden + row * a.chunks_per_row);
+        bulk_load(my_slots + (size_t)j * slot_bytes, src, addend_bytes, my_bars + j);
     };
     auto issue_residual = [&](uint32_t i) {
         const uint64_t row = blockIdx.x + (uint64_t)(team + teams * i) * gridDim.x;
         const uint32_t j = i % spt;
         mbar_arrive_expect_tx(my_bars + j, row_bytes);
-        bulk_load(my_slots + (size_t)j * slot_bytes + (kAdd ? row_bytes : 0u), a.residual + row * a.chunks_per_row, row_bytes,
+        bulk_load(my_slots + (size_t)j * slot_bytes + addend_bytes, a.residual + row * a.chunks_per_row, row_bytes,
                   my_bars + j);
     };
     auto issue = [&](uint32_t i) {
@@ -185,11 +201,16 @@ add_rmsnorm_stream_kernel(const norm_args a) {
     for (uint32_t f = tid; f < a.cols; f += blockDim.x) {
         gamma_sh[((f >> 2) & 1u) * (a.cols >> 1) + (f >> 3) * 4u + (f & 3u)] = __uint_as_float((uint32_t)a.gamma[f] << 16);
     }
+    if (kAddend == kScaledF32) {
+        for (uint32_t f = tid; f < a.cols; f += blockDim.x) wscale_sh[f] = __uint_as_float((uint32_t)a.weight_scale[f] << 16);
+    }
     const bool lut_safe = build_scale_lut(lut, a.codes ? a.G : 1.0f);  // contains the CTA barrier
 
     bool faulted = false;
     for (uint32_t i = 0; i < my_rows; ++i) {
         const uint32_t j = i % spt;
+        float token_scale = 1.0f;
+        if (kAddend == kScaledF32) token_scale = a.input_scale[blockIdx.x + (team + teams * i) * gridDim.x];
         // A wait that ran out raises the fault word; the team carries on (on whatever the slot
         // holds) so that its barriers stay matched, and stops waiting.
         if (!faulted && !mbar_wait(my_bars + j, (i / spt) & 1u)) faulted = true;
@@ -197,7 +218,10 @@ add_rmsnorm_stream_kernel(const norm_args a) {
         const uint64_t base = (uint64_t)row * a.chunks_per_row;
         uint8_t *slot = my_slots + (size_t)j * slot_bytes;
         const uint32_t *hid_sh = reinterpret_cast<const uint32_t *>(slot) + t;
-        uint32_t *res_sh = reinterpret_cast<uint32_t *>(slot + (kAdd ? row_bytes : 0u));
+        uint32_t *res_sh = reinterpret_cast<uint32_t *>(slot + addend_bytes);
+        const float2 *raw_sh = reinterpret_cast<const float2 *>(slot) + t;        // kScaledF32: feature pairs as F32
+        const float2 *ws_sh = reinterpret_cast<const float2 *>(wscale_sh) + t;
+        const float2 ts2 = make_float2(token_scale, token_scale);
 
         // sweep 1: merge in place; this thread's two fmaf chains (partials 2t and 2t+1)
         float2 p = make_float2(0.f, 0.f);
@@ -207,8 +231,13 @@ add_rmsnorm_stream_kernel(const norm_args a) {
             for (uint32_t k = 0; k < k_iters; ++k) {
                 if (kFull || 256u * k + 2u * t < a.cols) {
                     uint32_t m = res_w[128u * k];
-                    if (kAdd) {
+                    if (kAddend == kBf16) {
                         m = add_bf16x2(m, hid_sh[128u * k]);  // bf16(bf16(res) + bf16(add))
+                        res_w[128u * k] = m;
+                    } else if (kAddend == kScaledF32) {
+                        // addend = bf16((raw * weight_scale) * token_scale), the reference's epilogue expression
+                        const float2 h = __fmul2_rn(__fmul2_rn(raw_sh[128u * k], ws_sh[128u * k]), ts2);
+                        m = add_bf16x2(m, pack_bf16x2(h.x, h.y));
                         res_w[128u * k] = m;
                     }
                     const float2 v = make_float2(bf16_lo(m), bf16_hi(m));
@@ -286,9 +315,10 @@ add_rmsnorm_stream_kernel(const norm_args a) {
 // ---------------------------------------------------------------------------
 constexpr uint32_t kWideMaxChunksPerThread = 2u;  // 16384 columns = 2048 chunks over 1024 threads
 
-template <bool kAdd>
+template <int kAddend>
 __global__ void __launch_bounds__(1024, 1)
 add_rmsnorm_wide_row_kernel(const norm_args a) {
+    constexpr bool kAdd = kAddend != kNone;
     extern __shared__ __align__(16) uint8_t smem[];
     uint4 *merged_sh = reinterpret_cast<uint4 *>(smem);  // [chunks_per_row]
     __shared__ scale_lut_entry lut[128];
@@ -302,7 +332,9 @@ add_rmsnorm_wide_row_kernel(const norm_args a) {
     for (uint32_t row = blockIdx.x; row < a.rows; row += gridDim.x) {
         const uint64_t base = (uint64_t)row * a.chunks_per_row;
         uint32_t token_id = 0u;
-        if (kAdd && a.table) {
+        float token_scale = 1.0f;
+        if (kAddend == kScaledF32) token_scale = a.input_scale[row];
+        if (kAddend == kBf16 && a.table) {
             token_id = a.token_ids[row];
             if (token_id >= a.vocab && tid == 0u && a.status_word) {
                 atomicCAS(a.status_word, AXIOM_STATUS_WORD_OK, AXIOM_STATUS_WORD_BAD_ADDRESS);
@@ -317,12 +349,23 @@ add_rmsnorm_wide_row_kernel(const norm_args a) {
             if (q < a.chunks_per_row) {
                 m[c] = ld_stream(a.residual + base + q);
                 uint4 h = make_uint4(0u, 0u, 0u, 0u);
-                if (kAdd) {
+                if (kAddend == kBf16) {
                     if (a.table) {  // gathered addend: id >= vocab gives a zero row and raises the status word
                         if (token_id < a.vocab) h = ld_stream(a.table + (uint64_t)token_id * a.chunks_per_row + q);
                     } else {
                         h = ld_stream(a.hidden + base + q);
                     }
+                } else if (kAddend == kScaledF32) {
+                    // addend = bf16((raw * weight_scale) * token_scale), the reference's epilogue expression
+                    const float4 *raw = reinterpret_cast<const float4 *>(a.hidden_f32 + (uint64_t)row * a.cols) + 2u * q;
+                    const float4 r0 = raw[0], r1 = raw[1];
+                    const uint4 w = reinterpret_cast<const uint4 *>(a.weight_scale)[q];
+                    const float2 ts2 = make_float2(token_scale, token_scale);
+                    const float2 h0 = __fmul2_rn(__fmul2_rn(make_float2(r0.x, r0.y), make_float2(bf16_lo(w.x), bf16_hi(w.x))), ts2);
+                    const float2 h1 = __fmul2_rn(__fmul2_rn(make_float2(r0.z, r0.w), make_float2(bf16_lo(w.y), bf16_hi(w.y))), ts2);
+                    const float2 h2 = __fmul2_rn(__fmul2_rn(make_float2(r1.x, r1.y), make_float2(bf16_lo(w.z), bf16_hi(w.z))), ts2);
+                    const float2 h3 = __fmul2_rn(__fmul2_rn(make_float2(r1.z, r1.w), make_float2(bf16_lo(w.w), bf16_hi(w.w))), ts2);
+                    h = make_uint4(pack_bf16x2(h0.x, h0.y), pack_bf16x2(h1.x, h1.y), pack_bf16x2(h2.x, h2.y), pack_bf16x2(h3.x, h3.y));
                 }
                 gam[c] = gamma16[q];
                 if (kAdd) {
@@ -408,12 +451,12 @@ add_rmsnorm_wide_row_kernel(const norm_args a) {
 
 constexpr size_t kSmemBudget = 227u * 1024u;
 
-size_t stream_fixed_bytes(uint32_t cols, uint32_t teams) {
-    return (size_t)cols * sizeof(float) + 128u * sizeof(scale_lut_entry) + (size_t)teams * 256u * sizeof(float) +
-           (size_t)teams * kMaxSlotsPerTeam * sizeof(uint64_t);
+size_t stream_fixed_bytes(uint32_t cols, uint32_t teams, int addend = kBf16) {
+    return (size_t)cols * sizeof(float) * (addend == kScaledF32 ? 2u : 1u) + 128u * sizeof(scale_lut_entry) +
+           (size_t)teams * 256u * sizeof(float) + (size_t)teams * kMaxSlotsPerTeam * sizeof(uint64_t);
 }
 
-template <bool kAdd, bool kFull>
+template <int kAdd, bool kFull>
 void launch_stream_impl(const norm_args &a, uint32_t teams, size_t smem, cudaStream_t stream) {
     static bool configured[64] = {};  // the attribute is per device; one process may drive several
     int dev = 0;
@@ -426,10 +469,53 @@ void launch_stream_impl(const norm_args &a, uint32_t teams, size_t smem, cudaStr
     launch_chained(add_rmsnorm_stream_kernel<kAdd, kFull>, dim3(ctas), dim3(teams * kTeamThreads), smem, stream, a);
 }
 
-template <bool kAdd>
+template <int kAdd>
 void launch_stream(const norm_args &a, uint32_t teams, size_t smem, cudaStream_t stream) {
     if (a.cols % 1024u == 0u) launch_stream_impl<kAdd, true>(a, teams, smem, stream);
     else launch_stream_impl<kAdd, false>(a, teams, smem, stream);
+}
+
+// Picks the kernel and its shape for a prepared argument block.
+int launch_norm(norm_args &a, int addend, cudaStream_t stream) {
+    const uint32_t rows = a.rows, cols = a.cols;
+    // Stream kernel shape.  The kernel is bound by instruction issue, not by memory, so resident
+    // warps count for more than prefetch depth: eight teams with one slot each (while a team
+    // waits for its next row the other seven compute) beat five double-buffered teams at 5120
+    // columns (53.5 us against 56.0 us for 8192 rows).  Narrow rows get both: up to eight
+    // teams and as many slots per team as fit.
+    const size_t slot_bytes = (size_t)cols * 2u * (addend == kScaledF32 ? 3u : addend == kBf16 ? 2u : 1u);
+    auto teams_that_fit = [&](uint32_t slots) {
+        uint32_t t = kMaxTeams;
+        while (t != 0u && stream_fixed_bytes(cols, t, addend) + (size_t)t * slots * slot_bytes > kSmemBudget) --t;
+        return t;
+    };
+    const uint32_t single = teams_that_fit(1u), dual = teams_that_fit(2u);
+    uint32_t teams = single >= dual + 2u ? single : dual;
+    uint32_t spt = 0u;
+    if (teams != 0u) {
+        spt = (uint32_t)((kSmemBudget - stream_fixed_bytes(cols, teams, addend)) / (teams * slot_bytes));
+        if (spt > kMaxSlotsPerTeam) spt = kMaxSlotsPerTeam;
+    }
+    // Few rows (latency matters more than streaming), or rows too wide for one slot: one wide CTA per row.
+    if (rows < 2u * kSmCount || teams == 0u || spt == 0u) {
+        uint32_t threads = (a.chunks_per_row + 31u) & ~31u;
+        if (threads > 1024u) threads = 1024u;
+        if (threads < 128u) threads = 128u;  // the 256 partial sums are produced by the first 128 threads
+        const size_t row_smem = (size_t)a.chunks_per_row * sizeof(uint4);
+        const uint32_t ctas = rows < kSmCount * 8u ? rows : kSmCount * 8u;
+        if (addend == kScaledF32) launch_chained(add_rmsnorm_wide_row_kernel<kScaledF32>, dim3(ctas), dim3(threads), row_smem, stream, a);
+        else if (addend == kBf16) launch_chained(add_rmsnorm_wide_row_kernel<kBf16>, dim3(ctas), dim3(threads), row_smem, stream, a);
+        else launch_chained(add_rmsnorm_wide_row_kernel<kNone>, dim3(ctas), dim3(threads), row_smem, stream, a);
+        note_launch();
+        return AXIOM_OK;
+    }
+    a.ring_slots = spt;
+    const size_t smem = stream_fixed_bytes(cols, teams, addend) + (size_t)teams * spt * slot_bytes;
+    if (addend == kScaledF32) launch_stream<kScaledF32>(a, teams, smem, stream);
+    else if (addend == kBf16) launch_stream<kBf16>(a, teams, smem, stream);
+    else launch_stream<kNone>(a, teams, smem, stream);
+    note_launch();
+    return AXIOM_OK;
 }
 
 }  // namespace
@@ -463,7 +549,7 @@ int launch_gather_add_rmsnorm_nvfp4_bf16(const void *table, uint32_t vocab, cons
     if (threads > 1024u) threads = 1024u;
     if (threads < 128u) threads = 128u;
     const uint32_t ctas = rows < kSmCount * 8u ? rows : kSmCount * 8u;
-    launch_chained(add_rmsnorm_wide_row_kernel<true>, dim3(ctas), dim3(threads), (size_t)a.chunks_per_row * sizeof(uint4),
+    launch_chained(add_rmsnorm_wide_row_kernel<kBf16>, dim3(ctas), dim3(threads), (size_t)a.chunks_per_row * sizeof(uint4),
                    stream, a);
     note_launch();
     return AXIOM_OK;
@@ -496,43 +582,31 @@ int launch_add_rmsnorm_tap_nvfp4_bf16(const void *hidden, void *residual, const 
     a.groups = cols / kGroup;
     a.inner_tiles = (a.groups + 3u) / 4u;
 
-    // Stream kernel shape.  The kernel is bound by instruction issue, not by memory, so resident
-    // warps count for more than prefetch depth: eight teams with one slot each (while a team
-    // waits for its next row the other seven compute) beat five double-buffered teams at 5120
-    // columns (53.5 us against 56.0 us for 8192 rows).  Narrow rows get both: up to eight
-    // teams and as many slots per team as fit.
-    const size_t slot_bytes = (size_t)cols * 2u * (hidden ? 2u : 1u);
-    auto teams_that_fit = [&](uint32_t slots) {
-        uint32_t t = kMaxTeams;
-        while (t != 0u && stream_fixed_bytes(cols, t) + (size_t)t * slots * slot_bytes > kSmemBudget) --t;
-        return t;
-    };
-    const uint32_t single = teams_that_fit(1u), dual = teams_that_fit(2u);
-    uint32_t teams = single >= dual + 2u ? single : dual;
-    uint32_t spt = 0u;
-    if (teams != 0u) {
-        spt = (uint32_t)((kSmemBudget - stream_fixed_bytes(cols, teams)) / (teams * slot_bytes));
-        if (spt > kMaxSlotsPerTeam) spt = kMaxSlotsPerTeam;
-    }
-    // The widest row the entry points accept (16384 columns) still fits one team with one slot.
-    if (teams == 0u || spt == 0u) return AXIOM_ERR_INVALID_ARGUMENT;
-    // Few rows: latency matters more than streaming; one wide CTA per row.
-    if (rows < 2u * kSmCount) {
-        uint32_t threads = (a.chunks_per_row + 31u) & ~31u;
-        if (threads > 1024u) threads = 1024u;
-        if (threads < 128u) threads = 128u;  // the 256 partial sums are produced by the first 128 threads
-        const size_t row_smem = (size_t)a.chunks_per_row * sizeof(uint4);
-        if (hidden) launch_chained(add_rmsnorm_wide_row_kernel<true>, dim3(rows), dim3(threads), row_smem, stream, a);
-        else launch_chained(add_rmsnorm_wide_row_kernel<false>, dim3(rows), dim3(threads), row_smem, stream, a);
-        note_launch();
-        return AXIOM_OK;
-    }
-    a.ring_slots = spt;
-    const size_t smem = stream_fixed_bytes(cols, teams) + (size_t)teams * spt * slot_bytes;
-    if (hidden) launch_stream<true>(a, teams, smem, stream);
-    else launch_stream<false>(a, teams, smem, stream);
-    note_launch();
-    return AXIOM_OK;
+    return launch_norm(a, hidden ? kBf16 : kNone, stream);
+}
+
+int launch_fp8_epilogue_add_rmsnorm_nvfp4(const float *gemm_out, const void *weight_scale, const float *input_scale,
+                                          void *residual, const void *gamma, float eps, uint32_t rows, uint32_t cols,
+                                          float G, void *norm_out, uint8_t *codes, uint8_t *scales, uint32_t layout,
+                                          cudaStream_t stream) {
+    norm_args a{};
+    a.hidden_f32 = gemm_out;
+    a.weight_scale = (const uint16_t *)weight_scale;
+    a.input_scale = input_scale;
+    a.residual = (uint4 *)residual;
+    a.gamma = (const uint16_t *)gamma;
+    a.norm_out = (uint4 *)norm_out;
+    a.codes = (uint32_t *)codes;
+    a.scales = scales;
+    a.eps = eps;
+    a.G = G;
+    a.rows = rows;
+    a.cols = cols;
+    a.chunks_per_row = cols / 8u;
+    a.layout = layout;
+    a.groups = cols / kGroup;
+    a.inner_tiles = (a.groups + 3u) / 4u;
+    return launch_norm(a, kScaledF32, stream);
 }
 
 }  // namespace axb
@@ -605,5 +679,30 @@ extern "C" int axiom_qwen38_fused_add_rmsnorm_nvfp4_tap_bf16_device(
     if (rc != AXIOM_OK) return rc;
     launch_add_rmsnorm_tap_nvfp4_bf16(hidden_bf16, residual_bf16, gamma_bf16, eps, rows, cols, out_codes ? global_scale : 1.0f,
                                       norm_out_bf16, out_codes, out_scales, scale_layout, tap_out_bf16, (cudaStream_t)stream);
+    return launch_status();
+}
+
+extern "C" int axiom_qwen38_fused_fp8_epilogue_add_rmsnorm_nvfp4_device(
+        int device, const float *gemm_out_f32, const void *weight_scale_bf16, const float *input_scale, void *residual_bf16,
+        const void *gamma_bf16, float eps, uint32_t rows, uint32_t cols, float global_scale, void *norm_out_bf16,
+        uint8_t *out_codes, uint8_t *out_scales, uint32_t scale_layout, void *stream) {
+    if (!gemm_out_f32 || !weight_scale_bf16 || !input_scale || !residual_bf16 || !gamma_bf16 || rows == 0u || cols == 0u ||
+        (cols % kGroup) != 0u || cols > 16384u || scale_layout > AXIOM_SCALE_LAYOUT_TILED || !(eps > 0.0f) ||
+        !std::isfinite(eps)) {
+        return AXIOM_ERR_INVALID_ARGUMENT;
+    }
+    if ((out_codes == nullptr) != (out_scales == nullptr)) return AXIOM_ERR_INVALID_ARGUMENT;
+    if (!out_codes && !norm_out_bf16) return AXIOM_ERR_INVALID_ARGUMENT;
+    if (out_codes && !valid_scale(global_scale)) return AXIOM_ERR_INVALID_ARGUMENT;
+    if (!aligned16(gemm_out_f32) || !aligned16(weight_scale_bf16) || (reinterpret_cast<uintptr_t>(input_scale) & 3u) ||
+        !aligned16(residual_bf16) || !aligned16(gamma_bf16) || (norm_out_bf16 && !aligned16(norm_out_bf16)) ||
+        (out_codes && (reinterpret_cast<uintptr_t>(out_codes) & 3u))) {
+        return AXIOM_ERR_INVALID_ARGUMENT;
+    }
+    int rc = select_device(device);
+    if (rc != AXIOM_OK) return rc;
+    launch_fp8_epilogue_add_rmsnorm_nvfp4(gemm_out_f32, weight_scale_bf16, input_scale, residual_bf16, gamma_bf16, eps, rows, cols,
+                                          out_codes ? global_scale : 1.0f, norm_out_bf16, out_codes, out_scales, scale_layout,
+                                          (cudaStream_t)stream);
     return launch_status();
 }

@@ -183,7 +183,7 @@ def main():
     ap.add_argument("--skip-e2e", action="store_true")
     ap.add_argument("--skip-cpu", action="store_true")
     ap.add_argument("--only", default=None,
-                    choices=["add_rmsnorm", "add_rmsnorm_tiled", "nvfp4_quantize", "qk", "swiglu_fp8", "swiglu_nvfp4", "sigmoid_gate",
+                    choices=["add_rmsnorm", "add_rmsnorm_tiled", "fp8_epilogue", "nvfp4_quantize", "qk", "swiglu_fp8", "swiglu_nvfp4", "sigmoid_gate",
                              "top1", "chain"],
                     help="run one configuration alone (profiling aid): device-timed, no e2e / CPU legs")
     ap.add_argument("--rows", type=int, default=0, help="with --only: override the token count")
@@ -395,6 +395,8 @@ def bench_other_ops(torch, axk, wl, local, device, stream, peak, only=None, rows
 
     if only is None or only == "add_rmsnorm_tiled":
         bench_add_rmsnorm_tiled(torch, axk, wl, local, device, stream, timed, report, rows_override or 8192)
+    if want("fp8_epilogue"):
+        bench_fp8_epilogue(torch, axk, wl, local, device, stream, timed, report, rows_override or 8192)
     if want("nvfp4_quantize"):
         bench_nvfp4_quantize(torch, axk, wl, local, device, stream, timed, report, rows_override or 4096)
     if want("qk"):
@@ -427,6 +429,28 @@ def bench_add_rmsnorm_tiled(torch, axk, wl, local, device, stream, timed, report
     ms = timed(step)
     report("add_rmsnorm_nvfp4_tiled_scales", ms, bytes_add_rmsnorm_nvfp4(rows, cols), rows,
            "config 2, block scales in the cuBLASLt tile layout")
+
+
+def bench_fp8_epilogue(torch, axk, wl, local, device, stream, timed, report, rows):
+    # config 2 with the addend taken as raw F32 accumulators of an FP8 GEMM (scale epilogue folded into the prologue)
+    cols = COLS
+    sets = []
+    for s in range(NSETS):
+        _, residual, gamma = wl.add_rmsnorm_inputs_torch(torch, device, rows, cols)
+        g = torch.Generator(device=device).manual_seed(70 + s)
+        raw = torch.randn((rows, cols), generator=g, device=device, dtype=torch.float32) * 40.0
+        wscale = (0.01 + 0.005 * torch.rand(cols, generator=g, device=device)).to(torch.bfloat16)
+        iscale = 0.02 + 0.01 * torch.rand(rows, generator=g, device=device, dtype=torch.float32)
+        sets.append((raw, wscale, iscale, residual, gamma, torch.empty((rows, cols // 2), dtype=torch.uint8, device=device),
+                     torch.empty((rows, cols // 16), dtype=torch.uint8, device=device)))
+
+    def step(i):
+        raw, ws, isc, r, g, c, s = sets[i % NSETS]
+        axk.fp8_epilogue_add_rmsnorm_nvfp4(local, raw, ws, isc, r, g, wl.EPS, rows, cols, 90.0, None, c, s, 0, stream)
+
+    ms = timed(step)
+    report("fp8_epilogue_add_rmsnorm_nvfp4", ms, rows * cols * 4 + 2 * rows * cols * 2 + rows * cols // 2 + rows * cols // 16 +
+           cols * 4 + rows * 4, rows, "raw F32 GEMM accumulators + weight/token scales as the addend (FP8 path)")
 
 
 def bench_nvfp4_quantize(torch, axk, wl, local, device, stream, timed, report, rows):

@@ -190,6 +190,12 @@ int axiom_qwen38_fused_add_bf16_device(int device, const void *a_bf16, const voi
  * cols % 16 == 0, cols <= 16384. */
 int axiom_qwen38_fused_add_rmsnorm_nvfp4_bf16_device(int device, const void *hidden_bf16, void *residual_bf16, const void *gamma_bf16, float eps, uint32_t rows, uint32_t cols, float global_scale, void *norm_out_bf16, uint8_t *out_codes, uint8_t *out_scales, uint32_t scale_layout, void *stream);
 
+/* The same with the addend taken straight from an FP8 GEMM: gemm_out_f32 [rows x cols] holds raw accumulators and the
+ * addend is bf16((raw * weight_scale[feature]) * input_scale[token]) — fp8_group_row_scale_bf16_epilogue_kernel
+ * (src/axiom_qwen38_fp8.cu:250-262) evaluated in this kernel's prologue, so the scaled tensor never exists in HBM.
+ * weight_scale_bf16 [cols], input_scale [rows] (the per-token scales the activation quantizer produced). */
+int axiom_qwen38_fused_fp8_epilogue_add_rmsnorm_nvfp4_device(int device, const float *gemm_out_f32, const void *weight_scale_bf16, const float *input_scale, void *residual_bf16, const void *gamma_bf16, float eps, uint32_t rows, uint32_t cols, float global_scale, void *norm_out_bf16, uint8_t *out_codes, uint8_t *out_scales, uint32_t scale_layout, void *stream);
+
 /* The same with a layer tap: tap_out_bf16 [rows x cols] receives a second copy of the updated residual rows
  * (qwen38_capture_tap8_kernel, src/axiom_qwen38_model.cu:343-351, folded into the write of the residual). */
 int axiom_qwen38_fused_add_rmsnorm_nvfp4_tap_bf16_device(int device, const void *hidden_bf16, void *residual_bf16, const void *gamma_bf16, float eps, uint32_t rows, uint32_t cols, float global_scale, void *norm_out_bf16, uint8_t *out_codes, uint8_t *out_scales, uint32_t scale_layout, void *tap_out_bf16, void *stream);

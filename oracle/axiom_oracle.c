@@ -953,3 +953,24 @@ int axo_top1_f32(const float *logits, uint32_t rows, uint32_t vocab, uint32_t *o
     }
     return AXO_OK;
 }
+
+/* ------------------------------------------------------------------ */
+/* FP8 GEMM scale epilogue                                             */
+/* ------------------------------------------------------------------ */
+
+/* fp8_group_row_scale_bf16_epilogue_kernel (reference src/axiom_qwen38_fp8.cu:250-262):
+ * out[token][feature] = bf16((raw * weight_scale[feature]) * input_scale[token]), weight scales
+ * stored as BF16, token-major layout. */
+int axo_fp8_row_scale_epilogue_bf16(const float *raw, const uint16_t *weight_scale,
+                                    const float *input_scale, uint32_t rows, uint32_t cols,
+                                    uint16_t *out_bf16) {
+    if (!raw || !weight_scale || !input_scale || !out_bf16 || rows == 0u || cols == 0u) return AXO_INVALID;
+    AXO_PARALLEL_FOR
+    for (int64_t r = 0; r < (int64_t)rows; ++r) {
+        for (uint32_t c = 0; c < cols; ++c) {
+            const float scaled = raw[(size_t)r * cols + c] * axo_bf16_to_f32(weight_scale[c]);
+            out_bf16[(size_t)r * cols + c] = axo_f32_to_bf16(scaled * input_scale[r]);
+        }
+    }
+    return AXO_OK;
+}

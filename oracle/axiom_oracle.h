@@ -133,6 +133,11 @@ int axo_bf16_to_e4m3_scale1(const uint16_t *in, uint8_t *out, uint64_t count);
 int axo_embedding_gather_bf16(const uint16_t *table, uint32_t vocab, uint32_t hidden,
                               const uint32_t *ids, uint32_t tokens, uint16_t *out);
 
+/* ---- FP8 GEMM scale epilogue: bf16((raw * weight_scale[feature]) * input_scale[token]) ---- */
+int axo_fp8_row_scale_epilogue_bf16(const float *raw, const uint16_t *weight_scale,
+                                    const float *input_scale, uint32_t rows, uint32_t cols,
+                                    uint16_t *out_bf16);
+
 /* ---- greedy selection: rows x {float value, uint32 id, uint32 invalid} ---- */
 int axo_top1_f32(const float *logits, uint32_t rows, uint32_t vocab, uint32_t *out);
 

@@ -9,3 +9,10 @@ extern "C" int ref_quantize_columns_e4m3(const float *input, uint8_t *codes, flo
     }
     return cudaDeviceSynchronize() == cudaSuccess && cudaGetLastError() == cudaSuccess ? 0 : 3;
 }
+
+// out F32 [8][rows] raw accumulators, scaled and rounded in place: out = bf16((out * weight_scale[row]) * input_scale[column])
+extern "C" int ref_fp8_group_row_scale_bf16_epilogue(float *out, const uint16_t *weight_scale, const float *input_scale, uint32_t rows) {
+    const uint64_t count = (uint64_t)rows * AXIOM_QWEN38_FP8_BATCH;
+    fp8_group_row_scale_bf16_epilogue_kernel<<<(uint32_t)((count + kThreads - 1u) / kThreads), kThreads>>>(out, weight_scale, input_scale, rows);
+    return cudaDeviceSynchronize() == cudaSuccess && cudaGetLastError() == cudaSuccess ? 0 : 3;
+}

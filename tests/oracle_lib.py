@@ -268,6 +268,14 @@ def embedding_gather_bf16(table_bits, ids):
     return out
 
 
+def fp8_row_scale_epilogue_bf16(raw, weight_scale_bits, input_scale):
+    rows, cols = raw.shape
+    out = np.empty((rows, cols), np.uint16)
+    _ok(o().axo_fp8_row_scale_epilogue_bf16(_p(np.ascontiguousarray(raw)), _p(weight_scale_bits), _p(input_scale), rows, cols,
+                                            _p(out)), "fp8 epilogue")
+    return out
+
+
 def top1_f32(logits):
     rows, vocab = logits.shape
     out = np.empty((rows, 3), np.uint32)

@@ -178,3 +178,43 @@ def test_layer_tap_is_a_copy_of_the_updated_residual(axk, cuda_device, rows, wit
         assert np.array_equal(a, b)
     assert axk.add_rmsnorm_nvfp4_tap(0, None, dev(residual), dev(gamma), 1e-6, rows, cols, 80.0, None, None, None, 0,
                                      None) == axk.AXIOM_ERR_INVALID_ARGUMENT
+
+
+@pytest.mark.parametrize("rows,cols", [(8, 5120), (1, 1024), (600, 5120), (333, 2048), (300, 7168)])
+def test_fp8_gemm_epilogue_folded_into_the_prologue(axk, cuda_device, rows, cols):
+    """Raw F32 accumulators + per-feature BF16 weight scales + per-token input scales as the addend: the result equals
+    the epilogue evaluated separately (oracle) followed by the plain BF16 entry, bit for bit; and the epilogue
+    expression itself equals the reference's kernel on its 8-column batch."""
+    import torch
+    import ref_lib
+    from gpu_util import dev, host, sync
+
+    rng = np.random.default_rng(rows + cols)
+    raw = (rng.standard_normal((rows, cols)) * 37.0).astype(np.float32)
+    wscale = wl.to_bf16_bits((0.01 + 0.005 * rng.random(cols)).astype(np.float32))
+    iscale = (0.02 + 0.01 * rng.random(rows)).astype(np.float32)
+    _, residual, gamma = wl.add_rmsnorm_inputs_np(rows, cols)
+    addend = ol.fp8_row_scale_epilogue_bf16(raw, wscale, iscale)
+    if ref_lib.available() and rows == 8:
+        r = ref_lib.lib()
+        out = torch.from_numpy(raw.copy()).cuda()
+        ws_d, is_d = dev(wscale), torch.from_numpy(iscale).cuda()
+        assert r.ref_fp8_group_row_scale_bf16_epilogue(out.data_ptr(), ws_d.data_ptr(), is_d.data_ptr(), cols) == 0
+        assert np.array_equal(wl.to_bf16_bits(out.cpu().numpy()), addend)
+        assert np.array_equal(wl.from_bf16_bits(addend), out.cpu().numpy())
+    outs = []
+    for fused in (False, True):
+        res, g = dev(residual), dev(gamma)
+        norm = torch.zeros((rows, cols), dtype=torch.int16, device="cuda")
+        codes = torch.zeros((rows, cols // 2), dtype=torch.uint8, device="cuda")
+        scales = torch.zeros((rows, cols // 16), dtype=torch.uint8, device="cuda")
+        if fused:
+            raw_d, ws_d, is_d = torch.from_numpy(raw).cuda(), dev(wscale), torch.from_numpy(iscale).cuda()
+            assert axk.fp8_epilogue_add_rmsnorm_nvfp4(0, raw_d, ws_d, is_d, res, g, 1e-6, rows, cols, 70.0, norm, codes,
+                                                      scales, 0) == axk.AXIOM_OK
+        else:
+            assert axk.add_rmsnorm_nvfp4(0, dev(addend), res, g, 1e-6, rows, cols, 70.0, norm, codes, scales, 0) == axk.AXIOM_OK
+        sync()
+        outs.append([host(x, np.uint8) for x in (res, norm, codes, scales)])
+    for a, b in zip(*outs):
+        assert np.array_equal(a, b)
