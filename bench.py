@@ -297,7 +297,7 @@ def main():
         "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
                      "traffic": NCU_DRAM_BYTES_PER_LAUNCH if (ROWS, COLS) == (8192, 5120) else None,
                      "traffic_note": "dram__bytes_read.sum + dram__bytes_write.sum of one ncu capture of this launch "
-                                     "(profiles/add_rmsnorm_nvfp4_8192x5120.md); the write part is below the algorithmic "
+                                     "(summary committed under profiles/); the write part is below the algorithmic "
                                      "write bytes because lines still dirty in the 126 MB L2 at kernel end are not counted",
                      "peak_kind": peak_kind, "kernel": "add_rmsnorm_stream_kernel<true,true>",
                      "algorithmic_bytes_per_launch": algo},
