@@ -160,7 +160,7 @@ def reference_arm(args):
     line = {
         "impl": "reference", "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": args.gpus,
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": dt * 1e3 * (ROWS / sample_rows),
-        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16->f32->e2m1/e4m3",
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32", "io_dtype": "bf16 in; bf16 residual, e2m1 codes + e4m3 block scales out",
         "data": "synthetic",
         "config": dict(workload_config(ROWS, COLS), arm="CPU restatement of the reference's arithmetic (the reference has "
                        "no CPU implementation of this op), all host threads, bounded sample per step"),
@@ -292,7 +292,7 @@ def main():
     line = {
         "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
         "warmup": max(args.warmup, 3), "ms_per_step": ms, "higher_is_better": True, "scaling": "weak",
-        "vs_baseline": None, "dtype": "bf16->f32->e2m1/e4m3", "data": "synthetic",
+        "vs_baseline": None, "dtype": "f32", "io_dtype": "bf16 in; bf16 residual, e2m1 codes + e4m3 block scales out", "data": "synthetic",
         "config": workload_config(ROWS, COLS),
         "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
                      "traffic": NCU_DRAM_BYTES_PER_LAUNCH if (ROWS, COLS) == (8192, 5120) else None,
