@@ -123,6 +123,9 @@ __device__ __forceinline__ void norm_quant_sweep(const norm_args &a, const uint4
     }
 }
 
+// A row of zeros: the addend of a token whose id lies outside the embedding table (device arrays start zeroed).
+static __device__ __align__(16) uint8_t g_zero_row[16384u * 2u];
+
 constexpr uint32_t kTeamThreads = 128u;
 constexpr uint32_t kMaxTeams = 8u;
 constexpr uint32_t kMaxSlotsPerTeam = 4u;
@@ -173,13 +176,29 @@ add_rmsnorm_stream_kernel(const norm_args a) {
     // slot is dead as soon as sweep 1 has merged it into the residual half, so the NEXT row's
     // addend is requested right then (announced with expect_tx only) and only its residual has
     // to wait until sweep 2 and the bulk store of the merged row are done with the other half.
-    auto issue_addend = [&](uint32_t i) {  // thread 0 of the team
+    // `token` is the row's id when the addend is gathered from an embedding table (ids at or beyond the vocabulary
+    // read the row of zeros and raise the status word)
+    auto issue_addend = [&](uint32_t i, uint32_t token) {  // thread 0 of the team
         const uint64_t row = blockIdx.x + (uint64_t)(team + teams * i) * gridDim.x;
         const uint32_t j = i % spt;
         mbar_expect_tx(my_bars + j, addend_bytes);
-        const void *src = kAddend == kScaledF32 ? static_cast<const void *>(a.hidden_f32 + row * a.cols)
-                                                : static_cast<const void *>(a.hidden + row * a.chunks_per_row);
+        const void *src;
+        if (kAddend == kScaledF32) {
+            src = a.hidden_f32 + row * a.cols;
+        } else if (a.table) {
+            if (token < a.vocab) {
+                src = a.table + (uint64_t)token * a.chunks_per_row;
+            } else {
+                src = g_zero_row;
+                if (a.status_word) atomicCAS(a.status_word, AXIOM_STATUS_WORD_OK, AXIOM_STATUS_WORD_BAD_ADDRESS);
+            }
+        } else {
+            src = a.hidden + row * a.chunks_per_row;
+        }
         bulk_load(my_slots + (size_t)j * slot_bytes, src, addend_bytes, my_bars + j);
+    };
+    auto token_of_row = [&](uint32_t i) -> uint32_t {
+        return (kAddend == kBf16 && a.table) ? a.token_ids[blockIdx.x + (team + teams * i) * gridDim.x] : 0u;
     };
     auto issue_residual = [&](uint32_t i) {
         const uint64_t row = blockIdx.x + (uint64_t)(team + teams * i) * gridDim.x;
@@ -189,7 +208,7 @@ add_rmsnorm_stream_kernel(const norm_args a) {
                   my_bars + j);
     };
     auto issue = [&](uint32_t i) {
-        if (kAdd) issue_addend(i);
+        if (kAdd) issue_addend(i, token_of_row(i));
         issue_residual(i);
     };
     // the first rows are already on their way while the CTA prepares gamma and the scale table
@@ -211,6 +230,9 @@ add_rmsnorm_stream_kernel(const norm_args a) {
         const uint32_t j = i % spt;
         float token_scale = 1.0f;
         if (kAddend == kScaledF32) token_scale = a.input_scale[blockIdx.x + (team + teams * i) * gridDim.x];
+        // the id of the row whose addend is requested after sweep 1 (fetched now: its latency hides behind the sweep)
+        uint32_t next_token = 0u;
+        if (t == 0u && i + spt < my_rows) next_token = token_of_row(i + spt);
         // A wait that ran out raises the fault word; the team carries on (on whatever the slot
         // holds) so that its barriers stay matched, and stops waiting.
         if (!faulted && !mbar_wait(my_bars + j, (i / spt) & 1u)) faulted = true;
@@ -253,7 +275,7 @@ add_rmsnorm_stream_kernel(const norm_args a) {
             if (kAdd) bulk_store(a.residual + base, res_sh, row_bytes);
             if (a.tap) bulk_store(a.tap + base, res_sh, row_bytes);
             bulk_commit();
-            if (kAdd && i + spt < my_rows) issue_addend(i + spt);  // every thread is past its reads of the addend half
+            if (kAdd && i + spt < my_rows) issue_addend(i + spt, next_token);  // every thread is past its reads of the addend half
         }
         // Reference tree over the 256 partials c: strides 128,64,32 then 16,8,4,2,1.  With lane l
         // holding c = 8l + e, strides 128..8 are the lane butterfly 16,8,4,2,1 applied to each e
@@ -544,15 +566,7 @@ int launch_gather_add_rmsnorm_nvfp4_bf16(const void *table, uint32_t vocab, cons
     a.layout = layout;
     a.groups = cols / kGroup;
     a.inner_tiles = (a.groups + 3u) / 4u;
-    // one wide CTA per row at every row count: the gathered rows are scattered, there is nothing to stream
-    uint32_t threads = (a.chunks_per_row + 31u) & ~31u;
-    if (threads > 1024u) threads = 1024u;
-    if (threads < 128u) threads = 128u;
-    const uint32_t ctas = rows < kSmCount * 8u ? rows : kSmCount * 8u;
-    launch_chained(add_rmsnorm_wide_row_kernel<kBf16>, dim3(ctas), dim3(threads), (size_t)a.chunks_per_row * sizeof(uint4),
-                   stream, a);
-    note_launch();
-    return AXIOM_OK;
+    return launch_norm(a, kBf16, stream);
 }
 
 int launch_add_rmsnorm_nvfp4_bf16(const void *hidden, void *residual, const void *gamma, float eps, uint32_t rows,
