@@ -297,6 +297,7 @@ swiglu_nvfp4_kernel(const uint4 *__restrict__ in, const uint4 *__restrict__ othe
     dependency_wait();
     const uint32_t lane = threadIdx.x & 31u;
     const uint32_t warp = (blockIdx.x * kNvThreads + threadIdx.x) >> 5;
+    const uint32_t lane_tile_off = (lane >> 3) * 512u + ((lane >> 1) & 3u);  // tiled plane: (group/4, group%4) of lane/2
     uint32_t row = warp / col_groups, col = warp % col_groups;
     while (row < rows) {
         uint32_t rws[kNvUnroll], qs[kNvUnroll];
@@ -341,7 +342,14 @@ swiglu_nvfp4_kernel(const uint4 *__restrict__ in, const uint4 *__restrict__ othe
             if (oks[j] && codes) {
                 st_stream(codes + (uint64_t)rws[j] * chunks + qs[j], packed);
                 if ((lane & 1u) == 0u) {
-                    scales[scale_offset(rws[j], qs[j] >> 1, groups, inner_tiles, layout)] = (uint8_t)scale_code;
+                    // block (row, group): group = 16 * column group + lane / 2.  Canonical plane: row * groups + group.
+                    // Tiled plane: ((row/128) * inner_tiles + group/4) * 512 + (row%32) * 16 + ((row%128)/32) * 4 + group%4,
+                    // whose lane-dependent part is a per-thread constant and whose row part is uniform over the warp.
+                    const uint32_t r = rws[j], cg = qs[j] >> 5;
+                    const uint64_t off = layout == AXIOM_SCALE_LAYOUT_CANONICAL
+                            ? (uint64_t)r * groups + (qs[j] >> 1)
+                            : ((uint64_t)(r >> 7) * inner_tiles + 4u * cg) * 512u + (r & 31u) * 16u + ((r & 127u) >> 5) * 4u + lane_tile_off;
+                    scales[off] = (uint8_t)scale_code;
                 }
             }
         }
