@@ -33,6 +33,7 @@ SCALE_TILED = 1
 QK_FLAG_RING = 1
 QK_FLAG_PER_TOKEN_TABLE = 2
 QK_FLAG_CACHE_E4M3 = 4
+QK_FLAG_Q_GATE_INTERLEAVED = 8
 STATUS_WORD_OK = 0
 STATUS_WORD_BAD_ADDRESS = 1
 STATUS_WORD_NONFINITE = 4
@@ -62,7 +63,7 @@ class QkRopeArgs(C.Structure):
         ("n_blocks", u32),
         ("q_bf16", vp), ("k_bf16", vp), ("v_bf16", vp), ("q_gamma_bf16", vp), ("k_gamma_bf16", vp),
         ("inv_freq", vp), ("positions", vp), ("block_tables", vp), ("k_pool_bf16", vp), ("v_pool_bf16", vp),
-        ("k_out_bf16", vp), ("status_word", vp),
+        ("k_out_bf16", vp), ("status_word", vp), ("q_out_bf16", vp),
     ]
 
 
@@ -119,6 +120,7 @@ SIGNATURES = {
     "axiom_qwen38_fused_swiglu_fp8_bf16_device": (i32, [i32, vp, u32, u32, vp, vp, vp]),
     "axiom_qwen38_fused_swiglu_nvfp4_bf16_device": (i32, [i32, vp, u32, u32, f32, vp, vp, u32, vp]),
     "axiom_qwen38_fused_sigmoid_gate_nvfp4_bf16_device": (i32, [i32, vp, vp, u32, u32, f32, vp, vp, vp, u32, vp]),
+    "axiom_qwen38_fused_sigmoid_gate_heads_nvfp4_bf16_device": (i32, [i32, vp, vp, u32, u32, u32, f32, vp, vp, vp, u32, vp]),
     "axiom_qwen38_fused_top1_f32_device": (i32, [i32, vp, u32, u32, vp, vp]),
     "axiom_qwen38_fused_fp8_quantize_bf16_device": (i32, [i32, vp, u32, u32, vp, vp, vp, vp]),
     "axiom_qwen38_fused_embedding_gather_bf16_device": (i32, [i32, vp, u32, u32, vp, u32, vp, vp, vp]),
@@ -238,6 +240,13 @@ def gather_add_rmsnorm_nvfp4(device, table, vocab, token_ids, residual, gamma, e
         _ptr(codes), _ptr(scales), layout, _ptr(status_word), _stream_handle(stream))
 
 
+def sigmoid_gate_heads_nvfp4(device, attention, q_gate, rows, heads, head_dim, G, out_bf16, codes, scales,
+                             layout=SCALE_CANONICAL, stream=None):
+    return lib().axiom_qwen38_fused_sigmoid_gate_heads_nvfp4_bf16_device(
+        device, _ptr(attention), _ptr(q_gate), rows, heads, head_dim, G, _ptr(out_bf16), _ptr(codes), _ptr(scales), layout,
+        _stream_handle(stream))
+
+
 def sigmoid_gate_nvfp4(device, attention, gate, rows, width, G, out_bf16, codes, scales, layout=SCALE_CANONICAL, stream=None):
     return lib().axiom_qwen38_fused_sigmoid_gate_nvfp4_bf16_device(device, _ptr(attention), _ptr(gate), rows, width, G,
                                                                    _ptr(out_bf16), _ptr(codes), _ptr(scales), layout,
@@ -271,11 +280,11 @@ def yarn_mscale(factor: float) -> float:
 def make_qk_args(*, tokens, q_heads, k_heads, head_dim, rope_dim, flags=0, eps=1e-6, mscale=1.0, block_tokens=16,
                  n_layers=1, layer=0, pool_stride=0, tbl_stride=0, n_blocks=0, q=None, k=None, v=None,
                  q_gamma=None, k_gamma=None, inv_freq=None, positions=None, block_tables=None, k_pool=None,
-                 v_pool=None, k_out=None, status_word=None) -> QkRopeArgs:
+                 v_pool=None, k_out=None, status_word=None, q_out=None) -> QkRopeArgs:
     return QkRopeArgs(AXIOM_ABI_VERSION, C.sizeof(QkRopeArgs), tokens, q_heads, k_heads, head_dim, rope_dim, flags,
                       eps, mscale, block_tokens, n_layers, layer, pool_stride, tbl_stride, n_blocks, _ptr(q),
                       _ptr(k), _ptr(v), _ptr(q_gamma), _ptr(k_gamma), _ptr(inv_freq), _ptr(positions),
-                      _ptr(block_tables), _ptr(k_pool), _ptr(v_pool), _ptr(k_out), _ptr(status_word))
+                      _ptr(block_tables), _ptr(k_pool), _ptr(v_pool), _ptr(k_out), _ptr(status_word), _ptr(q_out))
 
 
 def qk_norm_rope_paged(device, args: QkRopeArgs, stream=None):

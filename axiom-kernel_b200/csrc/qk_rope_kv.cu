@@ -34,7 +34,9 @@ constexpr uint32_t kMaxHeads = 512u;
 constexpr uint32_t kMaxHeadDim = 256u;
 
 struct qk_dev_args {
-    uint4 *q;
+    const uint4 *q;          // source rows: q_heads heads at a pitch of q_head_stride elements
+    uint4 *q_out;            // destination rows, heads packed
+    uint32_t q_head_stride;  // head_dim, or 2 * head_dim when each head is followed by its gate values
     const uint4 *k;
     const uint4 *v;
     const uint16_t *q_gamma;
@@ -202,7 +204,8 @@ qk_norm_rope_paged_kernel(const qk_dev_args a) {
     const bool fp8_cache = (a.flags & AXIOM_QK_FLAG_CACHE_E4M3) != 0u;
 
     for (uint32_t t = blockIdx.x; t < a.tokens; t += gridDim.x) {
-        uint16_t *q_row = reinterpret_cast<uint16_t *>(a.q) + (uint64_t)t * q_elems;
+        const uint16_t *q_src = reinterpret_cast<const uint16_t *>(a.q) + (uint64_t)t * a.q_heads * a.q_head_stride;
+        uint16_t *q_row = reinterpret_cast<uint16_t *>(a.q_out) + (uint64_t)t * q_elems;
         const uint16_t *k_row = reinterpret_cast<const uint16_t *>(a.k) + (uint64_t)t * k_elems;
 
         uint2 xa[NPT], xb[NPT];
@@ -212,7 +215,7 @@ qk_norm_rope_paged_kernel(const qk_dev_args a) {
             xa[n] = make_uint2(0u, 0u);
             xb[n] = make_uint2(0u, 0u);
             if (kFast || h < heads) {
-                const uint16_t *row = h < a.q_heads ? q_row + h * D : k_row + (h - a.q_heads) * D;
+                const uint16_t *row = h < a.q_heads ? q_src + h * a.q_head_stride : k_row + (h - a.q_heads) * D;
                 xa[n] = ld_stream8(row + off_a);
                 xb[n] = ld_stream8(row + off_b);
             }
@@ -375,21 +378,37 @@ qk_norm_rope_stream_kernel(const qk_dev_args a, const qk_stream_geom g) {
     // are the older bulk group: only they have to be done reading) and slots - 1 tokens are
     // requested up front; fewer slots are refilled as soon as their own stores have drained.
     const uint32_t ahead = g.slots > 2u ? g.slots - 1u : g.slots;
-    auto issue = [&](uint32_t i) {  // the manager's first lane
+    // Requests token i into its slot; called by the whole manager warp.  A packed Q row is one copy;
+    // when every head is followed by its gate values the lanes fetch the heads' query halves one by
+    // one, so that the slot holds the same packed row either way.
+    const bool q_packed = a.q_head_stride == D;
+    auto issue = [&](uint32_t i, uint32_t lane) {
         const uint64_t tok = token_of(i);
         const uint32_t j = i % g.slots;
         uint8_t *slot = my_slots + (size_t)j * g.slot_bytes;
-        mbar_arrive_expect_tx(bars + j, q_bytes + k_bytes);
-        if (q_bytes) bulk_load(slot, reinterpret_cast<const uint8_t *>(a.q) + tok * q_bytes, q_bytes, bars + j);
-        if (k_bytes) bulk_load(slot + q_bytes, reinterpret_cast<const uint8_t *>(a.k) + tok * k_bytes, k_bytes, bars + j);
+        if (lane == 0u) {
+            mbar_arrive_expect_tx(bars + j, q_bytes + k_bytes);
+            if (q_bytes && q_packed) bulk_load(slot, reinterpret_cast<const uint8_t *>(a.q) + tok * q_bytes, q_bytes, bars + j);
+            if (k_bytes) bulk_load(slot + q_bytes, reinterpret_cast<const uint8_t *>(a.k) + tok * k_bytes, k_bytes, bars + j);
+        }
+        if (!q_packed) {
+            __syncwarp();
+            const uint8_t *row = reinterpret_cast<const uint8_t *>(a.q) + tok * a.q_heads * a.q_head_stride * 2u;
+            for (uint32_t h = lane; h < a.q_heads; h += 32u) {
+                bulk_load(slot + h * D * 2u, row + (size_t)h * a.q_head_stride * 2u, D * 2u, bars + j);
+            }
+        }
     };
 
     // the first tokens are requested before anything else is set up: nobody else touches the
     // barriers or the slots until the CTA barrier below
-    if (lead) {
-        for (uint32_t j = 0; j < g.slots; ++j) mbar_init(bars + j, 1u);
-        mbar_init_fence();
-        for (uint32_t i = 0; i < ahead && i < my_tokens; ++i) issue(i);
+    if (manager) {
+        if (lead) {
+            for (uint32_t j = 0; j < g.slots; ++j) mbar_init(bars + j, 1u);
+            mbar_init_fence();
+        }
+        __syncwarp();
+        for (uint32_t i = 0; i < ahead && i < my_tokens; ++i) issue(i, t - workers);
     }
     for (uint32_t i = tid; i < D; i += blockDim.x) {
         gq_sh[i] = a.q_heads ? __uint_as_float((uint32_t)a.q_gamma[i] << 16) : 0.0f;
@@ -449,12 +468,14 @@ qk_norm_rope_stream_kernel(const qk_dev_args a, const qk_stream_geom g) {
             // A wait that ran out raises the fault word; the team carries on (on whatever the slot
             // holds) so that its barriers stay matched, and stops waiting and storing.
             if (!faulted && !mbar_wait(bars + j, (i / g.slots) & 1u)) faulted = true;
+            faulted = __any_sync(0xffffffffu, faulted);  // one verdict for the warp: its lanes issue copies together
             team_sync(team, g.team_threads);  // the workers have rewritten the slot
             if (fp8_cache && g.slots <= 2u) team_sync(team, g.team_threads);  // ... and converted its K row (see the workers)
 
+            const uint32_t nxt = i + ahead;
             if (lead && !faulted) {
                 const uint8_t *src = slot;
-                if (q_bytes) bulk_store(reinterpret_cast<uint8_t *>(a.q) + (uint64_t)tok * q_bytes, src, q_bytes);
+                if (q_bytes) bulk_store(reinterpret_cast<uint8_t *>(a.q_out) + (uint64_t)tok * q_bytes, src, q_bytes);
                 if (k_bytes && a.k_out) bulk_store(reinterpret_cast<uint8_t *>(a.k_out) + (uint64_t)tok * k_bytes, src + q_bytes, k_bytes);
                 if (a.k_pool) {
                     if (in_pool) {
@@ -464,12 +485,14 @@ qk_norm_rope_stream_kernel(const qk_dev_args a, const qk_stream_geom g) {
                     }
                 }
                 bulk_commit();
-                const uint32_t nxt = i + ahead;
                 if (nxt < my_tokens) {
                     if (g.slots > 2u) bulk_wait_read_but_one();
                     else bulk_wait_read_all();
-                    issue(nxt);
                 }
+            }
+            if (!faulted && nxt < my_tokens) {
+                __syncwarp();  // the first lane's stores have finished reading the slot that is refilled
+                issue(nxt, ml);
             }
             pos_cur = pos_n1;
             pos_n1 = pos_n2;
@@ -706,7 +729,10 @@ unsigned int qk_fault_word() { return read_and_clear_pipeline_fault(); }
 
 int launch_qk_norm_rope_paged_bf16(const axiom_qk_rope_args *p, cudaStream_t stream) {
     qk_dev_args a{};
-    a.q = (uint4 *)p->q_bf16;
+    const bool has_q_out = p->struct_size >= sizeof(axiom_qk_rope_args) && p->q_out_bf16 != nullptr;
+    a.q = (const uint4 *)p->q_bf16;
+    a.q_out = has_q_out ? (uint4 *)p->q_out_bf16 : (uint4 *)p->q_bf16;
+    a.q_head_stride = (p->flags & AXIOM_QK_FLAG_Q_GATE_INTERLEAVED) ? 2u * p->head_dim : p->head_dim;
     a.k = (const uint4 *)p->k_bf16;
     a.v = (const uint4 *)p->v_bf16;
     a.q_gamma = (const uint16_t *)p->q_gamma_bf16;
@@ -776,9 +802,13 @@ extern "C" int axiom_qwen38_fused_yarn_inv_freq_device(int device, const axiom_r
 
 extern "C" int axiom_qwen38_fused_qk_norm_rope_paged_bf16_device(int device, const axiom_qk_rope_args *p,
                                                                  void *stream) {
-    if (!p || p->abi_version != AXIOM_ABI_VERSION || p->struct_size != sizeof(axiom_qk_rope_args)) {
+    if (!p || p->abi_version != AXIOM_ABI_VERSION ||
+        (p->struct_size != sizeof(axiom_qk_rope_args) && p->struct_size != offsetof(axiom_qk_rope_args, q_out_bf16))) {
         return AXIOM_ERR_INVALID_ARGUMENT;
     }
+    void *const q_out = p->struct_size == sizeof(axiom_qk_rope_args) ? p->q_out_bf16 : nullptr;
+    if (q_out && (!p->q_heads || !aligned16(q_out))) return AXIOM_ERR_INVALID_ARGUMENT;
+    if ((p->flags & AXIOM_QK_FLAG_Q_GATE_INTERLEAVED) && (!p->q_heads || !q_out)) return AXIOM_ERR_INVALID_ARGUMENT;
     if (p->tokens == 0u || (p->q_heads + p->k_heads) == 0u || (p->q_heads + p->k_heads) > kMaxHeads ||
         (uint64_t)(p->q_heads + p->k_heads) * (p->head_dim / 8u) > 4096u ||
         (p->head_dim != 64u && p->head_dim != 128u && p->head_dim != 256u) || p->rope_dim > p->head_dim ||

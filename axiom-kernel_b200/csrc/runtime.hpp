@@ -65,6 +65,9 @@ int launch_swiglu_nvfp4_bf16(const void *gate_up, uint32_t rows, uint32_t width,
                              uint8_t *scales, uint32_t layout, cudaStream_t stream);
 int launch_sigmoid_gate_nvfp4_bf16(const void *attention, const void *gate, uint32_t rows, uint32_t width, float G,
                                    void *out_bf16, uint8_t *codes, uint8_t *scales, uint32_t layout, cudaStream_t stream);
+int launch_sigmoid_gate_heads_nvfp4_bf16(const void *attention, const void *q_gate, uint32_t rows, uint32_t heads,
+                                         uint32_t head_dim, float G, void *out_bf16, uint8_t *codes, uint8_t *scales,
+                                         uint32_t layout, cudaStream_t stream);
 int launch_fp8_quantize_bf16(const void *input, uint32_t rows, uint32_t cols, uint8_t *codes, float *scales,
                              uint32_t *status_word, cudaStream_t stream);
 int launch_embedding_gather_bf16(const void *table, uint32_t vocab, uint32_t hidden, const uint32_t *ids,

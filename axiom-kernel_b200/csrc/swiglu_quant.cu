@@ -281,10 +281,10 @@ constexpr uint32_t kNvUnroll = 2u;  // warp tiles in flight per iteration
 // kFn = sigmoid: y = bf16(attention * sigmoid(gate)) (qwen38_sigmoid_gate_kernel, src/axiom_qwen38_attention.cu:
 // 470-479: the product is rounded to BF16 before anything consumes it), `in` holds the gates and `other` the
 // attention output, both [rows x chunks]; y is optionally written out as BF16 as well.
-template <bool kTable, gate_fn kFn>
+template <bool kTable, gate_fn kFn, bool kHeadGate>
 __global__ void __launch_bounds__(kNvThreads)
 swiglu_nvfp4_kernel(const uint4 *__restrict__ in, const uint4 *__restrict__ other, uint32_t row_stride,
-                    uint32_t rows, uint32_t chunks, uint32_t col_groups,
+                    uint32_t other_row_stride, uint32_t in_head_keep, uint32_t in_head_add, uint32_t rows, uint32_t chunks, uint32_t col_groups,
                     uint32_t step_rows, uint32_t step_cols, float G, uint4 *__restrict__ out_bf16,
                     uint32_t *__restrict__ codes,
                     uint8_t *__restrict__ scales, uint32_t layout, uint32_t groups, uint32_t inner_tiles,
@@ -308,9 +308,13 @@ swiglu_nvfp4_kernel(const uint4 *__restrict__ in, const uint4 *__restrict__ othe
             rws[j] = row;
             qs[j] = col * 32u + lane;
             oks[j] = row < rows && qs[j] < chunks;
-            const uint64_t at = (uint64_t)row * row_stride + qs[j];
-            g[j] = oks[j] ? ld_stream(in + at) : make_uint4(0u, 0u, 0u, 0u);
-            u[j] = oks[j] ? ld_stream(other + at) : make_uint4(0u, 0u, 0u, 0u);
+            // kHeadGate: `in` has a row pitch of its own and holds, per head, the head's other values
+            // first and then its gate values: chunk q of the row sits at q + (q rounded down to its
+            // head) + one head.  Otherwise both planes share the pitch and the chunk index.
+            const uint64_t other_at = (uint64_t)row * other_row_stride + qs[j];
+            const uint64_t in_at = kHeadGate ? (uint64_t)row * row_stride + qs[j] + (qs[j] & in_head_keep) + in_head_add : other_at;
+            g[j] = oks[j] ? ld_stream(in + in_at) : make_uint4(0u, 0u, 0u, 0u);
+            u[j] = oks[j] ? ld_stream(other + other_at) : make_uint4(0u, 0u, 0u, 0u);
             row += step_rows;
             col += step_cols;
             if (col >= col_groups) {
@@ -475,9 +479,10 @@ int launch_fp8_quantize_bf16(const void *input, uint32_t rows, uint32_t cols, ui
 
 // Shared launcher of the two gated NVFP4 ops.  `gate` / `other` are the two operand planes, row_stride their row
 // pitch in 16-byte chunks.
-template <gate_fn kFn>
-int launch_gated_nvfp4(const uint4 *gate, const uint4 *other, uint32_t row_stride, uint32_t rows, uint32_t width, float G,
-                       void *out_bf16, uint8_t *codes, uint8_t *scales, uint32_t layout, cudaStream_t stream) {
+template <gate_fn kFn, bool kHeadGate = false>
+int launch_gated_nvfp4(const uint4 *gate, const uint4 *other, uint32_t row_stride, uint32_t other_row_stride,
+                       uint32_t gate_head_chunks, uint32_t rows, uint32_t width, float G, void *out_bf16, uint8_t *codes,
+                       uint8_t *scales, uint32_t layout, cudaStream_t stream) {
     const uint32_t chunks = width / 8u;
     const uint32_t groups = width / kGroup;
     const uint32_t col_groups = (chunks + 31u) / 32u;
@@ -490,20 +495,23 @@ int launch_gated_nvfp4(const uint4 *gate, const uint4 *other, uint32_t row_strid
     uint64_t blocks = (tiles + warps_per_block - 1u) / warps_per_block;
     if (blocks > cap) blocks = cap;
     const uint32_t W = (uint32_t)blocks * warps_per_block;
+    const uint32_t head_keep = gate_head_chunks ? ~(gate_head_chunks - 1u) : 0u;  // gate_head_chunks is a power of two
     if (table) {
         static bool configured[64] = {};
         int dev = 0;
         cudaGetDevice(&dev);
         if (dev >= 0 && dev < 64 && !configured[dev]) {
-            cudaFuncSetAttribute(swiglu_nvfp4_kernel<true, kFn>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSiluTableBytes);
+            cudaFuncSetAttribute(swiglu_nvfp4_kernel<true, kFn, kHeadGate>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSiluTableBytes);
             configured[dev] = true;
         }
-        launch_chained(swiglu_nvfp4_kernel<true, kFn>, dim3((uint32_t)blocks), dim3(kNvThreads), kSiluTableBytes, stream,
-                       gate, other, row_stride, rows, chunks, col_groups, W / col_groups, W % col_groups, G, (uint4 *)out_bf16,
+        launch_chained(swiglu_nvfp4_kernel<true, kFn, kHeadGate>, dim3((uint32_t)blocks), dim3(kNvThreads), kSiluTableBytes, stream,
+                       gate, other, row_stride, other_row_stride, head_keep, gate_head_chunks, rows, chunks, col_groups,
+                       W / col_groups, W % col_groups, G, (uint4 *)out_bf16,
                        (uint32_t *)codes, scales, layout, groups, (groups + 3u) / 4u, device_table);
     } else {
-        launch_chained(swiglu_nvfp4_kernel<false, kFn>, dim3((uint32_t)blocks), dim3(kNvThreads), 0, stream,
-                       gate, other, row_stride, rows, chunks, col_groups, W / col_groups, W % col_groups, G, (uint4 *)out_bf16,
+        launch_chained(swiglu_nvfp4_kernel<false, kFn, kHeadGate>, dim3((uint32_t)blocks), dim3(kNvThreads), 0, stream,
+                       gate, other, row_stride, other_row_stride, head_keep, gate_head_chunks, rows, chunks, col_groups,
+                       W / col_groups, W % col_groups, G, (uint4 *)out_bf16,
                        (uint32_t *)codes, scales, layout, groups, (groups + 3u) / 4u, nullptr);
     }
     note_launch();
@@ -513,14 +521,24 @@ int launch_gated_nvfp4(const uint4 *gate, const uint4 *other, uint32_t row_strid
 int launch_swiglu_nvfp4_bf16(const void *gate_up, uint32_t rows, uint32_t width, float G, uint8_t *codes,
                              uint8_t *scales, uint32_t layout, cudaStream_t stream) {
     const uint4 *gate = (const uint4 *)gate_up;
-    return launch_gated_nvfp4<gate_fn::silu>(gate, gate + width / 8u, 2u * (width / 8u), rows, width, G, nullptr, codes,
-                                             scales, layout, stream);
+    return launch_gated_nvfp4<gate_fn::silu>(gate, gate + width / 8u, 2u * (width / 8u), 2u * (width / 8u), 0u, rows, width, G,
+                                             nullptr, codes, scales, layout, stream);
 }
 
 int launch_sigmoid_gate_nvfp4_bf16(const void *attention, const void *gate, uint32_t rows, uint32_t width, float G,
                                    void *out_bf16, uint8_t *codes, uint8_t *scales, uint32_t layout, cudaStream_t stream) {
-    return launch_gated_nvfp4<gate_fn::sigmoid>((const uint4 *)gate, (const uint4 *)attention, width / 8u, rows, width, G,
-                                                out_bf16, codes, scales, layout, stream);
+    return launch_gated_nvfp4<gate_fn::sigmoid>((const uint4 *)gate, (const uint4 *)attention, width / 8u, width / 8u, 0u, rows,
+                                                width, G, out_bf16, codes, scales, layout, stream);
+}
+
+// Gate values read where the q projection left them: q_gate is [rows][heads][2 * head_dim], each head's
+// gate values behind its query values.
+int launch_sigmoid_gate_heads_nvfp4_bf16(const void *attention, const void *q_gate, uint32_t rows, uint32_t heads,
+                                         uint32_t head_dim, float G, void *out_bf16, uint8_t *codes, uint8_t *scales,
+                                         uint32_t layout, cudaStream_t stream) {
+    const uint32_t width = heads * head_dim;
+    return launch_gated_nvfp4<gate_fn::sigmoid, true>((const uint4 *)q_gate, (const uint4 *)attention, 2u * (width / 8u), width / 8u,
+                                                      head_dim / 8u, rows, width, G, out_bf16, codes, scales, layout, stream);
 }
 
 }  // namespace axb
@@ -584,5 +602,24 @@ extern "C" int axiom_qwen38_fused_sigmoid_gate_nvfp4_bf16_device(
     if (rc != AXIOM_OK) return rc;
     launch_sigmoid_gate_nvfp4_bf16(attention_bf16, gate_bf16, rows, width, out_codes ? global_scale : 1.0f, out_bf16, out_codes,
                                    out_scales, scale_layout, (cudaStream_t)stream);
+    return launch_status();
+}
+
+extern "C" int axiom_qwen38_fused_sigmoid_gate_heads_nvfp4_bf16_device(
+        int device, const void *attention_bf16, const void *q_gate_bf16, uint32_t rows, uint32_t heads, uint32_t head_dim,
+        float global_scale, void *out_bf16, uint8_t *out_codes, uint8_t *out_scales, uint32_t scale_layout, void *stream) {
+    if (!attention_bf16 || !q_gate_bf16 || rows == 0u || heads == 0u || heads > 4096u ||
+        (head_dim != 64u && head_dim != 128u && head_dim != 256u) || scale_layout > AXIOM_SCALE_LAYOUT_TILED ||
+        !aligned16(attention_bf16) || !aligned16(q_gate_bf16) || (uint64_t)rows * (heads * head_dim / 8u) * 2u > 0xffffffffull) {
+        return AXIOM_ERR_INVALID_ARGUMENT;
+    }
+    if ((out_codes == nullptr) != (out_scales == nullptr)) return AXIOM_ERR_INVALID_ARGUMENT;
+    if (!out_codes && !out_bf16) return AXIOM_ERR_INVALID_ARGUMENT;
+    if (out_codes && (!valid_scale(global_scale) || (reinterpret_cast<uintptr_t>(out_codes) & 3u))) return AXIOM_ERR_INVALID_ARGUMENT;
+    if (out_bf16 && !aligned16(out_bf16)) return AXIOM_ERR_INVALID_ARGUMENT;
+    int rc = select_device(device);
+    if (rc != AXIOM_OK) return rc;
+    launch_sigmoid_gate_heads_nvfp4_bf16(attention_bf16, q_gate_bf16, rows, heads, head_dim, out_codes ? global_scale : 1.0f,
+                                         out_bf16, out_codes, out_scales, scale_layout, (cudaStream_t)stream);
     return launch_status();
 }

@@ -219,6 +219,11 @@ int axiom_qwen38_fused_swiglu_nvfp4_bf16_device(int device, const void *gate_up_
  * the output projection that follows it: y = bf16(attention * (1/(1+expf(-gate)))), optionally written to out_bf16,
  * and/or quantized to NVFP4 (both code outputs or neither).  attention, gate, out: [rows x width] BF16. width % 16 == 0. */
 int axiom_qwen38_fused_sigmoid_gate_nvfp4_bf16_device(int device, const void *attention_bf16, const void *gate_bf16, uint32_t rows, uint32_t width, float global_scale, void *out_bf16, uint8_t *out_codes, uint8_t *out_scales, uint32_t scale_layout, void *stream);
+/* The same op with the gate read where the q projection left it, which makes the gate half of
+ * qwen38_split_q_gate_round_k8_kernel (src/axiom_qwen38_attention.cu:431-453) unnecessary: q_gate_bf16 is
+ * [rows][heads][2*head_dim], each head's head_dim query values followed by its head_dim gate values; attention, out and
+ * the codes are [rows][heads*head_dim].  head_dim is 64, 128 or 256. */
+int axiom_qwen38_fused_sigmoid_gate_heads_nvfp4_bf16_device(int device, const void *attention_bf16, const void *q_gate_bf16, uint32_t rows, uint32_t heads, uint32_t head_dim, float global_scale, void *out_bf16, uint8_t *out_codes, uint8_t *out_scales, uint32_t scale_layout, void *stream);
 
 /* Greedy selection over rows of F32 logits.  Replaces qwen38_top1_8_kernel and the hierarchical pair
  * qwen38_top1_8_stage1/stage2_kernel with its `partials` scratch (src/axiom_qwen38_model.cu:408-600):
@@ -273,9 +278,14 @@ float axiom_qwen38_fused_yarn_mscale(float factor);
 #define AXIOM_QK_FLAG_PER_TOKEN_TABLE 2u /* token t uses block-table row t (batched decode); else row 0 (one sequence) */
 #define AXIOM_QK_FLAG_CACHE_E4M3 4u      /* k_pool / v_pool hold E4M3 codes at scale 1 (one byte per element) instead of
                                           * BF16: qwen38_kv_store_e4m3fn_scale1, src/axiom_qwen38_attention.cu:245-281 */
+#define AXIOM_QK_FLAG_Q_GATE_INTERLEAVED 8u /* q_bf16 is the q_proj output [tokens][q_heads][2*head_dim], each head holding
+                                          * its head_dim query values and then its head_dim gate values; only the query
+                                          * halves are read and the result goes to q_out_bf16 (required).  Replaces the q part of
+                                          * qwen38_split_q_gate_round_k8_kernel, src/axiom_qwen38_attention.cu:431-453; the gate
+                                          * halves stay where they are for axiom_qwen38_fused_sigmoid_gate_heads_nvfp4_bf16_device */
 typedef struct {
     uint32_t abi_version;     /* AXIOM_ABI_VERSION */
-    uint32_t struct_size;     /* sizeof(axiom_qk_rope_args) */
+    uint32_t struct_size;     /* sizeof(axiom_qk_rope_args); the size without q_out_bf16 is accepted too (q_out_bf16 = NULL) */
     uint32_t tokens;
     uint32_t q_heads;
     uint32_t k_heads;
@@ -302,6 +312,7 @@ typedef struct {
     void *v_pool_bf16;        /* optional */
     void *k_out_bf16;         /* optional */
     uint32_t *status_word;    /* optional */
+    void *q_out_bf16;         /* optional [tokens][q_heads][head_dim]: when set, q_bf16 is only read and the result goes here */
 } axiom_qk_rope_args;
 int axiom_qwen38_fused_qk_norm_rope_paged_bf16_device(int device, const axiom_qk_rope_args *args, void *stream);
 

@@ -36,7 +36,7 @@ def tolerance(q_in, gamma, inv_freq, positions, rope_dim, mscale, eps=1e-6):
 
 def run_case(axk, tokens, q_heads, k_heads, head_dim, rope_dim, *, n_blocks=64, block_tokens=16, n_layers=2, layer=1,
              pool_pad=0, ring=True, per_token=False, with_v=True, theta=1e6, factor=4.0, ctx=32768.0, max_base=100000,
-             seed=3, fp8_cache=False):
+             seed=3, fp8_cache=False, q_mode="inplace"):
     import torch
     from gpu_util import Guarded, dev, host, sync
 
@@ -57,23 +57,34 @@ def run_case(axk, tokens, q_heads, k_heads, head_dim, rope_dim, *, n_blocks=64, 
     cell = 1 if fp8_cache else 2  # bytes per cache element
     k_pool, v_pool = Guarded(pool_elems * cell), Guarded(pool_elems * cell)
     k_out = Guarded(tokens * kv_dim * 2)
-    qd, kd, vd = dev(q), dev(k), dev(v)
+    # q_mode: "inplace" rewrites Q; "out" leaves Q alone and writes q_out; "interleaved" reads the query halves of a
+    # [tokens][heads][2 * head_dim] q-projection output (gate values behind every head) and writes q_out
+    q_source = q
+    if q_mode == "interleaved":
+        gate_rng = np.random.default_rng(seed + 17)
+        q_source = np.concatenate([q, gate_rng.integers(0, 1 << 16, q.shape).astype(np.uint16)], axis=-1)
+    q_out = Guarded(tokens * q_heads * head_dim * 2) if q_mode != "inplace" else None
+    qd, kd, vd = dev(q_source), dev(k), dev(v)
     # every device tensor is named: the argument struct only carries raw addresses
     qgd, kgd, fd, pd, td = dev(qg), dev(kg), dev(inv_freq), dev(positions), dev(table)
     status = torch.zeros(1, dtype=torch.int32, device="cuda")
     flags = ((axk.QK_FLAG_RING if ring else 0) | (axk.QK_FLAG_PER_TOKEN_TABLE if per_token else 0) |
-             (axk.QK_FLAG_CACHE_E4M3 if fp8_cache else 0))
+             (axk.QK_FLAG_CACHE_E4M3 if fp8_cache else 0) |
+             (axk.QK_FLAG_Q_GATE_INTERLEAVED if q_mode == "interleaved" else 0))
     args = axk.make_qk_args(tokens=tokens, q_heads=q_heads, k_heads=k_heads, head_dim=head_dim, rope_dim=rope_dim,
                             flags=flags, eps=1e-6, mscale=mscale, block_tokens=block_tokens, n_layers=n_layers,
                             layer=layer, pool_stride=pool_stride, tbl_stride=table.shape[1], n_blocks=n_blocks,
                             q=qd, k=kd, v=vd if with_v else None, q_gamma=qgd, k_gamma=kgd,
                             inv_freq=fd, positions=pd, block_tables=td,
                             k_pool=k_pool.ptr, v_pool=v_pool.ptr if with_v else None, k_out=k_out.ptr,
-                            status_word=status)
+                            status_word=status, q_out=q_out.ptr if q_out else None)
     rc = axk.qk_norm_rope_paged(0, args)
     sync()
     assert rc == axk.AXIOM_OK
     assert k_pool.guards_intact() and v_pool.guards_intact() and k_out.guards_intact()
+    if q_out:
+        assert q_out.guards_intact()
+        assert np.array_equal(host(qd, np.uint16).reshape(q_source.shape), q_source)  # the source is only read
 
     # oracle on identical inputs, with poisoned pools of its own
     o_kpool = np.full(pool_elems, 0xFFFF, np.uint16)
@@ -82,7 +93,7 @@ def run_case(axk, tokens, q_heads, k_heads, head_dim, rope_dim, *, n_blocks=64, 
         q, k, v if with_v else None, qg, kg, inv_freq, positions, table, rope_dim=rope_dim, eps=1e-6, mscale=mscale,
         block_tokens=block_tokens, n_layers=n_layers, layer=layer, pool_stride=pool_stride, n_blocks=n_blocks,
         ring=ring, per_token_table=per_token, k_pool=o_kpool, v_pool=o_vpool if with_v else None, want_k_out=True)
-    got_q = host(qd, np.uint16).reshape(q.shape)
+    got_q = (q_out.payload(np.uint16) if q_out else host(qd, np.uint16)).reshape(q.shape)
     got_k = k_out.payload(np.uint16).reshape(k.shape)
     assert int(status.item()) == want_status
 
@@ -171,6 +182,58 @@ def test_e4m3_cache_flavour(axk, cuda_device, tokens):
     run_case(axk, tokens, 24, 4, 256, 64, n_blocks=256, n_layers=2, layer=1, pool_pad=64, fp8_cache=True, max_base=900,
              theta=1e7, ctx=262144.0)
     run_case(axk, tokens, 8, 2, 128, 128, n_blocks=64, fp8_cache=True, with_v=False, max_base=300)
+
+
+@pytest.mark.parametrize("q_mode", ["out", "interleaved"])
+@pytest.mark.parametrize("tokens", [1, 9, 64, 333, 597])
+def test_query_written_out_of_place_and_gate_interleaved_source(axk, cuda_device, tokens, q_mode):
+    """q_out_bf16 (per-token kernel below 296 tokens, streaming kernel above) and the q-projection layout with the
+    gate values behind every head: same results as the packed in-place call, source untouched."""
+    run_case(axk, tokens, 64, 8, 128, 128, n_blocks=1024, n_layers=1, layer=0, max_base=4000, q_mode=q_mode)
+    run_case(axk, tokens, 24, 4, 256, 64, n_blocks=256, n_layers=2, layer=1, max_base=900, theta=1e7, ctx=262144.0,
+             q_mode=q_mode)
+    run_case(axk, tokens, 5, 1, 64, 64, n_blocks=256, max_base=900, q_mode=q_mode, fp8_cache=(q_mode == "out"))
+
+
+def test_interleaved_source_matches_packed_call_bitwise(axk, cuda_device):
+    import torch
+    from gpu_util import dev, sync
+
+    tokens = 1024
+    q, k, v, qg, kg, positions, table = wl.qk_inputs_np(tokens, 64, 8, 128, 4096, seed=5)
+    inv_freq = ol.yarn_inv_freq(1e6, 4.0, 32768.0, 32.0, 1.0, 128)
+    mscale = float(ol.o().axo_yarn_mscale(4.0))
+    qgd, kgd, fd, td, pd, kd = dev(qg), dev(kg), dev(inv_freq), dev(table), dev(positions), dev(k)
+    gate = np.random.default_rng(0).integers(0, 1 << 16, q.shape).astype(np.uint16)
+    packed, source = dev(q), dev(np.concatenate([q, gate], axis=-1))
+    out = torch.zeros(tokens * 8192, dtype=torch.int16, device="cuda")
+    results = []
+    for flags, qbuf, q_out in ((axk.QK_FLAG_RING, packed, None),
+                               (axk.QK_FLAG_RING | axk.QK_FLAG_Q_GATE_INTERLEAVED, source, out)):
+        ko = torch.zeros(tokens * 1024, dtype=torch.int16, device="cuda")
+        args = axk.make_qk_args(tokens=tokens, q_heads=64, k_heads=8, head_dim=128, rope_dim=128, flags=flags, eps=1e-6,
+                                mscale=mscale, block_tokens=16, n_layers=1, layer=0, pool_stride=1024, tbl_stride=4096,
+                                n_blocks=4096, q=qbuf, k=kd, q_gamma=qgd, k_gamma=kgd, inv_freq=fd, positions=pd,
+                                block_tables=td, k_out=ko, q_out=q_out)
+        assert axk.qk_norm_rope_paged(0, args) == axk.AXIOM_OK
+        sync()
+        results.append(((q_out if q_out is not None else qbuf).cpu().numpy().view(np.uint16).reshape(-1), ko.cpu().numpy()))
+    assert np.array_equal(results[0][0], results[1][0]) and np.array_equal(results[0][1], results[1][1])
+    assert np.array_equal(source.cpu().numpy().view(np.uint16).reshape(tokens, 64, 256)[..., 128:], gate)
+    assert axk.lib().axiom_b200_pipeline_faults(0) == 0
+
+
+def test_interleaved_source_needs_q_out(axk, cuda_device):
+    import torch
+
+    buf = torch.zeros(1 << 16, dtype=torch.int16, device="cuda")
+    f = torch.zeros(64, dtype=torch.float32, device="cuda")
+    p = torch.zeros(4, dtype=torch.int32, device="cuda")
+    args = axk.make_qk_args(tokens=4, q_heads=4, k_heads=1, head_dim=128, rope_dim=128,
+                            flags=axk.QK_FLAG_Q_GATE_INTERLEAVED, eps=1e-6, mscale=1.0, block_tokens=16, n_layers=1,
+                            layer=0, pool_stride=128, tbl_stride=1, n_blocks=1, q=buf, k=buf, q_gamma=buf, k_gamma=buf,
+                            inv_freq=f, positions=p, k_out=buf)
+    assert axk.qk_norm_rope_paged(0, args) == axk.AXIOM_ERR_INVALID_ARGUMENT
 
 
 def test_streaming_and_per_token_kernels_agree_bitwise(axk, cuda_device):

@@ -202,3 +202,38 @@ def test_sigmoid_gate_nvfp4(axk, cuda_device, rows, width, layout):
     sync()
     assert np.array_equal(y2.cpu().numpy().view(np.uint16), got_y)
     assert axk.sigmoid_gate_nvfp4(0, a, g, rows, width, G, None, None, None, layout) == axk.AXIOM_ERR_INVALID_ARGUMENT
+
+
+@pytest.mark.parametrize("rows,heads,head_dim,layout", [(1, 64, 128, 0), (8, 24, 256, 1), (120, 5, 64, 1),
+                                                         (400, 64, 128, 1), (37, 3, 128, 0)])
+def test_sigmoid_gate_reads_gate_behind_each_head(axk, cuda_device, rows, heads, head_dim, layout):
+    """Gate taken from the q-projection output [rows][heads][2 * head_dim] (query values, then gate values, per head):
+    every output is bit-identical to the plain call on the de-interleaved gate plane, and the source is not written."""
+    from gpu_util import Guarded, dev, host, sync
+
+    width = heads * head_dim
+    rng = np.random.default_rng(rows * 11 + heads)
+    attn = wl.to_bf16_bits(rng.standard_normal((rows, width), dtype=np.float32))
+    gate = wl.to_bf16_bits(rng.standard_normal((rows, heads, head_dim), dtype=np.float32) * np.float32(2.0))
+    query = rng.integers(0, 1 << 16, gate.shape).astype(np.uint16)  # never read: any bit pattern
+    q_gate = np.concatenate([query, gate], axis=-1)
+    G = 300.0
+    a, g, qg = dev(attn), dev(gate.reshape(rows, width)), dev(q_gate)
+    nscale = int(axk.lib().axiom_nvfp4_scale_plane_bytes(rows, width // 16, layout))
+    outs = []
+    for strided in (False, True):
+        y, codes, scales = Guarded(rows * width * 2), Guarded(rows * width // 2), Guarded(nscale)
+        if layout == 1:
+            scales.raw[scales.pad:scales.pad + nscale] = 0
+        if strided:
+            rc = axk.sigmoid_gate_heads_nvfp4(0, a, qg, rows, heads, head_dim, G, y.ptr, codes.ptr, scales.ptr, layout)
+        else:
+            rc = axk.sigmoid_gate_nvfp4(0, a, g, rows, width, G, y.ptr, codes.ptr, scales.ptr, layout)
+        sync()
+        assert rc == axk.AXIOM_OK
+        assert y.guards_intact() and codes.guards_intact() and scales.guards_intact()
+        outs.append((y.payload(np.uint16).copy(), codes.payload().copy(), scales.payload().copy()))
+    for plain, strided in zip(*outs):
+        assert np.array_equal(plain, strided)
+    assert np.array_equal(host(qg, np.uint16).reshape(q_gate.shape), q_gate)
+    assert axk.sigmoid_gate_heads_nvfp4(0, a, qg, rows, heads, 96, G, None, None, None, layout) == axk.AXIOM_ERR_INVALID_ARGUMENT
