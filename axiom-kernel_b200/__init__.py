@@ -55,6 +55,14 @@ class RopeConfig(C.Structure):
                 ("original_context", f32), ("beta_fast", f32), ("beta_slow", f32)]
 
 
+class PagedKvView(C.Structure):
+    """axiom_paged_kv_view: the engine's device view of the paged KV arena."""
+    _fields_ = [
+        ("abi_version", u32), ("struct_size", u32), ("d_kpool", vp), ("d_vpool", vp), ("d_tbl", vp), ("d_meta", vp),
+        ("cap", u32), ("tbl_stride", u32), ("block_tokens", u32), ("n_layers", u32), ("kv_nphys", u32), ("kv_dim", u32),
+    ]
+
+
 class QkRopeArgs(C.Structure):
     _fields_ = [
         ("abi_version", u32), ("struct_size", u32), ("tokens", u32), ("q_heads", u32), ("k_heads", u32),
@@ -132,6 +140,8 @@ SIGNATURES = {
     "axiom_runtime_swiglu_fp8_bf16_device": (i32, [vp, *_BUF, u32, u32, *_BUF, *_BUF]),
     "axiom_runtime_swiglu_nvfp4_bf16_device": (i32, [vp, *_BUF, u32, u32, f32, *_BUF, *_BUF, u32]),
     "axiom_runtime_embedding_gather_bf16_device": (i32, [vp, *_BUF, u32, u32, *_BUF, u32, *_BUF]),
+    "axiom_runtime_qknorm_rope_yarn_paged_bf16_device": (i32, [vp, vp, u32, u32, u32, *_BUF, *_BUF, *_BUF, *_BUF, *_BUF, *_BUF,
+                                                                 u32, u32, u32, u32, f32, f32, *_BUF]),
     "axiom_runtime_nvfp4_quantize_bf16": (i32, [vp, vp, u32, u32, f32, vp, vp]),
     "axiom_runtime_add_rmsnorm_nvfp4_bf16": (i32, [vp, vp, vp, vp, f32, u32, u32, f32, vp, vp]),
     "axiom_runtime_swiglu_fp8_bf16": (i32, [vp, vp, u32, u32, vp, vp]),

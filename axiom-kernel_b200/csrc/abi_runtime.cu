@@ -237,6 +237,73 @@ extern "C" int axiom_runtime_swiglu_nvfp4_bf16_device(
     return finish_after_launch(nullptr);
 }
 
+extern "C" int axiom_runtime_qknorm_rope_yarn_paged_bf16_device(
+        axiom_runtime *runtime, const axiom_paged_kv_view *view, uint32_t layer, uint32_t n_active, uint32_t flags,
+        axiom_device_buffer *q, uint64_t q_offset, const axiom_device_buffer *k, uint64_t k_offset,
+        const axiom_device_buffer *v, uint64_t v_offset, const axiom_device_buffer *q_gamma, uint64_t q_gamma_offset,
+        const axiom_device_buffer *k_gamma, uint64_t k_gamma_offset, const axiom_device_buffer *inv_freq,
+        uint64_t inv_freq_offset, uint32_t q_heads, uint32_t k_heads, uint32_t head_dim, uint32_t rope_dim, float eps,
+        float mscale, axiom_device_buffer *status_word, uint64_t status_offset) {
+    int rc = runtime_ok(runtime);
+    if (rc != AXIOM_OK) return rc;
+    if (!view || view->abi_version != AXIOM_ABI_VERSION || view->struct_size != sizeof(axiom_paged_kv_view)) {
+        return AXIOM_ERR_INVALID_ARGUMENT;
+    }
+    if (n_active == 0u || n_active > 65535u || n_active > view->cap || k_heads == 0u || !k || !k_gamma ||
+        (flags & ~AXIOM_QK_FLAG_CACHE_E4M3) != 0u || (head_dim != 64u && head_dim != 128u && head_dim != 256u) ||
+        view->tbl_stride == 0u || view->block_tokens == 0u || view->n_layers == 0u || layer >= view->n_layers ||
+        view->kv_nphys == 0u || view->kv_dim < k_heads * head_dim || (view->kv_dim % 8u) != 0u ||
+        (uint64_t)(q_heads + k_heads) * head_dim > (1u << 20) || (q_heads != 0u && (!q || !q_gamma)) ||
+        (rope_dim != 0u && !inv_freq) || (v == nullptr) != (view->d_vpool == nullptr)) {
+        return AXIOM_ERR_INVALID_ARGUMENT;
+    }
+    if (!owned_by(runtime, view->d_kpool) || !owned_by(runtime, view->d_tbl) || !owned_by(runtime, view->d_meta) ||
+        !owned_by(runtime, k) || !owned_by(runtime, k_gamma) || (v && (!owned_by(runtime, v) || !owned_by(runtime, view->d_vpool))) ||
+        (q_heads && (!owned_by(runtime, q) || !owned_by(runtime, q_gamma))) || (rope_dim && !owned_by(runtime, inv_freq)) ||
+        (status_word && !owned_by(runtime, status_word))) {
+        return AXIOM_ERR_INVALID_ARGUMENT;
+    }
+    const uint64_t cell = (flags & AXIOM_QK_FLAG_CACHE_E4M3) ? 1u : 2u;
+    uint64_t pool_rows = 0, pool_bytes = 0, tbl_bytes = 0;
+    if (!mul_ok((uint64_t)view->kv_nphys * view->n_layers, view->block_tokens, &pool_rows) ||
+        !mul_ok(pool_rows, (uint64_t)view->kv_dim * cell, &pool_bytes) ||
+        !mul_ok((uint64_t)view->cap * view->tbl_stride, 4u, &tbl_bytes)) {
+        return AXIOM_ERR_INVALID_ARGUMENT;
+    }
+    const uint64_t q_bytes = (uint64_t)n_active * q_heads * head_dim * 2u, k_bytes = (uint64_t)n_active * k_heads * head_dim * 2u;
+    if (!span_ok(view->d_kpool, 0u, pool_bytes) || (v && !span_ok(view->d_vpool, 0u, pool_bytes)) ||
+        !span_ok(view->d_tbl, 0u, tbl_bytes) || !span_ok(view->d_meta, 0u, (uint64_t)view->cap * 8u) ||
+        !span_ok(k, k_offset, k_bytes) || (k_offset & 15u) || (v && (!span_ok(v, v_offset, k_bytes) || (v_offset & 15u))) ||
+        (q_heads && (!span_ok(q, q_offset, q_bytes) || (q_offset & 15u) ||
+                     !span_ok(q_gamma, q_gamma_offset, (uint64_t)head_dim * 2u) || (q_gamma_offset & 1u))) ||
+        !span_ok(k_gamma, k_gamma_offset, (uint64_t)head_dim * 2u) || (k_gamma_offset & 1u) ||
+        (rope_dim && (!span_ok(inv_freq, inv_freq_offset, (uint64_t)(rope_dim / 2u) * 4u) || (inv_freq_offset & 3u))) ||
+        (status_word && (!span_ok(status_word, status_offset, 4u) || (status_offset & 3u)))) {
+        return AXIOM_ERR_INVALID_ARGUMENT;
+    }
+    axiom_qk_rope_args a{};
+    a.abi_version = AXIOM_ABI_VERSION;
+    a.struct_size = sizeof a;
+    a.tokens = n_active; a.q_heads = q_heads; a.k_heads = k_heads; a.head_dim = head_dim; a.rope_dim = rope_dim;
+    a.flags = flags | AXIOM_QK_FLAG_PER_TOKEN_TABLE;
+    a.eps = eps; a.mscale = mscale;
+    a.block_tokens = view->block_tokens; a.n_layers = view->n_layers; a.layer = layer; a.pool_stride = view->kv_dim;
+    a.tbl_stride = view->tbl_stride; a.n_blocks = view->kv_nphys;
+    a.q_bf16 = q_heads ? at(q, q_offset) : nullptr;
+    a.k_bf16 = at(k, k_offset);
+    a.v_bf16 = v ? at(v, v_offset) : nullptr;
+    a.q_gamma_bf16 = q_heads ? at(q_gamma, q_gamma_offset) : nullptr;
+    a.k_gamma_bf16 = at(k_gamma, k_gamma_offset);
+    a.inv_freq = rope_dim ? (const float *)at(inv_freq, inv_freq_offset) : nullptr;
+    a.positions = (const uint32_t *)at(view->d_meta, (uint64_t)view->cap * 4u);
+    a.block_tables = (const int32_t *)at(view->d_tbl, 0u);
+    a.k_pool_bf16 = at(view->d_kpool, 0u);
+    a.v_pool_bf16 = v ? at(view->d_vpool, 0u) : nullptr;
+    a.status_word = status_word ? (uint32_t *)at(status_word, status_offset) : nullptr;
+    rc = axiom_qwen38_fused_qk_norm_rope_paged_bf16_device((int)runtime->device, &a, nullptr);
+    return rc != AXIOM_OK ? rc : finish_after_launch(nullptr);
+}
+
 extern "C" int axiom_runtime_embedding_gather_bf16_device(
         axiom_runtime *runtime, const axiom_device_buffer *table, uint64_t table_offset, uint32_t vocab,
         uint32_t hidden, const axiom_device_buffer *token_ids, uint64_t ids_offset, uint32_t tokens,

@@ -323,6 +323,31 @@ int axiom_runtime_swiglu_fp8_bf16_device(axiom_runtime *runtime, const axiom_dev
 int axiom_runtime_swiglu_nvfp4_bf16_device(axiom_runtime *runtime, const axiom_device_buffer *gate_up, uint64_t gate_up_offset, uint32_t rows, uint32_t width, float global_scale, axiom_device_buffer *out_codes, uint64_t codes_offset, axiom_device_buffer *out_scales, uint64_t scales_offset, uint32_t scale_layout);
 int axiom_runtime_embedding_gather_bf16_device(axiom_runtime *runtime, const axiom_device_buffer *table, uint64_t table_offset, uint32_t vocab, uint32_t hidden, const axiom_device_buffer *token_ids, uint64_t ids_offset, uint32_t tokens, axiom_device_buffer *out, uint64_t out_offset);
 
+/* The q/k call as a step-engine family provider makes it (forward_step / prefill_token hooks,
+ * include/axiom/axiom_engine.h:218-245): the paged-KV addressing comes from the engine's device view.  The view
+ * mirrors axiom_engine_dev (include/axiom/axiom_engine.h:183-198) plus the pool geometry of the arena
+ * (axiom_engine_kv_arena, :164-181; element offset (((pb*n_layers+L)*BT+slot)*kv_dim), :282-283); the pools hold BF16
+ * (E4M3 bytes with AXIOM_QK_FLAG_CACHE_E4M3) instead of F32.  Active sequence a (0 <= a < n_active <= cap, at most
+ * 65535 like axiom_runtime_kv_pool_store_paged_f32_device, src/axiom_cuda.cu:16982-16987) uses block-table row a and the
+ * position at d_meta byte offset cap*4 + a*4; a position beyond its row's tbl_stride blocks or a block id outside
+ * [0, kv_nphys) raises the status word and writes nothing.  q, k, v: [n_active][heads][head_dim] BF16 staging rows.
+ * flags: 0 or AXIOM_QK_FLAG_CACHE_E4M3.  Every span is checked against its buffer before the launch. */
+typedef struct {
+    uint32_t abi_version;     /* AXIOM_ABI_VERSION */
+    uint32_t struct_size;     /* sizeof(axiom_paged_kv_view) */
+    axiom_device_buffer *d_kpool;       /* kv_nphys * n_layers * block_tokens * kv_dim cache elements */
+    axiom_device_buffer *d_vpool;       /* same geometry; may be NULL together with v */
+    const axiom_device_buffer *d_tbl;   /* [cap][tbl_stride] int32 */
+    const axiom_device_buffer *d_meta;  /* [2*cap] u32: cache_tokens at byte 0, positions at byte cap*4 */
+    uint32_t cap;
+    uint32_t tbl_stride;
+    uint32_t block_tokens;    /* kv_bt (AXIOM_KV_BLOCK, default 16) */
+    uint32_t n_layers;
+    uint32_t kv_nphys;
+    uint32_t kv_dim;          /* elements per pool row; >= k_heads*head_dim, multiple of 8 */
+} axiom_paged_kv_view;
+int axiom_runtime_qknorm_rope_yarn_paged_bf16_device(axiom_runtime *runtime, const axiom_paged_kv_view *view, uint32_t layer, uint32_t n_active, uint32_t flags, axiom_device_buffer *q, uint64_t q_offset, const axiom_device_buffer *k, uint64_t k_offset, const axiom_device_buffer *v, uint64_t v_offset, const axiom_device_buffer *q_gamma, uint64_t q_gamma_offset, const axiom_device_buffer *k_gamma, uint64_t k_gamma_offset, const axiom_device_buffer *inv_freq, uint64_t inv_freq_offset, uint32_t q_heads, uint32_t k_heads, uint32_t head_dim, uint32_t rope_dim, float eps, float mscale, axiom_device_buffer *status_word, uint64_t status_offset);
+
 /* ---- host I/O flavour: pinned or pageable host pointers in, host pointers out.
  * Rows are streamed through runtime-owned staging buffers in chunks so the
  * upload of chunk i+1, the kernel on chunk i and the download of chunk i-1

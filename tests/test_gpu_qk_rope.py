@@ -236,6 +236,49 @@ def test_interleaved_source_needs_q_out(axk, cuda_device):
     assert axk.qk_norm_rope_paged(0, args) == axk.AXIOM_ERR_INVALID_ARGUMENT
 
 
+@pytest.mark.parametrize("tokens", [70, 600])
+def test_e4m3_page_records_of_the_kv_tier(axk, cuda_device, tokens):
+    """The reference's tier record (include/axiom/qwen38_kv_tier.h:9-19; written on the device by
+    qwen38_stream_store_kv_page_kernel, src/axiom_qwen38_attention.cu:1438-1449): a 256-token page is E4M3
+    K[256][kv_dim] followed by E4M3 V[256][kv_dim], 512 KiB at kv_dim 1024.  The paged addressing of the q/k call
+    expresses it with block_tokens = 256, two "layers" per page (the K half and the V half) and the V pool
+    pointer advanced by one half: every record is then produced by the kernel itself."""
+    import torch
+    from gpu_util import Guarded, dev, sync
+
+    q_heads, k_heads, D, rope_dim, pages = 24, 4, 256, 64, 4
+    kv_dim, page_tokens = k_heads * D, 256
+    half_bytes = page_tokens * kv_dim
+    q, k, v, qg, kg, _, _ = wl.qk_inputs_np(tokens, q_heads, k_heads, D, pages, seed=21)
+    positions = (1000 + np.arange(tokens)).astype(np.uint32)
+    table = np.array([[2, 0, 3, 1]], np.int32)
+    inv_freq = ol.yarn_inv_freq(1e7, 4.0, 262144.0, 32.0, 1.0, rope_dim)
+    mscale = float(ol.o().axo_yarn_mscale(4.0))
+    records = Guarded(pages * 2 * half_bytes)
+    qd, kd, vd, qgd, kgd, fd, pd, td = dev(q), dev(k), dev(v), dev(qg), dev(kg), dev(inv_freq), dev(positions), dev(table)
+    k_out = torch.zeros(tokens * kv_dim, dtype=torch.int16, device="cuda")
+    status = torch.zeros(1, dtype=torch.int32, device="cuda")
+    args = axk.make_qk_args(tokens=tokens, q_heads=q_heads, k_heads=k_heads, head_dim=D, rope_dim=rope_dim,
+                            flags=axk.QK_FLAG_RING | axk.QK_FLAG_CACHE_E4M3, eps=1e-6, mscale=mscale,
+                            block_tokens=page_tokens, n_layers=2, layer=0, pool_stride=kv_dim, tbl_stride=pages,
+                            n_blocks=pages, q=qd, k=kd, v=vd, q_gamma=qgd, k_gamma=kgd, inv_freq=fd, positions=pd,
+                            block_tables=td, k_pool=records.ptr, v_pool=records.ptr + half_bytes, k_out=k_out,
+                            status_word=status)
+    assert axk.qk_norm_rope_paged(0, args) == axk.AXIOM_OK
+    sync()
+    assert int(status.item()) == 0 and records.guards_intact()
+    got = records.payload().reshape(pages, 2, page_tokens, kv_dim)
+    want = np.full_like(got, 0xFF)
+    k_rot = k_out.cpu().numpy().view(np.uint16).reshape(tokens, kv_dim)
+    for t in range(tokens):
+        pos = int(positions[t])
+        page, slot = int(table[0, (pos // page_tokens) % pages]), pos % page_tokens
+        want[page, 0, slot] = ol.bf16_to_e4m3_scale1(k_rot[t])
+        want[page, 1, slot] = ol.bf16_to_e4m3_scale1(v[t].reshape(-1))
+    assert np.array_equal(got, want)
+    assert axk.lib().axiom_b200_pipeline_faults(0) == 0
+
+
 def test_streaming_and_per_token_kernels_agree_bitwise(axk, cuda_device):
     """The same 2048 tokens once in one call (streaming kernel) and once in calls of 128 (per-token kernel)."""
     import torch

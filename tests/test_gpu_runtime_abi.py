@@ -368,3 +368,84 @@ def test_launch_async_env_is_honoured(axk, rt):
     torch.cuda.synchronize()
     got = np.empty_like(a); ob.download(got)
     assert np.array_equal(got, a + a)
+
+
+def test_engine_view_qk_step_ragged_batch(axk, rt):
+    """One decode step of a ragged continuous batch as a step-engine family provider issues it: block tables and
+    positions come from the engine's device bookkeeping (d_tbl [cap][tbl_stride], positions at byte cap*4 of
+    d_meta), the pools are poisoned with 0xFF first and every written cell is recomputed on the host — the scheme
+    of the reference's paged-store parity tool (tools/axiom_paged_attn_parity_smoke.cpp:207-241), on BF16 pools."""
+    lib = axk.lib()
+    cap, n_active, tbl_stride, bt, n_layers, layer, nphys = 12, 7, 6, 16, 3, 1, 40
+    q_heads, k_heads, D, rope_dim = 16, 2, 128, 128
+    kv_dim = k_heads * D + 64  # a pool row wider than the K row: the tail lanes must stay untouched
+    rng = np.random.default_rng(77)
+    q, k, v, qg, kg, _, _ = wl.qk_inputs_np(n_active, q_heads, k_heads, D, nphys, seed=9)
+    lengths = np.array([0, 15, 16, 17, 63, 95, 40], np.uint32)  # cache length of each active sequence = write position
+    tbl = np.full((cap, tbl_stride), -1, np.int32)
+    free = list(rng.permutation(nphys))
+    for a in range(n_active):
+        for lb in range(int(lengths[a]) // bt + 1):
+            tbl[a, lb] = free.pop()
+    meta = np.zeros(2 * cap, np.uint32)
+    meta[:n_active] = lengths + 1
+    meta[cap:cap + n_active] = lengths
+    inv_freq = ol.yarn_inv_freq(1e6, 4.0, 32768.0, 32.0, 1.0, rope_dim)
+    mscale = float(ol.o().axo_yarn_mscale(4.0))
+    pool_elems = nphys * n_layers * bt * kv_dim
+    poison = np.full(pool_elems, 0xFFFF, np.uint16)
+    bufs = {name: buf_from(axk, rt, a) for name, a in dict(q=q, k=k, v=v, qg=qg, kg=kg, f=inv_freq, tbl=tbl, meta=meta,
+                                                           kpool=poison, vpool=poison, status=np.zeros(1, np.uint32)).items()}
+    view = axk.PagedKvView(axk.AXIOM_ABI_VERSION, C.sizeof(axk.PagedKvView), bufs["kpool"].handle, bufs["vpool"].handle,
+                           bufs["tbl"].handle, bufs["meta"].handle, cap, tbl_stride, bt, n_layers, nphys, kv_dim)
+
+    def call(n=n_active, lyr=layer, flags=0, view_=view):
+        return lib.axiom_runtime_qknorm_rope_yarn_paged_bf16_device(
+            rt.handle, C.byref(view_), lyr, n, flags, bufs["q"].handle, 0, bufs["k"].handle, 0, bufs["v"].handle, 0,
+            bufs["qg"].handle, 0, bufs["kg"].handle, 0, bufs["f"].handle, 0, q_heads, k_heads, D, rope_dim, 1e-6, mscale,
+            bufs["status"].handle, 0)
+
+    assert call() == axk.AXIOM_OK
+    got_q, got_kpool, got_vpool = np.empty_like(q), np.empty_like(poison), np.empty_like(poison)
+    status = np.ones(1, np.uint32)
+    for name, out in (("q", got_q), ("kpool", got_kpool), ("vpool", got_vpool), ("status", status)):
+        assert bufs[name].download(out) == axk.AXIOM_OK
+    assert int(status[0]) == 0
+    o_kpool, o_vpool = poison.copy(), poison.copy()
+    want_q, _, want_status = ol.qk_norm_rope_paged(
+        q, k, v, qg, kg, inv_freq, lengths[:n_active], tbl[:n_active], rope_dim=rope_dim, eps=1e-6, mscale=mscale,
+        block_tokens=bt, n_layers=n_layers, layer=layer, pool_stride=kv_dim, n_blocks=nphys, ring=False,
+        per_token_table=True, k_pool=o_kpool, v_pool=o_vpool, want_k_out=True)
+    assert want_status == 0
+    assert np.mean(got_q != want_q) < 0.02
+    assert np.all(np.abs(wl.from_bf16_bits(got_q) - wl.from_bf16_bits(want_q)) <=
+                  ol.bf16_ulp(np.abs(wl.from_bf16_bits(want_q))) * np.float32(4.0) + np.float32(1e-3))
+    # cells: exactly the oracle's, V bit for bit, K within the rotation tolerance and at the same addresses
+    assert np.array_equal(got_vpool, o_vpool)
+    assert np.array_equal(got_kpool != 0xFFFF, o_kpool != 0xFFFF)
+    for a in range(n_active):
+        pos = int(lengths[a])
+        base = ((int(tbl[a, pos // bt]) * n_layers + layer) * bt + pos % bt) * kv_dim
+        assert np.all(got_kpool[base:base + k_heads * D] != 0xFFFF) and np.all(got_kpool[base + k_heads * D:base + kv_dim] == 0xFFFF)
+    assert int((got_kpool != 0xFFFF).sum()) == n_active * k_heads * D
+
+    # a sequence whose position has no block yet (-1 in its row) raises the status word and writes nothing for it
+    meta2 = meta.copy()
+    meta2[cap + 2] = 5 * bt
+    assert bufs["meta"].upload(meta2) == axk.AXIOM_OK and bufs["kpool"].upload(poison) == axk.AXIOM_OK
+    assert call() == axk.AXIOM_OK
+    assert bufs["status"].download(status) == axk.AXIOM_OK and int(status[0]) == axk.STATUS_WORD_BAD_ADDRESS
+    assert bufs["kpool"].download(got_kpool) == axk.AXIOM_OK
+    assert int((got_kpool != 0xFFFF).sum()) == (n_active - 1) * k_heads * D
+
+    # validation: more sequences than slots, layer out of range, unknown flag, pool smaller than its geometry
+    inv = axk.AXIOM_ERR_INVALID_ARGUMENT
+    assert call(n=cap + 1) == inv and call(lyr=n_layers) == inv and call(flags=axk.QK_FLAG_RING) == inv and call(n=0) == inv
+    big = axk.PagedKvView(axk.AXIOM_ABI_VERSION, C.sizeof(axk.PagedKvView), bufs["kpool"].handle, bufs["vpool"].handle,
+                          bufs["tbl"].handle, bufs["meta"].handle, cap, tbl_stride, bt, n_layers, nphys + 1, kv_dim)
+    assert call(view_=big) == inv
+    wide = axk.PagedKvView(axk.AXIOM_ABI_VERSION, C.sizeof(axk.PagedKvView), bufs["kpool"].handle, bufs["vpool"].handle,
+                           bufs["tbl"].handle, bufs["meta"].handle, cap + 1, tbl_stride, bt, n_layers, nphys, kv_dim)
+    assert call(view_=wide) == inv
+    for b in bufs.values():
+        b.close()
