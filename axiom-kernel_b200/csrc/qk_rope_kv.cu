@@ -22,6 +22,8 @@
 // for short batches, and a persistent bulk-copy pipeline for long ones.
 // The frequency table is an input: it is evaluated once per model on the device
 // (yarn_inv_freq_kernel) instead of powf/logf per thread per call.
+#include <cuda.h>  // CUtensorMap and its enums only: the encoder is fetched through the runtime, nothing links libcuda
+
 #include "pipeline.cuh"
 #include "runtime.hpp"
 
@@ -37,6 +39,7 @@ struct qk_dev_args {
     const uint4 *q;          // source rows: q_heads heads at a pitch of q_head_stride elements
     uint4 *q_out;            // destination rows, heads packed
     uint32_t q_head_stride;  // head_dim, or 2 * head_dim when each head is followed by its gate values
+    uint32_t q_use_map;      // streaming kernel: the strided query halves of a token come through the tensor map
     const uint4 *k;
     const uint4 *v;
     const uint16_t *q_gamma;
@@ -324,6 +327,16 @@ qk_norm_rope_paged_kernel(const qk_dev_args a) {
 // is refilled at the end of token i, once its stores have finished reading shared memory (one
 // store group may stay pending), so loads run `slots - 1` tokens ahead.
 // ---------------------------------------------------------------------------
+// One box of a 3-D tensor map -> shared memory, completion counted in bytes on `bar`.  The
+// innermost coordinate times the element size has to be a multiple of 16 bytes (here it is 0),
+// the destination 128-byte aligned.
+__device__ __forceinline__ void tensor_load_3d(void *dst_shared, const CUtensorMap *map, int32_t x, int32_t y, int32_t z,
+                                               uint64_t *bar) {
+    asm volatile("cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4}], [%5];"
+                 ::"r"(smem_addr(dst_shared)), "l"(reinterpret_cast<uint64_t>(map)), "r"(x), "r"(y), "r"(z), "r"(smem_addr(bar))
+                 : "memory");
+}
+
 constexpr uint32_t kQkMaxSlots = 4u;
 constexpr uint32_t kQkVRegs = 2u;  // 16-byte V chunks a thread carries across the token's barrier
 constexpr uint32_t kQkStreamThreads = 896u;  // 28 warps: leaves 72 registers per thread
@@ -341,7 +354,7 @@ __device__ __forceinline__ void team_sync(uint32_t team, uint32_t threads) {
 
 template <int LPH, int NPT, bool kFullRot>
 __global__ void __launch_bounds__(kQkStreamThreads, 1)
-qk_norm_rope_stream_kernel(const qk_dev_args a, const qk_stream_geom g) {
+qk_norm_rope_stream_kernel(const qk_dev_args a, const qk_stream_geom g, const __grid_constant__ CUtensorMap q_map) {
     extern __shared__ __align__(128) uint8_t smem[];
     constexpr uint32_t D = LPH * 8u;
     const uint32_t half = a.rope_dim >> 1;
@@ -378,9 +391,11 @@ qk_norm_rope_stream_kernel(const qk_dev_args a, const qk_stream_geom g) {
     // are the older bulk group: only they have to be done reading) and slots - 1 tokens are
     // requested up front; fewer slots are refilled as soon as their own stores have drained.
     const uint32_t ahead = g.slots > 2u ? g.slots - 1u : g.slots;
-    // Requests token i into its slot; called by the whole manager warp.  A packed Q row is one copy;
-    // when every head is followed by its gate values the lanes fetch the heads' query halves one by
-    // one, so that the slot holds the same packed row either way.
+    // Requests token i into its slot; called by the whole manager warp.  A packed Q row is one copy.
+    // When every head is followed by its gate values, the query halves of the token are one box of a
+    // 3-D tensor map over (head_dim, heads at a pitch of two heads, tokens), which lands packed in
+    // the slot; without a map the lanes fetch the heads one by one.  The slot holds the same packed
+    // row in every case.
     const bool q_packed = a.q_head_stride == D;
     auto issue = [&](uint32_t i, uint32_t lane) {
         const uint64_t tok = token_of(i);
@@ -389,9 +404,10 @@ qk_norm_rope_stream_kernel(const qk_dev_args a, const qk_stream_geom g) {
         if (lane == 0u) {
             mbar_arrive_expect_tx(bars + j, q_bytes + k_bytes);
             if (q_bytes && q_packed) bulk_load(slot, reinterpret_cast<const uint8_t *>(a.q) + tok * q_bytes, q_bytes, bars + j);
+            else if (q_bytes && a.q_use_map) tensor_load_3d(slot, &q_map, 0, 0, (int32_t)tok, bars + j);
             if (k_bytes) bulk_load(slot + q_bytes, reinterpret_cast<const uint8_t *>(a.k) + tok * k_bytes, k_bytes, bars + j);
         }
-        if (!q_packed) {
+        if (!q_packed && !a.q_use_map) {
             __syncwarp();
             const uint8_t *row = reinterpret_cast<const uint8_t *>(a.q) + tok * a.q_heads * a.q_head_stride * 2u;
             for (uint32_t h = lane; h < a.q_heads; h += 32u) {
@@ -648,6 +664,34 @@ void launch_qk(const qk_dev_args &a, cudaStream_t stream) {
 #undef AXB_QK_LAUNCH
 }
 
+// Tensor map over the query halves of a q|gate-interleaved projection output: BF16, dimensions
+// (head_dim, heads, tokens), a head pitch of two heads, box = (head_dim, heads, 1) = one token's
+// packed Q row.  The driver's encoder is fetched through the runtime once; false (the kernel then
+// falls back to one bulk copy per head) when it is missing or refuses the shape.
+bool encode_strided_q_map(const qk_dev_args &a, CUtensorMap *map) {
+    using encode_fn = CUresult (*)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *,
+                                   const cuuint64_t *, const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave,
+                                   CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+    static const encode_fn encode = [] {
+        void *fn = nullptr;
+        cudaDriverEntryPointQueryResult found = cudaDriverEntryPointSymbolNotFound;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &found) != cudaSuccess ||
+            found != cudaDriverEntryPointSuccess) {
+            cudaGetLastError();
+            fn = nullptr;
+        }
+        return reinterpret_cast<encode_fn>(fn);
+    }();
+    if (!encode || a.q_heads > 256u || a.head_dim > 256u || a.tokens > 0x7fffffffu) return false;
+    const cuuint64_t dims[3] = {a.head_dim, a.q_heads, a.tokens};
+    const cuuint64_t strides[2] = {(cuuint64_t)a.q_head_stride * 2u, (cuuint64_t)a.q_heads * a.q_head_stride * 2u};  // bytes
+    const cuuint32_t box[3] = {a.head_dim, a.q_heads, 1u};
+    const cuuint32_t steps[3] = {1u, 1u, 1u};
+    return encode(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3u, const_cast<uint4 *>(a.q), dims, strides, box, steps,
+                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
 constexpr size_t kQkSmemBudget = 227u * 1024u;
 
 size_t qk_stream_smem(const qk_dev_args &a, const qk_stream_geom &g) {
@@ -689,16 +733,20 @@ bool launch_qk_stream(const qk_dev_args &a, cudaStream_t stream) {
     const size_t smem = qk_stream_smem(a, best);
     const uint32_t ctas = std::min<uint32_t>(kSmCount, (a.tokens + best.teams - 1u) / best.teams);
     const bool full = a.rope_dim == a.head_dim;
+    qk_dev_args a2 = a;
+    CUtensorMap q_map;
+    memset(&q_map, 0, sizeof q_map);
+    a2.q_use_map = a.q_heads != 0u && a.q_head_stride != a.head_dim && encode_strided_q_map(a, &q_map) ? 1u : 0u;
 #define AXB_QK_STREAM(NPT)                                                                               \
     do {                                                                                                 \
         if (full) {                                                                                      \
             auto kern = qk_norm_rope_stream_kernel<LPH, NPT, true>;                                      \
             cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kQkSmemBudget); \
-            launch_chained(kern, dim3(ctas), dim3(best.teams * best.team_threads), smem, stream, a, best);                       \
+            launch_chained(kern, dim3(ctas), dim3(best.teams * best.team_threads), smem, stream, a2, best, q_map);               \
         } else {                                                                                         \
             auto kern = qk_norm_rope_stream_kernel<LPH, NPT, false>;                                     \
             cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kQkSmemBudget); \
-            launch_chained(kern, dim3(ctas), dim3(best.teams * best.team_threads), smem, stream, a, best);                       \
+            launch_chained(kern, dim3(ctas), dim3(best.teams * best.team_threads), smem, stream, a2, best, q_map);               \
         }                                                                                                \
     } while (0)
     switch (best_npt) {

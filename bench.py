@@ -485,6 +485,20 @@ def bench_qk(torch, axk, wl, local, device, stream, timed, report, T):
     ms = timed(lambda i: axk.qk_norm_rope_paged(local, qk_sets[i % 2][0], stream))
     report("qk_norm_rope_paged_kv", ms, 2 * T * 64 * 128 * 2 + 2 * T * 8 * 128 * 2 + T * 4 + 4096 * 4 + 512, T,
            "config 3, Q in place, K to 16-token BF16 pages")
+    # the same tokens with Q read from a q|gate-interleaved projection output and written to q_out (same algorithmic
+    # bytes: the gate halves are not touched)
+    split_sets = []
+    for args, keep in qk_sets:
+        q = keep[0]
+        source = torch.cat([q.view(T, 64, 128), torch.zeros_like(q.view(T, 64, 128))], dim=2).contiguous()
+        out = torch.empty_like(q)
+        a2 = axk.QkRopeArgs.from_buffer_copy(args)
+        a2.flags |= axk.QK_FLAG_Q_GATE_INTERLEAVED
+        a2.q_bf16, a2.q_out_bf16 = source.data_ptr(), out.data_ptr()
+        split_sets.append((a2, source, out))
+    ms = timed(lambda i: axk.qk_norm_rope_paged(local, split_sets[i % 2][0], stream))
+    report("qk_norm_rope_paged_kv_split_q_gate", ms, 2 * T * 64 * 128 * 2 + 2 * T * 8 * 128 * 2 + T * 4 + 4096 * 4 + 512, T,
+           "config 3 with the query halves read from a [T][64][2*128] q|gate projection output")
 
 
 def bench_swiglu(torch, axk, wl, local, device, stream, timed, report, T, want):
