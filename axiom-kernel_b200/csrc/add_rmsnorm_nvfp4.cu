@@ -30,10 +30,8 @@ namespace axb {
 namespace {
 
 __device__ __forceinline__ void unpack8(const uint4 &v, float (&x)[8]) {
-    x[0] = bf16_lo(v.x); x[1] = bf16_hi(v.x);
-    x[2] = bf16_lo(v.y); x[3] = bf16_hi(v.y);
-    x[4] = bf16_lo(v.z); x[5] = bf16_hi(v.z);
-    x[6] = bf16_lo(v.w); x[7] = bf16_hi(v.w);
+    const float2 a = bf16x2_widen_fma(v.x), b = bf16x2_widen_fma(v.y), c = bf16x2_widen_fma(v.z), d = bf16x2_widen_fma(v.w);
+    x[0] = a.x; x[1] = a.y; x[2] = b.x; x[3] = b.y; x[4] = c.x; x[5] = c.y; x[6] = d.x; x[7] = d.y;
 }
 
 struct norm_args {
@@ -96,10 +94,10 @@ __device__ __forceinline__ void norm_quant_sweep(const norm_args &a, const uint4
             ga = gamma_a[128u * k];
             gb = gamma_b[128u * k];
         }
-        const float2 y0 = __fmul2_rn(__fmul2_rn(make_float2(bf16_lo(m.x), bf16_hi(m.x)), inv2), make_float2(ga.x, ga.y));
-        const float2 y1 = __fmul2_rn(__fmul2_rn(make_float2(bf16_lo(m.y), bf16_hi(m.y)), inv2), make_float2(ga.z, ga.w));
-        const float2 y2 = __fmul2_rn(__fmul2_rn(make_float2(bf16_lo(m.z), bf16_hi(m.z)), inv2), make_float2(gb.x, gb.y));
-        const float2 y3 = __fmul2_rn(__fmul2_rn(make_float2(bf16_lo(m.w), bf16_hi(m.w)), inv2), make_float2(gb.z, gb.w));
+        const float2 y0 = __fmul2_rn(__fmul2_rn(bf16x2_widen_fma(m.x), inv2), make_float2(ga.x, ga.y));
+        const float2 y1 = __fmul2_rn(__fmul2_rn(bf16x2_widen_fma(m.y), inv2), make_float2(ga.z, ga.w));
+        const float2 y2 = __fmul2_rn(__fmul2_rn(bf16x2_widen_fma(m.z), inv2), make_float2(gb.x, gb.y));
+        const float2 y3 = __fmul2_rn(__fmul2_rn(bf16x2_widen_fma(m.w), inv2), make_float2(gb.z, gb.w));
         const uint4 nrm = make_uint4(pack_bf16x2(y0.x, y0.y), pack_bf16x2(y1.x, y1.y), pack_bf16x2(y2.x, y2.y), pack_bf16x2(y3.x, y3.y));
         if (!kExact && norm_dst && ok) st_stream(norm_dst + 128u * k, nrm);
         if (code_dst) {
@@ -262,8 +260,7 @@ add_rmsnorm_stream_kernel(const norm_args a) {
                         m = add_bf16x2(m, pack_bf16x2(h.x, h.y));
                         res_w[128u * k] = m;
                     }
-                    const float2 v = make_float2(bf16_lo(m), bf16_hi(m));
-                    p = __ffma2_rn(v, v, p);
+                    p = bf16x2_square_accumulate(m, p);
                 }
             }
         }
@@ -383,10 +380,10 @@ add_rmsnorm_wide_row_kernel(const norm_args a) {
                     const float4 r0 = raw[0], r1 = raw[1];
                     const uint4 w = reinterpret_cast<const uint4 *>(a.weight_scale)[q];
                     const float2 ts2 = make_float2(token_scale, token_scale);
-                    const float2 h0 = __fmul2_rn(__fmul2_rn(make_float2(r0.x, r0.y), make_float2(bf16_lo(w.x), bf16_hi(w.x))), ts2);
-                    const float2 h1 = __fmul2_rn(__fmul2_rn(make_float2(r0.z, r0.w), make_float2(bf16_lo(w.y), bf16_hi(w.y))), ts2);
-                    const float2 h2 = __fmul2_rn(__fmul2_rn(make_float2(r1.x, r1.y), make_float2(bf16_lo(w.z), bf16_hi(w.z))), ts2);
-                    const float2 h3 = __fmul2_rn(__fmul2_rn(make_float2(r1.z, r1.w), make_float2(bf16_lo(w.w), bf16_hi(w.w))), ts2);
+                    const float2 h0 = __fmul2_rn(__fmul2_rn(make_float2(r0.x, r0.y), bf16x2_widen_fma(w.x)), ts2);
+                    const float2 h1 = __fmul2_rn(__fmul2_rn(make_float2(r0.z, r0.w), bf16x2_widen_fma(w.y)), ts2);
+                    const float2 h2 = __fmul2_rn(__fmul2_rn(make_float2(r1.x, r1.y), bf16x2_widen_fma(w.z)), ts2);
+                    const float2 h3 = __fmul2_rn(__fmul2_rn(make_float2(r1.z, r1.w), bf16x2_widen_fma(w.w)), ts2);
                     h = make_uint4(pack_bf16x2(h0.x, h0.y), pack_bf16x2(h1.x, h1.y), pack_bf16x2(h2.x, h2.y), pack_bf16x2(h3.x, h3.y));
                 }
                 gam[c] = gamma16[q];
@@ -409,8 +406,7 @@ add_rmsnorm_wide_row_kernel(const norm_args a) {
             for (uint32_t k = 0; k < k_iters; ++k) {
                 if (256u * k + 2u * tid < a.cols) {
                     const uint32_t w = words[128u * k];
-                    const float2 v = make_float2(bf16_lo(w), bf16_hi(w));
-                    p = __ffma2_rn(v, v, p);
+                    p = bf16x2_square_accumulate(w, p);
                 }
             }
             reinterpret_cast<float2 *>(partials)[tid] = p;
@@ -435,14 +431,14 @@ add_rmsnorm_wide_row_kernel(const norm_args a) {
             const uint32_t q = tid + c * blockDim.x;
             if (c * blockDim.x >= a.chunks_per_row) break;  // uniform: no thread has a chunk in this round
             const bool ok = q < a.chunks_per_row;
-            const float2 y0 = __fmul2_rn(__fmul2_rn(make_float2(bf16_lo(m[c].x), bf16_hi(m[c].x)), inv2),
-                                         make_float2(bf16_lo(gam[c].x), bf16_hi(gam[c].x)));
-            const float2 y1 = __fmul2_rn(__fmul2_rn(make_float2(bf16_lo(m[c].y), bf16_hi(m[c].y)), inv2),
-                                         make_float2(bf16_lo(gam[c].y), bf16_hi(gam[c].y)));
-            const float2 y2 = __fmul2_rn(__fmul2_rn(make_float2(bf16_lo(m[c].z), bf16_hi(m[c].z)), inv2),
-                                         make_float2(bf16_lo(gam[c].z), bf16_hi(gam[c].z)));
-            const float2 y3 = __fmul2_rn(__fmul2_rn(make_float2(bf16_lo(m[c].w), bf16_hi(m[c].w)), inv2),
-                                         make_float2(bf16_lo(gam[c].w), bf16_hi(gam[c].w)));
+            const float2 y0 = __fmul2_rn(__fmul2_rn(bf16x2_widen_fma(m[c].x), inv2),
+                                         bf16x2_widen_fma(gam[c].x));
+            const float2 y1 = __fmul2_rn(__fmul2_rn(bf16x2_widen_fma(m[c].y), inv2),
+                                         bf16x2_widen_fma(gam[c].y));
+            const float2 y2 = __fmul2_rn(__fmul2_rn(bf16x2_widen_fma(m[c].z), inv2),
+                                         bf16x2_widen_fma(gam[c].z));
+            const float2 y3 = __fmul2_rn(__fmul2_rn(bf16x2_widen_fma(m[c].w), inv2),
+                                         bf16x2_widen_fma(gam[c].w));
             const uint4 nrm = make_uint4(pack_bf16x2(y0.x, y0.y), pack_bf16x2(y1.x, y1.y), pack_bf16x2(y2.x, y2.y),
                                          pack_bf16x2(y3.x, y3.y));
             if (a.norm_out && ok) st_stream(a.norm_out + base + q, nrm);

@@ -89,6 +89,24 @@ inline cudaError_t launch_chained(void (*kernel)(KArgs...), dim3 grid, dim3 bloc
 
 __device__ __forceinline__ float bf16_lo(uint32_t packed) { return __uint_as_float(packed << 16); }
 __device__ __forceinline__ float bf16_hi(uint32_t packed) { return __uint_as_float(packed & 0xffff0000u); }
+// The two BF16 halves of `packed` as floats through the mixed-precision FMA of sm_100 (x * 1 + (-0) = x for every
+// x, signed zeros included): the widening runs on the FMA pipe and reads the halves in place, where the shift / mask
+// pair above occupies the ALU pipe.  For kernels whose ALU pipe is the busy one.
+// acc.x = fma(lo, lo, acc.x), acc.y = fma(hi, hi, acc.y) for the two BF16 halves of `packed`: the squares go into
+// the F32 accumulators with one rounding each, exactly fmaf(x, x, acc) on the widened values, without widening them.
+__device__ __forceinline__ float2 bf16x2_square_accumulate(uint32_t packed, float2 acc) {
+    asm("{\n\t.reg .b16 l, h;\n\tmov.b32 {l, h}, %2;\n\t"
+        "fma.rn.f32.bf16 %0, l, l, %0;\n\t"
+        "fma.rn.f32.bf16 %1, h, h, %1;\n\t}" : "+f"(acc.x), "+f"(acc.y) : "r"(packed));
+    return acc;
+}
+__device__ __forceinline__ float2 bf16x2_widen_fma(uint32_t packed) {
+    float2 v;
+    asm("{\n\t.reg .b16 l, h, one;\n\tmov.b32 {l, h}, %2;\n\tmov.b16 one, 0x3f80;\n\t"
+        "fma.rn.f32.bf16 %0, l, one, 0f80000000;\n\t"
+        "fma.rn.f32.bf16 %1, h, one, 0f80000000;\n\t}" : "=f"(v.x), "=f"(v.y) : "r"(packed));
+    return v;
+}
 
 // Two F32 -> packed BF16 pair, round-to-nearest-even (NaN stays NaN): `lo` lands in bits 0..15.
 __device__ __forceinline__ uint32_t pack_bf16x2(float lo, float hi) {

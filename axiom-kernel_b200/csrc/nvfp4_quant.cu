@@ -15,10 +15,8 @@ constexpr uint32_t kThreads = 256u;
 constexpr uint32_t kUnroll = 4u;  // 16-byte loads in flight per lane
 
 __device__ __forceinline__ void unpack8(const uint4 &v, float (&x)[8]) {
-    x[0] = bf16_lo(v.x); x[1] = bf16_hi(v.x);
-    x[2] = bf16_lo(v.y); x[3] = bf16_hi(v.y);
-    x[4] = bf16_lo(v.z); x[5] = bf16_hi(v.z);
-    x[6] = bf16_lo(v.w); x[7] = bf16_hi(v.w);
+    const float2 a = bf16x2_widen_fma(v.x), b = bf16x2_widen_fma(v.y), c = bf16x2_widen_fma(v.z), d = bf16x2_widen_fma(v.w);
+    x[0] = a.x; x[1] = a.y; x[2] = b.x; x[3] = b.y; x[4] = c.x; x[5] = c.y; x[6] = d.x; x[7] = d.y;
 }
 
 

@@ -123,8 +123,8 @@ __device__ __forceinline__ rot_regs load_rot(const float *cos_t, const float *si
 template <int LPH>
 __device__ __forceinline__ void qk_item(uint2 xa, uint2 xb, const float4 ga, const float4 gb, const rot_regs &r,
                                         bool rotary, double inv_d, double eps, uint2 *out_a, uint2 *out_b) {
-    const float2 fa0 = make_float2(bf16_lo(xa.x), bf16_hi(xa.x)), fa1 = make_float2(bf16_lo(xa.y), bf16_hi(xa.y));
-    const float2 fb0 = make_float2(bf16_lo(xb.x), bf16_hi(xb.x)), fb1 = make_float2(bf16_lo(xb.y), bf16_hi(xb.y));
+    const float2 fa0 = bf16x2_widen_fma(xa.x), fa1 = bf16x2_widen_fma(xa.y);
+    const float2 fb0 = bf16x2_widen_fma(xb.x), fb1 = bf16x2_widen_fma(xb.y);
     double s = 0.0, s_hi = 0.0;
     {
         const double d0 = (double)fa0.x, d1 = (double)fa0.y, d2 = (double)fa1.x, d3 = (double)fa1.y;
