@@ -156,6 +156,37 @@ def test_host_io_flavour(axk, rt):
     assert np.allclose(s8, want_s8, rtol=1e-6) and np.mean(c8 != want_c8) < 2e-3
 
 
+@pytest.mark.parametrize("rows", [40, 1500])
+def test_host_io_with_page_locked_buffers_matches_staged_path(axk, rt, rows):
+    """Page-locked (mapped) host buffers are read and written by the kernel itself, pageable ones go through the
+    staging slots: both give the same bytes, and a mix of the two kinds takes the staged path."""
+    import torch
+
+    lib = axk.lib()
+    cols, G = 5120, 300.0
+    hidden, residual, gamma = wl.add_rmsnorm_inputs_np(rows, cols)
+
+    def run(pin_in, pin_out):
+        def place(a, pin):
+            t = torch.from_numpy(a.view(np.int16) if a.dtype == np.uint16 else a).clone()
+            return t.pin_memory() if pin else t
+        h, r = place(hidden, pin_in), place(residual, pin_in)
+        c = place(np.zeros((rows, cols // 2), np.uint8), pin_out)
+        sc = place(np.zeros((rows, cols // 16), np.uint8), pin_out)
+        rc = lib.axiom_runtime_add_rmsnorm_nvfp4_bf16(rt.handle, h.data_ptr(), r.data_ptr(), gamma.ctypes.data, 1e-6, rows,
+                                                      cols, G, c.data_ptr(), sc.data_ptr())
+        assert rc == axk.AXIOM_OK
+        return r.numpy().view(np.uint16).copy(), c.numpy().copy(), sc.numpy().copy()
+
+    staged, direct, mixed = run(False, False), run(True, True), run(True, False)
+    for a, b, c in zip(staged, direct, mixed):
+        assert np.array_equal(a, b) and np.array_equal(a, c)
+    want_res, _, want_codes, want_scales = ol.add_rmsnorm_nvfp4_bf16(hidden, residual, gamma, 1e-6, G)
+    assert np.array_equal(direct[0], want_res)
+    assert np.mean(direct[1] != want_codes) < 0.02
+    assert lib.axiom_b200_pipeline_faults(0) == 0
+
+
 def f32buf(axk, rt, a):
     return buf_from(axk, rt, np.ascontiguousarray(a, np.float32))
 
