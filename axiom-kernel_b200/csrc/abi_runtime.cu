@@ -361,6 +361,15 @@ extern "C" int axiom_runtime_nvfp4_quantize_bf16(
     const uint64_t off_scales = off_codes + align256((uint64_t)chunk * code_row);
     staging_pool &p = runtime->staging;
     if ((rc = p.reserve(off_scales + align256((uint64_t)chunk * scale_row), 0u)) != AXIOM_OK) return rc;
+    {   // page-locked, mapped buffers: the kernel reads and writes them itself (see the add+RMSNorm entry below)
+        void *in_dev = mapped_alias(input_bf16_host), *codes_dev = mapped_alias(out_codes_host), *scales_dev = mapped_alias(out_scales_host);
+        if (in_dev && codes_dev && scales_dev && aligned16(in_dev) && !(reinterpret_cast<uintptr_t>(codes_dev) & 3u)) {
+            launch_nvfp4_quantize_bf16(in_dev, rows, cols, global_scale, (uint8_t *)codes_dev, (uint8_t *)scales_dev,
+                                       AXIOM_SCALE_LAYOUT_CANONICAL, p.stream[0]);
+            if (cudaStreamSynchronize(p.stream[0]) != cudaSuccess) return AXIOM_ERR_CUDA;
+            return cudaGetLastError() == cudaSuccess ? AXIOM_OK : AXIOM_ERR_CUDA;
+        }
+    }
     uint32_t slot = 0;
     for (uint32_t r0 = 0; r0 < rows; r0 += chunk, slot = (slot + 1u) % staging_pool::kSlots) {
         const uint32_t n = std::min(chunk, rows - r0);
@@ -443,6 +452,14 @@ extern "C" int axiom_runtime_swiglu_fp8_bf16(
     const uint64_t off_scales = off_codes + align256((uint64_t)chunk * code_row);
     staging_pool &p = runtime->staging;
     if ((rc = p.reserve(off_scales + align256((uint64_t)chunk * 4u), 0u)) != AXIOM_OK) return rc;
+    {   // page-locked, mapped buffers: the kernel reads and writes them itself
+        void *in_dev = mapped_alias(gate_up_bf16_host), *codes_dev = mapped_alias(out_codes_host), *scales_dev = mapped_alias(out_scales_host);
+        if (in_dev && codes_dev && scales_dev && aligned16(in_dev) && !(reinterpret_cast<uintptr_t>(codes_dev) & 7u)) {
+            rc = launch_swiglu_fp8_bf16(in_dev, rows, width, (uint8_t *)codes_dev, (float *)scales_dev, p.stream[0]);
+            if (cudaStreamSynchronize(p.stream[0]) != cudaSuccess) return AXIOM_ERR_CUDA;
+            return cudaGetLastError() == cudaSuccess ? rc : AXIOM_ERR_CUDA;
+        }
+    }
     uint32_t slot = 0;
     for (uint32_t r0 = 0; r0 < rows; r0 += chunk, slot = (slot + 1u) % staging_pool::kSlots) {
         const uint32_t n = std::min(chunk, rows - r0);

@@ -187,6 +187,28 @@ def test_host_io_with_page_locked_buffers_matches_staged_path(axk, rt, rows):
     assert lib.axiom_b200_pipeline_faults(0) == 0
 
 
+def test_host_io_quantize_and_swiglu_with_page_locked_buffers(axk, rt):
+    import torch
+
+    lib = axk.lib()
+    rows, cols, G = 700, 5120, 300.0
+    x = torch.from_numpy(wl.quantize_input_np(rows, cols, seed=4).view(np.int16)).pin_memory()
+    codes = torch.zeros((rows, cols // 2), dtype=torch.uint8).pin_memory()
+    scales = torch.zeros((rows, cols // 16), dtype=torch.uint8).pin_memory()
+    assert lib.axiom_runtime_nvfp4_quantize_bf16(rt.handle, x.data_ptr(), rows, cols, G, codes.data_ptr(), scales.data_ptr()) == axk.AXIOM_OK
+    want_codes, want_scales = ol.nvfp4_quantize_bf16(x.numpy().view(np.uint16), G)
+    assert np.array_equal(codes.numpy(), want_codes) and np.array_equal(scales.numpy(), want_scales)
+
+    gu_np = wl.swiglu_input_np(300, 17408)
+    gu = torch.from_numpy(gu_np.view(np.int16)).pin_memory()
+    c8 = torch.zeros((300, 17408), dtype=torch.uint8).pin_memory()
+    s8 = torch.zeros(300, dtype=torch.float32).pin_memory()
+    assert lib.axiom_runtime_swiglu_fp8_bf16(rt.handle, gu.data_ptr(), 300, 17408, c8.data_ptr(), s8.data_ptr()) == axk.AXIOM_OK
+    c8_staged = np.zeros((300, 17408), np.uint8); s8_staged = np.zeros(300, np.float32)
+    assert lib.axiom_runtime_swiglu_fp8_bf16(rt.handle, gu_np.ctypes.data, 300, 17408, c8_staged.ctypes.data, s8_staged.ctypes.data) == axk.AXIOM_OK
+    assert np.array_equal(c8.numpy(), c8_staged) and np.array_equal(s8.numpy(), s8_staged)
+
+
 def f32buf(axk, rt, a):
     return buf_from(axk, rt, np.ascontiguousarray(a, np.float32))
 
