@@ -338,7 +338,7 @@ def main():
                        "h2d_bytes_per_step": 2 * ROWS * COLS * 2 + COLS * 2,
                        "d2h_bytes_per_step": ROWS * COLS * 2 + ROWS * COLS // 2 + ROWS * COLS // 16,
                        "ms_per_step": e2e_ms, "steps": e2e_steps,
-                       "api": "axiom_runtime_add_rmsnorm_nvfp4_bf16 (pinned host buffers in and out)"}
+                       "api": "axiom_runtime_add_rmsnorm_nvfp4_bf16 (pinned host buffers in and out; the kernel reads and writes mapped host memory over PCIe, nothing is staged)"}
         rt.close()
         del h_hidden, h_res, h_codes, h_scales
 
