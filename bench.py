@@ -148,6 +148,9 @@ def reference_arm(args):
     wl = importlib.import_module("axiom-kernel_b200.workloads")
     sample_rows = 2048
     hidden, residual, gamma = wl.add_rmsnorm_inputs_np(sample_rows, COLS)
+    # all host cores, also under torchrun, which exports OMP_NUM_THREADS=1 to its workers
+    cores = len(os.sched_getaffinity(0)) if hasattr(os, "sched_getaffinity") else (os.cpu_count() or 1)
+    ol.o().axo_set_threads(cores)
     threads = ol.o().axo_get_threads()
     G = 100.0
     for _ in range(max(args.warmup, 1)):
