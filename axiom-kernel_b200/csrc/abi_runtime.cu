@@ -2,6 +2,8 @@
 // points.  Validation follows the reference runtime wrappers: NULLs, zero
 // sizes, divisibility, same-runtime, overflow-checked byte counts and span
 // checks come before anything is touched (src/axiom_runtime.cpp:3286-3340).
+#include <cstdlib>
+
 #include "runtime.hpp"
 
 #include <algorithm>
@@ -78,6 +80,10 @@ uint32_t chunk_rows_for(uint32_t rows, uint64_t bytes_per_row, uint32_t granule)
 // Device-side address of a host buffer the GPU can reach directly (page-locked and mapped: cudaHostAlloc,
 // cudaHostRegister or a framework's pinned allocator under unified addressing); nullptr for pageable memory.
 void *mapped_alias(const void *host) {
+    // AXIOM_B200_HOST_IO=staged keeps every host buffer on the staged path (for hosts where device access to
+    // page-locked memory is slower than the copy engines); read per call, like the reference's launch knobs
+    const char *knob = getenv("AXIOM_B200_HOST_IO");
+    if (knob && knob[0] == 's') return nullptr;
     cudaPointerAttributes attr{};
     if (cudaPointerGetAttributes(&attr, host) != cudaSuccess) {
         cudaGetLastError();

@@ -176,6 +176,29 @@ def reference_arm(args):
     return 0
 
 
+def bind_to_gpu_numa_node(torch, local):
+    """Keep this rank's threads (and so its page-locked buffers, placed by first touch) on the NUMA node the GPU hangs
+    off, as numactl would in a deployment; with several ranks per host the host-I/O leg otherwise crosses sockets.
+    Returns the node, or None when the topology cannot be read."""
+    try:
+        props = torch.cuda.get_device_properties(local)
+        address = f"{props.pci_domain_id:04x}:{props.pci_bus_id:02x}:{props.pci_device_id:02x}.0"
+        node = int(Path(f"/sys/bus/pci/devices/{address}/numa_node").read_text())
+        if node < 0:
+            return None
+        cpus = set()
+        for part in Path(f"/sys/devices/system/node/node{node}/cpulist").read_text().strip().split(","):
+            lo, _, hi = part.partition("-")
+            cpus.update(range(int(lo), int(hi or lo) + 1))
+        allowed = cpus & os.sched_getaffinity(0)
+        if not allowed:
+            return None
+        os.sched_setaffinity(0, allowed)
+        return node
+    except Exception:
+        return None
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -208,6 +231,7 @@ def main():
     if not torch.cuda.is_available():
         raise SystemExit("bench.py needs a CUDA device")
     torch.cuda.set_device(local)
+    numa_node = bind_to_gpu_numa_node(torch, local) if world > 1 else None
     dist = None
     if world > 1:
         import torch.distributed as dist_mod
@@ -337,10 +361,23 @@ def main():
         e2e_ms = (time.perf_counter() - t0) / e2e_steps * 1e3
         if dist:
             e2e_ms = sharding.max_over_ranks(dist, e2e_ms, device)
+        # the same leg with every buffer forced through the staging slots and the copy engines (informative)
+        os.environ["AXIOM_B200_HOST_IO"] = "staged"
+        e2e_step()
+        torch.cuda.synchronize()
+        t0 = time.perf_counter()
+        for _ in range(5):
+            e2e_step()
+        torch.cuda.synchronize()
+        staged_ms = (time.perf_counter() - t0) / 5 * 1e3
+        del os.environ["AXIOM_B200_HOST_IO"]
+        if dist:
+            staged_ms = sharding.max_over_ranks(dist, staged_ms, device)
         line["e2e"] = {"value": world * ROWS / (e2e_ms * 1e-3), "unit": UNIT,
                        "h2d_bytes_per_step": 2 * ROWS * COLS * 2 + COLS * 2,
                        "d2h_bytes_per_step": ROWS * COLS * 2 + ROWS * COLS // 2 + ROWS * COLS // 16,
-                       "ms_per_step": e2e_ms, "steps": e2e_steps,
+                       "ms_per_step": e2e_ms, "steps": e2e_steps, "staged_copy_engine_ms_per_step": staged_ms,
+                       "numa_node": numa_node,
                        "api": "axiom_runtime_add_rmsnorm_nvfp4_bf16 (pinned host buffers in and out; the kernel reads and writes mapped host memory over PCIe, nothing is staged)"}
         rt.close()
         del h_hidden, h_res, h_codes, h_scales
