@@ -179,8 +179,13 @@ def test_host_io_with_page_locked_buffers_matches_staged_path(axk, rt, rows):
         return r.numpy().view(np.uint16).copy(), c.numpy().copy(), sc.numpy().copy()
 
     staged, direct, mixed = run(False, False), run(True, True), run(True, False)
-    for a, b, c in zip(staged, direct, mixed):
-        assert np.array_equal(a, b) and np.array_equal(a, c)
+    os.environ["AXIOM_B200_HOST_IO"] = "staged"  # the knob that keeps page-locked buffers on the staged path
+    try:
+        forced = run(True, True)
+    finally:
+        del os.environ["AXIOM_B200_HOST_IO"]
+    for a, b, c, f in zip(staged, direct, mixed, forced):
+        assert np.array_equal(a, b) and np.array_equal(a, c) and np.array_equal(a, f)
     want_res, _, want_codes, want_scales = ol.add_rmsnorm_nvfp4_bf16(hidden, residual, gamma, 1e-6, G)
     assert np.array_equal(direct[0], want_res)
     assert np.mean(direct[1] != want_codes) < 0.02
