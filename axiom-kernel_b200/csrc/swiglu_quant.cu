@@ -279,7 +279,7 @@ fp8_rows_kernel(const uint4 *__restrict__ in, uint32_t rows, uint32_t chunks, ui
 // SwiGLU -> NVFP4: no row-wide dependency; lanes own one chunk of gate and the
 // matching chunk of up, lane pairs form a 16-value block.
 constexpr uint32_t kNvThreads = 512u;
-constexpr uint32_t kNvUnroll = 2u;  // warp tiles in flight per iteration
+constexpr uint32_t kNvUnroll = 3u;  // warp tiles in flight per iteration (59 registers; four would pass 64 and halve the resident CTAs)
 
 // A warp tile is 32 consecutive chunks of one row (column group `col` of `col_groups`); a warp
 // takes tiles warp, warp + W, ... and advances (row, col) incrementally, so no division runs
