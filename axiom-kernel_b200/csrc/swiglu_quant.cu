@@ -184,6 +184,12 @@ __device__ __forceinline__ float cta_max(float m, float *warp_max) {
     return kNan ? all : fmaxf(all, 0.0f);
 }
 
+// Two FP8 codes through IEEE divisions, out of line: the rare path of the row kernel (a scale the reciprocal
+// sequence is not exact for) calls it, so that the divisions' slow paths take no registers from the common path.
+static __device__ __noinline__ uint32_t e4m3_pair_by_division(float a, float b, float scale) {
+    return cvt_e4m3x2(__fdiv_rn(a, scale), __fdiv_rn(b, scale));
+}
+
 enum class row_op { swiglu, swiglu_table, plain_finite_only };
 
 // CPT = 16-byte chunks (8 values) per thread; blockDim.x * CPT >= width / 8.
@@ -286,8 +292,8 @@ fp8_rows_kernel(const uint4 *__restrict__ in, uint32_t rows, uint32_t chunks, ui
                 uint32_t w[2];
 #pragma unroll
                 for (int h = 0; h < 2; ++h) {
-                    w[h] = cvt_e4m3x2(__fdiv_rn(y[k][4 * h + 0], scale), __fdiv_rn(y[k][4 * h + 1], scale)) |
-                           (cvt_e4m3x2(__fdiv_rn(y[k][4 * h + 2], scale), __fdiv_rn(y[k][4 * h + 3], scale)) << 16);
+                    w[h] = e4m3_pair_by_division(y[k][4 * h + 0], y[k][4 * h + 1], scale) |
+                           (e4m3_pair_by_division(y[k][4 * h + 2], y[k][4 * h + 3], scale) << 16);
                 }
                 if (q < chunks) st_stream(out + q, make_uint2(w[0], w[1]));
             }
