@@ -71,6 +71,10 @@ __device__ __forceinline__ uint2 ld_stream8(const void *p) {
 // interval round to the same float, every value inside does, and that float is the answer.
 // Otherwise (about one value in 2^17), or when float(v) leaves the range where the
 // approximation is specified for normal numbers, the plain expression is evaluated.
+// The plain expression, out of line: the FP64 square root and division (and their slow paths) then take no
+// registers from the loop that calls inv_rms_from_sum.
+static __device__ __noinline__ float inv_rms_plain(double v) { return (float)(1.0 / sqrt(v)); }
+
 __device__ __forceinline__ float inv_rms_from_sum(double ss, double inv_d, double eps) {
     const double v = __fma_rn(ss, inv_d, eps);  // ss / D is exact (D is a power of two)
     const float vf = (float)v;
@@ -81,7 +85,7 @@ __device__ __forceinline__ float inv_rms_from_sum(double ss, double inv_d, doubl
     const double y = __fma_rn(__dmul_rn(0.5, y0d), r, y0d);
     const float lo = (float)__dmul_rn(y, 1.0 - 0x1p-41), hi = (float)__dmul_rn(y, 1.0 + 0x1p-41);
     if (lo == hi && vf > 1.0e-30f && vf < 1.0e30f) return lo;
-    return (float)(1.0 / sqrt(v));
+    return inv_rms_plain(v);
 }
 
 // One row of the rotary table: c = cosf(angle) * mscale, s = sinf(angle) * mscale with
