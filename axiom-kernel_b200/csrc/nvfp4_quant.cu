@@ -20,6 +20,18 @@ __device__ __forceinline__ void unpack8(const uint4 &v, float (&x)[8]) {
 }
 
 
+// One chunk through the exact path, out of line (the whole warp takes it together): code word in the low half of
+// the result, scale byte in the high half.
+static __device__ __noinline__ uint64_t quantize_chunk_exact(uint4 v, float G) {
+    float x[8];
+    unpack8(v, x);
+    float m = absmax8_drop_nan(x);  // an all-NaN block has maximum 0, as a running fmaxf from 0 gives
+    m = fmaxf(fmaxf(m, __shfl_xor_sync(0xffffffffu, m, 1)), 0.0f);
+    uint32_t scale_byte;
+    const uint32_t packed = nvfp4_quantize8_exact(x[0], x[1], x[2], x[3], x[4], x[5], x[6], x[7], m, G, &scale_byte);
+    return (uint64_t)packed | ((uint64_t)scale_byte << 32);
+}
+
 // Quantizes the kUnroll chunks a lane holds for one warp tile (lane pairs form the 16-value blocks).
 __device__ __forceinline__ void quantize_tile(const uint4 (&v)[kUnroll], float G, const scale_lut_entry *lut,
                                               bool lut_safe, uint32_t (&packed)[kUnroll],
@@ -36,11 +48,9 @@ __device__ __forceinline__ void quantize_tile(const uint4 (&v)[kUnroll], float G
     if (!lut_safe || __any_sync(0xffffffffu, needs_exact)) {
 #pragma unroll
         for (uint32_t j = 0; j < kUnroll; ++j) {
-            float x[8];
-            unpack8(v[j], x);
-            float m = absmax8_drop_nan(x);  // an all-NaN block has maximum 0, as a running fmaxf from 0 gives
-            m = fmaxf(fmaxf(m, __shfl_xor_sync(0xffffffffu, m, 1)), 0.0f);
-            packed[j] = nvfp4_quantize8_exact(x[0], x[1], x[2], x[3], x[4], x[5], x[6], x[7], m, G, &scale_byte[j]);
+            const uint64_t both = quantize_chunk_exact(v[j], G);
+            packed[j] = (uint32_t)both;
+            scale_byte[j] = (uint32_t)(both >> 32);
         }
     }
 }
