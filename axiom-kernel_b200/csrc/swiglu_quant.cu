@@ -346,7 +346,8 @@ swiglu_nvfp4_kernel(const uint4 *__restrict__ in, const uint4 *__restrict__ othe
             // head) + one head.  Otherwise both planes share the pitch and the chunk index.
             const uint64_t other_at = (uint64_t)row * other_row_stride + qs[j];
             const uint64_t in_at = kHeadGate ? (uint64_t)row * row_stride + qs[j] + (qs[j] & in_head_keep) + in_head_add : other_at;
-            g[j] = oks[j] ? ld_stream(in + in_at) : make_uint4(0u, 0u, 0u, 0u);
+            // lanes beyond the row hold gate 1.0: a zero would leave the table and send the warp down the rare path
+            g[j] = oks[j] ? ld_stream(in + in_at) : make_uint4(0x3f803f80u, 0x3f803f80u, 0x3f803f80u, 0x3f803f80u);
             u[j] = oks[j] ? ld_stream(other + other_at) : make_uint4(0u, 0u, 0u, 0u);
             row += step_rows;
             col += step_cols;
@@ -357,6 +358,7 @@ swiglu_nvfp4_kernel(const uint4 *__restrict__ in, const uint4 *__restrict__ othe
         }
 #pragma unroll
         for (uint32_t j = 0; j < kNvUnroll; ++j) {
+            if (rws[j] >= rows) continue;  // the whole tile lies beyond the last row (uniform over the warp)
             float y[8];
             swiglu8<kTable, kFn, kFn == gate_fn::silu, true>(silu_table, g[j], u[j], y);  // measured: 254.5 -> 249.7 us at 16384 x 17408
             if (kFn == gate_fn::sigmoid) {
