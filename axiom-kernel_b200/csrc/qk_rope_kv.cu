@@ -119,29 +119,31 @@ __device__ __forceinline__ rot_regs load_rot(const float *cos_t, const float *si
 }
 
 // One work item: eight dims of one head held by one lane (xa = dims off_a.., xb = dims off_b..).
-// Sums the squares in FP64 across the LPH lanes of the head (xor butterfly: every lane ends with
+// head_sum: the squares summed in FP64 across the LPH lanes of the head (xor butterfly: every lane ends with
 // the total; FP64 sums of BF16 squares are exact unless the row spans more than ~2^18 in
-// magnitude, so the order of the additions is immaterial), derives the head's factor in every
-// lane — the same instructions a single lane would cost, and no shared-memory round trip or
-// barrier — then normalises, rotates and packs.
+// magnitude, so the order of the additions is immaterial).
 template <int LPH>
-__device__ __forceinline__ void qk_item(uint2 xa, uint2 xb, const float4 ga, const float4 gb, const rot_regs &r,
-                                        bool rotary, double inv_d, double eps, uint2 *out_a, uint2 *out_b) {
+__device__ __forceinline__ double head_sum(uint2 xa, uint2 xb) {
     const float2 fa0 = bf16x2_widen_fma(xa.x), fa1 = bf16x2_widen_fma(xa.y);
     const float2 fb0 = bf16x2_widen_fma(xb.x), fb1 = bf16x2_widen_fma(xb.y);
+    const double d0 = (double)fa0.x, d1 = (double)fa0.y, d2 = (double)fa1.x, d3 = (double)fa1.y;
+    const double e0 = (double)fb0.x, e1 = (double)fb0.y, e2 = (double)fb1.x, e3 = (double)fb1.y;
     double s = 0.0, s_hi = 0.0;
-    {
-        const double d0 = (double)fa0.x, d1 = (double)fa0.y, d2 = (double)fa1.x, d3 = (double)fa1.y;
-        const double e0 = (double)fb0.x, e1 = (double)fb0.y, e2 = (double)fb1.x, e3 = (double)fb1.y;
-        s = __fma_rn(d0, d0, s); s_hi = __fma_rn(e0, e0, s_hi);
-        s = __fma_rn(d1, d1, s); s_hi = __fma_rn(e1, e1, s_hi);
-        s = __fma_rn(d2, d2, s); s_hi = __fma_rn(e2, e2, s_hi);
-        s = __fma_rn(d3, d3, s); s_hi = __fma_rn(e3, e3, s_hi);
-        s += s_hi;
-    }
+    s = __fma_rn(d0, d0, s); s_hi = __fma_rn(e0, e0, s_hi);
+    s = __fma_rn(d1, d1, s); s_hi = __fma_rn(e1, e1, s_hi);
+    s = __fma_rn(d2, d2, s); s_hi = __fma_rn(e2, e2, s_hi);
+    s = __fma_rn(d3, d3, s); s_hi = __fma_rn(e3, e3, s_hi);
+    s += s_hi;
 #pragma unroll
     for (int off = LPH / 2; off != 0; off >>= 1) s += __shfl_xor_sync(0xffffffffu, s, off);
-    const float inv = inv_rms_from_sum(s, inv_d, eps);
+    return s;
+}
+
+// qk_apply: normalises with the head's factor, rotates and packs.
+__device__ __forceinline__ void qk_apply(uint2 xa, uint2 xb, float inv, const float4 ga, const float4 gb, const rot_regs &r,
+                                         bool rotary, uint2 *out_a, uint2 *out_b) {
+    const float2 fa0 = bf16x2_widen_fma(xa.x), fa1 = bf16x2_widen_fma(xa.y);
+    const float2 fb0 = bf16x2_widen_fma(xb.x), fb1 = bf16x2_widen_fma(xb.y);
     const float2 inv2 = make_float2(inv, inv);
     // n = (x * inv) * gamma
     const float2 a0 = __fmul2_rn(__fmul2_rn(fa0, inv2), make_float2(ga.x, ga.y));
@@ -158,6 +160,15 @@ __device__ __forceinline__ void qk_item(uint2 xa, uint2 xb, const float4 ga, con
     }
     *out_a = make_uint2(pack_bf16x2(oa0.x, oa0.y), pack_bf16x2(oa1.x, oa1.y));
     *out_b = make_uint2(pack_bf16x2(ob0.x, ob0.y), pack_bf16x2(ob1.x, ob1.y));
+}
+
+// Both steps for one item, every lane deriving the head's factor itself — the same instructions a single
+// lane would cost, and no shared-memory round trip or barrier.
+template <int LPH>
+__device__ __forceinline__ void qk_item(uint2 xa, uint2 xb, const float4 ga, const float4 gb, const rot_regs &r,
+                                        bool rotary, double inv_d, double eps, uint2 *out_a, uint2 *out_b) {
+    const float inv = inv_rms_from_sum(head_sum<LPH>(xa, xb), inv_d, eps);
+    qk_apply(xa, xb, inv, ga, gb, r, rotary, out_a, out_b);
 }
 
 // BF16 -> E4M3 codes at scale 1 for the FP8 flavour of the cache (qwen38_kv_encode_e4m3fn_scale1,
@@ -554,6 +565,32 @@ qk_norm_rope_stream_kernel(const qk_dev_args a, const qk_stream_geom g, const __
 
         const float *cos_t = tables + (i & 1u) * (D / 2u) * 3u;
         const rot_regs r = load_rot(cos_t, cos_t + D / 2u, cos_t + D, off_a, rotary);
+        // Sweep 1: the sum of squares of every item.  The inverse rms of a head is the same in all LPH lanes
+        // that hold it, and a thread holds NPT heads: lane n of the head group evaluates the factor of item n
+        // and the group reads it back by shuffle, so the FP64 Newton step and its conversions run once per
+        // thread and token instead of once per item.  Sweep 2 re-reads the slot (two 8-byte shared loads per
+        // item, cheaper than keeping NPT items in registers across the exchange).
+        float inv[NPT];
+        {
+            double ss[NPT];
+            const uint8_t *item = slot + item0;
+#pragma unroll
+            for (int n = 0; n < NPT; ++n) {
+                ss[n] = head_sum<LPH>(*reinterpret_cast<const uint2 *>(item), *reinterpret_cast<const uint2 *>(item + b_delta));
+                item += item_step;
+            }
+            if constexpr (NPT <= LPH) {
+                double mine = ss[0];
+#pragma unroll
+                for (int n = 1; n < NPT; ++n) mine = l == (uint32_t)n ? ss[n] : mine;
+                const float inv_mine = inv_rms_from_sum(mine, inv_d, eps);
+#pragma unroll
+                for (int n = 0; n < NPT; ++n) inv[n] = __shfl_sync(0xffffffffu, inv_mine, n, LPH);
+            } else {
+#pragma unroll
+                for (int n = 0; n < NPT; ++n) inv[n] = inv_rms_from_sum(ss[n], inv_d, eps);
+            }
+        }
         uint8_t *item = slot + item0;
         uint32_t h = head0;
 #pragma unroll
@@ -564,7 +601,7 @@ qk_norm_rope_stream_kernel(const qk_dev_args a, const qk_stream_geom g, const __
             const float4 ga = *reinterpret_cast<const float4 *>(gamma + off_a);
             const float4 gb = *reinterpret_cast<const float4 *>(gamma + off_b);
             uint2 pa, pb;
-            qk_item<LPH>(*pa_ptr, *pb_ptr, ga, gb, r, rotary, inv_d, eps, &pa, &pb);
+            qk_apply(*pa_ptr, *pb_ptr, inv[n], ga, gb, r, rotary, &pa, &pb);
             *pa_ptr = pa;
             *pb_ptr = pb;
             item += item_step;

@@ -428,10 +428,37 @@ def bench_other_ops(torch, axk, wl, local, device, stream, peak, only=None, rows
             fn(i)
         return event_time_ms(torch, stream, fn, n)
 
+    copy_cache = {}
+
+    def matched_copy_ms(algo):
+        """dst.copy_(src) of algo/2 bytes (so the copy moves the same bytes: half read, half written), rotating
+        buffer pairs larger than L2 in total, timed with the same events on the same stream."""
+        if algo in copy_cache:
+            return copy_cache[algo]
+        half = max(16, algo // 2 // 16 * 16)
+        nsets = max(2, min(16, -(-400_000_000 // algo)))
+        src = [torch.empty(half, dtype=torch.uint8, device=device).random_(0, 255) for _ in range(nsets)]
+        dst = [torch.empty(half, dtype=torch.uint8, device=device) for _ in range(nsets)]
+
+        def step(i):
+            dst[i % nsets].copy_(src[i % nsets])
+
+        with torch.cuda.stream(stream):
+            for i in range(max(warm, 3)):
+                step(i)
+            ms = event_time_ms(torch, stream, step, max(20, min(iters, 100)))
+        del src, dst
+        copy_cache[algo] = ms
+        return ms
+
     def report(name, ms, algo, rows, note):
         gbs = algo / (ms * 1e-3) / 1e9
         out[name] = {"ms": ms, "gbs": gbs, "frac_of_peak": gbs / peak, "tokens_per_s": rows / (ms * 1e-3),
                      "algorithmic_bytes": algo, "note": note}
+        if algo >= (1 << 20):
+            cms = matched_copy_ms(algo)
+            out[name]["matched_copy_ms"] = cms
+            out[name]["frac_of_matched_copy"] = cms / ms
 
     if only is None or only == "add_rmsnorm_tiled":
         bench_add_rmsnorm_tiled(torch, axk, wl, local, device, stream, timed, report, rows_override or 8192)

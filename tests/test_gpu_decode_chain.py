@@ -8,6 +8,9 @@ import pytest
 
 import oracle_lib as ol
 
+from test_gpu_qk_rope import tolerance as qk_tolerance
+from test_gpu_swiglu import nvfp4_codes_are_correct_roundings
+
 pytestmark = pytest.mark.gpu
 wl = importlib.import_module("axiom-kernel_b200.workloads")
 
@@ -61,13 +64,20 @@ def test_chain(axk, cuda_device, m):
     assert np.array_equal(host(codes, np.uint8), own_codes) and np.array_equal(host(scales, np.uint8), own_scales)
     want_q, want_k, _ = ol.qk_norm_rope_paged(q, k, None, qg, kg, inv_freq, positions, btab, rope_dim=128, eps=1e-6,
                                               mscale=mscale, want_k_out=True)
-    assert np.mean(host(d["q"], np.uint16).reshape(q.shape) != want_q) < 0.02
-    assert np.mean(host(k_out, np.uint16).reshape(k.shape) != want_k) < 0.02
+    for got, want, src, g_bits in ((host(d["q"], np.uint16).reshape(q.shape), want_q, q, qg),
+                                   (host(k_out, np.uint16).reshape(k.shape), want_k, k, kg)):
+        # one BF16 ulp at the magnitude of the rotation terms, on every element (device cosf/sinf vs the C library's)
+        bound = qk_tolerance(src, g_bits, inv_freq, positions, 128, mscale)
+        assert np.all(np.abs(wl.from_bf16_bits(got) - wl.from_bf16_bits(want)) <= bound)
+        assert np.mean(got != want) < 0.02
     cells = host(pool, np.uint16).reshape(wl.KV_BLOCKS, 16, 1024)
     lb = (positions // 16) % wl.KV_BLOCKS
     assert np.array_equal(cells[btab[0, lb], positions % 16], host(k_out, np.uint16).reshape(m, 1024))
     want_mc, want_ms = ol.swiglu_nvfp4_bf16(gu, G2)
-    assert np.mean(host(mlp_codes, np.uint8) != want_mc) < 2e-3 and np.mean(host(mlp_scales, np.uint8) != want_ms) < 2e-3
+    got_mc, got_ms = host(mlp_codes, np.uint8).reshape(want_mc.shape), host(mlp_scales, np.uint8).reshape(want_ms.shape)
+    assert np.mean(got_mc != want_mc) < 2e-3 and np.mean(got_ms != want_ms) < 2e-3
+    # and every code and block scale is a correct rounding of the FP64 value up to the FP32 slack of expf
+    assert nvfp4_codes_are_correct_roundings(gu, G2, got_mc, got_ms)
 
 
 @pytest.mark.parametrize("m,cols", [(1, 5120), (8, 5120), (64, 1024), (300, 5120), (700, 2048)])

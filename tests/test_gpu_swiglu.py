@@ -46,17 +46,7 @@ def check_swiglu_fp8(axk, rows, width, seed=4):
     want_codes, want_scales = ol.swiglu_fp8_bf16(gu)
     assert np.all(np.abs(scales - want_scales) <= 4 * np.spacing(want_scales))
     assert np.mean(codes != want_codes) < 2e-3
-    # every code is a correct rounding of y/scale (FP64) up to the FP32 slack of y
-    table = e4m3_table()
-    q = silu_mul_f64(gu) / scales.astype(np.float64)[:, None]
-    got = table[codes]
-    mag = codes & 0x7f
-    step = np.where(mag < 8, 2.0 ** -9, np.exp2(np.floor(np.log2(np.maximum(np.abs(got), 2.0 ** -9))) - 3))
-    slack = np.abs(q) * 2.0 ** -21 + 1e-30
-    sat = np.abs(q) >= 448.0
-    ok = np.abs(got - q) <= 0.5 * step + slack
-    ok |= sat & (mag == 0x7e)
-    assert np.all(ok)
+    assert fp8_codes_are_correct_roundings(gu, codes, scales)
     return codes, scales
 
 
@@ -126,6 +116,9 @@ def test_swiglu_nvfp4(axk, cuda_device, rows, width, layout):
     want_plane = want_scales.reshape(-1) if layout == 0 else ol.scales_to_tiled(want_scales)
     assert np.mean(scales.payload() != want_plane) < 2e-3
     assert np.mean(codes.payload().reshape(rows, width // 2) != want_codes) < 2e-3
+    if layout == 0:  # and no code or scale is off by more than the FP32 slack of y allows
+        assert nvfp4_codes_are_correct_roundings(gu, G, codes.payload().reshape(rows, width // 2),
+                                                 scales.payload().reshape(rows, width // 16))
 
 
 def test_swiglu_flavours_agree_bitwise(axk, cuda_device):
@@ -160,9 +153,120 @@ def test_swiglu_flavours_agree_bitwise(axk, cuda_device):
             assert np.array_equal(a, b)
 
 
-def test_config4_full_size_sample(axk, cuda_device):
-    """T = 16384 is exercised at full width; the oracle checks a 512-row slab of it."""
-    check_swiglu_fp8(axk, 512, 17408, seed=4)
+def fp8_codes_are_correct_roundings(gu, codes, scales):
+    """Every E4M3 code is a correct rounding of the FP64-evaluated y/scale, up to the FP32 slack of y."""
+    table = e4m3_table()
+    q = silu_mul_f64(gu) / scales.astype(np.float64)[:, None]
+    got = table[codes]
+    mag = codes & 0x7f
+    step = np.where(mag < 8, 2.0 ** -9, np.exp2(np.floor(np.log2(np.maximum(np.abs(got), 2.0 ** -9))) - 3))
+    ok = np.abs(got - q) <= 0.5 * step + (np.abs(q) * 2.0 ** -21 + 1e-30)
+    ok |= (np.abs(q) >= 448.0) & (mag == 0x7e)
+    return bool(np.all(ok))
+
+
+E2M1_VALUES = np.array([0.0, 0.5, 1.0, 1.5, 2.0, 3.0, 4.0, 6.0], np.float64)
+E2M1_STEP = np.array([0.5, 0.5, 0.5, 0.5, 1.0, 1.0, 2.0, 2.0], np.float64)  # width of the rounding cell around a code
+
+
+def nvfp4_codes_are_correct_roundings(gu, G, codes, scales):
+    """Per-code bound for SwiGLU -> NVFP4 against an FP64 evaluation of y (no mismatch fraction):
+    every block scale is a correct E4M3 rounding of max|y|/6*G and every nibble a correct E2M1 rounding of
+    y / (e4m3(scale)/G), both up to the FP32 slack of y (device expf and the C library's differ in the last bits)."""
+    rows, w = codes.shape[0], codes.shape[1] * 2
+    y = silu_mul_f64(gu)
+    table = e4m3_table()
+    block_max = np.abs(y).reshape(rows, w // 16, 16).max(axis=2)
+    want = block_max / 6.0 * float(np.float32(G))
+    got = table[scales]
+    mag = scales & 0x7f
+    step = np.where(mag < 8, 2.0 ** -9, np.exp2(np.floor(np.log2(np.maximum(got, 2.0 ** -9))) - 3))
+    ok_scale = np.abs(got - want) <= 0.5 * step + want * 2.0 ** -20 + 1e-30
+    ok_scale |= (want >= 448.0) & (scales == 0x7e)
+    ok_scale |= (want < 2.0 ** -10) & (scales == 0x20)   # a zero magnitude is stored as +0.125
+    ok_scale |= (want <= 2.0 ** -10 * (1 + 2.0 ** -20)) & (scales == 0x01)
+    if not np.all(ok_scale):
+        return False
+    d = np.repeat(got / float(np.float32(G)), 16, axis=1)
+    q = y / d
+    lo, hi = codes & 0xF, codes >> 4
+    nib = np.empty((rows, w), np.uint8)
+    nib[:, 0::2], nib[:, 1::2] = lo, hi
+    val = E2M1_VALUES[nib & 7] * np.where(nib & 8, -1.0, 1.0)
+    ok = np.abs(val - q) <= 0.5 * E2M1_STEP[nib & 7] + np.abs(q) * 2.0 ** -20 + 1e-30
+    ok |= (np.abs(q) >= 6.0) & ((nib & 7) == 7)
+    ok &= (np.signbit(q) == ((nib & 8) != 0)) | (val == 0.0) | (np.abs(q) < 0.25 * (1 + 2.0 ** -20))
+    return bool(np.all(ok))
+
+
+CONFIG4_REFERENCE_ROWS = np.r_[0:40, 8190:8231, 16344:16384]
+
+
+def test_config4_full_size_fp8(axk, cuda_device):
+    """Config 4 at its stated size, T = 16384 x 2*17408 (1.14 GB in: byte offsets beyond 2^31, the persistent
+    grid wraps many times).  EVERY row is checked: scale within 4 FP32 ulps of the oracle's and every code a
+    correct rounding of the FP64 y/scale; rows at the start, across the middle and at the end are bit-equal
+    with the reference's own kernels (silu_mul_batch + quantize_columns_e4m3, 8 rows per launch)."""
+    import torch
+    import ref_lib
+    from gpu_util import sync
+
+    T, W = 16384, wl.FFN
+    gu_dev = wl.swiglu_input_torch(torch, torch.device("cuda", 0), T, W, seed=4)
+    codes = torch.full((T, W), 0xFF, dtype=torch.uint8, device="cuda")
+    scales = torch.full((T,), float("nan"), dtype=torch.float32, device="cuda")
+    assert axk.swiglu_fp8(0, gu_dev, T, W, codes, scales) == axk.AXIOM_OK
+    sync()
+    got_scales = scales.cpu().numpy()
+    assert np.all(np.isfinite(got_scales))
+    for r0 in range(0, T, 1024):
+        gu = gu_dev[r0:r0 + 1024].view(torch.int16).cpu().numpy().view(np.uint16)
+        c, s = codes[r0:r0 + 1024].cpu().numpy(), got_scales[r0:r0 + 1024]
+        want_codes, want_scales = ol.swiglu_fp8_bf16(gu)
+        assert np.all(np.abs(s - want_scales) <= 4 * np.spacing(want_scales)), f"scales of rows {r0}.."
+        assert np.mean(c != want_codes) < 2e-3
+        assert fp8_codes_are_correct_roundings(gu, c, s), f"a code of rows {r0}.. is not a correct rounding"
+    if ref_lib.available():
+        import ref_cases as rc
+
+        rows = torch.from_numpy(CONFIG4_REFERENCE_ROWS).cuda()
+        gu = gu_dev[rows].view(torch.int16).cpu().numpy().view(np.uint16)
+        ref_codes, ref_scales = rc.swiglu_fp8(gu)
+        assert np.array_equal(got_scales[CONFIG4_REFERENCE_ROWS], ref_scales)
+        assert np.array_equal(codes[rows].cpu().numpy(), ref_codes)
+
+
+def test_config4_full_size_nvfp4(axk, cuda_device):
+    """The same tensor through SwiGLU -> NVFP4 (the down-projection input), all 16384 rows: per-code and
+    per-scale bounds against an FP64 evaluation, and the rows listed above bit-equal with the reference's
+    silu_mul_quantize_batch_to_tc kernels (thread and warp variants)."""
+    import torch
+    import ref_lib
+    from gpu_util import sync
+
+    T, W = 16384, wl.FFN
+    G = 37.0
+    gu_dev = wl.swiglu_input_torch(torch, torch.device("cuda", 0), T, W, seed=4)
+    codes = torch.full((T, W // 2), 0xFF, dtype=torch.uint8, device="cuda")
+    scales = torch.full((T, W // 16), 0xFF, dtype=torch.uint8, device="cuda")
+    assert axk.swiglu_nvfp4(0, gu_dev, T, W, G, codes, scales, 0) == axk.AXIOM_OK
+    sync()
+    for r0 in range(0, T, 1024):
+        gu = gu_dev[r0:r0 + 1024].view(torch.int16).cpu().numpy().view(np.uint16)
+        c, s = codes[r0:r0 + 1024].cpu().numpy(), scales[r0:r0 + 1024].cpu().numpy()
+        assert nvfp4_codes_are_correct_roundings(gu, G, c, s), f"rows {r0}..: a code or scale is not a correct rounding"
+        want_codes, want_scales = ol.swiglu_nvfp4_bf16(gu, G)
+        assert np.mean(c != want_codes) < 2e-3 and np.mean(s != want_scales) < 2e-3
+    if ref_lib.available():
+        import ref_cases as rc
+
+        rows = torch.from_numpy(CONFIG4_REFERENCE_ROWS).cuda()
+        gu = gu_dev[rows].view(torch.int16).cpu().numpy().view(np.uint16)
+        got_codes, got_scales = codes[rows].cpu().numpy(), scales[rows].cpu().numpy()
+        for variant in ("thread", "warp"):
+            ref_codes, ref_plane = rc.swiglu_nvfp4(gu, G, variant)
+            assert np.array_equal(got_codes, ref_codes)
+            assert np.array_equal(ol.scales_to_tiled(got_scales), ref_plane)
 
 
 @pytest.mark.parametrize("rows,width,layout", [(1, 6144, 0), (8, 8192, 1), (3, 16, 0), (120, 6144, 1), (400, 2048, 0)])
