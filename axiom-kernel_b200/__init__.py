@@ -34,6 +34,7 @@ QK_FLAG_RING = 1
 QK_FLAG_PER_TOKEN_TABLE = 2
 QK_FLAG_CACHE_E4M3 = 4
 QK_FLAG_Q_GATE_INTERLEAVED = 8
+QK_FLAG_ROUND_AFTER_NORM = 16
 STATUS_WORD_OK = 0
 STATUS_WORD_BAD_ADDRESS = 1
 STATUS_WORD_NONFINITE = 4
@@ -71,7 +72,8 @@ class QkRopeArgs(C.Structure):
         ("n_blocks", u32),
         ("q_bf16", vp), ("k_bf16", vp), ("v_bf16", vp), ("q_gamma_bf16", vp), ("k_gamma_bf16", vp),
         ("inv_freq", vp), ("positions", vp), ("block_tables", vp), ("k_pool_bf16", vp), ("v_pool_bf16", vp),
-        ("k_out_bf16", vp), ("status_word", vp), ("q_out_bf16", vp),
+        ("k_out_bf16", vp), ("status_word", vp), ("q_out_bf16", vp), ("rope_table", vp), ("rope_table_positions", u32),
+        ("reserved0", u32),
     ]
 
 
@@ -290,11 +292,13 @@ def yarn_mscale(factor: float) -> float:
 def make_qk_args(*, tokens, q_heads, k_heads, head_dim, rope_dim, flags=0, eps=1e-6, mscale=1.0, block_tokens=16,
                  n_layers=1, layer=0, pool_stride=0, tbl_stride=0, n_blocks=0, q=None, k=None, v=None,
                  q_gamma=None, k_gamma=None, inv_freq=None, positions=None, block_tables=None, k_pool=None,
-                 v_pool=None, k_out=None, status_word=None, q_out=None) -> QkRopeArgs:
+                 v_pool=None, k_out=None, status_word=None, q_out=None, rope_table=None,
+                 rope_table_positions=0) -> QkRopeArgs:
     return QkRopeArgs(AXIOM_ABI_VERSION, C.sizeof(QkRopeArgs), tokens, q_heads, k_heads, head_dim, rope_dim, flags,
                       eps, mscale, block_tokens, n_layers, layer, pool_stride, tbl_stride, n_blocks, _ptr(q),
                       _ptr(k), _ptr(v), _ptr(q_gamma), _ptr(k_gamma), _ptr(inv_freq), _ptr(positions),
-                      _ptr(block_tables), _ptr(k_pool), _ptr(v_pool), _ptr(k_out), _ptr(status_word), _ptr(q_out))
+                      _ptr(block_tables), _ptr(k_pool), _ptr(v_pool), _ptr(k_out), _ptr(status_word), _ptr(q_out),
+                      _ptr(rope_table), rope_table_positions, 0)
 
 
 def qk_norm_rope_paged(device, args: QkRopeArgs, stream=None):

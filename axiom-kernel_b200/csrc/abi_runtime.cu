@@ -16,6 +16,7 @@ int staging_pool::reserve(uint64_t bytes_per_slot, uint64_t aux_need) {
             return AXIOM_ERR_CUDA;
         }
     }
+    if (!aux_ready && cudaEventCreateWithFlags(&aux_ready, cudaEventDisableTiming) != cudaSuccess) return AXIOM_ERR_CUDA;
     if (bytes_per_slot > slot_bytes) {
         for (int i = 0; i < kSlots; ++i) {
             if (slot[i]) (void)cudaFree(slot[i]);
@@ -54,6 +55,8 @@ void staging_pool::release() {
     }
     if (aux) (void)cudaFree(aux);
     aux = nullptr;
+    if (aux_ready) (void)cudaEventDestroy(aux_ready);
+    aux_ready = nullptr;
     slot_bytes = aux_bytes = 0;
 }
 
@@ -366,16 +369,20 @@ extern "C" int axiom_runtime_nvfp4_quantize_bf16(
     const uint64_t off_codes = align256((uint64_t)chunk * in_row);
     const uint64_t off_scales = off_codes + align256((uint64_t)chunk * code_row);
     staging_pool &p = runtime->staging;
-    if ((rc = p.reserve(off_scales + align256((uint64_t)chunk * scale_row), 0u)) != AXIOM_OK) return rc;
-    {   // page-locked, mapped buffers: the kernel reads and writes them itself (see the add+RMSNorm entry below)
+    if ((rc = p.reserve(0u, 0u)) != AXIOM_OK) return rc;  // the streams only: the mapped path stages nothing
+    {   // page-locked, mapped buffers: the kernel reads and writes them itself (see the add+RMSNorm entry below).
+        // One launch covers the tensor, so the launcher's 32-bit chunk count has to hold; larger inputs are staged
+        // (the staged loop launches per chunk of rows).
         void *in_dev = mapped_alias(input_bf16_host), *codes_dev = mapped_alias(out_codes_host), *scales_dev = mapped_alias(out_scales_host);
-        if (in_dev && codes_dev && scales_dev && aligned16(in_dev) && !(reinterpret_cast<uintptr_t>(codes_dev) & 3u)) {
+        if (in_dev && codes_dev && scales_dev && aligned16(in_dev) && !(reinterpret_cast<uintptr_t>(codes_dev) & 3u) &&
+            (uint64_t)rows * (cols / 8u) <= 0xffffffffull) {
             launch_nvfp4_quantize_bf16(in_dev, rows, cols, global_scale, (uint8_t *)codes_dev, (uint8_t *)scales_dev,
                                        AXIOM_SCALE_LAYOUT_CANONICAL, p.stream[0]);
             if (cudaStreamSynchronize(p.stream[0]) != cudaSuccess) return AXIOM_ERR_CUDA;
             return cudaGetLastError() == cudaSuccess ? AXIOM_OK : AXIOM_ERR_CUDA;
         }
     }
+    if ((rc = p.reserve(off_scales + align256((uint64_t)chunk * scale_row), 0u)) != AXIOM_OK) return rc;
     uint32_t slot = 0;
     for (uint32_t r0 = 0; r0 < rows; r0 += chunk, slot = (slot + 1u) % staging_pool::kSlots) {
         const uint32_t n = std::min(chunk, rows - r0);
@@ -408,9 +415,16 @@ extern "C" int axiom_runtime_add_rmsnorm_nvfp4_bf16(
     const uint64_t off_codes = off_res + align256((uint64_t)chunk * act_row);
     const uint64_t off_scales = off_codes + align256((uint64_t)chunk * code_row);
     staging_pool &p = runtime->staging;
-    if ((rc = p.reserve(off_scales + align256((uint64_t)chunk * scale_row), align256(act_row))) != AXIOM_OK) return rc;
-    // gamma is resident for the whole call; every slot stream starts after its upload
-    if (cudaMemcpy(p.aux, gamma_bf16_host, (size_t)act_row, cudaMemcpyHostToDevice) != cudaSuccess) return AXIOM_ERR_CUDA;
+    if ((rc = p.reserve(0u, align256(act_row))) != AXIOM_OK) return rc;  // streams and the gamma buffer; slots only when staging
+    // gamma is resident for the whole call.  It is uploaded on slot stream 0 and the other slot streams wait for the
+    // event behind it: the slot streams are non-blocking, so nothing else orders them after the copy.
+    if (cudaMemcpyAsync(p.aux, gamma_bf16_host, (size_t)act_row, cudaMemcpyHostToDevice, p.stream[0]) != cudaSuccess ||
+        cudaEventRecord(p.aux_ready, p.stream[0]) != cudaSuccess) {
+        return AXIOM_ERR_CUDA;
+    }
+    for (int i = 1; i < staging_pool::kSlots; ++i) {
+        if (cudaStreamWaitEvent(p.stream[i], p.aux_ready, 0) != cudaSuccess) return AXIOM_ERR_CUDA;
+    }
     // Page-locked, mapped host buffers are read and written by the kernel itself: one launch whose bulk copies cross
     // the bus in both directions at once, with no staging and no per-chunk copy set-up (about 8 us of idle link per
     // copy on the engines).  Rows must be 16-byte multiples for the bulk copies; anything else is staged.
@@ -423,6 +437,10 @@ extern "C" int axiom_runtime_add_rmsnorm_nvfp4_bf16(
                                       (uint8_t *)scales_dev, AXIOM_SCALE_LAYOUT_CANONICAL, s);
         if (cudaStreamSynchronize(s) != cudaSuccess) return AXIOM_ERR_CUDA;
         return cudaGetLastError() == cudaSuccess ? AXIOM_OK : AXIOM_ERR_CUDA;
+    }
+    if ((rc = p.reserve(off_scales + align256((uint64_t)chunk * scale_row), align256(act_row))) != AXIOM_OK) {
+        (void)wait_all(p);  // the gamma upload is still in flight
+        return rc;
     }
     uint32_t slot = 0;
     for (uint32_t r0 = 0; r0 < rows; r0 += chunk, slot = (slot + 1u) % staging_pool::kSlots) {
@@ -457,7 +475,7 @@ extern "C" int axiom_runtime_swiglu_fp8_bf16(
     const uint64_t off_codes = align256((uint64_t)chunk * in_row);
     const uint64_t off_scales = off_codes + align256((uint64_t)chunk * code_row);
     staging_pool &p = runtime->staging;
-    if ((rc = p.reserve(off_scales + align256((uint64_t)chunk * 4u), 0u)) != AXIOM_OK) return rc;
+    if ((rc = p.reserve(0u, 0u)) != AXIOM_OK) return rc;  // the streams only: the mapped path stages nothing
     {   // page-locked, mapped buffers: the kernel reads and writes them itself
         void *in_dev = mapped_alias(gate_up_bf16_host), *codes_dev = mapped_alias(out_codes_host), *scales_dev = mapped_alias(out_scales_host);
         if (in_dev && codes_dev && scales_dev && aligned16(in_dev) && !(reinterpret_cast<uintptr_t>(codes_dev) & 7u)) {
@@ -466,6 +484,7 @@ extern "C" int axiom_runtime_swiglu_fp8_bf16(
             return cudaGetLastError() == cudaSuccess ? rc : AXIOM_ERR_CUDA;
         }
     }
+    if ((rc = p.reserve(off_scales + align256((uint64_t)chunk * 4u), 0u)) != AXIOM_OK) return rc;
     uint32_t slot = 0;
     for (uint32_t r0 = 0; r0 < rows; r0 += chunk, slot = (slot + 1u) % staging_pool::kSlots) {
         const uint32_t n = std::min(chunk, rows - r0);

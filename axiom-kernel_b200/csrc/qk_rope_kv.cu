@@ -54,6 +54,8 @@ struct qk_dev_args {
     uint32_t tokens, q_heads, k_heads, head_dim, rope_dim, flags;
     float eps, mscale;
     uint32_t block_tokens, n_layers, layer, pool_stride, tbl_stride, n_blocks;
+    const float *rope_table;        // optional [rope_table_positions][head_dim]: cos(head_dim/2) | sin(head_dim/2) per position
+    uint32_t rope_table_positions;
 };
 
 __device__ __forceinline__ uint2 ld_stream8(const void *p) {
@@ -122,8 +124,7 @@ __device__ __forceinline__ rot_regs load_rot(const float *cos_t, const float *si
 // head_sum: the squares summed in FP64 across the LPH lanes of the head (xor butterfly: every lane ends with
 // the total; FP64 sums of BF16 squares are exact unless the row spans more than ~2^18 in
 // magnitude, so the order of the additions is immaterial).
-template <int LPH>
-__device__ __forceinline__ double head_sum(uint2 xa, uint2 xb) {
+__device__ __forceinline__ double lane_sum(uint2 xa, uint2 xb) {
     const float2 fa0 = bf16x2_widen_fma(xa.x), fa1 = bf16x2_widen_fma(xa.y);
     const float2 fb0 = bf16x2_widen_fma(xb.x), fb1 = bf16x2_widen_fma(xb.y);
     const double d0 = (double)fa0.x, d1 = (double)fa0.y, d2 = (double)fa1.x, d3 = (double)fa1.y;
@@ -133,10 +134,54 @@ __device__ __forceinline__ double head_sum(uint2 xa, uint2 xb) {
     s = __fma_rn(d1, d1, s); s_hi = __fma_rn(e1, e1, s_hi);
     s = __fma_rn(d2, d2, s); s_hi = __fma_rn(e2, e2, s_hi);
     s = __fma_rn(d3, d3, s); s_hi = __fma_rn(e3, e3, s_hi);
-    s += s_hi;
+    return s + s_hi;
+}
+
+template <int LPH>
+__device__ __forceinline__ double head_sum(uint2 xa, uint2 xb) {
+    double s = lane_sum(xa, xb);
 #pragma unroll
     for (int off = LPH / 2; off != 0; off >>= 1) s += __shfl_xor_sync(0xffffffffu, s, off);
     return s;
+}
+
+// The sums of NPT heads, each spread over the same LPH lanes, reduced so that every head's total lands in
+// ONE pair of lanes instead of in all of them (recursive halving: in each round a lane keeps half of its
+// partial sums and hands the other half to its partner, so the exchange shrinks from NPT values to one).
+// Head n's total ends in the lanes n * (LPH / P) .. of the group, P = NPT rounded up to a power of two; the
+// other lanes' results are not totals of anything.  For 6 heads on 16 lanes this is 14 64-bit exchanges
+// instead of 24.  The additions are exact for the same reason as in head_sum, so their order is immaterial.
+template <int NPT>
+struct pow2_at_least {
+    static constexpr int value = NPT <= 1 ? 1 : NPT <= 2 ? 2 : NPT <= 4 ? 4 : NPT <= 8 ? 8 : NPT <= 16 ? 16 : 32;
+};
+
+template <int LPH, int NPT>
+__device__ __forceinline__ double scatter_head_sums(const double (&ss)[NPT], uint32_t l) {
+    constexpr int P = pow2_at_least<NPT>::value;
+    static_assert(P <= LPH, "more heads per thread than lanes per head");
+    double a[P];
+#pragma unroll
+    for (int i = 0; i < P; ++i) a[i] = i < NPT ? ss[i] : 0.0;
+#pragma unroll
+    for (int C = P; C > 1; C >>= 1) {
+        const int half = C / 2;
+        const uint32_t bit = (uint32_t)(LPH * C / (2 * P));  // lane distance of this round's partner
+        const bool upper = (l & bit) != 0u;
+#pragma unroll
+        for (int i = 0; i < half; ++i) {
+            if (C == P && i + half >= NPT) {
+                a[i] += __shfl_xor_sync(0xffffffffu, a[i], bit);  // no head in the upper slot: nothing to choose
+            } else {
+                const double send = upper ? a[i] : a[i + half];
+                const double keep = upper ? a[i + half] : a[i];
+                a[i] = keep + __shfl_xor_sync(0xffffffffu, send, bit);
+            }
+        }
+    }
+#pragma unroll
+    for (int off = LPH / (2 * P); off != 0; off >>= 1) a[0] += __shfl_xor_sync(0xffffffffu, a[0], off);
+    return a[0];
 }
 
 // qk_apply: normalises with the head's factor, rotates and packs.
@@ -171,6 +216,51 @@ __device__ __forceinline__ void qk_item(uint2 xa, uint2 xb, const float4 ga, con
     qk_apply(xa, xb, inv, ga, gb, r, rotary, out_a, out_b);
 }
 
+// ---- the BF16 ("draft") rounding convention: qk_rmsnorm_rope_bf16_kernel + round_f32_to_bf16_inplace_kernel
+// (src/axiom_qwen38_dspark_compute.cu:250-300,210-213) ------------------------------------------------------------
+//   ss   = FP32 tree over the head: squares (exact for BF16 inputs), strides D/2, D/4, .. 1, r[i] += r[i + stride]
+//   inv  = rsqrtf(ss / D + eps)
+//   n    = bf16((x * inv) * gamma)            <- rounded BEFORE the rotation
+//   out[p] = bf16(n[p] * c - n[p+D/2] * s), out[p+D/2] = bf16(n[p] * s + n[p+D/2] * c)
+// With a lane holding dims 4l.. and D/2 + 4l.., the first tree level (i, i + D/2) is the lane's own two halves, the
+// levels down to stride 4 are lane butterflies (both partners compute the same FP32 sum, addition commutes), and
+// strides 2 and 1 combine the lane's four values: every addition has the operands of the reference's tree.
+template <int LPH>
+__device__ __forceinline__ float head_sum_f32_tree(uint2 xa, uint2 xb) {
+    const float2 fa0 = bf16x2_widen_fma(xa.x), fa1 = bf16x2_widen_fma(xa.y);
+    const float2 fb0 = bf16x2_widen_fma(xb.x), fb1 = bf16x2_widen_fma(xb.y);
+    float q0 = __fadd_rn(__fmul_rn(fa0.x, fa0.x), __fmul_rn(fb0.x, fb0.x));
+    float q1 = __fadd_rn(__fmul_rn(fa0.y, fa0.y), __fmul_rn(fb0.y, fb0.y));
+    float q2 = __fadd_rn(__fmul_rn(fa1.x, fa1.x), __fmul_rn(fb1.x, fb1.x));
+    float q3 = __fadd_rn(__fmul_rn(fa1.y, fa1.y), __fmul_rn(fb1.y, fb1.y));
+#pragma unroll
+    for (int off = LPH / 2; off != 0; off >>= 1) {
+        q0 = __fadd_rn(q0, __shfl_xor_sync(0xffffffffu, q0, off));
+        q1 = __fadd_rn(q1, __shfl_xor_sync(0xffffffffu, q1, off));
+        q2 = __fadd_rn(q2, __shfl_xor_sync(0xffffffffu, q2, off));
+        q3 = __fadd_rn(q3, __shfl_xor_sync(0xffffffffu, q3, off));
+    }
+    return __fadd_rn(__fadd_rn(q0, q2), __fadd_rn(q1, q3));
+}
+
+__device__ __forceinline__ void qk_apply_round_after_norm(uint2 xa, uint2 xb, float inv, const float4 ga, const float4 gb,
+                                                          const rot_regs &r, uint2 *out_a, uint2 *out_b) {
+    const float2 fa0 = bf16x2_widen_fma(xa.x), fa1 = bf16x2_widen_fma(xa.y);
+    const float2 fb0 = bf16x2_widen_fma(xb.x), fb1 = bf16x2_widen_fma(xb.y);
+    const float2 inv2 = make_float2(inv, inv);
+    const float2 ua0 = __fmul2_rn(__fmul2_rn(fa0, inv2), make_float2(ga.x, ga.y));
+    const float2 ua1 = __fmul2_rn(__fmul2_rn(fa1, inv2), make_float2(ga.z, ga.w));
+    const float2 ub0 = __fmul2_rn(__fmul2_rn(fb0, inv2), make_float2(gb.x, gb.y));
+    const float2 ub1 = __fmul2_rn(__fmul2_rn(fb1, inv2), make_float2(gb.z, gb.w));
+    // the normalised values exist in BF16 only
+    const float2 a0 = bf16x2_widen_fma(pack_bf16x2(ua0.x, ua0.y)), a1 = bf16x2_widen_fma(pack_bf16x2(ua1.x, ua1.y));
+    const float2 b0 = bf16x2_widen_fma(pack_bf16x2(ub0.x, ub0.y)), b1 = bf16x2_widen_fma(pack_bf16x2(ub1.x, ub1.y));
+    const float2 oa0 = __ffma2_rn(a0, r.c0, __fmul2_rn(b0, r.n0)), oa1 = __ffma2_rn(a1, r.c1, __fmul2_rn(b1, r.n1));
+    const float2 ob0 = __ffma2_rn(a0, r.s0, __fmul2_rn(b0, r.c0)), ob1 = __ffma2_rn(a1, r.s1, __fmul2_rn(b1, r.c1));
+    *out_a = make_uint2(pack_bf16x2(oa0.x, oa0.y), pack_bf16x2(oa1.x, oa1.y));
+    *out_b = make_uint2(pack_bf16x2(ob0.x, ob0.y), pack_bf16x2(ob1.x, ob1.y));
+}
+
 // BF16 -> E4M3 codes at scale 1 for the FP8 flavour of the cache (qwen38_kv_encode_e4m3fn_scale1,
 // src/axiom_qwen38_attention.cu:245-248: the saturating converter applied to the BF16-valued float).
 __device__ __forceinline__ uint32_t bf16x4_to_e4m3x4(const uint2 v) {
@@ -187,7 +277,7 @@ __device__ __forceinline__ uint2 bf16x8_to_e4m3x8(const uint4 v) {
 // pass-through branch.  One CTA barrier: the rotary table (threads below rope_dim/2) and the
 // cache address (thread 0) are produced while the Q/K loads are in flight.
 // ---------------------------------------------------------------------------
-template <int LPH, int NPT, bool kFast>
+template <int LPH, int NPT, bool kFast, bool kRoundAfterNorm = false>
 __global__ void __launch_bounds__(512, 1)
 qk_norm_rope_paged_kernel(const qk_dev_args a) {
     __shared__ __align__(16) float cos_sh[kMaxHeadDim / 2];
@@ -239,16 +329,22 @@ qk_norm_rope_paged_kernel(const qk_dev_args a) {
             }
         }
         const uint32_t pos = a.positions[t];
-        if (tid < half) {
-            float cv, sv;
-            rope_table_entry(pos, a.inv_freq[tid], a.mscale, &cv, &sv);
-            cos_sh[tid] = cv;
-            sin_sh[tid] = sv;
-            nsin_sh[tid] = -sv;
+        // rotary factors of the token: evaluated here, or read from the caller's [position][cos | sin] table
+        const bool from_table = kRoundAfterNorm && a.rope_table != nullptr;
+        if (from_table && pos >= a.rope_table_positions) {
+            // outside the table: the token is left as it is (the reference kernel returns), the status word says so
+            if (tid == 0u && a.status_word) atomicCAS(a.status_word, AXIOM_STATUS_WORD_OK, AXIOM_STATUS_WORD_BAD_ADDRESS);
+            continue;  // uniform over the CTA: every thread read the same position
         }
-        for (uint32_t p = tid + blockDim.x; p < half; p += blockDim.x) {  // CTAs narrower than the table
+        for (uint32_t p = tid; p < half; p += blockDim.x) {  // one round unless the CTA is narrower than the table
             float cv, sv;
-            rope_table_entry(pos, a.inv_freq[p], a.mscale, &cv, &sv);
+            if (from_table) {
+                const float *row = a.rope_table + (uint64_t)pos * D;
+                cv = row[p];
+                sv = row[half + p];
+            } else {
+                rope_table_entry(pos, a.inv_freq[p], a.mscale, &cv, &sv);
+            }
             cos_sh[p] = cv;
             sin_sh[p] = sv;
             nsin_sh[p] = -sv;
@@ -286,7 +382,13 @@ qk_norm_rope_paged_kernel(const qk_dev_args a) {
             const float4 ga = *reinterpret_cast<const float4 *>(gamma + off_a);
             const float4 gb = *reinterpret_cast<const float4 *>(gamma + off_b);
             uint2 pa, pb;
-            qk_item<LPH>(xa[n], xb[n], ga, gb, r, rotary, inv_d, eps, &pa, &pb);
+            if (kRoundAfterNorm) {
+                const float ss = head_sum_f32_tree<LPH>(xa[n], xb[n]);
+                const float inv = rsqrtf(__fadd_rn(__fdiv_rn(ss, (float)D), a.eps));
+                qk_apply_round_after_norm(xa[n], xb[n], inv, ga, gb, r, &pa, &pb);
+            } else {
+                qk_item<LPH>(xa[n], xb[n], ga, gb, r, rotary, inv_d, eps, &pa, &pb);
+            }
             if (kFast || h < heads) {
                 if (!is_k) {
                     uint16_t *dst = q_row + h * D;
@@ -566,9 +668,10 @@ qk_norm_rope_stream_kernel(const qk_dev_args a, const qk_stream_geom g, const __
         const float *cos_t = tables + (i & 1u) * (D / 2u) * 3u;
         const rot_regs r = load_rot(cos_t, cos_t + D / 2u, cos_t + D, off_a, rotary);
         // Sweep 1: the sum of squares of every item.  The inverse rms of a head is the same in all LPH lanes
-        // that hold it, and a thread holds NPT heads: lane n of the head group evaluates the factor of item n
-        // and the group reads it back by shuffle, so the FP64 Newton step and its conversions run once per
-        // thread and token instead of once per item.  Sweep 2 re-reads the slot (two 8-byte shared loads per
+        // that hold it, and a thread holds NPT heads: the lane sums are reduced so that head n's total lands in
+        // one lane pair of the group, that lane evaluates the head's factor and the group reads it back by
+        // shuffle, so the FP64 Newton step and its conversions run once per thread and token instead of once
+        // per item.  Sweep 2 re-reads the slot (two 8-byte shared loads per
         // item, cheaper than keeping NPT items in registers across the exchange).
         float inv[NPT];
         {
@@ -576,16 +679,15 @@ qk_norm_rope_stream_kernel(const qk_dev_args a, const qk_stream_geom g, const __
             const uint8_t *item = slot + item0;
 #pragma unroll
             for (int n = 0; n < NPT; ++n) {
-                ss[n] = head_sum<LPH>(*reinterpret_cast<const uint2 *>(item), *reinterpret_cast<const uint2 *>(item + b_delta));
+                const uint2 xa = *reinterpret_cast<const uint2 *>(item), xb = *reinterpret_cast<const uint2 *>(item + b_delta);
+                if constexpr (NPT <= LPH) ss[n] = lane_sum(xa, xb);
+                else ss[n] = head_sum<LPH>(xa, xb);
                 item += item_step;
             }
             if constexpr (NPT <= LPH) {
-                double mine = ss[0];
+                const float inv_mine = inv_rms_from_sum(scatter_head_sums<LPH, NPT>(ss, l), inv_d, eps);
 #pragma unroll
-                for (int n = 1; n < NPT; ++n) mine = l == (uint32_t)n ? ss[n] : mine;
-                const float inv_mine = inv_rms_from_sum(mine, inv_d, eps);
-#pragma unroll
-                for (int n = 0; n < NPT; ++n) inv[n] = __shfl_sync(0xffffffffu, inv_mine, n, LPH);
+                for (int n = 0; n < NPT; ++n) inv[n] = __shfl_sync(0xffffffffu, inv_mine, n * (LPH / pow2_at_least<NPT>::value), LPH);
             } else {
 #pragma unroll
                 for (int n = 0; n < NPT; ++n) inv[n] = inv_rms_from_sum(ss[n], inv_d, eps);
@@ -691,9 +793,11 @@ void launch_qk(const qk_dev_args &a, cudaStream_t stream) {
     }
     if (best_threads == 0u) { best_npt = 8u; best_threads = 512u; }
     const bool fast = best_waste == 0u && a.rope_dim == a.head_dim;
+    const bool round_after_norm = (a.flags & AXIOM_QK_FLAG_ROUND_AFTER_NORM) != 0u;
 #define AXB_QK_LAUNCH(NPT)                                                                              \
     do {                                                                                                 \
-        if (fast) launch_chained(qk_norm_rope_paged_kernel<LPH, NPT, true>, dim3(grid), dim3(best_threads), 0, stream, a);       \
+        if (round_after_norm) launch_chained(qk_norm_rope_paged_kernel<LPH, NPT, false, true>, dim3(grid), dim3(best_threads), 0, stream, a); \
+        else if (fast) launch_chained(qk_norm_rope_paged_kernel<LPH, NPT, true>, dim3(grid), dim3(best_threads), 0, stream, a);  \
         else launch_chained(qk_norm_rope_paged_kernel<LPH, NPT, false>, dim3(grid), dim3(best_threads), 0, stream, a);           \
     } while (0)
     switch (best_npt) {
@@ -806,7 +910,8 @@ bool launch_qk_stream(const qk_dev_args &a, cudaStream_t stream) {
 template <int LPH>
 void launch_qk_any(const qk_dev_args &a, cudaStream_t stream) {
     // The per-token kernel has the shortest latency; the streaming kernel the highest throughput.
-    if (a.tokens >= 2u * kSmCount && launch_qk_stream<LPH>(a, stream)) return;
+    // (the BF16 rounding convention exists in the per-token kernel only)
+    if (a.tokens >= 2u * kSmCount && !(a.flags & AXIOM_QK_FLAG_ROUND_AFTER_NORM) && launch_qk_stream<LPH>(a, stream)) return;
     launch_qk<LPH>(a, stream);
 }
 
@@ -818,7 +923,11 @@ unsigned int qk_fault_word() { return read_and_clear_pipeline_fault(); }
 
 int launch_qk_norm_rope_paged_bf16(const axiom_qk_rope_args *p, cudaStream_t stream) {
     qk_dev_args a{};
-    const bool has_q_out = p->struct_size >= sizeof(axiom_qk_rope_args) && p->q_out_bf16 != nullptr;
+    const bool has_q_out = p->struct_size >= offsetof(axiom_qk_rope_args, rope_table) && p->q_out_bf16 != nullptr;
+    if (p->struct_size >= sizeof(axiom_qk_rope_args)) {
+        a.rope_table = p->rope_table;
+        a.rope_table_positions = p->rope_table_positions;
+    }
     a.q = (const uint4 *)p->q_bf16;
     a.q_out = has_q_out ? (uint4 *)p->q_out_bf16 : (uint4 *)p->q_bf16;
     a.q_head_stride = (p->flags & AXIOM_QK_FLAG_Q_GATE_INTERLEAVED) ? 2u * p->head_dim : p->head_dim;
@@ -891,11 +1000,21 @@ extern "C" int axiom_qwen38_fused_yarn_inv_freq_device(int device, const axiom_r
 
 extern "C" int axiom_qwen38_fused_qk_norm_rope_paged_bf16_device(int device, const axiom_qk_rope_args *p,
                                                                  void *stream) {
+    // the struct has grown twice by appending: every earlier size is accepted, the missing members read as NULL / 0
     if (!p || p->abi_version != AXIOM_ABI_VERSION ||
-        (p->struct_size != sizeof(axiom_qk_rope_args) && p->struct_size != offsetof(axiom_qk_rope_args, q_out_bf16))) {
+        (p->struct_size != sizeof(axiom_qk_rope_args) && p->struct_size != offsetof(axiom_qk_rope_args, rope_table) &&
+         p->struct_size != offsetof(axiom_qk_rope_args, q_out_bf16))) {
         return AXIOM_ERR_INVALID_ARGUMENT;
     }
-    void *const q_out = p->struct_size == sizeof(axiom_qk_rope_args) ? p->q_out_bf16 : nullptr;
+    void *const q_out = p->struct_size >= offsetof(axiom_qk_rope_args, rope_table) ? p->q_out_bf16 : nullptr;
+    const float *const rope_table = p->struct_size == sizeof(axiom_qk_rope_args) ? p->rope_table : nullptr;
+    if (p->flags & AXIOM_QK_FLAG_ROUND_AFTER_NORM) {
+        // the BF16 convention is defined for full-head rotation; its cos/sin come from the table when one is given
+        if (p->rope_dim != p->head_dim || p->rope_dim == 0u) return AXIOM_ERR_INVALID_ARGUMENT;
+        if (rope_table && (p->rope_table_positions == 0u || (reinterpret_cast<uintptr_t>(rope_table) & 3u))) return AXIOM_ERR_INVALID_ARGUMENT;
+    } else if (rope_table) {
+        return AXIOM_ERR_INVALID_ARGUMENT;  // the table belongs to the BF16 convention
+    }
     if (q_out && (!p->q_heads || !aligned16(q_out))) return AXIOM_ERR_INVALID_ARGUMENT;
     if ((p->flags & AXIOM_QK_FLAG_Q_GATE_INTERLEAVED) && (!p->q_heads || !q_out)) return AXIOM_ERR_INVALID_ARGUMENT;
     if (p->tokens == 0u || (p->q_heads + p->k_heads) == 0u || (p->q_heads + p->k_heads) > kMaxHeads ||
@@ -905,7 +1024,7 @@ extern "C" int axiom_qwen38_fused_qk_norm_rope_paged_bf16_device(int device, con
         !std::isfinite(p->eps) || !std::isfinite(p->mscale) || !p->positions) {
         return AXIOM_ERR_INVALID_ARGUMENT;
     }
-    if (p->rope_dim != 0u && !p->inv_freq) return AXIOM_ERR_INVALID_ARGUMENT;
+    if (p->rope_dim != 0u && !p->inv_freq && !rope_table) return AXIOM_ERR_INVALID_ARGUMENT;
     if (p->q_heads && (!p->q_bf16 || !p->q_gamma_bf16 || !aligned16(p->q_bf16))) return AXIOM_ERR_INVALID_ARGUMENT;
     if (p->k_heads && (!p->k_bf16 || !p->k_gamma_bf16 || !aligned16(p->k_bf16))) return AXIOM_ERR_INVALID_ARGUMENT;
     if (p->k_heads && !p->k_pool_bf16 && !p->k_out_bf16) return AXIOM_ERR_INVALID_ARGUMENT;

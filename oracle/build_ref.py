@@ -2,7 +2,7 @@
 sm_100a from the sources where they lie under the reference tree (never copied), behind small
 launchers (oracle/ref/*.cu).  Test infrastructure only.
 
-    python oracle/build_ref.py [/path/to/reference]
+    python oracle/build_ref.py [/path/to/reference]     (default: $AXIOM_REFERENCE_DIR, else ../reference)
 
 Each reference unit is built with the flags the reference's Makefile uses for it: the qwen38 and
 precise units WITHOUT fast-math, the generic backend WITH --use_fast_math.  The reference's own
@@ -28,6 +28,8 @@ UNITS = [  # (source relative to oracle/ or to the reference root, fast_math, fr
     ("ref/ref_model.cu", False, False),
     ("ref/ref_attention.cu", False, False),
     ("ref/ref_generic_fast.cu", True, False),
+    ("ref/ref_bench.cu", False, False),
+    ("ref/ref_dspark.cu", False, False),
     ("src/axiom_qwen38_nvfp4.cu", False, True),
     ("src/axiom_cuda_precise.cu", False, True),
 ]
@@ -76,5 +78,8 @@ def build(ref_root: Path) -> Path:
 
 
 if __name__ == "__main__":
-    root = Path(sys.argv[1]) if len(sys.argv) > 1 else Path("/root/reference")
+    import os
+
+    # the reference tree: argument, else AXIOM_REFERENCE_DIR, else a checkout named "reference" beside this repository
+    root = Path(sys.argv[1]) if len(sys.argv) > 1 else Path(os.environ.get("AXIOM_REFERENCE_DIR") or HERE.parent.parent / "reference")
     print(build(root))

@@ -16,3 +16,8 @@ extern "C" int ref_fp8_group_row_scale_bf16_epilogue(float *out, const uint16_t 
     fp8_group_row_scale_bf16_epilogue_kernel<<<(uint32_t)((count + kThreads - 1u) / kThreads), kThreads>>>(out, weight_scale, input_scale, rows);
     return cudaDeviceSynchronize() == cudaSuccess && cudaGetLastError() == cudaSuccess ? 0 : 3;
 }
+
+// Enqueue-only twin for ref_bench.cu: one launch over n <= 8 columns, no synchronisation (quantize_input, src/axiom_qwen38_fp8.cu:830-846).
+extern "C" void ref_enqueue_quantize_columns_e4m3(const float *input, uint8_t *codes, float *scales, uint32_t cols, uint32_t n) {
+    quantize_columns_e4m3_kernel<<<n, kThreads>>>(input, codes, scales, cols);
+}

@@ -50,3 +50,8 @@ extern "C" int ref_top1_8(const float *logits, void *partials, void *results, in
     }
     return ref_done();
 }
+
+// Enqueue-only twin for ref_bench.cu: one 8-column launch, no synchronisation (src/axiom_qwen38_model.cu:1371-1373).
+extern "C" void ref_enqueue_add_bf16_rmsnorm8(float *residual, const float *addend, const float *weight, float *norm) {
+    qwen38_add_bf16_rmsnorm8_kernel<<<kBatch, kThreads>>>(residual, addend, weight, norm);
+}

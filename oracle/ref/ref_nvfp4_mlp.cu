@@ -50,3 +50,16 @@ extern "C" int ref_silu_mul_batch(const float *gate, const float *up, float *out
     silu_mul_batch_kernel<<<(count + 255u) / 256u, 256>>>(gate, up, out, count);
     return ref_done();
 }
+
+// Enqueue-only twins for the timing loops of ref_bench.cu: one launch of the reference's default (warp) kernel
+// on the legacy stream, no synchronisation — the way the reference issues it per M = 8 batch
+// (projection_run, src/axiom_qwen38_nvfp4_mlp.cu:1347-1381).
+extern "C" void ref_enqueue_quantize_to_tc_warp(const float *input, float G, uint8_t *codes, uint8_t *scales_tc,
+                                                uint32_t cols, uint32_t columns) {
+    const uint32_t groups = cols / 16u, inner_tiles = (groups + 3u) / 4u, total = groups * columns;
+    quantize_batch_to_tc_warp_kernel<<<(total + 15u) / 16u, 256>>>(input, G, codes, scales_tc, cols, groups, inner_tiles, columns);
+}
+
+extern "C" void ref_enqueue_silu_mul_batch(const float *gate, const float *up, float *out, uint32_t count) {
+    silu_mul_batch_kernel<<<(count + 255u) / 256u, 256>>>(gate, up, out, count);
+}

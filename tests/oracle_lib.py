@@ -244,6 +244,23 @@ def qk_norm_rope_paged(q_bits, k_bits, v_bits, q_gamma, k_gamma, inv_freq, posit
     return q_out, k_out, int(status[0])
 
 
+def qk_norm_rope_round_after_norm(x_bits, gamma, rope_table, positions, eps=1e-6):
+    """The BF16 ("draft") rounding convention; x_bits [T, H, D] (returns a copy), rope_table [P, D] = cos | sin."""
+    tokens, heads, head_dim = x_bits.shape
+    out = x_bits.copy()
+    status = np.zeros(1, np.uint32)
+    table = np.ascontiguousarray(rope_table, np.float32)
+    _ok(o().axo_qk_norm_rope_round_after_norm_bf16(_p(out), _p(gamma), _p(table), table.shape[0], _p(positions), tokens, heads,
+                                                   head_dim, C.c_float(eps), _p(status)), "qk_norm_rope_round_after_norm")
+    return out, int(status[0])
+
+
+def rope_table_host(inv_freq, head_dim, mscale, positions):
+    out = np.empty((positions, head_dim), np.float32)
+    _ok(o().axo_rope_table_host(_p(inv_freq), head_dim, C.c_float(mscale), positions, _p(out)), "rope_table_host")
+    return out
+
+
 def sigmoid_gate_nvfp4_bf16(attention_bits, gate_bits, G):
     rows, width = attention_bits.shape
     out = np.empty_like(attention_bits)

@@ -166,3 +166,15 @@ def qk_temporal8(q_bits, k_bits, v_bits, qg_bits, kg_bits, base_position: int, y
     k_rows = bits_of(kref[base_position:base_position + 8]).reshape(8, REF_K_HEADS, REF_HEAD_DIM)
     v_rows = bits_of(vref[base_position:base_position + 8]).reshape(8, REF_K_HEADS, REF_HEAD_DIM)
     return bits_of(q), k_rows, v_rows, kc[base_position:base_position + 8].cpu().numpy()
+
+
+def draft_qk_norm_rope(x_bits: np.ndarray, gamma_bits: np.ndarray, rope_table: np.ndarray, first_position: int):
+    """The reference's BF16-convention q/k kernel followed by its BF16 rounding pass; x_bits [T, H, 128], token t at
+    position first_position + t.  Returns the BF16 bits of the result."""
+    tokens, heads, _ = x_bits.shape
+    x = f32_dev(x_bits)
+    w = torch.from_numpy(gamma_bits.view(np.int16)).cuda()
+    table = torch.from_numpy(np.ascontiguousarray(rope_table, np.float32)).cuda()
+    ok(ref_lib.lib().ref_dspark_qk_norm_rope_round(w.data_ptr(), x.data_ptr(), table.data_ptr(), table.shape[0], heads, tokens,
+                                                   first_position), "dspark qk_norm_rope + round")
+    return bits_of(x)

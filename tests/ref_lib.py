@@ -23,6 +23,7 @@ SIGNATURES = {
     "ref_qk_norm_partial_rope_cache_temporal8": [vp, vp, vp, vp, vp, vp, vp, vp, vp, u32, u32, i32],
     "ref_qk_norm_partial_rope_cache8": [vp, vp, vp, vp, vp, vp, vp, vp, vp, u32, u32, u32, i32],
     "ref_sigmoid_gate8": [vp, vp, vp],
+    "ref_dspark_qk_norm_rope_round": [vp, vp, vp, u32, u32, u32, u32],
     "ref_fp8_group_row_scale_bf16_epilogue": [vp, vp, vp, u32],
     "ref_top1_8": [vp, vp, vp, i32],
     "ref_q8_0_embedding_gather_f32": [vp, vp, u32, u32, u32],

@@ -396,3 +396,55 @@ def test_config3_full_size(axk, cuda_device):
     lb = (positions // 16) % 4096
     assert np.array_equal(cells[table[0, lb], positions % 16], got_k.reshape(tokens, 1024))
     assert int((cells != 0xFFFF).any(axis=2).sum()) == tokens
+
+
+def test_round_after_norm_convention_contract(axk, cuda_device):
+    """The flag's argument checks and its two cos/sin sources: partial rotation is refused, a table without the flag is
+    refused, a position outside the table leaves the token untouched and raises the status word, and without a table
+    the factors come from inv_freq and mscale (compared with the CPU restatement fed with the same device-style table)."""
+    import torch
+    from gpu_util import dev, host, sync
+
+    tokens, heads = 12, 4
+    rng = np.random.default_rng(8)
+    q = wl.to_bf16_bits(rng.standard_normal((tokens, heads, 128), dtype=np.float32))
+    g = wl.to_bf16_bits(1.0 + 0.02 * rng.standard_normal(128, dtype=np.float32))
+    inv_freq = ol.yarn_inv_freq(1e6, 4.0, 32768.0, 32.0, 1.0, 128)
+    mscale = float(ol.o().axo_yarn_mscale(4.0))
+    positions = np.arange(20, 20 + tokens).astype(np.uint32)
+    table = ol.rope_table_host(inv_freq, 128, mscale, 28)       # positions 28..31 are outside
+    qd, gd, fd, pd, td = dev(q), dev(g), dev(inv_freq), dev(positions), dev(table)
+    status = torch.zeros(1, dtype=torch.int32, device="cuda")
+
+    def args(**kw):
+        base = dict(tokens=tokens, q_heads=heads, k_heads=0, head_dim=128, rope_dim=128, flags=axk.QK_FLAG_ROUND_AFTER_NORM,
+                    eps=1e-6, mscale=mscale, q=qd, q_gamma=gd, inv_freq=fd, positions=pd, status_word=status)
+        base.update(kw)
+        return axk.make_qk_args(**base)
+
+    inv = axk.AXIOM_ERR_INVALID_ARGUMENT
+    assert axk.qk_norm_rope_paged(0, args(rope_dim=64)) == inv
+    assert axk.qk_norm_rope_paged(0, args(flags=0, rope_table=td, rope_table_positions=28)) == inv
+    assert axk.qk_norm_rope_paged(0, args(rope_table=td, rope_table_positions=0)) == inv
+    assert np.array_equal(host(qd, np.uint16).reshape(q.shape), q)   # nothing ran
+    # table source, 4 tokens outside
+    assert axk.qk_norm_rope_paged(0, args(rope_table=td, rope_table_positions=28)) == axk.AXIOM_OK
+    sync()
+    got = host(qd, np.uint16).reshape(q.shape)
+    want, st = ol.qk_norm_rope_round_after_norm(q, g, table, positions)
+    assert st == 1 and int(status.item()) == axk.STATUS_WORD_BAD_ADDRESS
+    assert np.array_equal(got[8:], q[8:])
+    # three BF16 ulps at the magnitude of the rotation terms: the operands are rounded before the rotation, and the
+    # CPU restatement's inverse square root is not the device's
+    a, b = wl.from_bf16_bits(got[:8]), wl.from_bf16_bits(want[:8])
+    assert np.all(np.abs(a - b) <= 3 * tolerance(q[:8], g, inv_freq, positions[:8], 128, mscale))
+    # inv_freq source: same convention, factors evaluated on the device
+    qd2 = dev(q)
+    status.zero_()
+    assert axk.qk_norm_rope_paged(0, args(q=qd2)) == axk.AXIOM_OK
+    sync()
+    full_table = ol.rope_table_host(inv_freq, 128, mscale, 32)
+    want2, _ = ol.qk_norm_rope_round_after_norm(q, g, full_table, positions)
+    a, b = wl.from_bf16_bits(host(qd2, np.uint16).reshape(q.shape)), wl.from_bf16_bits(want2)
+    assert int(status.item()) == 0
+    assert np.all(np.abs(a - b) <= 3 * tolerance(q, g, inv_freq, positions, 128, mscale))

@@ -96,7 +96,8 @@ def test_plain_fp8_quantizer_bit_exact(axk, cuda_device):
         assert codes.guards_intact() and scales.guards_intact()
 
 
-@pytest.mark.parametrize("rows,width,layout", [(1, 17408, 0), (8, 17408, 1), (3, 16, 0), (70, 1024, 1), (256, 17408, 0)])
+@pytest.mark.parametrize("rows,width,layout", [(1, 17408, 0), (8, 17408, 1), (3, 16, 0), (70, 1024, 1), (256, 17408, 0),
+                                                (300, 1024, 1), (1000, 17408, 0), (333, 4096 + 256, 1), (297, 512 + 16, 0)])
 def test_swiglu_nvfp4(axk, cuda_device, rows, width, layout):
     from gpu_util import Guarded, dev, sync
 
@@ -269,7 +270,8 @@ def test_config4_full_size_nvfp4(axk, cuda_device):
             assert np.array_equal(ol.scales_to_tiled(got_scales), ref_plane)
 
 
-@pytest.mark.parametrize("rows,width,layout", [(1, 6144, 0), (8, 8192, 1), (3, 16, 0), (120, 6144, 1), (400, 2048, 0)])
+@pytest.mark.parametrize("rows,width,layout", [(1, 6144, 0), (8, 8192, 1), (3, 16, 0), (120, 6144, 1), (400, 2048, 0),
+                                                (600, 4096, 1), (310, 8192, 1), (299, 256 + 16, 0)])
 def test_sigmoid_gate_nvfp4(axk, cuda_device, rows, width, layout):
     """y = bf16(attention * sigmoid(gate)) and its NVFP4 image vs the oracle: y within one BF16 ulp (device
     expf), codes re-derived bit-exactly from the kernel's own y."""

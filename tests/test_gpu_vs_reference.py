@@ -131,7 +131,7 @@ def test_fp8_quantizers_bit_exact(axk, cuda_device):
         assert int(status.item()) == twin_status == 4
 
 
-@pytest.mark.parametrize("rows,width", [(8, 17408), (40, 4096), (3, 64), (16, 11008)])
+@pytest.mark.parametrize("rows,width", [(8, 17408), (40, 4096), (3, 64), (16, 11008), (320, 1024), (304, 17408)])
 def test_swiglu_fp8_and_nvfp4_bit_exact(axk, cuda_device, rows, width):
     import torch
     import ref_cases as rc
@@ -197,6 +197,56 @@ def test_yarn_table_and_qk_norm_rope_bit_exact(axk, cuda_device):
     assert np.array_equal(host(qd, np.uint16).reshape(q.shape), ref_q)
     assert np.array_equal(k_cache.cpu().numpy(), ref_kcache)
     assert np.array_equal(v_cache.cpu().numpy().reshape(-1), ol.bf16_to_e4m3_scale1(v).reshape(-1))
+
+
+@pytest.mark.parametrize("q_heads,k_heads,tokens,first", [(40, 8, 8, 0), (40, 8, 16, 1000), (64, 8, 8, 99990), (40, 8, 300, 5)])
+def test_round_after_norm_convention_bit_exact(axk, cuda_device, q_heads, k_heads, tokens, first):
+    """AXIOM_QK_FLAG_ROUND_AFTER_NORM against the reference's qk_rmsnorm_rope_bf16_kernel + round_f32_to_bf16 pass
+    (the draft's geometry, 40 q / 8 kv heads x 128 with full-head rotation, and the benchmark's 64 / 8 x 128), cos/sin
+    from a host-built [position][cos | sin] table as the reference builds it: Q, K and the cached K rows bit for bit."""
+    import torch
+    import ref_cases as rc
+    from gpu_util import dev, host, sync
+
+    rng = np.random.default_rng(q_heads + tokens)
+    q = wl.to_bf16_bits(rng.standard_normal((tokens, q_heads, 128), dtype=np.float32))
+    k = wl.to_bf16_bits(rng.standard_normal((tokens, k_heads, 128), dtype=np.float32) * np.float32(3.0))
+    qg = wl.to_bf16_bits(1.0 + 0.02 * rng.standard_normal(128, dtype=np.float32))
+    kg = wl.to_bf16_bits(1.0 + 0.02 * rng.standard_normal(128, dtype=np.float32))
+    inv_freq = ol.yarn_inv_freq(1e6, 4.0, 32768.0, 32.0, 1.0, 128, host_table=True)
+    table = ol.rope_table_host(inv_freq, 128, float(ol.o().axo_yarn_mscale(4.0)), first + tokens)
+    positions = (first + np.arange(tokens)).astype(np.uint32)
+    want_q = rc.draft_qk_norm_rope(q, qg, table, first)
+    want_k = rc.draft_qk_norm_rope(k, kg, table, first)
+
+    n_blocks = (first + tokens) // 16 + 1
+    btab = np.random.default_rng(3).permutation(n_blocks).astype(np.int32).reshape(1, n_blocks)
+    qd, kd, qgd, kgd, td, pd, bd = dev(q), dev(k), dev(qg), dev(kg), dev(table), dev(positions), dev(btab)
+    pool = torch.full((n_blocks * 16 * k_heads * 128,), -1, dtype=torch.int16, device="cuda")
+    k_out = torch.zeros((tokens, k_heads, 128), dtype=torch.int16, device="cuda")
+    status = torch.zeros(1, dtype=torch.int32, device="cuda")
+    args = axk.make_qk_args(tokens=tokens, q_heads=q_heads, k_heads=k_heads, head_dim=128, rope_dim=128,
+                            flags=axk.QK_FLAG_ROUND_AFTER_NORM, eps=1e-6, mscale=1.0, block_tokens=16, n_layers=1, layer=0,
+                            pool_stride=k_heads * 128, tbl_stride=n_blocks, n_blocks=n_blocks, q=qd, k=kd, q_gamma=qgd,
+                            k_gamma=kgd, positions=pd, block_tables=bd, k_pool=pool, k_out=k_out, status_word=status,
+                            rope_table=td, rope_table_positions=table.shape[0])
+    assert axk.qk_norm_rope_paged(0, args) == axk.AXIOM_OK
+    sync()
+    assert int(status.item()) == 0
+    assert np.array_equal(host(qd, np.uint16).reshape(q.shape), want_q)
+    assert np.array_equal(host(k_out, np.uint16).reshape(k.shape), want_k)
+    cells = host(pool, np.uint16).reshape(n_blocks, 16, k_heads * 128)
+    assert np.array_equal(cells[btab[0, positions // 16], positions % 16], want_k.reshape(tokens, -1))
+    # and the CPU restatement stays within one BF16 ulp of the kernels (its inverse square root is not the device's)
+    cpu_q, st = ol.qk_norm_rope_round_after_norm(q, qg, table, positions)
+    assert st == 0
+    # (a one-ulp difference of the factor can flip the BF16 rounding of both rotation operands, so the bound is three
+    # BF16 ulps at the magnitude of the rotation terms: one per operand and one for the final rounding)
+    from test_gpu_qk_rope import tolerance
+
+    a, b = wl.from_bf16_bits(cpu_q), wl.from_bf16_bits(want_q)
+    assert np.all(np.abs(a - b) <= 3 * tolerance(q, qg, inv_freq, positions, 128, float(ol.o().axo_yarn_mscale(4.0))))
+    assert np.mean(cpu_q != want_q) < 0.05
 
 
 def test_sigmoid_gate_bit_exact(axk, cuda_device):

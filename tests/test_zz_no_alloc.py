@@ -29,8 +29,11 @@ def _static_call(axk, x, G, layout):
 
 
 def test_static_entry_matches_runtime_entry_on_two_calls_in_a_row(axk, cuda_device):
+    import torch
+
     lib = axk.lib()
     rt = axk.Runtime(0)
+    calls = 0
     try:
         # call 1: tiled scale plane with padding (rows % 128 != 0, groups % 4 != 0); call 2: canonical, larger
         for rows, cols, layout, seed in ((200, 1072, axk.SCALE_TILED, 0), (600, 5120, axk.SCALE_CANONICAL, 1),
@@ -40,8 +43,12 @@ def test_static_entry_matches_runtime_entry_on_two_calls_in_a_row(axk, cuda_devi
             want_codes = np.empty((rows, cols // 2), np.uint8)
             want_scales = np.empty((rows, cols // 16), np.uint8)
             assert lib.axiom_runtime_nvfp4_quantize_bf16(rt.handle, _p(x), rows, cols, G, _p(want_codes), _p(want_scales)) == 0
+            free_before = torch.cuda.mem_get_info(0)[0] if calls else None
             rc, codes, scales = _static_call(axk, x, G, layout)
             assert rc == axk.AXIOM_OK
+            if calls:  # after the first call on the device (which loads the array's module) nothing is reserved any more
+                assert torch.cuda.mem_get_info(0)[0] == free_before
+            calls += 1
             assert np.array_equal(codes, want_codes)
             want_plane = want_scales.reshape(-1) if layout == axk.SCALE_CANONICAL else ol.scales_to_tiled(want_scales)
             assert np.array_equal(scales, want_plane)  # includes the zero padding of the tiled plane
