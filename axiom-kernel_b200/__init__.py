@@ -77,6 +77,17 @@ class QkRopeArgs(C.Structure):
     ]
 
 
+class LayerGlue(C.Structure):
+    """axiom_layer_glue: buffers of one decoder layer's elementwise launches."""
+    _fields_ = [
+        ("abi_version", u32), ("struct_size", u32), ("columns", u32), ("hidden", u32), ("ffn", u32), ("scale_layout", u32),
+        ("eps", f32), ("gate_up_input_scale", f32), ("down_input_scale", f32), ("reserved0", u32),
+        ("residual_bf16", vp), ("mixer_out_bf16", vp), ("post_norm_gamma_bf16", vp), ("mlp_in_codes", vp), ("mlp_in_scales", vp),
+        ("gate_up_bf16", vp), ("mlp_mid_codes", vp), ("mlp_mid_scales", vp), ("mlp_out_bf16", vp), ("tap_out_bf16", vp),
+        ("next_norm_gamma_bf16", vp), ("next_norm_out_bf16", vp),
+    ]
+
+
 class AxiomError(RuntimeError):
     def __init__(self, status: int, where: str):
         self.status = status
@@ -153,6 +164,13 @@ SIGNATURES = {
     "axiom_b200_static_scratch_bytes": (u64, []),
     "axiom_b200_nvfp4_quantize_bf16_host_static": (i32, [C.c_int, vp, u32, u32, f32, u32, vp, vp, vp]),
     "axiom_b200_pipeline_faults": (u32, [i32]),
+    "axiom_b200_prepare": (i32, [i32]),
+    "axiom_qwen38_fused_layer_post_mixer_device": (i32, [i32, C.POINTER(LayerGlue), vp]),
+    "axiom_qwen38_fused_layer_mlp_mid_device": (i32, [i32, C.POINTER(LayerGlue), vp]),
+    "axiom_qwen38_fused_layer_post_mlp_device": (i32, [i32, C.POINTER(LayerGlue), vp]),
+    "axiom_b200_test_arm_wait_timeout": (i32, [u32, u32]),
+    "axiom_qwen38_fused_fp8_quantize_static_bf16_device": (i32, [i32, vp, u32, u32, f32, vp, vp]),
+    "axiom_qwen38_fused_swiglu_fp8_static_bf16_device": (i32, [i32, vp, u32, u32, f32, vp, vp]),
 }
 
 _lib = None
@@ -270,6 +288,16 @@ def top1(device, logits, rows, vocab, results, stream=None):
     return lib().axiom_qwen38_fused_top1_f32_device(device, _ptr(logits), rows, vocab, _ptr(results), _stream_handle(stream))
 
 
+def fp8_quantize_static(device, x_bf16, rows, cols, scale, codes, stream=None):
+    return lib().axiom_qwen38_fused_fp8_quantize_static_bf16_device(device, _ptr(x_bf16), rows, cols, scale, _ptr(codes),
+                                                                   _stream_handle(stream))
+
+
+def swiglu_fp8_static(device, gate_up, rows, width, scale, codes, stream=None):
+    return lib().axiom_qwen38_fused_swiglu_fp8_static_bf16_device(device, _ptr(gate_up), rows, width, scale, _ptr(codes),
+                                                                 _stream_handle(stream))
+
+
 def fp8_quantize(device, x_bf16, rows, cols, codes, scales, status_word=None, stream=None):
     return lib().axiom_qwen38_fused_fp8_quantize_bf16_device(
         device, _ptr(x_bf16), rows, cols, _ptr(codes), _ptr(scales), _ptr(status_word), _stream_handle(stream))
@@ -299,6 +327,28 @@ def make_qk_args(*, tokens, q_heads, k_heads, head_dim, rope_dim, flags=0, eps=1
                       _ptr(k), _ptr(v), _ptr(q_gamma), _ptr(k_gamma), _ptr(inv_freq), _ptr(positions),
                       _ptr(block_tables), _ptr(k_pool), _ptr(v_pool), _ptr(k_out), _ptr(status_word), _ptr(q_out),
                       _ptr(rope_table), rope_table_positions, 0)
+
+
+def make_layer_glue(*, columns, hidden, ffn, scale_layout=SCALE_TILED, eps=1e-6, gate_up_input_scale=1.0, down_input_scale=1.0,
+                    residual=None, mixer_out=None, post_norm_gamma=None, mlp_in_codes=None, mlp_in_scales=None, gate_up=None,
+                    mlp_mid_codes=None, mlp_mid_scales=None, mlp_out=None, tap_out=None, next_norm_gamma=None,
+                    next_norm_out=None) -> LayerGlue:
+    return LayerGlue(AXIOM_ABI_VERSION, C.sizeof(LayerGlue), columns, hidden, ffn, scale_layout, eps, gate_up_input_scale,
+                     down_input_scale, 0, _ptr(residual), _ptr(mixer_out), _ptr(post_norm_gamma), _ptr(mlp_in_codes),
+                     _ptr(mlp_in_scales), _ptr(gate_up), _ptr(mlp_mid_codes), _ptr(mlp_mid_scales), _ptr(mlp_out), _ptr(tap_out),
+                     _ptr(next_norm_gamma), _ptr(next_norm_out))
+
+
+def layer_post_mixer(device, glue: LayerGlue, stream=None):
+    return lib().axiom_qwen38_fused_layer_post_mixer_device(device, C.byref(glue), _stream_handle(stream))
+
+
+def layer_mlp_mid(device, glue: LayerGlue, stream=None):
+    return lib().axiom_qwen38_fused_layer_mlp_mid_device(device, C.byref(glue), _stream_handle(stream))
+
+
+def layer_post_mlp(device, glue: LayerGlue, stream=None):
+    return lib().axiom_qwen38_fused_layer_post_mlp_device(device, C.byref(glue), _stream_handle(stream))
 
 
 def qk_norm_rope_paged(device, args: QkRopeArgs, stream=None):

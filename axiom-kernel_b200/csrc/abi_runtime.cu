@@ -118,6 +118,16 @@ extern "C" uint32_t axiom_b200_pipeline_faults(int device) {
     return add_rmsnorm_fault_word() | swiglu_fault_word() | qk_fault_word();
 }
 
+extern "C" int axiom_b200_prepare(int device) {
+    int rc = select_device(device);
+    if (rc != AXIOM_OK) return rc;
+    prepare_add_rmsnorm_unit();
+    prepare_qk_unit();
+    const bool tables = prepare_gated_unit();
+    if (cudaDeviceSynchronize() != cudaSuccess || cudaGetLastError() != cudaSuccess) return AXIOM_ERR_CUDA;
+    return tables ? AXIOM_OK : AXIOM_ERR_CUDA;
+}
+
 extern "C" int axiom_runtime_nvfp4_quantize_bf16_device(
         axiom_runtime *runtime, const axiom_device_buffer *input, uint64_t input_offset, uint32_t rows,
         uint32_t cols, float global_scale, axiom_device_buffer *out_codes, uint64_t codes_offset,

@@ -60,6 +60,10 @@ struct norm_args {
     const float *hidden_f32;        // [rows x cols]
     const uint16_t *weight_scale;   // [cols] BF16
     const float *input_scale;       // [rows]
+    // test hook (axiom_b200_test_arm_wait_timeout): the first row of team 0 of CTA 0 announces this many bytes more
+    // than its copies deliver, so its barrier never completes, and waits give up after spin_limit polls (0 = default)
+    uint32_t inject_tx;
+    uint32_t spin_limit;
 };
 
 // What is added to the residual before the norm.
@@ -148,6 +152,7 @@ add_rmsnorm_stream_kernel(const norm_args a) {
     scale_lut_entry *lut = reinterpret_cast<scale_lut_entry *>(wscale_sh + (kAddend == kScaledF32 ? a.cols : 0u));
     float *partials = reinterpret_cast<float *>(lut + 128);                      // [teams][256]
     uint64_t *bars = reinterpret_cast<uint64_t *>(partials + teams * 256u);      // [teams][kMaxSlotsPerTeam]
+    volatile uint32_t *team_fault = reinterpret_cast<volatile uint32_t *>(bars + teams * kMaxSlotsPerTeam);  // [teams]
 
     const uint32_t tid = threadIdx.x, team = tid / kTeamThreads, t = tid % kTeamThreads, lane = tid & 31u;
     const uint32_t warp_in_team = t >> 5;
@@ -158,9 +163,11 @@ add_rmsnorm_stream_kernel(const norm_args a) {
     if (t == 0u) {
         for (uint32_t j = 0; j < spt; ++j) mbar_init(my_bars + j, 1u);
         mbar_init_fence();
+        team_fault[team] = 0u;
     }
     team_barrier(team);
     dependency_wait();
+    const uint32_t spin_limit = a.spin_limit ? a.spin_limit : kSpinLimit;
 
     // rows of this CTA: blockIdx.x + n * gridDim.x; this team takes n = team + teams * i
     const uint32_t cta_rows = blockIdx.x < a.rows ? (a.rows - blockIdx.x + gridDim.x - 1u) / gridDim.x : 0u;
@@ -201,7 +208,7 @@ add_rmsnorm_stream_kernel(const norm_args a) {
     auto issue_residual = [&](uint32_t i) {
         const uint64_t row = blockIdx.x + (uint64_t)(team + teams * i) * gridDim.x;
         const uint32_t j = i % spt;
-        mbar_arrive_expect_tx(my_bars + j, row_bytes);
+        mbar_arrive_expect_tx(my_bars + j, row_bytes + ((blockIdx.x | team | i) == 0u ? a.inject_tx : 0u));
         bulk_load(my_slots + (size_t)j * slot_bytes + addend_bytes, a.residual + row * a.chunks_per_row, row_bytes,
                   my_bars + j);
     };
@@ -223,7 +230,6 @@ add_rmsnorm_stream_kernel(const norm_args a) {
     }
     const bool lut_safe = build_scale_lut(lut, a.codes ? a.G : 1.0f);  // contains the CTA barrier
 
-    bool faulted = false;
     for (uint32_t i = 0; i < my_rows; ++i) {
         const uint32_t j = i % spt;
         float token_scale = 1.0f;
@@ -231,9 +237,12 @@ add_rmsnorm_stream_kernel(const norm_args a) {
         // the id of the row whose addend is requested after sweep 1 (fetched now: its latency hides behind the sweep)
         uint32_t next_token = 0u;
         if (t == 0u && i + spt < my_rows) next_token = token_of_row(i + spt);
-        // A wait that ran out raises the fault word; the team carries on (on whatever the slot
-        // holds) so that its barriers stay matched, and stops waiting.
-        if (!faulted && !mbar_wait(my_bars + j, (i / spt) & 1u)) faulted = true;
+        // A wait that ran out raises the device's fault word and the team's flag.  The flag is read by the whole
+        // team behind the barrier that follows sweep 1 (which only touches shared memory), so the team decides as
+        // one: it writes nothing for this row or any later one, waits — bounded again — for the copies it still
+        // has in flight, and leaves.  Its rows keep their old contents; the caller learns of it from
+        // axiom_b200_pipeline_faults().
+        if (!mbar_wait(my_bars + j, (i / spt) & 1u, spin_limit)) team_fault[team] = 1u;
         const uint32_t row = blockIdx.x + (team + teams * i) * gridDim.x;
         const uint64_t base = (uint64_t)row * a.chunks_per_row;
         uint8_t *slot = my_slots + (size_t)j * slot_bytes;
@@ -267,6 +276,11 @@ add_rmsnorm_stream_kernel(const norm_args a) {
         reinterpret_cast<float2 *>(my_partials)[t] = p;
         if (stores) fence_async_shared();
         team_barrier(team);
+        if (team_fault[team] != 0u) {
+            // rows i+1 .. i+spt-1 were requested in full; nothing later was (the addend of row i+spt is requested below)
+            for (uint32_t n = i + 1u; n < i + spt && n < my_rows; ++n) (void)mbar_wait(my_bars + n % spt, (n / spt) & 1u, spin_limit);
+            break;
+        }
         if (stores && t == 0u) {
             // the merged row leaves as one bulk store (two with a tap); the slot stays in use until it has been read
             if (kAdd) bulk_store(a.residual + base, res_sh, row_bytes);
@@ -471,18 +485,13 @@ constexpr size_t kSmemBudget = 227u * 1024u;
 
 size_t stream_fixed_bytes(uint32_t cols, uint32_t teams, int addend = kBf16) {
     return (size_t)cols * sizeof(float) * (addend == kScaledF32 ? 2u : 1u) + 128u * sizeof(scale_lut_entry) +
-           (size_t)teams * 256u * sizeof(float) + (size_t)teams * kMaxSlotsPerTeam * sizeof(uint64_t);
+           (size_t)teams * 256u * sizeof(float) + (size_t)teams * kMaxSlotsPerTeam * sizeof(uint64_t) +
+           (size_t)kMaxTeams * sizeof(uint32_t);  // barriers, then one fault flag per team
 }
 
 template <int kAdd, bool kFull>
 void launch_stream_impl(const norm_args &a, uint32_t teams, size_t smem, cudaStream_t stream) {
-    static bool configured[64] = {};  // the attribute is per device; one process may drive several
-    int dev = 0;
-    cudaGetDevice(&dev);
-    if (dev >= 0 && dev < 64 && !configured[dev]) {
-        cudaFuncSetAttribute(add_rmsnorm_stream_kernel<kAdd, kFull>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmemBudget);
-        configured[dev] = true;
-    }
+    allow_dynamic_smem<add_rmsnorm_stream_kernel<kAdd, kFull>>(kSmemBudget);
     const uint32_t ctas = a.rows < kSmCount ? a.rows : kSmCount;
     launch_chained(add_rmsnorm_stream_kernel<kAdd, kFull>, dim3(ctas), dim3(teams * kTeamThreads), smem, stream, a);
 }
@@ -492,6 +501,9 @@ void launch_stream(const norm_args &a, uint32_t teams, size_t smem, cudaStream_t
     if (a.cols % 1024u == 0u) launch_stream_impl<kAdd, true>(a, teams, smem, stream);
     else launch_stream_impl<kAdd, false>(a, teams, smem, stream);
 }
+
+// One-shot test hook state (axiom_b200_test_arm_wait_timeout): consumed by the next streaming launch.
+uint32_t g_armed_inject_tx = 0u, g_armed_spin_limit = 0u;
 
 // Picks the kernel and its shape for a prepared argument block.
 int launch_norm(norm_args &a, int addend, cudaStream_t stream) {
@@ -528,6 +540,9 @@ int launch_norm(norm_args &a, int addend, cudaStream_t stream) {
         return AXIOM_OK;
     }
     a.ring_slots = spt;
+    a.inject_tx = g_armed_inject_tx;
+    a.spin_limit = g_armed_spin_limit;
+    g_armed_inject_tx = g_armed_spin_limit = 0u;
     const size_t smem = stream_fixed_bytes(cols, teams, addend) + (size_t)teams * spt * slot_bytes;
     if (addend == kScaledF32) launch_stream<kScaledF32>(a, teams, smem, stream);
     else if (addend == kBf16) launch_stream<kBf16>(a, teams, smem, stream);
@@ -539,6 +554,16 @@ int launch_norm(norm_args &a, int addend, cudaStream_t stream) {
 }  // namespace
 
 unsigned int add_rmsnorm_fault_word() { return read_and_clear_pipeline_fault(); }
+
+// Everything a first launch would set up lazily, for axiom_b200_prepare().
+void prepare_add_rmsnorm_unit() {
+    allow_dynamic_smem<add_rmsnorm_stream_kernel<kNone, true>>(kSmemBudget);
+    allow_dynamic_smem<add_rmsnorm_stream_kernel<kNone, false>>(kSmemBudget);
+    allow_dynamic_smem<add_rmsnorm_stream_kernel<kBf16, true>>(kSmemBudget);
+    allow_dynamic_smem<add_rmsnorm_stream_kernel<kBf16, false>>(kSmemBudget);
+    allow_dynamic_smem<add_rmsnorm_stream_kernel<kScaledF32, true>>(kSmemBudget);
+    allow_dynamic_smem<add_rmsnorm_stream_kernel<kScaledF32, false>>(kSmemBudget);
+}
 
 int launch_gather_add_rmsnorm_nvfp4_bf16(const void *table, uint32_t vocab, const uint32_t *token_ids, void *residual,
                                          const void *gamma, float eps, uint32_t rows, uint32_t cols, float G,
@@ -622,6 +647,13 @@ int launch_fp8_epilogue_add_rmsnorm_nvfp4(const float *gemm_out, const void *wei
 }  // namespace axb
 
 using namespace axb;
+
+extern "C" int axiom_b200_test_arm_wait_timeout(uint32_t extra_bytes, uint32_t spin_limit) {
+    if ((extra_bytes % 16u) != 0u || extra_bytes > (1u << 19) || spin_limit > (1u << 20)) return AXIOM_ERR_INVALID_ARGUMENT;
+    g_armed_inject_tx = extra_bytes;
+    g_armed_spin_limit = spin_limit;
+    return AXIOM_OK;
+}
 
 extern "C" int axiom_qwen38_fused_add_rmsnorm_nvfp4_bf16_device(
         int device, const void *hidden_bf16, void *residual_bf16, const void *gamma_bf16, float eps,

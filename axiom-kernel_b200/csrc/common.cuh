@@ -87,6 +87,22 @@ inline cudaError_t launch_chained(void (*kernel)(KArgs...), dim3 grid, dim3 bloc
     return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
 }
 
+// Raises the dynamic shared-memory limit of one kernel, once per device (the attribute is per device; one
+// process may drive several).  The kernel is a template argument so that every kernel has a flag of its own.
+template <auto Kernel>
+inline void allow_dynamic_smem(size_t bytes) {
+    static bool done[64] = {};
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) {
+        cudaFuncSetAttribute(Kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)bytes);
+        return;
+    }
+    if (!done[dev]) {
+        cudaFuncSetAttribute(Kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)bytes);
+        done[dev] = true;
+    }
+}
+
 __device__ __forceinline__ float bf16_lo(uint32_t packed) { return __uint_as_float(packed << 16); }
 __device__ __forceinline__ float bf16_hi(uint32_t packed) { return __uint_as_float(packed & 0xffff0000u); }
 // The two BF16 halves of `packed` as floats through the mixed-precision FMA of sm_100 (x * 1 + (-0) = x for every

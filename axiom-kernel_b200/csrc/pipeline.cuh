@@ -58,9 +58,9 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t *bar, uint32_t parity) {
     return done != 0u;
 }
 
-// Bounded wait; false (and the fault flag raised) when the phase never completed.
-__device__ __forceinline__ bool mbar_wait(uint64_t *bar, uint32_t parity) {
-    for (uint32_t spin = 0; spin < kSpinLimit; ++spin) {
+// Bounded wait; false (and the fault flag raised) when the phase never completed within `limit` polls.
+__device__ __forceinline__ bool mbar_wait(uint64_t *bar, uint32_t parity, uint32_t limit = kSpinLimit) {
+    for (uint32_t spin = 0; spin < limit; ++spin) {
         if (mbar_try_wait(bar, parity)) return true;
     }
     atomicOr(&g_pipeline_fault, 1u);

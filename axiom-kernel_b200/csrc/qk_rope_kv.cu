@@ -813,11 +813,9 @@ void launch_qk(const qk_dev_args &a, cudaStream_t stream) {
 // (head_dim, heads, tokens), a head pitch of two heads, box = (head_dim, heads, 1) = one token's
 // packed Q row.  The driver's encoder is fetched through the runtime once; false (the kernel then
 // falls back to one bulk copy per head) when it is missing or refuses the shape.
-bool encode_strided_q_map(const qk_dev_args &a, CUtensorMap *map) {
-    using encode_fn = CUresult (*)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *,
-                                   const cuuint64_t *, const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave,
-                                   CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
-    static const encode_fn encode = [] {
+// The driver's cuTensorMapEncodeTiled, fetched through the runtime once per process (nullptr when it is missing).
+void *tensor_map_encoder() {
+    static void *const encoder = [] {
         void *fn = nullptr;
         cudaDriverEntryPointQueryResult found = cudaDriverEntryPointSymbolNotFound;
         if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &found) != cudaSuccess ||
@@ -825,8 +823,16 @@ bool encode_strided_q_map(const qk_dev_args &a, CUtensorMap *map) {
             cudaGetLastError();
             fn = nullptr;
         }
-        return reinterpret_cast<encode_fn>(fn);
+        return fn;
     }();
+    return encoder;
+}
+
+bool encode_strided_q_map(const qk_dev_args &a, CUtensorMap *map) {
+    using encode_fn = CUresult (*)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *,
+                                   const cuuint64_t *, const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave,
+                                   CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+    static const encode_fn encode = reinterpret_cast<encode_fn>(tensor_map_encoder());
     if (!encode || a.q_heads > 256u || a.head_dim > 256u || a.tokens > 0x7fffffffu) return false;
     const cuuint64_t dims[3] = {a.head_dim, a.q_heads, a.tokens};
     const cuuint64_t strides[2] = {(cuuint64_t)a.q_head_stride * 2u, (cuuint64_t)a.q_heads * a.q_head_stride * 2u};  // bytes
@@ -886,11 +892,11 @@ bool launch_qk_stream(const qk_dev_args &a, cudaStream_t stream) {
     do {                                                                                                 \
         if (full) {                                                                                      \
             auto kern = qk_norm_rope_stream_kernel<LPH, NPT, true>;                                      \
-            cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kQkSmemBudget); \
+            allow_dynamic_smem<qk_norm_rope_stream_kernel<LPH, NPT, true>>(kQkSmemBudget);               \
             launch_chained(kern, dim3(ctas), dim3(best.teams * best.team_threads), smem, stream, a2, best, q_map);               \
         } else {                                                                                         \
             auto kern = qk_norm_rope_stream_kernel<LPH, NPT, false>;                                     \
-            cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kQkSmemBudget); \
+            allow_dynamic_smem<qk_norm_rope_stream_kernel<LPH, NPT, false>>(kQkSmemBudget);              \
             launch_chained(kern, dim3(ctas), dim3(best.teams * best.team_threads), smem, stream, a2, best, q_map);               \
         }                                                                                                \
     } while (0)
@@ -920,6 +926,32 @@ bool is_pow2(uint32_t v) { return v && !(v & (v - 1u)); }
 }  // namespace
 
 unsigned int qk_fault_word() { return read_and_clear_pipeline_fault(); }
+
+namespace {
+template <int LPH>
+void prepare_qk_stream_kernels() {
+    allow_dynamic_smem<qk_norm_rope_stream_kernel<LPH, 2, true>>(kQkSmemBudget);
+    allow_dynamic_smem<qk_norm_rope_stream_kernel<LPH, 2, false>>(kQkSmemBudget);
+    allow_dynamic_smem<qk_norm_rope_stream_kernel<LPH, 3, true>>(kQkSmemBudget);
+    allow_dynamic_smem<qk_norm_rope_stream_kernel<LPH, 3, false>>(kQkSmemBudget);
+    allow_dynamic_smem<qk_norm_rope_stream_kernel<LPH, 4, true>>(kQkSmemBudget);
+    allow_dynamic_smem<qk_norm_rope_stream_kernel<LPH, 4, false>>(kQkSmemBudget);
+    allow_dynamic_smem<qk_norm_rope_stream_kernel<LPH, 6, true>>(kQkSmemBudget);
+    allow_dynamic_smem<qk_norm_rope_stream_kernel<LPH, 6, false>>(kQkSmemBudget);
+    allow_dynamic_smem<qk_norm_rope_stream_kernel<LPH, 8, true>>(kQkSmemBudget);
+    allow_dynamic_smem<qk_norm_rope_stream_kernel<LPH, 8, false>>(kQkSmemBudget);
+    allow_dynamic_smem<qk_norm_rope_stream_kernel<LPH, 9, true>>(kQkSmemBudget);
+    allow_dynamic_smem<qk_norm_rope_stream_kernel<LPH, 9, false>>(kQkSmemBudget);
+}
+}  // namespace
+
+// Everything a first launch would set up lazily, for axiom_b200_prepare().
+void prepare_qk_unit() {
+    prepare_qk_stream_kernels<8>();
+    prepare_qk_stream_kernels<16>();
+    prepare_qk_stream_kernels<32>();
+    (void)tensor_map_encoder();
+}
 
 int launch_qk_norm_rope_paged_bf16(const axiom_qk_rope_args *p, cudaStream_t stream) {
     qk_dev_args a{};

@@ -80,6 +80,10 @@ int launch_qk_norm_rope_paged_bf16(const axiom_qk_rope_args *args, cudaStream_t 
 unsigned int add_rmsnorm_fault_word();
 unsigned int swiglu_fault_word();
 unsigned int qk_fault_word();
+// one-time set-up of each unit on the current device (axiom_b200_prepare)
+void prepare_add_rmsnorm_unit();
+void prepare_qk_unit();
+bool prepare_gated_unit();
 
 // argument validation shared by the raw, buffer and host flavours
 int check_nvfp4_quantize(const void *input, uint32_t rows, uint32_t cols, float G, const void *codes,

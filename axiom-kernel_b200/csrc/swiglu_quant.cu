@@ -21,6 +21,8 @@
 // array and every CTA copies it into shared memory (16-byte loads, L2 hits); a
 // call that arrives during stream capture before that one-time fill lets each CTA
 // fill its own copy instead.
+#include <math_constants.h>
+
 #include "pipeline.cuh"
 #include "runtime.hpp"
 
@@ -195,11 +197,14 @@ enum class row_op { swiglu, swiglu_table, plain_finite_only };
 // CPT = 16-byte chunks (8 values) per thread; blockDim.x * CPT >= width / 8.
 constexpr uint32_t kMaxRowThreads = 576u;
 
-template <int CPT, row_op kOp>
+// kStatic: the scale is an argument (quantize_columns_static_e4m3_kernel, src/axiom_qwen38_fp8.cu:96-107) — no row
+// maximum, no CTA reduction, no scale output; every thread decides for its own values whether the reciprocal
+// sequence is exact and takes IEEE divisions otherwise (NaN / infinity / quotients near overflow).
+template <int CPT, row_op kOp, bool kStatic = false>
 __global__ void __launch_bounds__(kMaxRowThreads, CPT <= 4 ? 2 : 1)
 fp8_rows_kernel(const uint4 *__restrict__ in, uint32_t rows, uint32_t chunks, uint32_t in_chunks_per_row,
                 uint2 *__restrict__ codes, float *__restrict__ scales, uint32_t *__restrict__ status_word,
-                const float *__restrict__ device_table) {
+                const float *__restrict__ device_table, float given_scale) {
     extern __shared__ __align__(16) float silu_table[];
     __shared__ float warp_max[32];
     constexpr bool kSwiglu = kOp != row_op::plain_finite_only;
@@ -247,8 +252,8 @@ fp8_rows_kernel(const uint4 *__restrict__ in, uint32_t rows, uint32_t chunks, ui
                 }
             }
         }
-        m = kSwiglu ? cta_max<true>(m, warp_max) : cta_max<false>(m, warp_max);
-        if (kSwiglu && !(m == m)) {
+        if (!kStatic) m = kSwiglu ? cta_max<true>(m, warp_max) : cta_max<false>(m, warp_max);
+        if (!kStatic && kSwiglu && !(m == m)) {
             // a NaN somewhere in the row: the reference's maximum drops it
             float d = 0.0f;
 #pragma unroll
@@ -257,14 +262,19 @@ fp8_rows_kernel(const uint4 *__restrict__ in, uint32_t rows, uint32_t chunks, ui
             nonfinite = true;
         }
         float scale = m == 0.0f ? 1.0f : __fdiv_rn(m, 448.0f);
-        if (kSwiglu) {
+        if (kStatic) {
+            scale = given_scale;
+            // the plain flavour keeps non-finite values out of its maximum: fold them back in for the range test
+            if (nonfinite || !(m == m)) m = CUDART_INF_F;
+        } else if (kSwiglu) {
             if (!isfinite(scale) || scale <= 0.0f) scale = 1.0f;
         } else if (nonfinite && status_word) {
             atomicCAS(status_word, AXIOM_STATUS_WORD_OK, AXIOM_STATUS_WORD_NONFINITE);
         }
-        if (tid == 0u) scales[row] = scale;
+        if (!kStatic && tid == 0u) scales[row] = scale;
         const float r = __frcp_rn(scale);
-        const bool safe = divisor_is_safe(scale, r, m) && !nonfinite;  // uniform over the CTA
+        // uniform over the CTA for the per-row scale, per thread (its own maximum) for a given scale
+        const bool safe = divisor_is_safe(scale, r, m) && (kStatic || !nonfinite);
         uint2 *out = codes + (uint64_t)row * chunks;
         if (safe) {
             // negated residual-corrected quotients (signed zeros survive), signs flipped back on the codes
@@ -611,9 +621,17 @@ const float *device_gate_table(cudaStream_t stream) {
 
 const float *device_silu_table(cudaStream_t stream) { return device_gate_table<gate_fn::silu>(stream); }
 
-template <row_op kOp>
+template <row_op kOp, bool kStatic>
+void configure_fp8_rows() {
+    allow_dynamic_smem<fp8_rows_kernel<1, kOp, kStatic>>(kSiluTableBytes);
+    allow_dynamic_smem<fp8_rows_kernel<2, kOp, kStatic>>(kSiluTableBytes);
+    allow_dynamic_smem<fp8_rows_kernel<4, kOp, kStatic>>(kSiluTableBytes);
+    allow_dynamic_smem<fp8_rows_kernel<8, kOp, kStatic>>(kSiluTableBytes);
+}
+
+template <row_op kOp, bool kStatic = false>
 int launch_fp8_rows(const void *in, uint32_t rows, uint32_t width, uint32_t in_chunks_per_row, uint8_t *codes,
-                    float *scales, uint32_t *status_word, cudaStream_t stream) {
+                    float *scales, uint32_t *status_word, cudaStream_t stream, float given_scale = 0.0f) {
     const uint32_t chunks = width / 8u;
     const row_shape s = pick_row_shape(chunks);
     if (s.threads == 0u) return AXIOM_ERR_INVALID_ARGUMENT;
@@ -625,23 +643,12 @@ int launch_fp8_rows(const void *in, uint32_t rows, uint32_t width, uint32_t in_c
     const uint32_t ctas = rows < cap ? rows : cap;
     const uint4 *src = (const uint4 *)in;
     uint2 *dst = (uint2 *)codes;
-    if (kTable) {
-        static bool configured[64] = {};
-        int dev = 0;
-        cudaGetDevice(&dev);
-        if (dev >= 0 && dev < 64 && !configured[dev]) {
-            cudaFuncSetAttribute(fp8_rows_kernel<1, kOp>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSiluTableBytes);
-            cudaFuncSetAttribute(fp8_rows_kernel<2, kOp>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSiluTableBytes);
-            cudaFuncSetAttribute(fp8_rows_kernel<4, kOp>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSiluTableBytes);
-            cudaFuncSetAttribute(fp8_rows_kernel<8, kOp>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSiluTableBytes);
-            configured[dev] = true;
-        }
-    }
+    if (kTable) configure_fp8_rows<kOp, kStatic>();
     switch (s.cpt) {
-    case 1: launch_chained(fp8_rows_kernel<1, kOp>, dim3(ctas), dim3(s.threads), smem, stream, src, rows, chunks, in_chunks_per_row, dst, scales, status_word, device_table); break;
-    case 2: launch_chained(fp8_rows_kernel<2, kOp>, dim3(ctas), dim3(s.threads), smem, stream, src, rows, chunks, in_chunks_per_row, dst, scales, status_word, device_table); break;
-    case 4: launch_chained(fp8_rows_kernel<4, kOp>, dim3(ctas), dim3(s.threads), smem, stream, src, rows, chunks, in_chunks_per_row, dst, scales, status_word, device_table); break;
-    default: launch_chained(fp8_rows_kernel<8, kOp>, dim3(ctas), dim3(s.threads), smem, stream, src, rows, chunks, in_chunks_per_row, dst, scales, status_word, device_table); break;
+    case 1: launch_chained(fp8_rows_kernel<1, kOp, kStatic>, dim3(ctas), dim3(s.threads), smem, stream, src, rows, chunks, in_chunks_per_row, dst, scales, status_word, device_table, given_scale); break;
+    case 2: launch_chained(fp8_rows_kernel<2, kOp, kStatic>, dim3(ctas), dim3(s.threads), smem, stream, src, rows, chunks, in_chunks_per_row, dst, scales, status_word, device_table, given_scale); break;
+    case 4: launch_chained(fp8_rows_kernel<4, kOp, kStatic>, dim3(ctas), dim3(s.threads), smem, stream, src, rows, chunks, in_chunks_per_row, dst, scales, status_word, device_table, given_scale); break;
+    default: launch_chained(fp8_rows_kernel<8, kOp, kStatic>, dim3(ctas), dim3(s.threads), smem, stream, src, rows, chunks, in_chunks_per_row, dst, scales, status_word, device_table, given_scale); break;
     }
     note_launch();
     return AXIOM_OK;
@@ -656,6 +663,8 @@ constexpr uint32_t kCopiedTableMinRows = 96u;
 
 unsigned int swiglu_fault_word() { return read_and_clear_pipeline_fault(); }
 
+
+
 int launch_swiglu_fp8_bf16(const void *gate_up, uint32_t rows, uint32_t width, uint8_t *codes, float *scales,
                            cudaStream_t stream) {
     if (rows >= kTableMinRows) {
@@ -664,9 +673,32 @@ int launch_swiglu_fp8_bf16(const void *gate_up, uint32_t rows, uint32_t width, u
     return launch_fp8_rows<row_op::swiglu>(gate_up, rows, width, width / 4u, codes, scales, nullptr, stream);
 }
 
+// Given-scale flavours: the same row kernels without the row maximum (one pass, nothing to reduce).
+int launch_fp8_quantize_static_bf16(const void *input, uint32_t rows, uint32_t cols, float scale, uint8_t *codes,
+                                    cudaStream_t stream) {
+    return launch_fp8_rows<row_op::plain_finite_only, true>(input, rows, cols, cols / 8u, codes, nullptr, nullptr, stream, scale);
+}
+
+int launch_swiglu_fp8_static_bf16(const void *gate_up, uint32_t rows, uint32_t width, float scale, uint8_t *codes,
+                                  cudaStream_t stream) {
+    if (rows >= kTableMinRows) {
+        return launch_fp8_rows<row_op::swiglu_table, true>(gate_up, rows, width, width / 4u, codes, nullptr, nullptr, stream, scale);
+    }
+    return launch_fp8_rows<row_op::swiglu, true>(gate_up, rows, width, width / 4u, codes, nullptr, nullptr, stream, scale);
+}
+
 int launch_fp8_quantize_bf16(const void *input, uint32_t rows, uint32_t cols, uint8_t *codes, float *scales,
                              uint32_t *status_word, cudaStream_t stream) {
     return launch_fp8_rows<row_op::plain_finite_only>(input, rows, cols, cols / 8u, codes, scales, status_word, stream);
+}
+
+template <gate_fn kFn>
+void configure_gated_stream() {
+    allow_dynamic_smem<gated_nvfp4_stream_kernel<kFn, true, true, true>>(kSiluTableBytes);
+    allow_dynamic_smem<gated_nvfp4_stream_kernel<kFn, false, true, true>>(kSiluTableBytes);
+    allow_dynamic_smem<gated_nvfp4_stream_kernel<kFn, true, false, true>>(kSiluTableBytes);
+    allow_dynamic_smem<gated_nvfp4_stream_kernel<kFn, false, false, true>>(kSiluTableBytes);
+    allow_dynamic_smem<gated_nvfp4_stream_kernel<kFn, false, true, false>>(kSiluTableBytes);
 }
 
 // Shared launcher of the two gated NVFP4 ops.  `gate` / `other` are the two operand planes, row_stride their row
@@ -693,40 +725,28 @@ int launch_gated_nvfp4(const uint4 *gate, const uint4 *other, uint32_t row_strid
         const uint32_t ctas = kSmCount * 2u;
         const uint32_t warps = ctas * warps_per_block;
         const uint32_t per_warp = (uint32_t)((tiles + warps - 1u) / warps);
-        // one instantiation per (scale layout, outputs asked for); the shared-memory attribute is set per device
-        auto launch = [&](auto kernel, int slot) {
-            static bool configured[64][8] = {};
-            int dev = 0;
-            cudaGetDevice(&dev);
-            if (dev >= 0 && dev < 64 && !configured[dev][slot]) {
-                cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSiluTableBytes);
-                configured[dev][slot] = true;
-            }
+        // one instantiation per (scale layout, outputs asked for)
+        configure_gated_stream<kFn>();
+        auto launch = [&](auto kernel) {
             launch_chained(kernel, dim3(ctas), dim3(kNvThreads), kSiluTableBytes, stream, gate, other, row_stride, other_row_stride,
                            (uint32_t)tiles, per_warp, col_groups, G, (uint4 *)out_bf16, (uint32_t *)codes, scales,
                            (groups + 3u) / 4u, device_table);
         };
         const bool tiled = layout == AXIOM_SCALE_LAYOUT_TILED;
         if (codes && out_bf16) {
-            if (tiled) launch(gated_nvfp4_stream_kernel<kFn, true, true, true>, 0);
-            else launch(gated_nvfp4_stream_kernel<kFn, false, true, true>, 1);
+            if (tiled) launch(gated_nvfp4_stream_kernel<kFn, true, true, true>);
+            else launch(gated_nvfp4_stream_kernel<kFn, false, true, true>);
         } else if (codes) {
-            if (tiled) launch(gated_nvfp4_stream_kernel<kFn, true, false, true>, 2);
-            else launch(gated_nvfp4_stream_kernel<kFn, false, false, true>, 3);
+            if (tiled) launch(gated_nvfp4_stream_kernel<kFn, true, false, true>);
+            else launch(gated_nvfp4_stream_kernel<kFn, false, false, true>);
         } else {
-            launch(gated_nvfp4_stream_kernel<kFn, false, true, false>, 4);
+            launch(gated_nvfp4_stream_kernel<kFn, false, true, false>);
         }
         note_launch();
         return AXIOM_OK;
     }
     if (table) {
-        static bool configured[64] = {};
-        int dev = 0;
-        cudaGetDevice(&dev);
-        if (dev >= 0 && dev < 64 && !configured[dev]) {
-            cudaFuncSetAttribute(swiglu_nvfp4_kernel<true, kFn, kHeadGate>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSiluTableBytes);
-            configured[dev] = true;
-        }
+        allow_dynamic_smem<swiglu_nvfp4_kernel<true, kFn, kHeadGate>>(kSiluTableBytes);
         launch_chained(swiglu_nvfp4_kernel<true, kFn, kHeadGate>, dim3((uint32_t)blocks), dim3(kNvThreads), kSiluTableBytes, stream,
                        gate, other, row_stride, other_row_stride, head_keep, gate_head_chunks, rows, chunks, col_groups,
                        W / col_groups, W % col_groups, G, (uint4 *)out_bf16,
@@ -764,6 +784,21 @@ int launch_sigmoid_gate_heads_nvfp4_bf16(const void *attention, const void *q_ga
                                                       head_dim / 8u, rows, width, G, out_bf16, codes, scales, layout, stream);
 }
 
+// Everything a first launch would set up lazily, for axiom_b200_prepare(): both gate tables (one small kernel and one
+// stream synchronisation each) and the shared-memory limits of every table kernel.  False when a table could not
+// be filled (the kernels then keep filling a copy per CTA).
+bool prepare_gated_unit() {
+    const bool tables = device_gate_table<gate_fn::silu>(nullptr) != nullptr && device_gate_table<gate_fn::sigmoid>(nullptr) != nullptr;
+    configure_fp8_rows<row_op::swiglu_table, false>();
+    configure_fp8_rows<row_op::swiglu_table, true>();
+    configure_gated_stream<gate_fn::silu>();
+    configure_gated_stream<gate_fn::sigmoid>();
+    allow_dynamic_smem<swiglu_nvfp4_kernel<true, gate_fn::silu, false>>(kSiluTableBytes);
+    allow_dynamic_smem<swiglu_nvfp4_kernel<true, gate_fn::sigmoid, false>>(kSiluTableBytes);
+    allow_dynamic_smem<swiglu_nvfp4_kernel<true, gate_fn::sigmoid, true>>(kSiluTableBytes);
+    return tables;
+}
+
 }  // namespace axb
 
 using namespace axb;
@@ -791,6 +826,30 @@ extern "C" int axiom_qwen38_fused_fp8_quantize_bf16_device(
     int rc = select_device(device);
     if (rc != AXIOM_OK) return rc;
     rc = launch_fp8_quantize_bf16(input_bf16, rows, cols, out_codes, out_scales, status_word, (cudaStream_t)stream);
+    return rc != AXIOM_OK ? rc : launch_status();
+}
+
+extern "C" int axiom_qwen38_fused_fp8_quantize_static_bf16_device(
+        int device, const void *input_bf16, uint32_t rows, uint32_t cols, float scale, uint8_t *out_codes, void *stream) {
+    if (!input_bf16 || !out_codes || rows == 0u || cols == 0u || (cols % 8u) != 0u || cols > 36864u || !valid_scale(scale) ||
+        !aligned16(input_bf16) || (reinterpret_cast<uintptr_t>(out_codes) & 7u)) {
+        return AXIOM_ERR_INVALID_ARGUMENT;
+    }
+    int rc = select_device(device);
+    if (rc != AXIOM_OK) return rc;
+    rc = launch_fp8_quantize_static_bf16(input_bf16, rows, cols, scale, out_codes, (cudaStream_t)stream);
+    return rc != AXIOM_OK ? rc : launch_status();
+}
+
+extern "C" int axiom_qwen38_fused_swiglu_fp8_static_bf16_device(
+        int device, const void *gate_up_bf16, uint32_t rows, uint32_t width, float scale, uint8_t *out_codes, void *stream) {
+    if (!gate_up_bf16 || !out_codes || rows == 0u || width == 0u || (width % 8u) != 0u || width > 36864u ||
+        !valid_scale(scale) || !aligned16(gate_up_bf16) || (reinterpret_cast<uintptr_t>(out_codes) & 7u)) {
+        return AXIOM_ERR_INVALID_ARGUMENT;
+    }
+    int rc = select_device(device);
+    if (rc != AXIOM_OK) return rc;
+    rc = launch_swiglu_fp8_static_bf16(gate_up_bf16, rows, width, scale, out_codes, (cudaStream_t)stream);
     return rc != AXIOM_OK ? rc : launch_status();
 }
 

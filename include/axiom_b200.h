@@ -237,10 +237,54 @@ typedef struct {
 } axiom_top1_result;
 int axiom_qwen38_fused_top1_f32_device(int device, const float *logits, uint32_t rows, uint32_t vocab, axiom_top1_result *results, void *stream);
 
+/* The elementwise launches of ONE decoder layer, in the reference's order, as three calls that sit between the
+ * layer's contractions (src/axiom_qwen38_model.cu:1357-1401; verify-block twin :1854-2000):
+ *   post_mixer: residual += mixer_out; NVFP4(rmsnorm(residual) * post_norm_gamma) -> mlp_in_*      (:1371-1373 +
+ *               src/axiom_qwen38_nvfp4_mlp.cu:1347-1381)
+ *   mlp_mid:    NVFP4(silu(gate) * up) of gate_up -> mlp_mid_*                    (src/axiom_qwen38_nvfp4_mlp.cu:1531-1561)
+ *   post_mlp:   residual += mlp_out; tap_out = residual (optional, qwen38_capture_tap8_kernel :343-351);
+ *               next_norm_out = bf16(rmsnorm(residual) * next_norm_gamma): the next layer's input norm
+ *               (src/axiom_qwen38_gdn.cu:177-220, src/axiom_qwen38_attention.cu:318-340) or the final norm (:1418)
+ * Each call is one kernel, asynchronous on `stream` and capturable.  Members a call does not use may be NULL / 0. */
+typedef struct {
+    uint32_t abi_version;            /* AXIOM_ABI_VERSION */
+    uint32_t struct_size;            /* sizeof(axiom_layer_glue) */
+    uint32_t columns;                /* token columns; the reference's fixed batch is 8 */
+    uint32_t hidden;                 /* 5120 */
+    uint32_t ffn;                    /* 17408 */
+    uint32_t scale_layout;           /* layout of both block-scale planes */
+    float eps;
+    float gate_up_input_scale;       /* NVFP4 global multiplier of the gate_up projection's input */
+    float down_input_scale;          /* NVFP4 global multiplier of the down projection's input */
+    uint32_t reserved0;              /* 0 */
+    void *residual_bf16;             /* [columns][hidden] running hidden state, updated in place */
+    const void *mixer_out_bf16;      /* [columns][hidden] attention / DeltaNet mixer output */
+    const void *post_norm_gamma_bf16;/* [hidden] */
+    uint8_t *mlp_in_codes;           /* [columns][hidden/2] */
+    uint8_t *mlp_in_scales;
+    const void *gate_up_bf16;        /* [columns][2*ffn], gate first */
+    uint8_t *mlp_mid_codes;          /* [columns][ffn/2] */
+    uint8_t *mlp_mid_scales;
+    const void *mlp_out_bf16;        /* [columns][hidden] down projection output */
+    void *tap_out_bf16;              /* optional [columns][hidden] */
+    const void *next_norm_gamma_bf16;/* [hidden] */
+    void *next_norm_out_bf16;        /* [columns][hidden] */
+} axiom_layer_glue;
+int axiom_qwen38_fused_layer_post_mixer_device(int device, const axiom_layer_glue *glue, void *stream);
+int axiom_qwen38_fused_layer_mlp_mid_device(int device, const axiom_layer_glue *glue, void *stream);
+int axiom_qwen38_fused_layer_post_mlp_device(int device, const axiom_layer_glue *glue, void *stream);
+
 /* Replaces quantize_bf16_rows_e4m3_kernel (src/axiom_qwen38_mtp_compute.cu:239-278)
  * and, for BF16-valued input, quantize_columns_e4m3_kernel.  status_word
  * (optional, device) receives AXIOM_STATUS_WORD_NONFINITE via compare-and-swap. cols % 8 == 0. */
 int axiom_qwen38_fused_fp8_quantize_bf16_device(int device, const void *input_bf16, uint32_t rows, uint32_t cols, uint8_t *out_codes, float *out_scales, uint32_t *status_word, void *stream);
+
+/* Given-scale flavours of the two E4M3 quantizers: code = e4m3_satfinite(x / scale) with the scale an argument.
+ * Replace quantize_columns_static_e4m3_kernel (src/axiom_qwen38_fp8.cu:96-107, the ModelOpt branch of
+ * quantize_input, :830-840) for a BF16 tensor and for silu(gate)*up of a fused [gate | up] row.  One pass, no
+ * per-token scale output.  scale finite and > 0; cols (width) % 8 == 0. */
+int axiom_qwen38_fused_fp8_quantize_static_bf16_device(int device, const void *input_bf16, uint32_t rows, uint32_t cols, float scale, uint8_t *out_codes, void *stream);
+int axiom_qwen38_fused_swiglu_fp8_static_bf16_device(int device, const void *gate_up_bf16, uint32_t rows, uint32_t width, float scale, uint8_t *out_codes, void *stream);
 
 /* Replaces qwen38_embedding_gather_columns_kernel (src/axiom_qwen38_model.cu:321-341):
  * id >= vocab gives a zero row and AXIOM_STATUS_WORD_BAD_ADDRESS.  hidden % 8 == 0. */
@@ -398,6 +442,16 @@ uint64_t axiom_nvfp4_scale_plane_offset(uint32_t row, uint32_t group, uint32_t g
 uint64_t axiom_b200_static_scratch_bytes(void);
 int axiom_b200_nvfp4_quantize_bf16_host_static(int device, const void *input_bf16_host, uint32_t rows, uint32_t cols, float global_scale, uint32_t scale_layout, uint8_t *out_codes_host, uint8_t *out_scales_host, void *stream);
 
+/* Optional one-time set-up of `device`.  The stream-explicit entries set a few things up lazily on their first
+ * use: the two gate tables of the SwiGLU / sigmoid-gate kernels (one small fill kernel each AND a synchronisation of
+ * the caller's stream, skipped while that stream is capturing), the dynamic shared-memory limits of the pipelined
+ * kernels, and the driver's tensor-map encoder.  This call does all of that at once and synchronises the device;
+ * after it has returned AXIOM_OK, no stream-explicit entry on that device launches anything but its own kernel or
+ * synchronises anything, whichever comes first — so a first call may sit inside a stream capture.  Call it once
+ * per device at start-up (the reference's objects do the equivalent in their create functions,
+ * include/axiom/qwen38_nvfp4_mlp.h:111-117: "allocation-free and asynchronous" forward calls). */
+int axiom_b200_prepare(int device);
+
 /* Number of kernel launches issued by this library in this process (bench bookkeeping). */
 uint64_t axiom_b200_kernel_launch_count(void);
 
@@ -406,6 +460,13 @@ uint64_t axiom_b200_kernel_launch_count(void);
  * synchronises `device`, returns the OR of those words (0 = no fault) and
  * clears them. */
 uint32_t axiom_b200_pipeline_faults(int device);
+
+/* TEST HOOK, not for production use.  Arms the NEXT launch of the streaming add + RMSNorm kernel (296 rows and
+ * more) so that the first row of its first team announces `extra_bytes` more than its copies deliver: that team's
+ * barrier never completes, its bounded wait gives up after `spin_limit` polls (0 = the default 2^18), the team
+ * writes none of its rows and the kernel returns normally with axiom_b200_pipeline_faults() != 0.  Nothing
+ * faults, traps or hangs; every other team's rows are complete.  extra_bytes % 16 == 0. */
+int axiom_b200_test_arm_wait_timeout(uint32_t extra_bytes, uint32_t spin_limit);
 
 #ifdef __cplusplus
 }

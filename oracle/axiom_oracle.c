@@ -247,6 +247,15 @@ int axo_fp8_quantize_f32(const float *input, uint32_t rows, uint32_t cols,
     return AXO_OK;
 }
 
+/* Static-scale flavour quantize_columns_static_e4m3_kernel (src/axiom_qwen38_fp8.cu:96-107; the ModelOpt
+ * branch of quantize_input, :830-840): code = e4m3_satfinite(x / scale) with a scale given by the caller. */
+int axo_fp8_quantize_static_f32(const float *input, uint64_t count, float scale, uint8_t *codes) {
+    if (!input || !codes) return AXO_INVALID;
+    AXO_PARALLEL_FOR
+    for (int64_t i = 0; i < (int64_t)count; ++i) codes[i] = axo_e4m3_encode_satfinite(input[i] / scale);
+    return AXO_OK;
+}
+
 /* BF16-input twin quantize_bf16_rows_e4m3_kernel
  * (src/axiom_qwen38_mtp_compute.cu:239-278): non-finite inputs are skipped by
  * the max and raise the status word (4 = runtime error). */

@@ -129,6 +129,9 @@ int axo_qk_norm_rope_round_after_norm_bf16(uint16_t *x, const uint16_t *gamma, c
 /* host rotary table of that convention (src/axiom_qwen38_dspark_compute.cu:1459-1513) */
 int axo_rope_table_host(const float *inv_freq, uint32_t head_dim, float mscale, uint32_t positions, float *out);
 
+/* static-scale E4M3 quantizer (src/axiom_qwen38_fp8.cu:96-107) */
+int axo_fp8_quantize_static_f32(const float *input, uint64_t count, float scale, uint8_t *codes);
+
 /* y = bf16(attention * sigmoid(gate)), optional BF16 copy, optional NVFP4 quantize of y */
 int axo_sigmoid_gate_nvfp4_bf16(const uint16_t *attention, const uint16_t *gate, uint32_t rows,
                                 uint32_t width, float global_scale, uint16_t *out_bf16,

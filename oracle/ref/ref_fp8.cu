@@ -21,3 +21,13 @@ extern "C" int ref_fp8_group_row_scale_bf16_epilogue(float *out, const uint16_t 
 extern "C" void ref_enqueue_quantize_columns_e4m3(const float *input, uint8_t *codes, float *scales, uint32_t cols, uint32_t n) {
     quantize_columns_e4m3_kernel<<<n, kThreads>>>(input, codes, scales, cols);
 }
+
+// Static-scale flavour (the ModelOpt branch of quantize_input): input F32 [columns][cols], 8 columns per launch.
+extern "C" int ref_quantize_columns_static_e4m3(const float *input, uint8_t *codes, float scale, uint32_t cols, uint32_t columns) {
+    for (uint32_t c0 = 0; c0 < columns; c0 += AXIOM_QWEN38_FP8_BATCH) {
+        const uint32_t n = columns - c0 < AXIOM_QWEN38_FP8_BATCH ? columns - c0 : AXIOM_QWEN38_FP8_BATCH;
+        quantize_columns_static_e4m3_kernel<<<dim3((cols + kThreads - 1u) / kThreads, n), kThreads>>>(
+                input + (size_t)c0 * cols, codes + (size_t)c0 * cols, scale, cols);
+    }
+    return cudaDeviceSynchronize() == cudaSuccess && cudaGetLastError() == cudaSuccess ? 0 : 3;
+}

@@ -149,6 +149,13 @@ def fp8_quantize_f32(x: np.ndarray):
     return codes, scales
 
 
+def fp8_quantize_static_f32(x: np.ndarray, scale: float) -> np.ndarray:
+    x = np.ascontiguousarray(x, np.float32)
+    codes = np.empty(x.shape, np.uint8)
+    _ok(o().axo_fp8_quantize_static_f32(_p(x), x.size, C.c_float(scale), _p(codes)), "fp8_quantize_static_f32")
+    return codes
+
+
 def fp8_quantize_bf16(x_bits: np.ndarray):
     rows, cols = x_bits.shape
     codes = np.empty((rows, cols), np.uint8)

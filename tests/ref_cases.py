@@ -178,3 +178,10 @@ def draft_qk_norm_rope(x_bits: np.ndarray, gamma_bits: np.ndarray, rope_table: n
     ok(ref_lib.lib().ref_dspark_qk_norm_rope_round(w.data_ptr(), x.data_ptr(), table.data_ptr(), table.shape[0], heads, tokens,
                                                    first_position), "dspark qk_norm_rope + round")
     return bits_of(x)
+
+
+def fp8_quantize_static_f32(x: torch.Tensor, scale: float):
+    rows, cols = x.shape
+    codes = torch.zeros((rows, cols), dtype=torch.uint8, device="cuda")
+    ok(ref_lib.lib().ref_quantize_columns_static_e4m3(x.data_ptr(), codes.data_ptr(), scale, cols, rows), "quantize_columns_static_e4m3")
+    return codes.cpu().numpy()

@@ -14,6 +14,7 @@ SIGNATURES = {
     "ref_silu_mul_quantize_batch_to_tc": [vp, f32, vp, vp, u32, u32, i32],
     "ref_silu_mul_batch": [vp, vp, vp, u32],
     "ref_quantize_columns_e4m3": [vp, vp, vp, u32, u32],
+    "ref_quantize_columns_static_e4m3": [vp, vp, f32, u32, u32],
     "ref_quantize_bf16_rows_e4m3": [vp, vp, vp, u32, u32, vp],
     "ref_add_bf16_inplace": [vp, vp, u64],
     "ref_add_bf16_rmsnorm8": [vp, vp, vp, vp, u32],

@@ -124,6 +124,51 @@ def test_no_bounded_wait_ran_out(axk, cuda_device):
     assert axk.lib().axiom_b200_pipeline_faults(0) == 0
 
 
+def test_a_wait_that_runs_out_skips_its_rows_and_raises_the_fault_word(axk, cuda_device):
+    """The give-up path of the bounded waits, exercised without faulting anything: the test hook makes the first
+    row of one team announce 16 bytes more than its copies deliver, so that team's barrier never completes and its
+    wait runs out after 2000 polls.  The kernel must return, the fault word must be raised, the rows of that team
+    must keep their old contents (nothing is computed from a slot that was never declared complete), every other
+    row must be what an undisturbed launch produces — and the next launch must be clean."""
+    import torch
+    from gpu_util import dev, host, sync
+
+    rows, cols, G = 5000, 5120, 80.0
+    hidden, residual, gamma = wl.add_rmsnorm_inputs_np(rows, cols)
+    lib = axk.lib()
+
+    def launch(arm):
+        h, r, g = dev(hidden), dev(residual), dev(gamma)
+        codes = torch.full((rows, cols // 2), 0xEE, dtype=torch.uint8, device="cuda")
+        scales = torch.full((rows, cols // 16), 0xEE, dtype=torch.uint8, device="cuda")
+        if arm:
+            assert lib.axiom_b200_test_arm_wait_timeout(16, 2000) == axk.AXIOM_OK
+        assert axk.add_rmsnorm_nvfp4(0, h, r, g, wl.EPS, rows, cols, G, None, codes, scales, 0) == axk.AXIOM_OK
+        sync()
+        return host(r, np.uint16).reshape(rows, cols), host(codes, np.uint8).reshape(rows, -1), host(scales, np.uint8).reshape(rows, -1)
+
+    assert lib.axiom_b200_pipeline_faults(0) == 0
+    want_res, want_codes, want_scales = launch(arm=False)
+    assert lib.axiom_b200_pipeline_faults(0) == 0
+    got_res, got_codes, got_scales = launch(arm=True)
+    assert lib.axiom_b200_pipeline_faults(0) != 0          # raised ...
+    assert lib.axiom_b200_pipeline_faults(0) == 0          # ... and cleared by the read
+    skipped = np.flatnonzero((got_codes == 0xEE).all(axis=1))
+    assert 0 in skipped and 1 <= skipped.size <= 8 and np.all(skipped % 148 == 0)   # rows of CTA 0 only, row 0 among them
+    assert np.array_equal(got_res[skipped], residual[skipped])                       # untouched: residual not merged,
+    assert (got_scales[skipped] == 0xEE).all()                                       # nothing quantized
+    done = np.setdiff1d(np.arange(rows), skipped)
+    assert np.array_equal(got_res[done], want_res[done]) and np.array_equal(got_codes[done], want_codes[done])
+    assert np.array_equal(got_scales[done], want_scales[done])
+    # the hook is one-shot: the next launch is undisturbed
+    again = launch(arm=False)
+    assert lib.axiom_b200_pipeline_faults(0) == 0
+    for a, b in zip(again, (want_res, want_codes, want_scales)):
+        assert np.array_equal(a, b)
+    inv = axk.AXIOM_ERR_INVALID_ARGUMENT
+    assert lib.axiom_b200_test_arm_wait_timeout(8, 100) == inv
+
+
 def test_residual_add_over_all_exponents(axk, cuda_device):
     """Random finite BF16 bit patterns (every exponent, both signs, denormals): the merged residual is
     bf16(f32(a) + f32(b)) bit for bit, in the pipelined kernel (packed BF16 add) and in the CTA kernel."""

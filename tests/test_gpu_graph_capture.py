@@ -106,3 +106,46 @@ def test_layer_stages_replay_from_a_graph(axk, cuda_device, m):
             assert np.array_equal(got[name], want[name]), name
     assert int(out["status"].item()) == 0
     assert axk.lib().axiom_b200_pipeline_faults(0) == 0
+
+
+PREPARE_PROBE = r"""
+import importlib, sys, torch
+sys.path.insert(0, {root!r})
+axk = importlib.import_module("axiom-kernel_b200")
+lib = axk.lib()
+torch.cuda.set_device(0)
+rows, width = 320, 1024
+a = torch.randn((rows, width), device="cuda").to(torch.bfloat16)
+g = torch.randn((rows, width), device="cuda").to(torch.bfloat16)
+gu = torch.randn((rows, 2 * width), device="cuda").to(torch.bfloat16)
+codes = torch.empty((rows, width // 2), dtype=torch.uint8, device="cuda")
+scales = torch.empty((rows, width // 16), dtype=torch.uint8, device="cuda")
+c8 = torch.empty((rows, width), dtype=torch.uint8, device="cuda")
+s8 = torch.empty(rows, dtype=torch.float32, device="cuda")
+torch.cuda.synchronize()
+if {prepare}:
+    assert lib.axiom_b200_prepare(0) == 0
+before = int(lib.axiom_b200_kernel_launch_count())
+assert axk.sigmoid_gate_nvfp4(0, a, g, rows, width, 50.0, None, codes, scales, 0) == 0
+assert axk.swiglu_fp8(0, gu, rows, width, c8, s8) == 0
+torch.cuda.synchronize()
+print(int(lib.axiom_b200_kernel_launch_count()) - before)
+"""
+
+
+def test_prepare_takes_the_lazy_set_up_out_of_the_first_calls(axk, cuda_device):
+    """In a fresh process the first sigmoid-gate and SwiGLU calls that use the gate tables each launch a fill kernel
+    (and synchronise their stream) before their own kernel; after axiom_b200_prepare they launch their own kernel only."""
+    import subprocess
+    import sys
+    from pathlib import Path
+
+    root = str(Path(__file__).resolve().parent.parent)
+    counts = {}
+    for prepare in (False, True):
+        res = subprocess.run([sys.executable, "-c", PREPARE_PROBE.format(root=root, prepare=prepare)], capture_output=True,
+                             text=True, timeout=300)
+        assert res.returncode == 0, res.stderr[-2000:]
+        counts[prepare] = int(res.stdout.strip().splitlines()[-1])
+    assert counts[True] == 2       # the two kernels themselves
+    assert counts[False] == 4      # plus one table fill each

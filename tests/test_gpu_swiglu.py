@@ -96,6 +96,43 @@ def test_plain_fp8_quantizer_bit_exact(axk, cuda_device):
         assert codes.guards_intact() and scales.guards_intact()
 
 
+@pytest.mark.parametrize("rows,cols,scale", [(1, 8, 1.0), (5, 5120, 0.0123), (300, 1024, 3.0e-3), (7, 36864, 2.5), (64, 264, 1.0e-30)])
+def test_static_scale_fp8_quantizer_bit_exact(axk, cuda_device, rows, cols, scale):
+    """Given-scale E4M3 quantizer (no transcendental): bit-exact with the oracle, specials included."""
+    from gpu_util import Guarded, dev, sync
+
+    x = wl.quantize_input_np(rows, cols, seed=cols + rows)
+    flat = x.reshape(-1)
+    flat[:12] = wl.to_bf16_bits(np.array([0.0, -0.0, 448.0 * scale, -448.0 * scale, 1e30, -1e30, np.inf, -np.inf, np.nan,
+                                           464.0 * scale, 1e-38, 3.0e38], np.float32))[: min(12, flat.size)]
+    codes = Guarded(rows * cols)
+    assert axk.fp8_quantize_static(0, dev(x), rows, cols, scale, codes.ptr) == axk.AXIOM_OK
+    sync()
+    assert codes.guards_intact()
+    want = ol.fp8_quantize_static_f32(wl.from_bf16_bits(x), scale)
+    assert np.array_equal(codes.payload().reshape(rows, cols), want)
+    inv = axk.AXIOM_ERR_INVALID_ARGUMENT
+    assert axk.fp8_quantize_static(0, dev(x), rows, cols, 0.0, codes.ptr) == inv
+    assert axk.fp8_quantize_static(0, dev(x), rows, cols, float("nan"), codes.ptr) == inv
+
+
+@pytest.mark.parametrize("rows,width,scale", [(3, 64, 0.01), (40, 17408, 0.02), (600, 2048, 0.004)])
+def test_static_scale_swiglu_fp8(axk, cuda_device, rows, width, scale):
+    """SwiGLU with a given scale: every code is a correct rounding of the FP64 y / scale, and almost all equal the
+    oracle's (device expf vs the C library's)."""
+    from gpu_util import Guarded, dev, sync
+
+    gu = wl.swiglu_input_np(rows, width, seed=rows)
+    codes = Guarded(rows * width)
+    assert axk.swiglu_fp8_static(0, dev(gu), rows, width, scale, codes.ptr) == axk.AXIOM_OK
+    sync()
+    assert codes.guards_intact()
+    got = codes.payload().reshape(rows, width)
+    want = ol.fp8_quantize_static_f32(ol.swiglu_f32(gu), scale)
+    assert np.mean(got != want) < 2e-3
+    assert fp8_codes_are_correct_roundings(gu, got, np.full(rows, scale, np.float32))
+
+
 @pytest.mark.parametrize("rows,width,layout", [(1, 17408, 0), (8, 17408, 1), (3, 16, 0), (70, 1024, 1), (256, 17408, 0),
                                                 (300, 1024, 1), (1000, 17408, 0), (333, 4096 + 256, 1), (297, 512 + 16, 0)])
 def test_swiglu_nvfp4(axk, cuda_device, rows, width, layout):

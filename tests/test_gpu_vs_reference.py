@@ -131,6 +131,26 @@ def test_fp8_quantizers_bit_exact(axk, cuda_device):
         assert int(status.item()) == twin_status == 4
 
 
+def test_static_scale_fp8_bit_exact(axk, cuda_device):
+    """Given-scale flavours against quantize_columns_static_e4m3_kernel: a BF16 tensor, and silu(gate)*up through the
+    reference's silu_mul_batch_kernel followed by that quantizer."""
+    import torch
+    import ref_cases as rc
+    from gpu_util import dev, sync
+
+    for rows, cols, scale in [(8, 5120, 0.011), (24, 17408, 0.5), (3, 64, 1.0e-3), (320, 1024, 0.02)]:
+        bits = wl.quantize_input_np(rows, cols, seed=cols)
+        bits[0, :4] = [0x7F80, 0xFF80, 0x7FC0, 0x8000]
+        codes = torch.zeros((rows, cols), dtype=torch.uint8, device="cuda")
+        assert axk.fp8_quantize_static(0, dev(bits), rows, cols, scale, codes) == 0
+        sync()
+        assert np.array_equal(codes.cpu().numpy(), rc.fp8_quantize_static_f32(rc.f32_dev(bits), scale))
+        gu = wl.swiglu_input_np(rows, cols, seed=rows)
+        assert axk.swiglu_fp8_static(0, dev(gu), rows, cols, scale, codes) == 0
+        sync()
+        assert np.array_equal(codes.cpu().numpy(), rc.fp8_quantize_static_f32(rc.swiglu_f32(gu), scale))
+
+
 @pytest.mark.parametrize("rows,width", [(8, 17408), (40, 4096), (3, 64), (16, 11008), (320, 1024), (304, 17408)])
 def test_swiglu_fp8_and_nvfp4_bit_exact(axk, cuda_device, rows, width):
     import torch
