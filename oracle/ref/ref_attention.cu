@@ -45,3 +45,9 @@ extern "C" int ref_sigmoid_gate8(const float *attention, const float *gate, floa
     qwen38_sigmoid_gate_kernel<<<static_cast<uint32_t>((count + kThreads - 1u) / kThreads), kThreads>>>(attention, gate, out);
     return ref_done();
 }
+
+// the attention block's input norm: weight F32 [kHidden], input / out F32 [8][kHidden] (kHidden = 5120)
+extern "C" int ref_attention_rmsnorm8(const float *weight, const float *input, float *out) {
+    qwen38_attention_rmsnorm8_kernel<<<kBatch, kThreads>>>(weight, input, out);
+    return ref_done();
+}

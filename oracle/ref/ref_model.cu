@@ -55,3 +55,10 @@ extern "C" int ref_top1_8(const float *logits, void *partials, void *results, in
 extern "C" void ref_enqueue_add_bf16_rmsnorm8(float *residual, const float *addend, const float *weight, float *norm) {
     qwen38_add_bf16_rmsnorm8_kernel<<<kBatch, kThreads>>>(residual, addend, weight, norm);
 }
+
+// taps: F32 [tap_count][8][5120]; copies the 8 hidden columns into slot tap_index (qwen38_capture_tap8_kernel)
+extern "C" int ref_capture_tap8(const float *hidden, float *taps, uint32_t tap_index) {
+    const uint64_t count = (uint64_t)kHidden * kBatch;
+    qwen38_capture_tap8_kernel<<<(uint32_t)((count + kThreads - 1u) / kThreads), kThreads>>>(hidden, taps, tap_index);
+    return ref_done();
+}

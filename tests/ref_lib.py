@@ -24,6 +24,8 @@ SIGNATURES = {
     "ref_qk_norm_partial_rope_cache_temporal8": [vp, vp, vp, vp, vp, vp, vp, vp, vp, u32, u32, i32],
     "ref_qk_norm_partial_rope_cache8": [vp, vp, vp, vp, vp, vp, vp, vp, vp, u32, u32, u32, i32],
     "ref_sigmoid_gate8": [vp, vp, vp],
+    "ref_attention_rmsnorm8": [vp, vp, vp],
+    "ref_capture_tap8": [vp, vp, u32],
     "ref_dspark_qk_norm_rope_round": [vp, vp, vp, u32, u32, u32, u32],
     "ref_fp8_group_row_scale_bf16_epilogue": [vp, vp, vp, u32],
     "ref_top1_8": [vp, vp, vp, i32],
