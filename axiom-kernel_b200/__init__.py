@@ -165,6 +165,11 @@ SIGNATURES = {
     "axiom_b200_nvfp4_quantize_bf16_host_static": (i32, [C.c_int, vp, u32, u32, f32, u32, vp, vp, vp]),
     "axiom_b200_pipeline_faults": (u32, [i32]),
     "axiom_b200_prepare": (i32, [i32]),
+    # include/axiom_b200_engine.h (typed structures: axiom-kernel_b200/engine.py)
+    "axiom_b200_step_provider_create": (i32, [vp, vp, C.POINTER(vp)]),
+    "axiom_b200_step_provider_destroy": (None, [vp]),
+    "axiom_b200_step_provider_forward_step": (i32, [vp, vp, i32, vp]),
+    "axiom_b200_step_provider_scratch": (vp, [vp, u32]),
     "axiom_qwen38_fused_layer_post_mixer_device": (i32, [i32, C.POINTER(LayerGlue), vp]),
     "axiom_qwen38_fused_layer_mlp_mid_device": (i32, [i32, C.POINTER(LayerGlue), vp]),
     "axiom_qwen38_fused_layer_post_mlp_device": (i32, [i32, C.POINTER(LayerGlue), vp]),

@@ -60,6 +60,10 @@ int launch_add_rmsnorm_nvfp4_bf16(const void *hidden, void *residual, const void
 int launch_add_rmsnorm_tap_nvfp4_bf16(const void *hidden, void *residual, const void *gamma, float eps, uint32_t rows,
                                       uint32_t cols, float G, void *norm_out, uint8_t *codes, uint8_t *scales,
                                       uint32_t layout, void *tap, cudaStream_t stream);
+int launch_gather_add_rmsnorm_nvfp4_bf16(const void *table, uint32_t vocab, const uint32_t *token_ids, void *residual,
+                                         const void *gamma, float eps, uint32_t rows, uint32_t cols, float G,
+                                         void *norm_out, uint8_t *codes, uint8_t *scales, uint32_t layout,
+                                         uint32_t *status_word, cudaStream_t stream);
 int launch_swiglu_fp8_bf16(const void *gate_up, uint32_t rows, uint32_t width, uint8_t *codes, float *scales,
                            cudaStream_t stream);
 int launch_swiglu_nvfp4_bf16(const void *gate_up, uint32_t rows, uint32_t width, float G, uint8_t *codes,

@@ -6,11 +6,11 @@ import re
 from pathlib import Path
 
 ROOT = Path(__file__).resolve().parent.parent
-HEADER = ROOT / "include" / "axiom_b200.h"
+HEADERS = [ROOT / "include" / "axiom_b200.h", ROOT / "include" / "axiom_b200_engine.h"]
 
 
 def declared_functions():
-    text = re.sub(r"/\*.*?\*/", "", HEADER.read_text(), flags=re.S)
+    text = re.sub(r"/\*.*?\*/", "", "\n".join(h.read_text() for h in HEADERS), flags=re.S)
     text = re.sub(r"//[^\n]*", "", text)
     names = re.findall(r"\b(axiom_[a-z0-9_]+)\s*\(", text)
     return sorted(set(names))

@@ -13,6 +13,7 @@ PROGRAM = r"""
 #include <stdio.h>
 #include <string.h>
 #include "axiom_b200.h"
+#include "axiom_b200_engine.h"
 
 int main(void) {
     axiom_abi_info info;
@@ -32,6 +33,13 @@ int main(void) {
     /* argument checks come before any device work */
     if (axiom_qwen38_fused_qk_norm_rope_paged_bf16_device(0, &args, NULL) != AXIOM_ERR_INVALID_ARGUMENT) return 6;
     if (axiom_qwen38_fused_swiglu_fp8_bf16_device(0, NULL, 1u, 8u, NULL, NULL, NULL) != AXIOM_ERR_INVALID_ARGUMENT) return 7;
+    {
+        axiom_engine_seq seq;
+        axiom_b200_step_provider *provider = NULL;
+        memset(&seq, 0, sizeof seq);
+        if (axiom_b200_step_provider_create(NULL, NULL, &provider) != AXIOM_ERR_INVALID_ARGUMENT || provider != NULL) return 8;
+        if (axiom_b200_step_provider_forward_step(NULL, NULL, 0, NULL) != AXIOM_ERR_INVALID_ARGUMENT) return 9;
+    }
     printf("%s\n", axiom_version());
     return 0;
 }
