@@ -352,7 +352,7 @@ template <int kAddend>
 __global__ void __launch_bounds__(1024, 1)
 add_rmsnorm_wide_row_kernel(const norm_args a) {
     constexpr bool kAdd = kAddend != kNone;
-    extern __shared__ __align__(16) uint8_t smem[];
+    extern __shared__ __align__(128) uint8_t smem[];
     uint4 *merged_sh = reinterpret_cast<uint4 *>(smem);  // [chunks_per_row]
     __shared__ scale_lut_entry lut[128];
     __shared__ __align__(16) float partials[256];
@@ -360,6 +360,8 @@ add_rmsnorm_wide_row_kernel(const norm_args a) {
     const uint32_t tid = threadIdx.x, lane = tid & 31u;
     const uint4 *gamma16 = reinterpret_cast<const uint4 *>(a.gamma);
     allow_dependents();
+    // the divisor table depends on a scalar argument only: it is built while the previous kernel on the stream drains
+    const bool lut_safe = build_scale_lut(lut, a.codes ? a.G : 1.0f);
     dependency_wait();
 
     for (uint32_t row = blockIdx.x; row < a.rows; row += gridDim.x) {
@@ -410,7 +412,7 @@ add_rmsnorm_wide_row_kernel(const norm_args a) {
                 merged_sh[q] = m[c];
             }
         }
-        const bool lut_safe = build_scale_lut(lut, a.codes ? a.G : 1.0f);  // CTA barrier inside: merged_sh is complete
+        __syncthreads();  // merged_sh is complete
 
         // partial sums 2t, 2t+1: features 256k + 2t, 2t+1 in k order (the reference's chains)
         if (tid < 128u) {
@@ -482,6 +484,11 @@ add_rmsnorm_wide_row_kernel(const norm_args a) {
 }
 
 constexpr size_t kSmemBudget = 227u * 1024u;
+// Below this many rows the one-CTA-per-row kernel is used (measured crossover with the streaming kernel).
+#ifndef AXB_WIDE_ROW_BELOW_ROWS
+#define AXB_WIDE_ROW_BELOW_ROWS (2u * 148u)
+#endif
+constexpr uint32_t kWideRowBelowRows = AXB_WIDE_ROW_BELOW_ROWS;
 
 size_t stream_fixed_bytes(uint32_t cols, uint32_t teams, int addend = kBf16) {
     return (size_t)cols * sizeof(float) * (addend == kScaledF32 ? 2u : 1u) + 128u * sizeof(scale_lut_entry) +
@@ -527,7 +534,7 @@ int launch_norm(norm_args &a, int addend, cudaStream_t stream) {
         if (spt > kMaxSlotsPerTeam) spt = kMaxSlotsPerTeam;
     }
     // Few rows (latency matters more than streaming), or rows too wide for one slot: one wide CTA per row.
-    if (rows < 2u * kSmCount || teams == 0u || spt == 0u) {
+    if (rows < kWideRowBelowRows || teams == 0u || spt == 0u) {
         uint32_t threads = (a.chunks_per_row + 31u) & ~31u;
         if (threads > 1024u) threads = 1024u;
         if (threads < 128u) threads = 128u;  // the 256 partial sums are produced by the first 128 threads
