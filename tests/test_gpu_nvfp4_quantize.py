@@ -44,6 +44,29 @@ def test_matches_oracle_bit_exact(axk, cuda_device, rows, cols, layout):
         assert np.array_equal(scales, ol.scales_to_tiled(want_scales))
 
 
+@pytest.mark.parametrize("rows,cols,layout", [(129, 5120, 0), (300, 1072, 1), (5, 48, 0)])
+def test_code_buffer_aligned_to_four_bytes_only(axk, cuda_device, rows, cols, layout):
+    """The block-per-lane kernel stores 8-byte code words; a code buffer that is only 4-byte aligned takes the
+    chunk-per-lane kernel instead.  Same bytes."""
+    import torch
+    from gpu_util import dev, sync
+
+    x = wl.quantize_input_np(rows, cols, seed=rows + cols)
+    G = wl.nvfp4_global_scale(float(np.abs(wl.from_bf16_bits(x)).max()))
+    backing = torch.full((rows * cols // 2 + 64,), 0xFF, dtype=torch.uint8, device="cuda")
+    nscale = int(axk.lib().axiom_nvfp4_scale_plane_bytes(rows, cols // 16, layout))
+    scales = torch.zeros(nscale, dtype=torch.uint8, device="cuda")
+    assert axk.nvfp4_quantize(0, dev(x), rows, cols, G, backing.data_ptr() + 4, scales, layout) == axk.AXIOM_OK
+    sync()
+    raw = backing.cpu().numpy()
+    want_codes, want_scales = ol.nvfp4_quantize_bf16(x, G)
+    assert np.array_equal(raw[4:4 + rows * cols // 2].reshape(rows, cols // 2), want_codes)
+    assert (raw[:4] == 0xFF).all() and (raw[4 + rows * cols // 2:] == 0xFF).all()
+    want_plane = want_scales.reshape(-1) if layout == 0 else ol.scales_to_tiled(want_scales)
+    assert np.array_equal(scales.cpu().numpy(), want_plane)
+    assert axk.nvfp4_quantize(0, dev(x), rows, cols, G, backing.data_ptr() + 2, scales, layout) == axk.AXIOM_ERR_INVALID_ARGUMENT
+
+
 @pytest.mark.parametrize("G", [1.0, 0.37, 123.456, 2688.0 / 7.3, 3.3e4, 1e-3])
 def test_global_scale_sweep(axk, cuda_device, G):
     x = wl.quantize_input_np(64, 2048, seed=11)
