@@ -135,6 +135,13 @@ constexpr uint32_t kMaxSlotsPerTeam = 4u;
 __device__ __forceinline__ void team_barrier(uint32_t team) {
     asm volatile("bar.sync %0, %1;" ::"r"(team + 1u), "r"(kTeamThreads) : "memory");
 }
+// The same barrier carrying a vote: true in every thread of the team when any of them passed true.
+__device__ __forceinline__ bool team_barrier_any(uint32_t team, bool flag) {
+    uint32_t any;
+    asm volatile("{\n\t.reg .pred in, out;\n\tsetp.ne.u32 in, %3, 0;\n\tbar.red.or.pred out, %1, %2, in;\n\tselp.u32 %0, 1, 0, out;\n\t}"
+                 : "=r"(any) : "r"(team + 1u), "r"(kTeamThreads), "r"((uint32_t)flag) : "memory");
+    return any != 0u;
+}
 
 // Shared memory: [teams x slots x slot_bytes][gamma F32, two planes][scale table][partials teams x 256][barriers]
 template <int kAddend, bool kFull>
@@ -152,7 +159,6 @@ add_rmsnorm_stream_kernel(const norm_args a) {
     scale_lut_entry *lut = reinterpret_cast<scale_lut_entry *>(wscale_sh + (kAddend == kScaledF32 ? a.cols : 0u));
     float *partials = reinterpret_cast<float *>(lut + 128);                      // [teams][256]
     uint64_t *bars = reinterpret_cast<uint64_t *>(partials + teams * 256u);      // [teams][kMaxSlotsPerTeam]
-    volatile uint32_t *team_fault = reinterpret_cast<volatile uint32_t *>(bars + teams * kMaxSlotsPerTeam);  // [teams]
 
     const uint32_t tid = threadIdx.x, team = tid / kTeamThreads, t = tid % kTeamThreads, lane = tid & 31u;
     const uint32_t warp_in_team = t >> 5;
@@ -163,7 +169,6 @@ add_rmsnorm_stream_kernel(const norm_args a) {
     if (t == 0u) {
         for (uint32_t j = 0; j < spt; ++j) mbar_init(my_bars + j, 1u);
         mbar_init_fence();
-        team_fault[team] = 0u;
     }
     team_barrier(team);
     dependency_wait();
@@ -237,12 +242,11 @@ add_rmsnorm_stream_kernel(const norm_args a) {
         // the id of the row whose addend is requested after sweep 1 (fetched now: its latency hides behind the sweep)
         uint32_t next_token = 0u;
         if (t == 0u && i + spt < my_rows) next_token = token_of_row(i + spt);
-        // A wait that ran out raises the device's fault word and the team's flag.  The flag is read by the whole
-        // team behind the barrier that follows sweep 1 (which only touches shared memory), so the team decides as
-        // one: it writes nothing for this row or any later one, waits — bounded again — for the copies it still
-        // has in flight, and leaves.  Its rows keep their old contents; the caller learns of it from
-        // axiom_b200_pipeline_faults().
-        if (!mbar_wait(my_bars + j, (i / spt) & 1u, spin_limit)) team_fault[team] = 1u;
+        // A wait that ran out raises the device's fault word.  The barrier that follows sweep 1 (which only touches
+        // shared memory) carries the threads' verdicts as a vote, so the team decides as one: it writes nothing for
+        // this row or any later one, waits — bounded again — for the copies it still has in flight, and leaves.
+        // Its rows keep their old contents; the caller learns of it from axiom_b200_pipeline_faults().
+        const bool gave_up = !mbar_wait(my_bars + j, (i / spt) & 1u, spin_limit);
         const uint32_t row = blockIdx.x + (team + teams * i) * gridDim.x;
         const uint64_t base = (uint64_t)row * a.chunks_per_row;
         uint8_t *slot = my_slots + (size_t)j * slot_bytes;
@@ -275,8 +279,7 @@ add_rmsnorm_stream_kernel(const norm_args a) {
         }
         reinterpret_cast<float2 *>(my_partials)[t] = p;
         if (stores) fence_async_shared();
-        team_barrier(team);
-        if (team_fault[team] != 0u) {
+        if (team_barrier_any(team, gave_up)) {
             // rows i+1 .. i+spt-1 were requested in full; nothing later was (the addend of row i+spt is requested below)
             for (uint32_t n = i + 1u; n < i + spt && n < my_rows; ++n) (void)mbar_wait(my_bars + n % spt, (n / spt) & 1u, spin_limit);
             break;
@@ -492,8 +495,7 @@ constexpr uint32_t kWideRowBelowRows = AXB_WIDE_ROW_BELOW_ROWS;
 
 size_t stream_fixed_bytes(uint32_t cols, uint32_t teams, int addend = kBf16) {
     return (size_t)cols * sizeof(float) * (addend == kScaledF32 ? 2u : 1u) + 128u * sizeof(scale_lut_entry) +
-           (size_t)teams * 256u * sizeof(float) + (size_t)teams * kMaxSlotsPerTeam * sizeof(uint64_t) +
-           (size_t)kMaxTeams * sizeof(uint32_t);  // barriers, then one fault flag per team
+           (size_t)teams * 256u * sizeof(float) + (size_t)teams * kMaxSlotsPerTeam * sizeof(uint64_t);
 }
 
 template <int kAdd, bool kFull>

@@ -332,6 +332,7 @@ def main():
     ap.add_argument("--skip-ops", action="store_true", help="only the headline workload")
     ap.add_argument("--skip-e2e", action="store_true")
     ap.add_argument("--skip-cpu", action="store_true")
+    ap.add_argument("--skip-reference-gpu", action="store_true", help="leave the reference's own kernels out (profiling aid)")
     ap.add_argument("--only", default=None,
                     choices=["add_rmsnorm", "add_rmsnorm_tiled", "fp8_epilogue", "nvfp4_quantize", "qk", "swiglu_fp8", "swiglu_nvfp4", "sigmoid_gate",
                              "top1", "chain"],
@@ -528,7 +529,7 @@ def main():
         line["strong"] = rounded(bench_strong(torch, axk, wl, sharding, dist, world, rank, local, device, stream, G, peak,
                                               iters=max(20, min(args.steps, 100)), warm=max(args.warmup, 3)))
         # the reference's own kernels on the same rows (rank 0; outside every product timed region)
-        if rank == 0:
+        if rank == 0 and not args.skip_reference_gpu:
             try:
                 line["reference_gpu"] = reference_gpu_baseline(torch, wl, device, G)
             except Exception as exc:
