@@ -169,7 +169,9 @@ nvfp4_quantize_bf16_kernel(const uint4 *__restrict__ in, uint32_t total_chunks, 
 // 11.5 us, depth 3 at 64 registers (spilling) 11.2 / 12.2, depth 3 or 4 with three CTAs 11.2 / 11.6-11.9, depth 2
 // with five CTAs 11.2 / 12.6; the chunk-per-lane kernel below 11.5 / 12.5.  At 54 MB per launch the remaining time is
 // the dependent-launch floor: first-load latency after the previous kernel has drained, and the drain of the
-// last stores (a plain copy of the same bytes takes 12.4 us).
+// last stores (a plain copy of the same bytes takes 12.4 us).  Hinting the first tiles into L2 before the dependency
+// wait (cp.async.bulk.prefetch.L2) was measured too and changes nothing: the CTAs of a launch become resident as
+// the previous launch's CTAs retire, so there is no earlier moment to hint from.
 // ---------------------------------------------------------------------------
 #ifndef AXB_Q_DEPTH
 #define AXB_Q_DEPTH 2
@@ -211,12 +213,12 @@ nvfp4_quantize_blocks_kernel(const uint4 *__restrict__ in, uint32_t total_blocks
     const uint32_t lane = threadIdx.x & 31u;
     const uint32_t warp = (blockIdx.x * kBlkThreads + threadIdx.x) >> 5;
     allow_dependents();
+    const uint64_t first64 = (uint64_t)warp * blocks_per_warp;
+    const uint32_t first = (uint32_t)(first64 < total_blocks ? first64 : total_blocks);
+    const uint32_t count = total_blocks - first < blocks_per_warp ? total_blocks - first : blocks_per_warp;
     const bool lut_safe = build_scale_lut(lut, G);  // depends on the scalar argument only
     dependency_wait();
-    const uint64_t first64 = (uint64_t)warp * blocks_per_warp;
-    if (first64 >= total_blocks) return;
-    const uint32_t first = (uint32_t)first64;
-    const uint32_t count = total_blocks - first < blocks_per_warp ? total_blocks - first : blocks_per_warp;
+    if (count == 0u) return;
     const uint32_t tiles = (count + 31u) / 32u;
 
     const uint4 *src = in + 2u * (uint64_t)(first + lane);   // two 16-byte words per block

@@ -138,7 +138,30 @@ def main():
     assert r.ref_sigmoid_gate8(a32.data_ptr(), g32.data_ptr(), o32.data_ptr()) == 0
     fx["sg_attention"], fx["sg_gate"], fx["sg_out"] = attn, gate, wl.to_bf16_bits(o32.cpu().numpy())
 
+    # 8. the BF16 ("draft") rounding convention of q/k norm + RoPE: qk_rmsnorm_rope_bf16_kernel + round_f32_to_bf16,
+    #    40 query heads x 128 as in the draft, cos/sin from a host-built [position][cos | sin] table
+    import oracle_lib as ol  # the table is an INPUT of both sides; it is stored with the fixture
+
+    dr = np.random.default_rng(31)
+    dq = wl.to_bf16_bits(dr.standard_normal((8, 40, 128), dtype=np.float32))
+    dg = wl.to_bf16_bits(1.0 + 0.02 * dr.standard_normal(128, dtype=np.float32))
+    d_first = 4090
+    d_inv = ol.yarn_inv_freq(1e6, 4.0, 32768.0, 32.0, 1.0, 128, host_table=True)
+    d_table = ol.rope_table_host(d_inv, 128, float(ol.o().axo_yarn_mscale(4.0)), d_first + 8)
+    fx["d_q"], fx["d_gamma"], fx["d_first"], fx["d_table_rows"] = dq, dg, np.uint32(d_first), d_table[d_first:d_first + 8].copy()
+    fx["d_out"] = rc.draft_qk_norm_rope(dq, dg, d_table, d_first)
+
+    # 9. given-scale E4M3 quantizer (quantize_columns_static_e4m3_kernel), specials included
+    sy = wl.quantize_input_np(8, 512, seed=17)
+    sy[0, :6] = [0x7F80, 0xFF80, 0x7FC0, 0x8000, 0x0000, 0x7F7F]
+    fx["fs_in"], fx["fs_scale"] = sy, np.float32(0.0123)
+    fx["fs_codes"] = rc.fp8_quantize_static_f32(rc.f32_dev(sy), 0.0123)
+
     path = out_dir / "reference_b200.npz"
+    if path.exists():  # every array of the committed fixture must come out the same: the kernels are deterministic
+        old = np.load(path)
+        for name in old.files:
+            assert np.array_equal(old[name], fx[name]), f"{name} changed"
     np.savez_compressed(path, **fx)
     print(f"wrote {path} ({path.stat().st_size} bytes, {len(fx)} arrays) on {torch.cuda.get_device_name(0)}")
 

@@ -115,3 +115,26 @@ def test_generic_f32_ops(fx):
     assert np.array_equal(ol.add_f32(fx["g_a"], fx["g_b"]), fx["g_add"])
     assert np.allclose(ol.silu_mul_f32(fx["g_a"], fx["g_b"]), fx["g_silu_mul"], rtol=1e-3, atol=1e-5)
     assert np.allclose(ol.silu_mul_f32(fx["g_a"], fx["g_b"], 3.0), fx["g_silu_mul_clamp3"], rtol=1e-3, atol=1e-5)
+
+
+def test_round_after_norm_convention(fx):
+    """The draft's q/k convention against the reference kernel's output: the rotary table rows are inputs of both
+    sides; the oracle's inverse square root is the C library's, so three BF16 ulps at the operands' magnitude."""
+    first = int(fx["d_first"])
+    table = np.zeros((first + 8, 128), np.float32)
+    table[first:] = fx["d_table_rows"]
+    positions = (first + np.arange(8)).astype(np.uint32)
+    got, status = ol.qk_norm_rope_round_after_norm(fx["d_q"], fx["d_gamma"], table, positions)
+    assert status == 0
+    a, b = wl.from_bf16_bits(got), wl.from_bf16_bits(fx["d_out"])
+    x = wl.from_bf16_bits(fx["d_q"]).astype(np.float64)
+    n = np.abs(x / np.sqrt((x ** 2).mean(-1, keepdims=True) + 1e-6)) * 1.2     # |normalised operand| * gamma * mscale, roughly
+    mag = np.maximum(n[..., :64], n[..., 64:])
+    bound = 3 * ol.bf16_ulp(np.concatenate([mag, mag], axis=-1).astype(np.float32) * np.float32(1.2))
+    assert np.all(np.abs(a - b) <= bound)
+    assert np.mean(got != fx["d_out"]) < 0.05
+
+
+def test_static_scale_fp8_bit_exact(fx):
+    codes = ol.fp8_quantize_static_f32(wl.from_bf16_bits(fx["fs_in"]), float(fx["fs_scale"]))
+    assert np.array_equal(codes, fx["fs_codes"])
