@@ -74,6 +74,14 @@ __device__ __forceinline__ void bulk_load(void *dst_shared, const void *src_glob
                  : "memory");
 }
 
+// Asks the memory system to bring `bytes` of global memory into L2 (no destination, no completion to wait for, no
+// architectural effect).  Address and size are multiples of 16.  The register-pipelined kernels issue it for the
+// data of their NEXT iteration while they convert the current one, so that DRAM stays busy during the arithmetic
+// and the next loads find their lines in L2.
+__device__ __forceinline__ void bulk_prefetch_l2(const void *src_global, uint32_t bytes) {
+    asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(src_global), "r"(bytes) : "memory");
+}
+
 // shared -> global, tracked by the issuing thread's bulk group.
 __device__ __forceinline__ void bulk_store(void *dst_global, const void *src_shared, uint32_t bytes) {
     asm volatile("cp.async.bulk.global.shared::cta.bulk_group [%0], [%1], %2;"
