@@ -163,26 +163,18 @@ __device__ __forceinline__ void swiglu8(const float *table, const uint4 &g, cons
     }
 }
 
-// Maximum over the CTA; every thread receives it.  kNan: NaN-propagating (a NaN anywhere in the
-// row gives NaN), otherwise fmaxf semantics with the clamp that makes an all-NaN row give 0.
-template <bool kNan>
-__device__ __forceinline__ float cta_max(float m, float *warp_max) {
+// Maximum over the CTA; every thread receives it.  The operands are magnitudes: non-negative floats, +infinity, or
+// the canonical NaN that max.NaN.f32 produces (0x7fffffff).  On those the unsigned order of the bit patterns is
+// the order of the values with NaN on top, so the maximum of a warp is one redux.sync instead of five shuffles and
+// five maxima — NaN-propagating where a NaN can occur (the callers that must drop NaN pass none).
+__device__ __forceinline__ float cta_max(float m, uint32_t *warp_max) {
     const uint32_t lane = threadIdx.x & 31u, warp = threadIdx.x >> 5, warps = (blockDim.x + 31u) >> 5;
-#pragma unroll
-    for (uint32_t off = 16u; off != 0u; off >>= 1u) {
-        const float o = __shfl_xor_sync(0xffffffffu, m, off);
-        m = kNan ? max_nan(m, o) : fmaxf(m, o);
-    }
-    if (lane == 0u) warp_max[warp] = m;
+    const uint32_t mine = __reduce_max_sync(0xffffffffu, __float_as_uint(m));
+    if (lane == 0u) warp_max[warp] = mine;
     __syncthreads();
-    float all = lane < warps ? warp_max[lane] : 0.0f;
-#pragma unroll
-    for (uint32_t off = 16u; off != 0u; off >>= 1u) {
-        const float o = __shfl_xor_sync(0xffffffffu, all, off);
-        all = kNan ? max_nan(all, o) : fmaxf(all, o);
-    }
+    const uint32_t all = __reduce_max_sync(0xffffffffu, lane < warps ? warp_max[lane] : 0u);
     __syncthreads();  // warp_max is reused; measured: alternating two staging buffers to drop this barrier is 4 % slower
-    return kNan ? all : fmaxf(all, 0.0f);
+    return __uint_as_float(all);
 }
 
 // Two FP8 codes through IEEE divisions, out of line: the rare path of the row kernel (a scale the reciprocal
@@ -195,20 +187,26 @@ enum class row_op { swiglu, swiglu_table, plain_finite_only };
 
 // CPT = 16-byte chunks (8 values) per thread; blockDim.x * CPT >= width / 8.
 constexpr uint32_t kMaxRowThreads = 576u;
+constexpr int kMlpRowThreads = 544;  // 17408 / (4 chunks x 8 values)
 
 // kStatic: the scale is an argument (quantize_columns_static_e4m3_kernel, src/axiom_qwen38_fp8.cu:96-107) — no row
 // maximum, no CTA reduction, no scale output; every thread decides for its own values whether the reciprocal
 // sequence is exact and takes IEEE divisions otherwise (NaN / infinity / quotients near overflow).
-template <int CPT, row_op kOp, bool kStatic = false>
-__global__ void __launch_bounds__(kMaxRowThreads, CPT <= 4 ? 2 : 1)
+// kThreads != 0: the CTA has exactly kThreads threads and the row exactly kThreads * CPT chunks — no thread is past
+// the end of the row and every offset inside a row is a compile-time constant (no predicates, no zero fill, no
+// per-chunk address arithmetic).
+template <int CPT, row_op kOp, bool kStatic = false, int kThreads = 0>
+__global__ void __launch_bounds__(kThreads ? kThreads : kMaxRowThreads, CPT <= 4 ? 2 : 1)
 fp8_rows_kernel(const uint4 *__restrict__ in, uint32_t rows, uint32_t chunks, uint32_t in_chunks_per_row,
                 uint2 *__restrict__ codes, float *__restrict__ scales, uint32_t *__restrict__ status_word,
                 const float *__restrict__ device_table, float given_scale) {
     extern __shared__ __align__(16) float silu_table[];
-    __shared__ float warp_max[32];
+    __shared__ uint32_t warp_max[32];
     constexpr bool kSwiglu = kOp != row_op::plain_finite_only;
     constexpr bool kTable = kOp == row_op::swiglu_table;
     const uint32_t tid = threadIdx.x;
+    const uint32_t threads = kThreads ? (uint32_t)kThreads : blockDim.x;
+    if (kThreads) chunks = (uint32_t)kThreads * CPT;
     allow_dependents();
     if (kTable) build_silu_table(silu_table, device_table);  // the device table never changes once filled
     dependency_wait();
@@ -229,8 +227,8 @@ fp8_rows_kernel(const uint4 *__restrict__ in, uint32_t rows, uint32_t chunks, ui
             uint4 g[CPT], u[CPT];
 #pragma unroll
             for (int k = 0; k < CPT; ++k) {
-                const uint32_t q = tid + blockDim.x * k;
-                const bool ok = q < chunks;
+                const uint32_t q = tid + threads * k;
+                const bool ok = kThreads != 0 || q < chunks;
                 g[k] = ok ? ld_stream(gate + q) : make_uint4(0u, 0u, 0u, 0u);
                 u[k] = ok ? ld_stream(up + q) : make_uint4(0u, 0u, 0u, 0u);
             }
@@ -243,8 +241,8 @@ fp8_rows_kernel(const uint4 *__restrict__ in, uint32_t rows, uint32_t chunks, ui
             uint4 g[CPT];
 #pragma unroll
             for (int k = 0; k < CPT; ++k) {
-                const uint32_t q = tid + blockDim.x * k;
-                g[k] = q < chunks ? ld_stream(gate + q) : make_uint4(0u, 0u, 0u, 0u);
+                const uint32_t q = tid + threads * k;
+                g[k] = (kThreads != 0 || q < chunks) ? ld_stream(gate + q) : make_uint4(0u, 0u, 0u, 0u);
             }
 #pragma unroll
             for (int k = 0; k < CPT; ++k) {
@@ -258,13 +256,13 @@ fp8_rows_kernel(const uint4 *__restrict__ in, uint32_t rows, uint32_t chunks, ui
                 }
             }
         }
-        if (!kStatic) m = kSwiglu ? cta_max<true>(m, warp_max) : cta_max<false>(m, warp_max);
+        if (!kStatic) m = cta_max(m, warp_max);
         if (!kStatic && kSwiglu && !(m == m)) {
             // a NaN somewhere in the row: the reference's maximum drops it
             float d = 0.0f;
 #pragma unroll
             for (int k = 0; k < CPT; ++k) d = fmaxf(d, absmax8_drop_nan(y[k]));
-            m = cta_max<false>(d, warp_max);
+            m = cta_max(d, warp_max);
             nonfinite = true;
         }
         float scale = m == 0.0f ? 1.0f : __fdiv_rn(m, 448.0f);
@@ -287,7 +285,7 @@ fp8_rows_kernel(const uint4 *__restrict__ in, uint32_t rows, uint32_t chunks, ui
             const float2 nr2 = make_float2(-r, -r), d2 = make_float2(scale, scale);
 #pragma unroll
             for (int k = 0; k < CPT; ++k) {
-                const uint32_t q = tid + blockDim.x * k;
+                const uint32_t q = tid + threads * k;
                 uint32_t c[4];
 #pragma unroll
                 for (int i = 0; i < 4; ++i) {
@@ -296,7 +294,7 @@ fp8_rows_kernel(const uint4 *__restrict__ in, uint32_t rows, uint32_t chunks, ui
                     const float2 nq = __ffma2_rn(__ffma2_rn(d2, t, v), nr2, t);
                     c[i] = cvt_e4m3x2(nq.x, nq.y);
                 }
-                if (q < chunks) {
+                if (kThreads != 0 || q < chunks) {
                     st_stream(out + q, make_uint2(__byte_perm(c[0], c[1], 0x5410) ^ 0x80808080u,
                                                   __byte_perm(c[2], c[3], 0x5410) ^ 0x80808080u));
                 }
@@ -304,14 +302,14 @@ fp8_rows_kernel(const uint4 *__restrict__ in, uint32_t rows, uint32_t chunks, ui
         } else {
 #pragma unroll
             for (int k = 0; k < CPT; ++k) {
-                const uint32_t q = tid + blockDim.x * k;
+                const uint32_t q = tid + threads * k;
                 uint32_t w[2];
 #pragma unroll
                 for (int h = 0; h < 2; ++h) {
                     w[h] = e4m3_pair_by_division(y[k][4 * h + 0], y[k][4 * h + 1], scale) |
                            (e4m3_pair_by_division(y[k][4 * h + 2], y[k][4 * h + 3], scale) << 16);
                 }
-                if (q < chunks) st_stream(out + q, make_uint2(w[0], w[1]));
+                if (kThreads != 0 || q < chunks) st_stream(out + q, make_uint2(w[0], w[1]));
             }
         }
     }
@@ -639,6 +637,7 @@ void configure_fp8_rows() {
     allow_dynamic_smem<fp8_rows_kernel<2, kOp, kStatic>>(kSiluTableBytes);
     allow_dynamic_smem<fp8_rows_kernel<4, kOp, kStatic>>(kSiluTableBytes);
     allow_dynamic_smem<fp8_rows_kernel<8, kOp, kStatic>>(kSiluTableBytes);
+    allow_dynamic_smem<fp8_rows_kernel<4, kOp, kStatic, kMlpRowThreads>>(kSiluTableBytes);
 }
 
 template <row_op kOp, bool kStatic = false>
@@ -656,6 +655,14 @@ int launch_fp8_rows(const void *in, uint32_t rows, uint32_t width, uint32_t in_c
     const uint4 *src = (const uint4 *)in;
     uint2 *dst = (uint2 *)codes;
     if (kTable) configure_fp8_rows<kOp, kStatic>();
+#ifndef AXB_NO_MLP_GEOMETRY
+    if (kTable && s.cpt == 4u && s.threads * 4u == chunks && s.threads == kMlpRowThreads) {
+        // the reference model's MLP width (17408 = 544 threads x 4 chunks x 8): row geometry as compile-time constants
+        launch_chained(fp8_rows_kernel<4, kOp, kStatic, kMlpRowThreads>, dim3(ctas), dim3(s.threads), smem, stream, src, rows, chunks, in_chunks_per_row, dst, scales, status_word, device_table, given_scale);
+        note_launch();
+        return AXIOM_OK;
+    }
+#endif
     switch (s.cpt) {
     case 1: launch_chained(fp8_rows_kernel<1, kOp, kStatic>, dim3(ctas), dim3(s.threads), smem, stream, src, rows, chunks, in_chunks_per_row, dst, scales, status_word, device_table, given_scale); break;
     case 2: launch_chained(fp8_rows_kernel<2, kOp, kStatic>, dim3(ctas), dim3(s.threads), smem, stream, src, rows, chunks, in_chunks_per_row, dst, scales, status_word, device_table, given_scale); break;

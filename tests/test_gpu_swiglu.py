@@ -74,6 +74,39 @@ def test_swiglu_fp8_special_rows(axk, cuda_device):
     assert np.array_equal(codes[[0, 1, 3, 5]], want_codes[[0, 1, 3, 5]])
 
 
+def test_swiglu_fp8_special_rows_at_the_mlp_width(axk, cuda_device):
+    """The same special rows where the row kernel runs with its geometry as compile-time constants (width 17408,
+    enough rows for persistent CTAs with the silu table): zero rows, an infinite product, a NaN, gates beyond
+    both ends of the table.  Bit-equal with the reference's kernels when they are built."""
+    import ref_lib
+
+    rows, w = 300, wl.FFN
+    gu = wl.swiglu_input_np(rows, w, seed=11)
+    x = np.zeros((6, 2 * w), np.float32)
+    x[1, :w] = 1.0
+    x[2, :w] = np.linspace(-90, 90, w); x[2, w:] = 1.0
+    x[3, 0] = np.inf; x[3, w] = 1.0; x[3, 1] = 2.0; x[3, w + 1] = 3.0
+    x[4, 5] = np.nan; x[4, w:] = 1.0; x[4, 7] = 4.0
+    x[5, :w] = -200.0; x[5, w:] = 5.0
+    special = [0, 1, 150, 151, 298, 299]
+    gu[special] = wl.to_bf16_bits(x)
+    gu[7, 17] = 0x0001          # a subnormal gate (under the table)
+    gu[8, w - 1] = 0x4300       # 128.0: the first magnitude past the table
+    gu[9, 3] = 0x8000           # -0
+    codes, scales = run_swiglu_fp8(axk, gu)
+    want_codes, want_scales = ol.swiglu_fp8_bf16(gu)
+    assert np.all(np.abs(scales - want_scales) <= 4 * np.spacing(want_scales))
+    assert scales[0] == 1.0 and scales[1] == 1.0 and scales[151] == 1.0
+    assert np.mean(codes != want_codes) < 2e-3
+    assert np.array_equal(codes[[0, 1, 151, 299]], want_codes[[0, 1, 151, 299]])
+    if ref_lib.available():
+        import ref_cases as rc
+
+        ref_codes, ref_scales = rc.swiglu_fp8(gu)
+        assert np.array_equal(scales, ref_scales)
+        assert np.array_equal(codes, ref_codes)
+
+
 def test_plain_fp8_quantizer_bit_exact(axk, cuda_device):
     from gpu_util import Guarded, dev, sync
     import torch
