@@ -183,7 +183,7 @@ static __device__ __noinline__ uint32_t e4m3_pair_by_division(float a, float b, 
     return cvt_e4m3x2(__fdiv_rn(a, scale), __fdiv_rn(b, scale));
 }
 
-enum class row_op { swiglu, swiglu_table, plain_finite_only };
+enum class row_op { swiglu, swiglu_table };
 
 // CPT = 16-byte chunks (8 values) per thread; blockDim.x * CPT >= width / 8.
 constexpr uint32_t kMaxRowThreads = 576u;
@@ -202,7 +202,6 @@ fp8_rows_kernel(const uint4 *__restrict__ in, uint32_t rows, uint32_t chunks, ui
                 const float *__restrict__ device_table, float given_scale) {
     extern __shared__ __align__(16) float silu_table[];
     __shared__ uint32_t warp_max[32];
-    constexpr bool kSwiglu = kOp != row_op::plain_finite_only;
     constexpr bool kTable = kOp == row_op::swiglu_table;
     const uint32_t tid = threadIdx.x;
     const uint32_t threads = kThreads ? (uint32_t)kThreads : blockDim.x;
@@ -213,16 +212,15 @@ fp8_rows_kernel(const uint4 *__restrict__ in, uint32_t rows, uint32_t chunks, ui
     for (uint32_t row = blockIdx.x; row < rows; row += gridDim.x) {
         const uint4 *gate = in + (uint64_t)row * in_chunks_per_row;
         // the row this CTA takes next, hinted into L2 while this one is converted: a CTA holds a whole row in
-        // registers between its loads and its stores, so without the hint DRAM idles through the arithmetic
-        // (plain BF16 -> FP8 at 16384 x 8192: 111.9 -> 100.2 us; the SwiGLU flavour is bound by its arithmetic and
-        // does not move)
+        // registers between its loads and its stores (the plain BF16 -> FP8 kernel gained 10 % from the same hint;
+        // this one is bound by its instruction count and did not move either way)
         if (tid == 0u && row + gridDim.x < rows) {
-            bulk_prefetch_l2(in + (uint64_t)(row + gridDim.x) * in_chunks_per_row, (kSwiglu ? 2u : 1u) * chunks * 16u);
+            bulk_prefetch_l2(in + (uint64_t)(row + gridDim.x) * in_chunks_per_row, 2u * chunks * 16u);
         }
         float y[CPT][8];
-        float m = 0.0f;       // NaN-propagating maximum (swiglu) / finite-only maximum (plain)
+        float m = 0.0f;  // NaN-propagating maximum
         bool nonfinite = false;
-        if (kSwiglu) {
+        {
             const uint4 *up = gate + chunks;
             uint4 g[CPT], u[CPT];
 #pragma unroll
@@ -237,27 +235,9 @@ fp8_rows_kernel(const uint4 *__restrict__ in, uint32_t rows, uint32_t chunks, ui
                 swiglu8<kTable>(silu_table, g[k], u[k], y[k]);
                 m = max_nan(m, absmax8_nan(y[k]));
             }
-        } else {
-            uint4 g[CPT];
-#pragma unroll
-            for (int k = 0; k < CPT; ++k) {
-                const uint32_t q = tid + threads * k;
-                g[k] = (kThreads != 0 || q < chunks) ? ld_stream(gate + q) : make_uint4(0u, 0u, 0u, 0u);
-            }
-#pragma unroll
-            for (int k = 0; k < CPT; ++k) {
-                unpack8(g[k], y[k]);
-#pragma unroll
-                for (int i = 0; i < 8; ++i) {
-                    // non-finite inputs do not take part in the maximum and raise the status word
-                    const bool fin = (__float_as_uint(y[k][i]) & 0x7f800000u) != 0x7f800000u;
-                    nonfinite |= !fin;
-                    m = fmaxf(m, fin ? fabsf(y[k][i]) : 0.0f);
-                }
-            }
         }
         if (!kStatic) m = cta_max(m, warp_max);
-        if (!kStatic && kSwiglu && !(m == m)) {
+        if (!kStatic && !(m == m)) {
             // a NaN somewhere in the row: the reference's maximum drops it
             float d = 0.0f;
 #pragma unroll
@@ -268,12 +248,9 @@ fp8_rows_kernel(const uint4 *__restrict__ in, uint32_t rows, uint32_t chunks, ui
         float scale = m == 0.0f ? 1.0f : __fdiv_rn(m, 448.0f);
         if (kStatic) {
             scale = given_scale;
-            // the plain flavour keeps non-finite values out of its maximum: fold them back in for the range test
-            if (nonfinite || !(m == m)) m = CUDART_INF_F;
-        } else if (kSwiglu) {
-            if (!isfinite(scale) || scale <= 0.0f) scale = 1.0f;
-        } else if (nonfinite && status_word) {
-            atomicCAS(status_word, AXIOM_STATUS_WORD_OK, AXIOM_STATUS_WORD_NONFINITE);
+            if (!(m == m)) m = CUDART_INF_F;  // fails the range test below
+        } else if (!isfinite(scale) || scale <= 0.0f) {
+            scale = 1.0f;
         }
         if (!kStatic && tid == 0u) scales[row] = scale;
         const float r = __frcp_rn(scale);
@@ -310,6 +287,107 @@ fp8_rows_kernel(const uint4 *__restrict__ in, uint32_t rows, uint32_t chunks, ui
                            (e4m3_pair_by_division(y[k][4 * h + 2], y[k][4 * h + 3], scale) << 16);
                 }
                 if (kThreads != 0 || q < chunks) st_stream(out + q, make_uint2(w[0], w[1]));
+            }
+        }
+    }
+}
+
+// ---- plain BF16 -> FP8 rows ------------------------------------------------------------------
+// quantize_columns_e4m3 on BF16 storage: nothing has to be widened before the scale is known.  A thread keeps its
+// chunks as the packed words it loaded (4 registers per chunk instead of 8 floats) and takes the row maximum on the
+// BF16 magnitudes themselves — the unsigned order of |x| patterns is the order of the values, with infinity and NaN
+// (>= 0x7f80) on top — two packed instructions per word.  A row whose maximum pattern is non-finite is redone with
+// those values left out (the reference's maximum skips them and raises the status word).  The widening then
+// happens once, on the FMA pipe, right before the division.
+__device__ __forceinline__ uint32_t magnitude_max4(uint32_t m, const uint4 &w) {
+    m = __vmaxu2(m, w.x & 0x7fff7fffu);
+    m = __vmaxu2(m, w.y & 0x7fff7fffu);
+    m = __vmaxu2(m, w.z & 0x7fff7fffu);
+    return __vmaxu2(m, w.w & 0x7fff7fffu);
+}
+static __device__ __noinline__ uint32_t finite_magnitude_max4(uint32_t m, uint4 w) {
+    const uint32_t words[4] = {w.x, w.y, w.z, w.w};
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        const uint32_t lo = words[i] & 0x7fffu, hi = (words[i] >> 16) & 0x7fffu;
+        if (lo < 0x7f80u && lo > m) m = lo;
+        if (hi < 0x7f80u && hi > m) m = hi;
+    }
+    return m;
+}
+// eight codes of one chunk by IEEE divisions, out of line
+static __device__ __noinline__ uint2 e4m3x8_of_bf16_by_division(uint4 w, float scale) {
+    float v[8];
+    unpack8(w, v);
+    return make_uint2(e4m3_pair_by_division(v[0], v[1], scale) | (e4m3_pair_by_division(v[2], v[3], scale) << 16),
+                      e4m3_pair_by_division(v[4], v[5], scale) | (e4m3_pair_by_division(v[6], v[7], scale) << 16));
+}
+
+template <int CPT, bool kStatic>
+__global__ void __launch_bounds__(kMaxRowThreads)
+fp8_plain_rows_kernel(const uint4 *__restrict__ in, uint32_t rows, uint32_t chunks, uint32_t in_chunks_per_row,
+                      uint2 *__restrict__ codes, float *__restrict__ scales, uint32_t *__restrict__ status_word,
+                      float given_scale) {
+    __shared__ uint32_t warp_max[32];
+    const uint32_t tid = threadIdx.x, threads = blockDim.x;
+    allow_dependents();
+    dependency_wait();
+    for (uint32_t row = blockIdx.x; row < rows; row += gridDim.x) {
+        const uint4 *src = in + (uint64_t)row * in_chunks_per_row;
+        // the row this CTA takes next, hinted into L2 while this one is converted
+        if (tid == 0u && row + gridDim.x < rows) bulk_prefetch_l2(in + (uint64_t)(row + gridDim.x) * in_chunks_per_row, chunks * 16u);
+        uint4 w[CPT];
+#pragma unroll
+        for (int k = 0; k < CPT; ++k) {
+            const uint32_t q = tid + threads * k;
+            w[k] = q < chunks ? ld_stream(src + q) : make_uint4(0u, 0u, 0u, 0u);
+        }
+        uint32_t packed = 0u;
+#pragma unroll
+        for (int k = 0; k < CPT; ++k) packed = magnitude_max4(packed, w[k]);
+        uint32_t top = max(packed & 0xffffu, packed >> 16);  // BF16 pattern of the largest magnitude, non-finite included
+        if (!kStatic) top = __float_as_uint(cta_max(__uint_as_float(top), warp_max));
+        bool nonfinite = top >= 0x7f80u;
+        if (!kStatic && nonfinite) {
+            uint32_t mine = 0u;
+#pragma unroll
+            for (int k = 0; k < CPT; ++k) mine = finite_magnitude_max4(mine, w[k]);
+            top = __float_as_uint(cta_max(__uint_as_float(mine), warp_max));
+            if (tid == 0u && status_word) atomicCAS(status_word, AXIOM_STATUS_WORD_OK, AXIOM_STATUS_WORD_NONFINITE);
+        }
+        // kStatic: this thread's own maximum, for the range test only (non-finite: +infinity fails it)
+        const float m = __uint_as_float(top << 16);
+        float scale = kStatic ? given_scale : (m == 0.0f ? 1.0f : __fdiv_rn(m, 448.0f));
+        if (!kStatic && tid == 0u) scales[row] = scale;
+        const float r = __frcp_rn(scale);
+        // uniform over the CTA for the per-row scale, per thread for a given scale
+        const bool safe = divisor_is_safe(scale, r, m) && !nonfinite;
+        uint2 *out = codes + (uint64_t)row * chunks;
+        if (safe) {
+            // negated residual-corrected quotients (signed zeros survive), signs flipped back on the codes
+            const float2 nr2 = make_float2(-r, -r), d2 = make_float2(scale, scale);
+#pragma unroll
+            for (int k = 0; k < CPT; ++k) {
+                const uint32_t q = tid + threads * k;
+                const uint32_t words[4] = {w[k].x, w[k].y, w[k].z, w[k].w};
+                uint32_t c[4];
+#pragma unroll
+                for (int i = 0; i < 4; ++i) {
+                    const float2 v = bf16x2_widen_fma(words[i]);
+                    const float2 t = __fmul2_rn(v, nr2);
+                    const float2 nq = __ffma2_rn(__ffma2_rn(d2, t, v), nr2, t);
+                    c[i] = cvt_e4m3x2(nq.x, nq.y);
+                }
+                if (q < chunks) {
+                    st_stream(out + q, make_uint2(__byte_perm(c[0], c[1], 0x5410) ^ 0x80808080u,
+                                                  __byte_perm(c[2], c[3], 0x5410) ^ 0x80808080u));
+                }
+            }
+        } else {
+#pragma unroll
+            for (int k = 0; k < CPT; ++k) {
+                const uint32_t q = tid + threads * k;
+                if (q < chunks) st_stream(out + q, e4m3x8_of_bf16_by_division(w[k], scale));
             }
         }
     }
@@ -577,8 +655,11 @@ struct row_shape {
     uint32_t cpt;
 };
 
-// Smallest padding first, then the larger CTA (shorter per-row latency).
-row_shape pick_row_shape(uint32_t chunks) {
+// Smallest padding first; between equal paddings the larger CTA (shorter per-row latency), or — many_rows — the
+// smaller one with more chunks per thread: more loads in flight per thread and more CTAs per SM, whose load and
+// store phases then interleave (plain BF16 -> FP8 at 16384 x 8192: 91 us with 512 x 2, 79 with 256 x 4, 73 with
+// 128 x 8).  Up to one warp of padding per CTA is accepted for that.
+row_shape pick_row_shape(uint32_t chunks, bool many_rows = false) {
     static const uint32_t cpts[] = {1u, 2u, 4u, 8u};
     row_shape best{0u, 0u};
     uint64_t best_pad = ~0ull;
@@ -587,8 +668,9 @@ row_shape pick_row_shape(uint32_t chunks) {
         threads = (threads + 31u) & ~31u;
         if (threads < 64u) threads = 64u;
         if (threads > kMaxRowThreads) continue;
-        const uint64_t pad = (uint64_t)threads * cpt - chunks;
-        if (pad < best_pad || (pad == best_pad && threads > best.threads)) {
+        uint64_t pad = (uint64_t)threads * cpt - chunks;
+        if (many_rows && pad * 32u <= chunks) pad = 0u;  // at most 1/32 of the row
+        if (pad < best_pad || (pad == best_pad && (many_rows ? threads < best.threads : threads > best.threads))) {
             best_pad = pad;
             best = row_shape{threads, cpt};
         }
@@ -655,14 +737,12 @@ int launch_fp8_rows(const void *in, uint32_t rows, uint32_t width, uint32_t in_c
     const uint4 *src = (const uint4 *)in;
     uint2 *dst = (uint2 *)codes;
     if (kTable) configure_fp8_rows<kOp, kStatic>();
-#ifndef AXB_NO_MLP_GEOMETRY
     if (kTable && s.cpt == 4u && s.threads * 4u == chunks && s.threads == kMlpRowThreads) {
         // the reference model's MLP width (17408 = 544 threads x 4 chunks x 8): row geometry as compile-time constants
         launch_chained(fp8_rows_kernel<4, kOp, kStatic, kMlpRowThreads>, dim3(ctas), dim3(s.threads), smem, stream, src, rows, chunks, in_chunks_per_row, dst, scales, status_word, device_table, given_scale);
         note_launch();
         return AXIOM_OK;
     }
-#endif
     switch (s.cpt) {
     case 1: launch_chained(fp8_rows_kernel<1, kOp, kStatic>, dim3(ctas), dim3(s.threads), smem, stream, src, rows, chunks, in_chunks_per_row, dst, scales, status_word, device_table, given_scale); break;
     case 2: launch_chained(fp8_rows_kernel<2, kOp, kStatic>, dim3(ctas), dim3(s.threads), smem, stream, src, rows, chunks, in_chunks_per_row, dst, scales, status_word, device_table, given_scale); break;
@@ -693,9 +773,29 @@ int launch_swiglu_fp8_bf16(const void *gate_up, uint32_t rows, uint32_t width, u
 }
 
 // Given-scale flavours: the same row kernels without the row maximum (one pass, nothing to reduce).
+template <bool kStatic>
+int launch_fp8_plain_rows(const void *in, uint32_t rows, uint32_t cols, uint8_t *codes, float *scales, uint32_t *status_word,
+                          cudaStream_t stream, float given_scale) {
+    const uint32_t chunks = cols / 8u;
+    const row_shape s = pick_row_shape(chunks, rows >= 4u * kSmCount);
+    if (s.threads == 0u) return AXIOM_ERR_INVALID_ARGUMENT;
+    const uint32_t cap = kSmCount * 16u;
+    const uint32_t ctas = rows < cap ? rows : cap;
+    const uint4 *src = (const uint4 *)in;
+    uint2 *dst = (uint2 *)codes;
+    switch (s.cpt) {
+    case 1: launch_chained(fp8_plain_rows_kernel<1, kStatic>, dim3(ctas), dim3(s.threads), 0, stream, src, rows, chunks, chunks, dst, scales, status_word, given_scale); break;
+    case 2: launch_chained(fp8_plain_rows_kernel<2, kStatic>, dim3(ctas), dim3(s.threads), 0, stream, src, rows, chunks, chunks, dst, scales, status_word, given_scale); break;
+    case 4: launch_chained(fp8_plain_rows_kernel<4, kStatic>, dim3(ctas), dim3(s.threads), 0, stream, src, rows, chunks, chunks, dst, scales, status_word, given_scale); break;
+    default: launch_chained(fp8_plain_rows_kernel<8, kStatic>, dim3(ctas), dim3(s.threads), 0, stream, src, rows, chunks, chunks, dst, scales, status_word, given_scale); break;
+    }
+    note_launch();
+    return AXIOM_OK;
+}
+
 int launch_fp8_quantize_static_bf16(const void *input, uint32_t rows, uint32_t cols, float scale, uint8_t *codes,
                                     cudaStream_t stream) {
-    return launch_fp8_rows<row_op::plain_finite_only, true>(input, rows, cols, cols / 8u, codes, nullptr, nullptr, stream, scale);
+    return launch_fp8_plain_rows<true>(input, rows, cols, codes, nullptr, nullptr, stream, scale);
 }
 
 int launch_swiglu_fp8_static_bf16(const void *gate_up, uint32_t rows, uint32_t width, float scale, uint8_t *codes,
@@ -708,7 +808,7 @@ int launch_swiglu_fp8_static_bf16(const void *gate_up, uint32_t rows, uint32_t w
 
 int launch_fp8_quantize_bf16(const void *input, uint32_t rows, uint32_t cols, uint8_t *codes, float *scales,
                              uint32_t *status_word, cudaStream_t stream) {
-    return launch_fp8_rows<row_op::plain_finite_only>(input, rows, cols, cols / 8u, codes, scales, status_word, stream);
+    return launch_fp8_plain_rows<false>(input, rows, cols, codes, scales, status_word, stream, 0.0f);
 }
 
 template <gate_fn kFn>
