@@ -334,7 +334,7 @@ def main():
     ap.add_argument("--skip-cpu", action="store_true")
     ap.add_argument("--skip-reference-gpu", action="store_true", help="leave the reference's own kernels out (profiling aid)")
     ap.add_argument("--only", default=None,
-                    choices=["add_rmsnorm", "add_rmsnorm_tiled", "fp8_epilogue", "nvfp4_quantize", "qk", "swiglu_fp8", "swiglu_nvfp4", "sigmoid_gate",
+                    choices=["add_rmsnorm", "add_rmsnorm_tiled", "fp8_epilogue", "nvfp4_quantize", "qk", "swiglu_fp8", "swiglu_nvfp4", "sigmoid_gate", "fp8_quantize",
                              "top1", "chain"],
                     help="run one configuration alone (profiling aid): device-timed, no e2e / CPU legs")
     ap.add_argument("--rows", type=int, default=0, help="with --only: override the token count")
@@ -506,10 +506,39 @@ def main():
         del os.environ["AXIOM_B200_HOST_IO"]
         if dist:
             staged_ms = sharding.max_over_ranks(dist, staged_ms, device)
+        # the bare transfers of one step (inputs host -> device on one stream, results device -> host on another, both
+        # directions at once, nothing computed): what the host link allows for these bytes, every rank at the same time
+        d_in = [torch.empty_like(h_hidden, device=device), torch.empty_like(h_res, device=device)]
+        d_out = [torch.empty_like(h_res, device=device), torch.empty_like(h_codes, device=device), torch.empty_like(h_scales, device=device)]
+        h_res_out = torch.empty_like(h_res).pin_memory()
+        up, down = torch.cuda.Stream(device), torch.cuda.Stream(device)
+
+        def bare_transfers():
+            with torch.cuda.stream(up):
+                d_in[0].copy_(h_hidden, non_blocking=True)
+                d_in[1].copy_(h_res, non_blocking=True)
+            with torch.cuda.stream(down):
+                h_res_out.copy_(d_out[0], non_blocking=True)
+                h_codes.copy_(d_out[1], non_blocking=True)
+                h_scales.copy_(d_out[2], non_blocking=True)
+
+        bare_transfers()
+        torch.cuda.synchronize()
+        if dist:
+            dist.barrier()
+        t0 = time.perf_counter()
+        for _ in range(5):
+            bare_transfers()
+        torch.cuda.synchronize()
+        link_ms = (time.perf_counter() - t0) / 5 * 1e3
+        if dist:
+            link_ms = sharding.max_over_ranks(dist, link_ms, device)
+        del d_in, d_out, h_res_out
         line["e2e"] = {"value": world * ROWS / (e2e_ms * 1e-3), "unit": UNIT,
                        "h2d_bytes_per_step": 2 * ROWS * COLS * 2 + COLS * 2,
                        "d2h_bytes_per_step": ROWS * COLS * 2 + ROWS * COLS // 2 + ROWS * COLS // 16,
                        "ms_per_step": e2e_ms, "steps": e2e_steps, "staged_copy_engine_ms_per_step": staged_ms,
+                       "bare_transfers_ms_per_step": link_ms,
                        "numa_node": numa_node,
                        "api": "axiom_runtime_add_rmsnorm_nvfp4_bf16, pinned host buffers; the kernel reads and writes mapped host memory over PCIe"}
         if solo_ms:
@@ -629,6 +658,8 @@ def bench_other_ops(torch, axk, wl, local, device, stream, peak, only=None, rows
         bench_swiglu(torch, axk, wl, local, device, stream, timed, report, rows_override or 16384, want)
     if want("sigmoid_gate"):
         bench_sigmoid_gate(torch, axk, wl, local, device, stream, timed, report, rows_override or 8192)
+    if want("fp8_quantize"):
+        bench_fp8_quantize(torch, axk, wl, local, device, stream, timed, report, rows_override or 16384)
     if want("top1"):
         bench_top1(torch, axk, wl, local, device, stream, timed, report)
     if want("chain"):
@@ -856,6 +887,19 @@ def bench_sigmoid_gate(torch, axk, wl, local, device, stream, timed, report, T):
                                                 sets[i % 2][3], 1, stream))
     report("sigmoid_gate_nvfp4", ms, 2 * T * W * 2 + T * W // 2 + T * W // 16, T,
            "attention * sigmoid(gate) -> NVFP4 with tiled scales (o_proj input), 64 heads x 128")
+
+
+def bench_fp8_quantize(torch, axk, wl, local, device, stream, timed, report, T):
+    # plain BF16 -> FP8 E4M3 rows (the activation quantizer in front of an FP8 contraction): per-row scale, and a given one
+    W = 8192
+    n = 2
+    xs = [wl.quantize_input_torch(torch, device, T, W, seed=70 + s) for s in range(n)]
+    cs = [torch.empty((T, W), dtype=torch.uint8, device=device) for _ in range(n)]
+    sc = torch.empty((T,), dtype=torch.float32, device=device)
+    ms = timed(lambda i: axk.fp8_quantize(local, xs[i % n], T, W, cs[i % n], sc, None, stream))
+    report("fp8_quantize", ms, T * W * 3 + T * 4, T, "BF16 -> FP8 E4M3 with a per-row scale, [T x 8192]")
+    ms = timed(lambda i: axk.fp8_quantize_static(local, xs[i % n], T, W, 0.01, cs[i % n], stream))
+    report("fp8_quantize_static", ms, T * W * 3, T, "BF16 -> FP8 E4M3 with a given scale, [T x 8192]")
 
 
 def bench_top1(torch, axk, wl, local, device, stream, timed, report):
