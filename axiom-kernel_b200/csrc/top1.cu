@@ -8,7 +8,9 @@
 // `partials` array, stage 2 over it, :510-600) becomes one launch: a thread-block cluster of
 // eight CTAs owns a row, every CTA reduces its eighth of the vocabulary with 16-byte loads, and
 // the eight partial results meet in the first CTA's shared memory over the cluster's
-// distributed shared memory — no global scratch, no second kernel.
+// distributed shared memory — no global scratch, no second kernel.  With many rows there are enough CTAs without
+// splitting a row, and the cluster's co-scheduling and barriers cost more than they give (256 x 151 936: 42.7 us
+// with clusters of eight): from kTop1SingleFromRows rows on a CTA takes a whole row.
 #include "runtime.hpp"
 
 #include <cooperative_groups.h>
@@ -50,20 +52,22 @@ __device__ __forceinline__ void top1_warp(top1_candidate *best) {
     }
 }
 
-__global__ void __cluster_dims__(kTop1Cluster, 1, 1) __launch_bounds__(kTop1Threads)
-top1_rows_kernel(const float *__restrict__ logits, uint32_t vocab, axiom_top1_result *__restrict__ results) {
+// kParts: CTAs per row — kTop1Cluster (a cluster per row) or 1 (no cluster).
+template <uint32_t kParts>
+__device__ __forceinline__ void top1_rows_body(const float *__restrict__ logits, uint32_t vocab,
+                                               axiom_top1_result *__restrict__ results) {
     __shared__ top1_candidate warp_best[kTop1Threads / 32u];
-    __shared__ top1_candidate cluster_best[kTop1Cluster];
-    cg::cluster_group cluster = cg::this_cluster();
-    const uint32_t part = cluster.block_rank();
-    const uint32_t row = blockIdx.x / kTop1Cluster;
+    __shared__ top1_candidate cluster_best[kParts];
+    uint32_t part = 0u;
+    if (kParts > 1u) part = cg::this_cluster().block_rank();
+    const uint32_t row = blockIdx.x / kParts;
     const uint32_t tid = threadIdx.x, lane = tid & 31u, warp = tid >> 5;
     allow_dependents();
     dependency_wait();
     // First half of a cluster barrier: by the time a CTA has scanned its slice and passes the matching wait
     // below, every CTA of the cluster has started, which the store into rank 0's shared memory requires
     // (distributed shared memory may only be accessed once the owning CTA is running).
-    asm volatile("barrier.cluster.arrive.relaxed.aligned;" ::: "memory");
+    if (kParts > 1u) asm volatile("barrier.cluster.arrive.relaxed.aligned;" ::: "memory");
 
     // this CTA's slice of the row, in units of four logits when the row allows 16-byte loads
     const float *row_logits = logits + (uint64_t)row * vocab;
@@ -71,7 +75,7 @@ top1_rows_kernel(const float *__restrict__ logits, uint32_t vocab, axiom_top1_re
     const bool vector = (vocab % 4u) == 0u && (reinterpret_cast<uintptr_t>(logits) & 15u) == 0u;
     if (vector) {
         const uint32_t quads = vocab / 4u;
-        const uint32_t per = (quads + kTop1Cluster - 1u) / kTop1Cluster;
+        const uint32_t per = (quads + kParts - 1u) / kParts;
         const uint32_t lo = part * per, hi = lo + per < quads ? lo + per : quads;
         const float4 *src = reinterpret_cast<const float4 *>(row_logits);
         constexpr uint32_t kBatch = 4u;  // loads in flight per thread (8 measured slower at 256 rows)
@@ -98,27 +102,29 @@ top1_rows_kernel(const float *__restrict__ logits, uint32_t vocab, axiom_top1_re
             }
         }
     } else {
-        const uint32_t per = (vocab + kTop1Cluster - 1u) / kTop1Cluster;
+        const uint32_t per = (vocab + kParts - 1u) / kParts;
         const uint32_t lo = part * per, hi = lo + per < vocab ? lo + per : vocab;
         for (uint32_t i = lo + tid; i < hi; i += kTop1Threads) top1_see(row_logits[i], i, &best);
     }
     top1_warp(&best);
     if (lane == 0u) warp_best[warp] = best;
     __syncthreads();
-    asm volatile("barrier.cluster.wait.aligned;" ::: "memory");  // free once the slice is scanned: all CTAs arrived long ago
+    if (kParts > 1u) asm volatile("barrier.cluster.wait.aligned;" ::: "memory");  // free once the slice is scanned: all CTAs arrived long ago
     if (warp == 0u) {
         best = lane < kTop1Threads / 32u ? warp_best[lane] : top1_candidate{-CUDART_INF_F, 0xffffffffu, 0u};
         top1_warp(&best);
-        if (lane == 0u) {
+        if (kParts > 1u && lane == 0u) {
             // deposit this CTA's result in the first CTA's shared memory
-            top1_candidate *dst = cluster.map_shared_rank(cluster_best, 0);
+            top1_candidate *dst = cg::this_cluster().map_shared_rank(cluster_best, 0);
             dst[part] = best;
         }
     }
-    cluster.sync();
+    if (kParts > 1u) cg::this_cluster().sync();
     if (part == 0u && warp == 0u) {
-        best = lane < kTop1Cluster ? cluster_best[lane] : top1_candidate{-CUDART_INF_F, 0xffffffffu, 0u};
-        top1_warp(&best);
+        if (kParts > 1u) {
+            best = lane < kParts ? cluster_best[lane] : top1_candidate{-CUDART_INF_F, 0xffffffffu, 0u};
+            top1_warp(&best);
+        }
         if (lane == 0u) {
             results[row].value = best.value;
             results[row].token_id = best.id;
@@ -126,6 +132,21 @@ top1_rows_kernel(const float *__restrict__ logits, uint32_t vocab, axiom_top1_re
         }
     }
 }
+
+__global__ void __cluster_dims__(kTop1Cluster, 1, 1) __launch_bounds__(kTop1Threads)
+top1_rows_kernel(const float *__restrict__ logits, uint32_t vocab, axiom_top1_result *__restrict__ results) {
+    top1_rows_body<kTop1Cluster>(logits, vocab, results);
+}
+
+__global__ void __launch_bounds__(kTop1Threads)
+top1_whole_rows_kernel(const float *__restrict__ logits, uint32_t vocab, axiom_top1_result *__restrict__ results) {
+    top1_rows_body<1u>(logits, vocab, results);
+}
+
+#ifndef AXB_TOP1_SINGLE_FROM_ROWS
+#define AXB_TOP1_SINGLE_FROM_ROWS 128
+#endif
+constexpr uint32_t kTop1SingleFromRows = AXB_TOP1_SINGLE_FROM_ROWS;
 
 }  // namespace
 }  // namespace axb
@@ -139,7 +160,11 @@ extern "C" int axiom_qwen38_fused_top1_f32_device(int device, const float *logit
     }
     int rc = select_device(device);
     if (rc != AXIOM_OK) return rc;
-    launch_chained(top1_rows_kernel, dim3(rows * kTop1Cluster), dim3(kTop1Threads), 0, (cudaStream_t)stream, logits, vocab, results);
+    if (rows >= kTop1SingleFromRows) {
+        launch_chained(top1_whole_rows_kernel, dim3(rows), dim3(kTop1Threads), 0, (cudaStream_t)stream, logits, vocab, results);
+    } else {
+        launch_chained(top1_rows_kernel, dim3(rows * kTop1Cluster), dim3(kTop1Threads), 0, (cudaStream_t)stream, logits, vocab, results);
+    }
     note_launch();
     return launch_status();
 }

@@ -24,7 +24,8 @@ def run(axk, logits):
     return out.cpu().numpy().view(np.uint32)
 
 
-@pytest.mark.parametrize("rows,vocab", [(1, 248320), (8, 151936), (3, 7), (5, 4099), (64, 32000), (2, 33)])
+@pytest.mark.parametrize("rows,vocab", [(1, 248320), (8, 151936), (3, 7), (5, 4099), (64, 32000), (2, 33),
+                                         (127, 4100), (128, 4100), (130, 7), (200, 151936), (300, 4099)])
 def test_top1_matches_oracle(axk, cuda_device, rows, vocab):
     rng = np.random.default_rng(rows * 131 + vocab)
     logits = rng.standard_normal((rows, vocab)).astype(np.float32) * 3
@@ -52,6 +53,13 @@ def test_top1_unaligned_rows_take_the_scalar_path(axk, cuda_device):
     assert axk.top1(0, x[1:], 4, 1000, out) == axk.AXIOM_OK   # base 4-byte aligned only
     sync()
     assert np.array_equal(out.cpu().numpy().view(np.uint32), ol.top1_f32(backing[1:].reshape(4, 1000)))
+    # the same with enough rows for one CTA per row
+    backing = rng.standard_normal(150 * 1000 + 1).astype(np.float32)
+    x = torch.from_numpy(backing).cuda()
+    out = torch.zeros((150, 3), dtype=torch.int32, device="cuda")
+    assert axk.top1(0, x[1:], 150, 1000, out) == axk.AXIOM_OK
+    sync()
+    assert np.array_equal(out.cpu().numpy().view(np.uint32), ol.top1_f32(backing[1:].reshape(150, 1000)))
 
 
 @pytest.mark.skipif(not ref_lib.available(), reason="reference harness library not built")
