@@ -8,9 +8,8 @@
 // `partials` array, stage 2 over it, :510-600) becomes one launch: a thread-block cluster of
 // eight CTAs owns a row, every CTA reduces its eighth of the vocabulary with 16-byte loads, and
 // the eight partial results meet in the first CTA's shared memory over the cluster's
-// distributed shared memory — no global scratch, no second kernel.  With many rows there are enough CTAs without
-// splitting a row, and the cluster's co-scheduling and barriers cost more than they give (256 x 151 936: 42.7 us
-// with clusters of eight): from kTop1SingleFromRows rows on a CTA takes a whole row.
+// distributed shared memory — no global scratch, no second kernel.  With more rows there are enough CTAs with
+// smaller clusters, and from 256 rows on without splitting a row at all: the launcher picks 8, 4, 2 or 1 CTAs per row.
 #include "runtime.hpp"
 
 #include <cooperative_groups.h>
@@ -21,7 +20,6 @@ namespace cg = cooperative_groups;
 namespace axb {
 namespace {
 
-constexpr uint32_t kTop1Cluster = 8u;
 constexpr uint32_t kTop1Threads = 512u;
 
 struct top1_candidate {
@@ -52,8 +50,8 @@ __device__ __forceinline__ void top1_warp(top1_candidate *best) {
     }
 }
 
-// kParts: CTAs per row — kTop1Cluster (a cluster per row) or 1 (no cluster).
-template <uint32_t kParts>
+// kParts: CTAs per row — a cluster of that many, or 1 (no cluster).
+template <uint32_t kParts, uint32_t kBatch>
 __device__ __forceinline__ void top1_rows_body(const float *__restrict__ logits, uint32_t vocab,
                                                axiom_top1_result *__restrict__ results) {
     __shared__ top1_candidate warp_best[kTop1Threads / 32u];
@@ -78,7 +76,6 @@ __device__ __forceinline__ void top1_rows_body(const float *__restrict__ logits,
         const uint32_t per = (quads + kParts - 1u) / kParts;
         const uint32_t lo = part * per, hi = lo + per < quads ? lo + per : quads;
         const float4 *src = reinterpret_cast<const float4 *>(row_logits);
-        constexpr uint32_t kBatch = 4u;  // loads in flight per thread (8 measured slower at 256 rows)
         for (uint32_t q0 = lo + tid; q0 < hi; q0 += kBatch * kTop1Threads) {
             float4 v[kBatch];
 #pragma unroll
@@ -133,20 +130,24 @@ __device__ __forceinline__ void top1_rows_body(const float *__restrict__ logits,
     }
 }
 
-__global__ void __cluster_dims__(kTop1Cluster, 1, 1) __launch_bounds__(kTop1Threads)
+// kBatch = 16-byte loads in flight per thread
+template <uint32_t kParts, uint32_t kBatch>
+__global__ void __cluster_dims__(kParts, 1, 1) __launch_bounds__(kTop1Threads)
 top1_rows_kernel(const float *__restrict__ logits, uint32_t vocab, axiom_top1_result *__restrict__ results) {
-    top1_rows_body<kTop1Cluster>(logits, vocab, results);
+    top1_rows_body<kParts, kBatch>(logits, vocab, results);
 }
 
+template <uint32_t kBatch>
 __global__ void __launch_bounds__(kTop1Threads)
 top1_whole_rows_kernel(const float *__restrict__ logits, uint32_t vocab, axiom_top1_result *__restrict__ results) {
-    top1_rows_body<1u>(logits, vocab, results);
+    top1_rows_body<1u, kBatch>(logits, vocab, results);
 }
 
-#ifndef AXB_TOP1_SINGLE_FROM_ROWS
-#define AXB_TOP1_SINGLE_FROM_ROWS 128
-#endif
-constexpr uint32_t kTop1SingleFromRows = AXB_TOP1_SINGLE_FROM_ROWS;
+template <uint32_t kParts, uint32_t kBatch>
+void launch_top1(const float *logits, uint32_t rows, uint32_t vocab, axiom_top1_result *results, cudaStream_t stream) {
+    if constexpr (kParts == 1u) launch_chained(top1_whole_rows_kernel<kBatch>, dim3(rows), dim3(kTop1Threads), 0, stream, logits, vocab, results);
+    else launch_chained(top1_rows_kernel<kParts, kBatch>, dim3(rows * kParts), dim3(kTop1Threads), 0, stream, logits, vocab, results);
+}
 
 }  // namespace
 }  // namespace axb
@@ -160,11 +161,19 @@ extern "C" int axiom_qwen38_fused_top1_f32_device(int device, const float *logit
     }
     int rc = select_device(device);
     if (rc != AXIOM_OK) return rc;
-    if (rows >= kTop1SingleFromRows) {
-        launch_chained(top1_whole_rows_kernel, dim3(rows), dim3(kTop1Threads), 0, (cudaStream_t)stream, logits, vocab, results);
-    } else {
-        launch_chained(top1_rows_kernel, dim3(rows * kTop1Cluster), dim3(kTop1Threads), 0, (cudaStream_t)stream, logits, vocab, results);
-    }
+    cudaStream_t st = (cudaStream_t)stream;
+    // CTAs per row: about 256 CTAs in all (a little under two per SM), at most a cluster of eight per row and at
+    // least one CTA per row.  Measured at vocab 151 936 (us, best of parts 8/4/2/1): 8 rows 5.8 (8), 32 rows 7.1 (8),
+    // 64 rows 12.5 (4; 15.2 with 8), 128 rows 19.3 (2; 23.9 with 8), 256 rows 32.1 (1; 42.9 with 8), 1024 rows 97.6
+    // (1; 154.9 with 8).  Eight loads in flight per thread while all CTAs are resident at once, four beyond that.
+    uint32_t parts = 8u;
+    while (parts > 1u && rows * parts > 256u) parts >>= 1;
+    const bool deep = rows * parts <= 2u * kSmCount;
+    if (parts == 8u) launch_top1<8, 8>(logits, rows, vocab, results, st);
+    else if (parts == 4u) launch_top1<4, 8>(logits, rows, vocab, results, st);
+    else if (parts == 2u) launch_top1<2, 8>(logits, rows, vocab, results, st);
+    else if (deep) launch_top1<1, 8>(logits, rows, vocab, results, st);
+    else launch_top1<1, 4>(logits, rows, vocab, results, st);
     note_launch();
     return launch_status();
 }
