@@ -111,7 +111,9 @@ def test_plain_fp8_quantizer_bit_exact(axk, cuda_device):
     from gpu_util import Guarded, dev, sync
     import torch
 
-    for rows, cols in [(1, 8), (3, 5120), (8, 17408), (130, 1024), (5, 36864)]:
+    # from 4 x 148 rows on the launcher prefers more chunks per thread in smaller CTAs
+    for rows, cols in [(1, 8), (3, 5120), (8, 17408), (130, 1024), (5, 36864), (700, 8192), (600, 5120), (593, 17408),
+                       (640, 264), (1200, 4096 + 8)]:
         x = wl.quantize_input_np(rows, cols, seed=cols)
         if rows >= 3:
             x[1, :] = 0
@@ -129,7 +131,8 @@ def test_plain_fp8_quantizer_bit_exact(axk, cuda_device):
         assert codes.guards_intact() and scales.guards_intact()
 
 
-@pytest.mark.parametrize("rows,cols,scale", [(1, 8, 1.0), (5, 5120, 0.0123), (300, 1024, 3.0e-3), (7, 36864, 2.5), (64, 264, 1.0e-30)])
+@pytest.mark.parametrize("rows,cols,scale", [(1, 8, 1.0), (5, 5120, 0.0123), (300, 1024, 3.0e-3), (7, 36864, 2.5), (64, 264, 1.0e-30),
+                                              (700, 8192, 0.02), (600, 5120, 1.5), (640, 264, 7.0e-3)])
 def test_static_scale_fp8_quantizer_bit_exact(axk, cuda_device, rows, cols, scale):
     """Given-scale E4M3 quantizer (no transcendental): bit-exact with the oracle, specials included."""
     from gpu_util import Guarded, dev, sync

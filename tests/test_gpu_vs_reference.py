@@ -112,7 +112,7 @@ def test_fp8_quantizers_bit_exact(axk, cuda_device):
     import ref_cases as rc
     from gpu_util import dev, sync
 
-    for rows, cols in [(8, 5120), (24, 17408), (3, 64)]:
+    for rows, cols in [(8, 5120), (24, 17408), (3, 64), (640, 8192), (600, 5120)]:
         bits = wl.quantize_input_np(rows, cols, seed=cols)
         bits[0, :] = 0
         codes = torch.zeros((rows, cols), dtype=torch.uint8, device="cuda")
