@@ -131,6 +131,42 @@ def test_plain_fp8_quantizer_bit_exact(axk, cuda_device):
         assert codes.guards_intact() and scales.guards_intact()
 
 
+def test_plain_fp8_quantizer_every_bf16_value(axk, cuda_device):
+    """Every finite BF16 value under a row maximum M, for maxima from the smallest subnormal to the largest finite
+    value (rows of one sign each, zero padded): scales and codes bit-equal with the oracle.  Then every one of the
+    65536 patterns, NaN and infinities included, through the given-scale flavour at several scales."""
+    from gpu_util import Guarded, dev, sync
+    import torch
+
+    cols = 32768
+    maxima = [0x0001, 0x007f, 0x0080, 0x0c00, 0x3b80, 0x3f80, 0x43e0, 0x43e1, 0x4400, 0x5000, 0x7000, 0x7f00, 0x7f7f]
+    rows = []
+    for m in maxima:
+        mags = np.arange(0, m + 1, dtype=np.uint16)
+        for sign in (0x0000, 0x8000):
+            row = np.zeros(cols, np.uint16)
+            row[: mags.size] = mags | sign
+            rows.append(np.roll(row, 37 * len(rows)))   # the maximum is not always in the first thread's chunk
+    x = np.stack(rows)
+    codes, scales = Guarded(x.size), Guarded(x.shape[0] * 4)
+    status = torch.zeros(1, dtype=torch.int32, device="cuda")
+    assert axk.fp8_quantize(0, dev(x), x.shape[0], cols, codes.ptr, scales.ptr, status) == axk.AXIOM_OK
+    sync()
+    want_codes, want_scales, want_status = ol.fp8_quantize_bf16(x)
+    assert np.array_equal(scales.payload(np.float32), want_scales)
+    assert np.array_equal(codes.payload().reshape(x.shape), want_codes)
+    assert int(status.item()) == want_status == 0 and codes.guards_intact() and scales.guards_intact()
+
+    every = np.arange(65536, dtype=np.uint16).reshape(2, cols)
+    for scale in (1.0, 0.0123, 3.0e-3, 1.0e-30, 1.0e30, 2.0 ** -126, 448.0):
+        out = Guarded(every.size)
+        assert axk.fp8_quantize_static(0, dev(every), 2, cols, scale, out.ptr) == axk.AXIOM_OK
+        sync()
+        want = ol.fp8_quantize_static_f32(wl.from_bf16_bits(every), scale)
+        assert np.array_equal(out.payload().reshape(every.shape), want), scale
+        assert out.guards_intact()
+
+
 @pytest.mark.parametrize("rows,cols,scale", [(1, 8, 1.0), (5, 5120, 0.0123), (300, 1024, 3.0e-3), (7, 36864, 2.5), (64, 264, 1.0e-30),
                                               (700, 8192, 0.02), (600, 5120, 1.5), (640, 264, 7.0e-3)])
 def test_static_scale_fp8_quantizer_bit_exact(axk, cuda_device, rows, cols, scale):
