@@ -198,8 +198,8 @@ constexpr int kMlpRowThreads = 544;  // 17408 / (4 chunks x 8 values)
 template <int CPT, row_op kOp, bool kStatic = false, int kThreads = 0>
 __global__ void __launch_bounds__(kThreads ? kThreads : kMaxRowThreads, CPT <= 4 ? 2 : 1)
 fp8_rows_kernel(const uint4 *__restrict__ in, uint32_t rows, uint32_t chunks, uint32_t in_chunks_per_row,
-                uint2 *__restrict__ codes, float *__restrict__ scales, uint32_t *__restrict__ status_word,
-                const float *__restrict__ device_table, float given_scale) {
+                uint2 *__restrict__ codes, float *__restrict__ scales, const float *__restrict__ device_table,
+                float given_scale) {
     extern __shared__ __align__(16) float silu_table[];
     __shared__ uint32_t warp_max[32];
     constexpr bool kTable = kOp == row_op::swiglu_table;
@@ -724,7 +724,7 @@ void configure_fp8_rows() {
 
 template <row_op kOp, bool kStatic = false>
 int launch_fp8_rows(const void *in, uint32_t rows, uint32_t width, uint32_t in_chunks_per_row, uint8_t *codes,
-                    float *scales, uint32_t *status_word, cudaStream_t stream, float given_scale = 0.0f) {
+                    float *scales, cudaStream_t stream, float given_scale = 0.0f) {
     const uint32_t chunks = width / 8u;
     const row_shape s = pick_row_shape(chunks);
     if (s.threads == 0u) return AXIOM_ERR_INVALID_ARGUMENT;
@@ -739,15 +739,15 @@ int launch_fp8_rows(const void *in, uint32_t rows, uint32_t width, uint32_t in_c
     if (kTable) configure_fp8_rows<kOp, kStatic>();
     if (kTable && s.cpt == 4u && s.threads * 4u == chunks && s.threads == kMlpRowThreads) {
         // the reference model's MLP width (17408 = 544 threads x 4 chunks x 8): row geometry as compile-time constants
-        launch_chained(fp8_rows_kernel<4, kOp, kStatic, kMlpRowThreads>, dim3(ctas), dim3(s.threads), smem, stream, src, rows, chunks, in_chunks_per_row, dst, scales, status_word, device_table, given_scale);
+        launch_chained(fp8_rows_kernel<4, kOp, kStatic, kMlpRowThreads>, dim3(ctas), dim3(s.threads), smem, stream, src, rows, chunks, in_chunks_per_row, dst, scales, device_table, given_scale);
         note_launch();
         return AXIOM_OK;
     }
     switch (s.cpt) {
-    case 1: launch_chained(fp8_rows_kernel<1, kOp, kStatic>, dim3(ctas), dim3(s.threads), smem, stream, src, rows, chunks, in_chunks_per_row, dst, scales, status_word, device_table, given_scale); break;
-    case 2: launch_chained(fp8_rows_kernel<2, kOp, kStatic>, dim3(ctas), dim3(s.threads), smem, stream, src, rows, chunks, in_chunks_per_row, dst, scales, status_word, device_table, given_scale); break;
-    case 4: launch_chained(fp8_rows_kernel<4, kOp, kStatic>, dim3(ctas), dim3(s.threads), smem, stream, src, rows, chunks, in_chunks_per_row, dst, scales, status_word, device_table, given_scale); break;
-    default: launch_chained(fp8_rows_kernel<8, kOp, kStatic>, dim3(ctas), dim3(s.threads), smem, stream, src, rows, chunks, in_chunks_per_row, dst, scales, status_word, device_table, given_scale); break;
+    case 1: launch_chained(fp8_rows_kernel<1, kOp, kStatic>, dim3(ctas), dim3(s.threads), smem, stream, src, rows, chunks, in_chunks_per_row, dst, scales, device_table, given_scale); break;
+    case 2: launch_chained(fp8_rows_kernel<2, kOp, kStatic>, dim3(ctas), dim3(s.threads), smem, stream, src, rows, chunks, in_chunks_per_row, dst, scales, device_table, given_scale); break;
+    case 4: launch_chained(fp8_rows_kernel<4, kOp, kStatic>, dim3(ctas), dim3(s.threads), smem, stream, src, rows, chunks, in_chunks_per_row, dst, scales, device_table, given_scale); break;
+    default: launch_chained(fp8_rows_kernel<8, kOp, kStatic>, dim3(ctas), dim3(s.threads), smem, stream, src, rows, chunks, in_chunks_per_row, dst, scales, device_table, given_scale); break;
     }
     note_launch();
     return AXIOM_OK;
@@ -767,9 +767,9 @@ unsigned int swiglu_fault_word() { return read_and_clear_pipeline_fault(); }
 int launch_swiglu_fp8_bf16(const void *gate_up, uint32_t rows, uint32_t width, uint8_t *codes, float *scales,
                            cudaStream_t stream) {
     if (rows >= kTableMinRows) {
-        return launch_fp8_rows<row_op::swiglu_table>(gate_up, rows, width, width / 4u, codes, scales, nullptr, stream);
+        return launch_fp8_rows<row_op::swiglu_table>(gate_up, rows, width, width / 4u, codes, scales, stream);
     }
-    return launch_fp8_rows<row_op::swiglu>(gate_up, rows, width, width / 4u, codes, scales, nullptr, stream);
+    return launch_fp8_rows<row_op::swiglu>(gate_up, rows, width, width / 4u, codes, scales, stream);
 }
 
 // Given-scale flavours: the same row kernels without the row maximum (one pass, nothing to reduce).
@@ -801,9 +801,9 @@ int launch_fp8_quantize_static_bf16(const void *input, uint32_t rows, uint32_t c
 int launch_swiglu_fp8_static_bf16(const void *gate_up, uint32_t rows, uint32_t width, float scale, uint8_t *codes,
                                   cudaStream_t stream) {
     if (rows >= kTableMinRows) {
-        return launch_fp8_rows<row_op::swiglu_table, true>(gate_up, rows, width, width / 4u, codes, nullptr, nullptr, stream, scale);
+        return launch_fp8_rows<row_op::swiglu_table, true>(gate_up, rows, width, width / 4u, codes, nullptr, stream, scale);
     }
-    return launch_fp8_rows<row_op::swiglu, true>(gate_up, rows, width, width / 4u, codes, nullptr, nullptr, stream, scale);
+    return launch_fp8_rows<row_op::swiglu, true>(gate_up, rows, width, width / 4u, codes, nullptr, stream, scale);
 }
 
 int launch_fp8_quantize_bf16(const void *input, uint32_t rows, uint32_t cols, uint8_t *codes, float *scales,
