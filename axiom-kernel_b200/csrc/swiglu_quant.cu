@@ -658,7 +658,7 @@ struct row_shape {
 // Smallest padding first; between equal paddings the larger CTA (shorter per-row latency), or — many_rows — the
 // smaller one with more chunks per thread: more loads in flight per thread and more CTAs per SM, whose load and
 // store phases then interleave (plain BF16 -> FP8 at 16384 x 8192: 91 us with 512 x 2, 79 with 256 x 4, 73 with
-// 128 x 8).  Up to one warp of padding per CTA is accepted for that.
+// 128 x 8).  Padding of up to 1/32 of the row is accepted for that.
 row_shape pick_row_shape(uint32_t chunks, bool many_rows = false) {
     static const uint32_t cpts[] = {1u, 2u, 4u, 8u};
     row_shape best{0u, 0u};
