@@ -514,9 +514,8 @@ qk_norm_rope_stream_kernel(const qk_dev_args a, const qk_stream_geom g, const __
     // the slot; without a map the lanes fetch the heads one by one.  The slot holds the same packed
     // row in every case.
     const bool q_packed = a.q_head_stride == D;
-    auto issue = [&](uint32_t i, uint32_t lane) {
+    auto issue = [&](uint32_t i, uint32_t j, uint32_t lane) {  // j = i % slots
         const uint64_t tok = token_of(i);
-        const uint32_t j = i % g.slots;
         uint8_t *slot = my_slots + (size_t)j * g.slot_bytes;
         if (lane == 0u) {
             mbar_arrive_expect_tx(bars + j, q_bytes + k_bytes);
@@ -541,7 +540,7 @@ qk_norm_rope_stream_kernel(const qk_dev_args a, const qk_stream_geom g, const __
             mbar_init_fence();
         }
         __syncwarp();
-        for (uint32_t i = 0; i < ahead && i < my_tokens; ++i) issue(i, t - workers);
+        for (uint32_t i = 0; i < ahead && i < my_tokens; ++i) issue(i, i, t - workers);  // ahead <= slots
     }
     for (uint32_t i = tid; i < D; i += blockDim.x) {
         gq_sh[i] = a.q_heads ? __uint_as_float((uint32_t)a.q_gamma[i] << 16) : 0.0f;
@@ -583,8 +582,10 @@ qk_norm_rope_stream_kernel(const qk_dev_args a, const qk_stream_geom g, const __
         team_sync(team, g.team_threads);
 
         bool faulted = false;
+        // slot of token i and the parity of its barrier (i % slots, (i / slots) & 1), and the slot of token i + ahead,
+        // all advanced by one per token instead of divided out
+        uint32_t j = 0u, phase = 0u, j_next = ahead % g.slots;
         for (uint32_t i = 0; i < my_tokens; ++i) {
-            const uint32_t j = i % g.slots;
             const uint32_t tok = token_of(i);
             const uint32_t pos_n2 = i + 2u < my_tokens ? a.positions[token_of(i + 2u)] : 0u;
             int32_t pb_n1 = -1;
@@ -600,7 +601,7 @@ qk_norm_rope_stream_kernel(const qk_dev_args a, const qk_stream_geom g, const __
             uint8_t *slot = my_slots + (size_t)j * g.slot_bytes;
             // A wait that ran out raises the fault word; the team carries on (on whatever the slot
             // holds) so that its barriers stay matched, and stops waiting and storing.
-            if (!faulted && !mbar_wait(bars + j, (i / g.slots) & 1u)) faulted = true;
+            if (!faulted && !mbar_wait(bars + j, phase)) faulted = true;
             faulted = __any_sync(0xffffffffu, faulted);  // one verdict for the warp: its lanes issue copies together
             team_sync(team, g.team_threads);  // the workers have rewritten the slot
             if (fp8_cache && g.slots <= 2u) team_sync(team, g.team_threads);  // ... and converted its K row (see the workers)
@@ -625,11 +626,16 @@ qk_norm_rope_stream_kernel(const qk_dev_args a, const qk_stream_geom g, const __
             }
             if (!faulted && nxt < my_tokens) {
                 __syncwarp();  // the first lane's stores have finished reading the slot that is refilled
-                issue(nxt, ml);
+                issue(nxt, j_next, ml);
             }
             pos_cur = pos_n1;
             pos_n1 = pos_n2;
             pb_cur = pb_n1;
+            if (++j == g.slots) {
+                j = 0u;
+                phase ^= 1u;
+            }
+            if (++j_next == g.slots) j_next = 0u;
         }
         if (lead) bulk_wait_read_all();
         return;
@@ -648,8 +654,8 @@ qk_norm_rope_stream_kernel(const qk_dev_args a, const qk_stream_geom g, const __
     team_sync(team, g.team_threads);  // the first rotary table is there
 
     bool faulted = false;
+    uint32_t j = 0u, phase = 0u;  // i % slots and (i / slots) & 1
     for (uint32_t i = 0; i < my_tokens; ++i) {
-        const uint32_t j = i % g.slots;
         const uint32_t tok = token_of(i);
         // V is a plain copy into the token's cache row: too small to deserve slot space.  The
         // team's first threads read it now and write it after the barrier, when the manager has
@@ -663,7 +669,7 @@ qk_norm_rope_stream_kernel(const qk_dev_args a, const qk_stream_geom g, const __
             }
         }
         uint8_t *slot = my_slots + (size_t)j * g.slot_bytes;
-        if (!faulted && !mbar_wait(bars + j, (i / g.slots) & 1u)) faulted = true;
+        if (!faulted && !mbar_wait(bars + j, phase)) faulted = true;
 
         const float *cos_t = tables + (i & 1u) * (D / 2u) * 3u;
         const rot_regs r = load_rot(cos_t, cos_t + D / 2u, cos_t + D, off_a, rotary);
@@ -753,6 +759,10 @@ qk_norm_rope_stream_kernel(const qk_dev_args a, const qk_stream_geom g, const __
         }
         // with one or two slots the manager refills THIS slot next: everyone has to be done reading it
         if (fp8_cache && g.slots <= 2u) team_sync(team, g.team_threads);
+        if (++j == g.slots) {
+            j = 0u;
+            phase ^= 1u;
+        }
     }
 }
 
