@@ -26,8 +26,6 @@
 #include "pipeline.cuh"
 #include "runtime.hpp"
 
-#include <type_traits>
-
 namespace axb {
 
 namespace {
@@ -604,41 +602,32 @@ gated_nvfp4_stream_kernel(const uint4 *__restrict__ gate, const uint4 *__restric
 
     while (remaining != 0u) {
         const uint32_t in_row = col_groups - col;
-        const uint32_t avail = remaining < in_row ? remaining : in_row;  // tiles left in this row for this warp
         uint32_t n;
         uint32_t outside = 0u;
         bool needs_exact = false;
-        // kN tiles of one row: all loads first, then the conversions (no branch between them)
-        auto tiles = [&](auto count) {
-            constexpr uint32_t kN = decltype(count)::value;
-            uint4 g[kN], u[kN];
+        if (remaining >= kGatedUnroll && in_row >= kGatedUnroll) {
+            n = kGatedUnroll;
+            uint4 g[kGatedUnroll], u[kGatedUnroll];
 #pragma unroll
-            for (uint32_t j = 0; j < kN; ++j) {
+            for (uint32_t j = 0; j < kGatedUnroll; ++j) {
                 g[j] = ld_stream(pg + 32u * j);
                 u[j] = ld_stream(po + 32u * j);
             }
             // SwiGLU (gate and up halves of one row): the tiles of the next iteration, hinted into L2 while these are
             // converted (223 -> 217 us at 16384 x 17408; with two separate operand planes, the sigmoid gate, the same
             // hint costs 2 %, so it is not issued there)
-            if (kN == kGatedUnroll && kFn == gate_fn::silu && lane < 2u && avail >= 2u * kGatedUnroll) {
+            if (kFn == gate_fn::silu && lane < 2u && remaining >= 2u * kGatedUnroll && in_row >= 2u * kGatedUnroll) {
                 bulk_prefetch_l2((lane == 0u ? pg : po) - lane + 32u * kGatedUnroll, kGatedUnroll * 512u);
             }
 #pragma unroll
-            for (uint32_t j = 0; j < kN; ++j) {
+            for (uint32_t j = 0; j < kGatedUnroll; ++j) {
                 gated_tile_fast<kFn, kBf16Out, kCodes>(silu_table, lut, G, g[j], u[j], pb + 32u * j, pc + 32u * j,
                                                        ps + kScaleStep * j, scale_lane, &outside, &needs_exact);
             }
-        };
-        // the tail of a row (or of the warp's range) keeps what parallelism it has: two tiles together, not one by one
-        if (avail >= kGatedUnroll) {
-            n = kGatedUnroll;
-            tiles(std::integral_constant<uint32_t, kGatedUnroll>{});
-        } else if (avail == 2u) {
-            n = 2u;
-            tiles(std::integral_constant<uint32_t, 2u>{});
         } else {
             n = 1u;
-            tiles(std::integral_constant<uint32_t, 1u>{});
+            const uint4 g = ld_stream(pg), u = ld_stream(po);
+            gated_tile_fast<kFn, kBf16Out, kCodes>(silu_table, lut, G, g, u, pb, pc, ps, scale_lane, &outside, &needs_exact);
         }
         if (__any_sync(0xffffffffu, (outside & 0x60006000u) != 0u || needs_exact) || (kCodes && !lut_safe)) {
             gated_tiles_exact<kFn>(pg, po, n, G, pb, pc, ps, kScaleStep, scale_lane);
