@@ -450,7 +450,7 @@ def main():
                      "traffic": profiled_dram_bytes() if (ROWS, COLS) == (8192, 5120) else None,
                      "traffic_source": "not measured by this run: dram__bytes_read.sum + dram__bytes_write.sum of one ncu "
                                        "capture of this launch, read from profiles/" + HEADLINE_PROFILE.name,
-                     "peak_kind": peak_kind, "kernel": "add_rmsnorm_stream_kernel<true,true>",
+                     "peak_kind": peak_kind, "kernel": "add_rmsnorm_stream_kernel<kBf16, true, 5120>",
                      "algorithmic_bytes_per_launch": algo},
         "gpu_launches": launches,
         "clocks": clocks,
