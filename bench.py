@@ -919,6 +919,32 @@ def bench_chain(torch, axk, wl, local, device, stream, timed, peak):
     axk.check(axk.yarn_inv_freq(local, 128, wl.ROPE_THETA, wl.YARN_FACTOR, wl.YARN_ORIGINAL_CONTEXT, 32.0, 1.0, inv_freq, stream), "yarn")
     status = torch.zeros(1, dtype=torch.int32, device=device)
     chain = {}
+    # the launch floor of this box, measured the same way: the smallest kernel of the library (a 64-element BF16 add,
+    # one CTA) three times per "chain", back to back and as eight chains per graph
+    fa, fb = torch.zeros(64, dtype=torch.bfloat16, device=device), torch.zeros(64, dtype=torch.bfloat16, device=device)
+    fo = torch.empty(64, dtype=torch.bfloat16, device=device)
+
+    def floor_chain(_i, s=stream):
+        for _ in range(3):
+            axk.add_bf16(local, fa, fb, fo, 64, s)
+
+    floor_eager_us = timed(floor_chain, n=200) * 1e3
+    floor_graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(floor_graph, stream=stream):
+        for _ in range(8):
+            floor_chain(0, torch.cuda.current_stream())
+    for _ in range(3):
+        floor_graph.replay()
+    f0, f1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    torch.cuda.synchronize()
+    f0.record()
+    for _ in range(50):
+        floor_graph.replay()
+    f1.record()
+    torch.cuda.synchronize()
+    chain["launch_floor"] = {"eager_us": floor_eager_us, "graph8_us_per_chain": f0.elapsed_time(f1) / (50 * 8) * 1e3,
+                             "what": "three launches of a one-CTA kernel (64-element BF16 add) in place of the three stages"}
+    del floor_graph
     for m in (1, 8, 64, 256):
         ids = torch.randint(0, wl.VOCAB, (m,), device=device).to(torch.int32)
         _, residual, gamma = wl.add_rmsnorm_inputs_torch(torch, device, m)
