@@ -974,8 +974,25 @@ def bench_chain(torch, axk, wl, local, device, stream, timed, peak):
                 fn(_i, s)
 
         eager_us = timed(run_chain, n=200) * 1e3
-        # each stage alone, back to back on the stream (the larger of its duration and the launch rate)
-        stage_us = {name: timed(fn, n=200) * 1e3 for name, fn in stages.items()}
+        # each stage alone: 24 launches of it in one graph (device-side time per launch; eager launches of kernels
+        # this short are bound by the host's launch rate)
+        stage_us = {}
+        for name, fn in stages.items():
+            sg = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(sg, stream=stream):
+                for _ in range(24):
+                    fn(0, torch.cuda.current_stream())
+            for _ in range(3):
+                sg.replay()
+            s0, s1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            torch.cuda.synchronize()
+            s0.record()
+            for _ in range(20):
+                sg.replay()
+            s1.record()
+            torch.cuda.synchronize()
+            stage_us[name] = s0.elapsed_time(s1) / (20 * 24) * 1e3
+            del sg
         graph = torch.cuda.CUDAGraph()
         with torch.cuda.graph(graph, stream=stream):
             run_chain(0, torch.cuda.current_stream())
