@@ -197,11 +197,14 @@ __device__ __forceinline__ void qk_apply(uint2 xa, uint2 xb, float inv, const fl
     const float2 b1 = __fmul2_rn(__fmul2_rn(fb1, inv2), make_float2(gb.z, gb.w));
     float2 oa0 = a0, oa1 = a1, ob0 = b0, ob1 = b1;
     if (rotary) {
-        // out[p] = fma(first, c, -(second*s)); out[p+half] = fma(first, s, second*c)
+        // out[p] = fma(first, c, -(second*s)); out[p+half] = fma(second, c, first*s): which product of
+        // `first * sine + second * cosine` (src/axiom_qwen38_attention.cu:534-535) the reference's build fuses was
+        // settled against its kernel on 2.2 M rotated pairs (the other choice differs in 1.6e-5 of them, mostly
+        // where the two terms cancel, and in the sign of results that underflow to zero)
         oa0 = __ffma2_rn(a0, r.c0, __fmul2_rn(b0, r.n0));
         oa1 = __ffma2_rn(a1, r.c1, __fmul2_rn(b1, r.n1));
-        ob0 = __ffma2_rn(a0, r.s0, __fmul2_rn(b0, r.c0));
-        ob1 = __ffma2_rn(a1, r.s1, __fmul2_rn(b1, r.c1));
+        ob0 = __ffma2_rn(b0, r.c0, __fmul2_rn(a0, r.s0));
+        ob1 = __ffma2_rn(b1, r.c1, __fmul2_rn(a1, r.s1));
     }
     *out_a = make_uint2(pack_bf16x2(oa0.x, oa0.y), pack_bf16x2(oa1.x, oa1.y));
     *out_b = make_uint2(pack_bf16x2(ob0.x, ob0.y), pack_bf16x2(ob1.x, ob1.y));
@@ -255,6 +258,7 @@ __device__ __forceinline__ void qk_apply_round_after_norm(uint2 xa, uint2 xb, fl
     // the normalised values exist in BF16 only
     const float2 a0 = bf16x2_widen_fma(pack_bf16x2(ua0.x, ua0.y)), a1 = bf16x2_widen_fma(pack_bf16x2(ua1.x, ua1.y));
     const float2 b0 = bf16x2_widen_fma(pack_bf16x2(ub0.x, ub0.y)), b1 = bf16x2_widen_fma(pack_bf16x2(ub1.x, ub1.y));
+    // here the reference's build fuses the FIRST product of both sums (checked against its kernel on 14 M pairs)
     const float2 oa0 = __ffma2_rn(a0, r.c0, __fmul2_rn(b0, r.n0)), oa1 = __ffma2_rn(a1, r.c1, __fmul2_rn(b1, r.n1));
     const float2 ob0 = __ffma2_rn(a0, r.s0, __fmul2_rn(b0, r.c0)), ob1 = __ffma2_rn(a1, r.s1, __fmul2_rn(b1, r.c1));
     *out_a = make_uint2(pack_bf16x2(oa0.x, oa0.y), pack_bf16x2(oa1.x, oa1.y));

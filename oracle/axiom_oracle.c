@@ -575,7 +575,10 @@ static double sum_squares_tree_f64(const float *x, uint32_t n) {
  * in FP64; n = (x*inv)*w in FP32; NeoX pairs (p, p+rope_dim/2); angle =
  * (float)pos * f; cos and sin each multiplied by mscale; a single BF16 rounding
  * at the end.  The two rotation sums are fma(first, c, -(second*s)) and
- * fma(first, s, second*c). */
+ * fma(second, c, first*s): the contraction the reference's build applies to
+ * `first * cosine - second * sine` and `first * sine + second * cosine`,
+ * settled against its kernel on the GPU (the draft kernel below fuses the
+ * first product of both sums). */
 static void qk_head(const uint16_t *in, const uint16_t *gamma, uint32_t head_dim, uint32_t rope_dim,
                     float eps, const float *cosine, const float *sine, uint16_t *out) {
     float x[1024], n[1024];
@@ -587,7 +590,7 @@ static void qk_head(const uint16_t *in, const uint16_t *gamma, uint32_t head_dim
     for (uint32_t p = 0; p < half; ++p) {
         const float first = n[p], second = n[p + half];
         out[p] = axo_f32_to_bf16(fmaf(first, cosine[p], -(second * sine[p])));
-        out[p + half] = axo_f32_to_bf16(fmaf(first, sine[p], second * cosine[p]));
+        out[p + half] = axo_f32_to_bf16(fmaf(second, cosine[p], first * sine[p]));
     }
     for (uint32_t i = rope_dim; i < head_dim; ++i) out[i] = axo_f32_to_bf16(n[i]);
 }

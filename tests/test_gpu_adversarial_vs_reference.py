@@ -1,0 +1,171 @@
+"""Differential test on adversarial inputs: the CUDA path against the reference's own kernels (oracle/_ref) on
+BF16 tensors drawn to hit the rare paths — uniformly random bit patterns (every exponent, NaN, infinities,
+subnormals), per-row magnitudes over the whole FP32 exponent range, many exact ties, sprinkled special values — at
+random shapes on both sides of every kernel switch (few rows / streaming, table / direct silu, chunks per thread),
+with global scales and given scales over many decades.  Every comparison is bit-exact."""
+import importlib
+
+import numpy as np
+import pytest
+
+import ref_lib
+
+pytestmark = [pytest.mark.gpu, pytest.mark.skipif(not ref_lib.available(), reason="oracle/_ref is built only where the reference tree is present")]
+wl = importlib.import_module("axiom-kernel_b200.workloads")
+
+SPECIALS = np.array([0x0000, 0x8000, 0x7f80, 0xff80, 0x7fc0, 0xffc0, 0x0001, 0x8001, 0x007f, 0x0080, 0x7f7f, 0xff7f,
+                     0x3f80, 0x43e0, 0x40c0], np.uint16)
+
+
+def adversarial(rng, rows, cols):
+    kind = rng.integers(0, 5)
+    if kind == 0:
+        return rng.integers(0, 65536, (rows, cols), dtype=np.uint16)
+    x = rng.standard_normal((rows, cols)).astype(np.float32)
+    with np.errstate(all="ignore"):
+        if kind == 1:
+            x *= np.float32(10.0) ** rng.uniform(-38, 38, (rows, 1)).astype(np.float32)
+        elif kind == 2:
+            x *= np.float32(2.0) ** rng.integers(-8, 8, (rows, cols)).astype(np.float32)
+        elif kind == 3:
+            x *= np.float32(10.0) ** rng.uniform(-3, 3, (rows, 1)).astype(np.float32)
+        else:
+            x = np.round(x * 4) / 4
+        bits = wl.to_bf16_bits(x)
+    n = rng.integers(0, max(2, rows * cols // 2000))
+    bits.reshape(-1)[rng.integers(0, rows * cols, n)] = SPECIALS[rng.integers(0, SPECIALS.size, n)]
+    return bits
+
+
+def dev(a):
+    import torch
+
+    return torch.from_numpy(a.view(np.int16) if a.dtype == np.uint16 else a).cuda()
+
+
+def decade(rng, lo, hi):
+    return float(np.float32(10.0 ** rng.uniform(lo, hi)))
+
+
+@pytest.mark.parametrize("seed", range(12))
+def test_quantizers_on_adversarial_tensors(axk, cuda_device, seed):
+    import torch
+    import ref_cases as rc
+
+    rng = np.random.default_rng(1000 + seed)
+    # BF16 -> NVFP4, tiled scale plane (the reference's thread kernel: it agrees with the exported entry on all-NaN blocks)
+    rows, cols = int(rng.choice([1, 3, 17, 129, 300, 700])), int(rng.choice([16, 528, 1024, 5120, 17408]))
+    rows = min(rows, max(1, 3_000_000 // cols))
+    bits, G = adversarial(rng, rows, cols), decade(rng, -4, 5)
+    codes = torch.zeros((rows, cols // 2), dtype=torch.uint8, device="cuda")
+    plane = torch.zeros(int(axk.lib().axiom_nvfp4_scale_plane_bytes(rows, cols // 16, 1)), dtype=torch.uint8, device="cuda")
+    assert axk.nvfp4_quantize(0, dev(bits), rows, cols, G, codes, plane, 1) == 0
+    torch.cuda.synchronize()
+    ref_codes, ref_plane = rc.nvfp4_quantize(bits, G, "thread")
+    assert np.array_equal(codes.cpu().numpy(), ref_codes) and np.array_equal(plane.cpu().numpy(), ref_plane), (rows, cols, G)
+
+    # BF16 -> FP8 rows: per-row scale with status word, and a given scale
+    rows, cols = int(rng.choice([1, 5, 64, 300, 650])), int(rng.choice([8, 264, 1024, 5120, 8192, 17408]))
+    rows = min(rows, max(1, 4_000_000 // cols))
+    bits = adversarial(rng, rows, cols)
+    codes = torch.zeros((rows, cols), dtype=torch.uint8, device="cuda")
+    scales = torch.zeros(rows, dtype=torch.float32, device="cuda")
+    status = torch.zeros(1, dtype=torch.int32, device="cuda")
+    assert axk.fp8_quantize(0, dev(bits), rows, cols, codes, scales, status) == 0
+    torch.cuda.synchronize()
+    ref_codes, ref_scales, ref_status = rc.fp8_quantize_bf16(bits)
+    assert np.array_equal(codes.cpu().numpy(), ref_codes), (rows, cols)
+    assert np.array_equal(scales.cpu().numpy().view(np.uint32), ref_scales.view(np.uint32)) and int(status.item()) == ref_status
+    scale = decade(rng, -30, 30)
+    assert axk.fp8_quantize_static(0, dev(bits), rows, cols, scale, codes) == 0
+    torch.cuda.synchronize()
+    assert np.array_equal(codes.cpu().numpy(), rc.fp8_quantize_static_f32(rc.f32_dev(bits), scale)), (rows, cols, scale)
+
+
+@pytest.mark.parametrize("seed", range(12))
+def test_swiglu_on_adversarial_tensors(axk, cuda_device, seed):
+    import torch
+    import ref_cases as rc
+
+    rng = np.random.default_rng(2000 + seed)
+    rows, w = int(rng.choice([1, 8, 95, 96, 300, 600])), int(rng.choice([16, 512, 2048, 4096 + 256, 17408]))
+    rows = min(rows, max(1, 2_500_000 // w))
+    gu = adversarial(rng, rows, 2 * w)
+    if seed % 2:  # gates a model produces, next to arbitrary up values
+        gu[:, :w] = wl.to_bf16_bits(rng.standard_normal((rows, w)).astype(np.float32) * np.float32(rng.choice([0.5, 1.5, 8.0, 60.0])))
+    c8 = torch.zeros((rows, w), dtype=torch.uint8, device="cuda")
+    s8 = torch.zeros(rows, dtype=torch.float32, device="cuda")
+    assert axk.swiglu_fp8(0, dev(gu), rows, w, c8, s8) == 0
+    torch.cuda.synchronize()
+    ref_codes, ref_scales = rc.swiglu_fp8(gu)
+    assert np.array_equal(c8.cpu().numpy(), ref_codes), (rows, w)
+    assert np.array_equal(s8.cpu().numpy().view(np.uint32), ref_scales.view(np.uint32))
+    scale = decade(rng, -6, 6)
+    assert axk.swiglu_fp8_static(0, dev(gu), rows, w, scale, c8) == 0
+    torch.cuda.synchronize()
+    assert np.array_equal(c8.cpu().numpy(), rc.fp8_quantize_static_f32(rc.swiglu_f32(gu), scale)), (rows, w, scale)
+    G = decade(rng, -3, 4)
+    c4 = torch.zeros((rows, w // 2), dtype=torch.uint8, device="cuda")
+    plane = torch.zeros(int(axk.lib().axiom_nvfp4_scale_plane_bytes(rows, w // 16, 1)), dtype=torch.uint8, device="cuda")
+    assert axk.swiglu_nvfp4(0, dev(gu), rows, w, G, c4, plane, 1) == 0
+    torch.cuda.synchronize()
+    ref_c4, ref_plane = rc.swiglu_nvfp4(gu, G, "thread")
+    assert np.array_equal(c4.cpu().numpy(), ref_c4) and np.array_equal(plane.cpu().numpy(), ref_plane), (rows, w, G)
+
+
+@pytest.mark.parametrize("seed", range(8))
+def test_add_rmsnorm_nvfp4_on_adversarial_tensors(axk, cuda_device, seed):
+    import torch
+    import ref_cases as rc
+
+    rng = np.random.default_rng(3000 + seed)
+    rows, cols = int(rng.choice([8, 64, 296, 304, 1024])), 5120
+    hidden, residual = adversarial(rng, rows, cols), adversarial(rng, rows, cols)
+    gamma = wl.to_bf16_bits((1 + rng.standard_normal(cols) * rng.choice([0.02, 1.0])).astype(np.float32))
+    with_add = bool(seed % 2)
+    ref_res, ref_norm = rc.add_rmsnorm(hidden if with_add else None, residual, gamma)
+    G = decade(rng, -4, 5)
+    ref_codes, ref_plane = rc.nvfp4_quantize(ref_norm, G, "thread")
+    r = dev(residual)
+    norm = torch.zeros((rows, cols), dtype=torch.int16, device="cuda")
+    codes = torch.zeros((rows, cols // 2), dtype=torch.uint8, device="cuda")
+    plane = torch.zeros(ref_plane.size, dtype=torch.uint8, device="cuda")
+    assert axk.add_rmsnorm_nvfp4(0, dev(hidden) if with_add else None, r, dev(gamma), 1e-6, rows, cols, G, norm, codes, plane, 1) == 0
+    torch.cuda.synchronize()
+    assert np.array_equal(r.cpu().numpy().view(np.uint16).reshape(rows, cols), ref_res)
+    assert np.array_equal(norm.cpu().numpy().view(np.uint16).reshape(rows, cols), ref_norm)
+    assert np.array_equal(codes.cpu().numpy(), ref_codes) and np.array_equal(plane.cpu().numpy(), ref_plane), (rows, with_add, G)
+
+
+@pytest.mark.parametrize("tokens,seed", [(8, 0), (40, 1), (304, 2), (600, 3)])
+def test_qk_norm_rope_on_adversarial_tensors(axk, cuda_device, tokens, seed):
+    """q/k RMSNorm + partial NeoX RoPE (YaRN) at the reference's geometry (24 q / 4 kv heads x 256, rope_dim 64): the
+    per-token kernel (few tokens) and the streaming kernel (from 296 tokens) against the reference's temporal-8 kernel
+    run group by group, eight consecutive positions per group from a random base."""
+    import torch
+    import ref_cases as rc
+
+    rng = np.random.default_rng(4000 + seed)
+    H, KH, D = rc.REF_Q_HEADS, rc.REF_K_HEADS, rc.REF_HEAD_DIM
+    q = adversarial(rng, tokens, H * D).reshape(tokens, H, D)
+    k = adversarial(rng, tokens, KH * D).reshape(tokens, KH, D)
+    v = wl.to_bf16_bits(rng.standard_normal((tokens, KH, D), dtype=np.float32))  # V is not part of this call: the reference just carries it
+    qg = wl.to_bf16_bits(1.0 + 0.3 * rng.standard_normal(D, dtype=np.float32))
+    kg = wl.to_bf16_bits(1.0 + 0.3 * rng.standard_normal(D, dtype=np.float32))
+    bases = rng.integers(0, 250000, tokens // 8)
+    positions = (bases[:, None] + np.arange(8)[None, :]).reshape(-1).astype(np.uint32)
+    ref_q, ref_k = np.empty_like(q), np.empty_like(k)
+    for g, base in enumerate(bases):
+        s = slice(8 * g, 8 * g + 8)
+        ref_q[s], ref_k[s], ref_v, _ = rc.qk_temporal8(q[s], k[s], v[s], qg, kg, int(base))
+        assert np.array_equal(ref_v, v[s])
+    inv = torch.zeros(32, dtype=torch.float32, device="cuda")
+    assert axk.yarn_inv_freq(0, 64, rc.REF_THETA, rc.REF_YARN_FACTOR, rc.REF_YARN_CTX, 32.0, 1.0, inv) == 0
+    qd, kd, qgd, kgd, pd = dev(q), dev(k), dev(qg), dev(kg), dev(positions)
+    k_out = torch.zeros((tokens, KH, D), dtype=torch.int16, device="cuda")
+    args = axk.make_qk_args(tokens=tokens, q_heads=H, k_heads=KH, head_dim=D, rope_dim=64, eps=1e-6, mscale=rc.REF_MSCALE,
+                            q=qd, k=kd, q_gamma=qgd, k_gamma=kgd, inv_freq=inv, positions=pd, k_out=k_out)
+    assert axk.qk_norm_rope_paged(0, args) == 0
+    torch.cuda.synchronize()
+    assert np.array_equal(qd.cpu().numpy().view(np.uint16).reshape(q.shape), ref_q)
+    assert np.array_equal(k_out.cpu().numpy().view(np.uint16).reshape(k.shape), ref_k)
