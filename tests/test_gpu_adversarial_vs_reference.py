@@ -169,3 +169,94 @@ def test_qk_norm_rope_on_adversarial_tensors(axk, cuda_device, tokens, seed):
     torch.cuda.synchronize()
     assert np.array_equal(qd.cpu().numpy().view(np.uint16).reshape(q.shape), ref_q)
     assert np.array_equal(k_out.cpu().numpy().view(np.uint16).reshape(k.shape), ref_k)
+
+
+@pytest.mark.parametrize("seed", range(6))
+def test_sigmoid_gate_on_adversarial_tensors(axk, cuda_device, seed):
+    """attention * sigmoid(gate) rounded to BF16 (qwen38_sigmoid_gate_kernel on its [8 x 6144] batch), direct and
+    through the tabulated flavour (the same rows repeated until the call is large enough for the table)."""
+    import torch
+
+    r = ref_lib.lib()
+    rng = np.random.default_rng(5000 + seed)
+    rows, width = 8, 6144
+    attn, gate = adversarial(rng, rows, width), adversarial(rng, rows, width)
+    if seed % 2:
+        gate = wl.to_bf16_bits(rng.standard_normal((rows, width)).astype(np.float32) * np.float32(rng.choice([1.0, 6.0, 40.0])))
+    a32 = torch.from_numpy(wl.from_bf16_bits(attn)).cuda()
+    g32 = torch.from_numpy(wl.from_bf16_bits(gate)).cuda()
+    out32 = torch.zeros_like(a32)
+    assert r.ref_sigmoid_gate8(a32.data_ptr(), g32.data_ptr(), out32.data_ptr()) == 0
+    want = out32.cpu().numpy().view(np.uint32)
+    assert not (want & 0xFFFF).any()
+    want = (want >> 16).astype(np.uint16)
+    for reps in (1, 50):
+        a, g = dev(np.tile(attn, (reps, 1))), dev(np.tile(gate, (reps, 1)))
+        y = torch.zeros((rows * reps, width), dtype=torch.int16, device="cuda")
+        assert axk.sigmoid_gate_nvfp4(0, a, g, rows * reps, width, 1.0, y, None, None, 0) == axk.AXIOM_OK
+        torch.cuda.synchronize()
+        got = y.cpu().numpy().view(np.uint16)
+        nan = lambda b: (b & 0x7FFF) > 0x7F80
+        same = (got[:rows] == want) | (nan(got[:rows]) & nan(want))       # NaN payloads are not part of the contract
+        assert same.all(), reps
+        assert np.array_equal(got[-rows:], got[:rows])
+
+
+@pytest.mark.parametrize("seed", range(4))
+def test_top1_on_adversarial_logits(axk, cuda_device, seed):
+    """Greedy selection over F32 bit patterns with many ties, infinities and NaN, against both reference paths."""
+    import torch
+    import oracle_lib as ol
+
+    r = ref_lib.lib()
+    rng = np.random.default_rng(6000 + seed)
+    vocab = 248320
+    if seed == 0:
+        logits = rng.integers(0, 2 ** 32, (8, vocab), dtype=np.uint32).view(np.float32)          # every pattern
+    elif seed == 1:
+        logits = np.round(rng.standard_normal((8, vocab)).astype(np.float32) * 2) / 2             # ties at the maximum
+    elif seed == 2:
+        logits = rng.standard_normal((8, vocab)).astype(np.float32)
+        logits[rng.integers(0, 8, 4000), rng.integers(0, vocab, 4000)] = np.float32(np.inf)
+        logits[3] = np.float32(-np.inf)
+        logits[5, ::2] = np.float32(np.nan)
+    else:
+        logits = np.full((8, vocab), np.float32(-3.0e38))
+        logits[:, -1] = np.float32(-2.9e38)                                                        # the winner is the last element
+        logits[2] = np.float32(7.0)                                                                # all equal: id 0 wins
+    x = torch.from_numpy(np.ascontiguousarray(logits)).cuda()
+    partials = torch.zeros(8 * 256 * 3, dtype=torch.int32, device="cuda")
+    out = torch.full((8, 3), 0x55555555, dtype=torch.int32, device="cuda")
+    assert axk.top1(0, x, 8, vocab, out) == axk.AXIOM_OK
+    torch.cuda.synchronize()
+    got = out.cpu().numpy().view(np.uint32)
+    assert np.array_equal(got, ol.top1_f32(logits))
+    for hierarchical in (0, 1):
+        res = torch.zeros((8, 3), dtype=torch.int32, device="cuda")
+        assert r.ref_top1_8(x.data_ptr(), partials.data_ptr(), res.data_ptr(), hierarchical) == 0
+        assert np.array_equal(res.cpu().numpy().view(np.uint32), got), hierarchical
+
+
+@pytest.mark.parametrize("seed", range(4))
+def test_round_after_norm_convention_on_adversarial_tensors(axk, cuda_device, seed):
+    """The draft / SGLang convention (AXIOM_QK_FLAG_ROUND_AFTER_NORM) against qk_rmsnorm_rope_bf16_kernel + the BF16
+    rounding pass on adversarial heads."""
+    import torch
+    import oracle_lib as ol
+    import ref_cases as rc
+
+    rng = np.random.default_rng(7000 + seed)
+    heads, tokens, first = 40, int(rng.choice([8, 64, 320])), int(rng.integers(0, 20000))
+    q = adversarial(rng, tokens, heads * 128).reshape(tokens, heads, 128)
+    qg = wl.to_bf16_bits(1.0 + 0.3 * rng.standard_normal(128, dtype=np.float32))
+    inv_freq = ol.yarn_inv_freq(1e6, 4.0, 32768.0, 32.0, 1.0, 128, host_table=True)
+    table = ol.rope_table_host(inv_freq, 128, float(ol.o().axo_yarn_mscale(4.0)), first + tokens)
+    positions = (first + np.arange(tokens)).astype(np.uint32)
+    want = rc.draft_qk_norm_rope(q, qg, table, first)
+    qd, qgd, td, pd = dev(q), dev(qg), dev(table), dev(positions)
+    args = axk.make_qk_args(tokens=tokens, q_heads=heads, k_heads=0, head_dim=128, rope_dim=128,
+                            flags=axk.QK_FLAG_ROUND_AFTER_NORM, eps=1e-6, mscale=1.0, q=qd, q_gamma=qgd, positions=pd,
+                            rope_table=td, rope_table_positions=table.shape[0])
+    assert axk.qk_norm_rope_paged(0, args) == axk.AXIOM_OK
+    torch.cuda.synchronize()
+    assert np.array_equal(qd.cpu().numpy().view(np.uint16).reshape(q.shape), want)
