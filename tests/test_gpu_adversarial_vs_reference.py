@@ -260,3 +260,39 @@ def test_round_after_norm_convention_on_adversarial_tensors(axk, cuda_device, se
     assert axk.qk_norm_rope_paged(0, args) == axk.AXIOM_OK
     torch.cuda.synchronize()
     assert np.array_equal(qd.cpu().numpy().view(np.uint16).reshape(q.shape), want)
+
+
+@pytest.mark.parametrize("seed", range(6))
+def test_e4m3_kv_cache_on_adversarial_tensors(axk, cuda_device, seed):
+    """The E4M3 (scale 1) cache flavour: K after norm + RoPE and V as they land in the cache rows, against the
+    reference kernel's own cache bytes, for arbitrary K and V values (NaN, infinities, values beyond +-448)."""
+    import torch
+    import ref_cases as rc
+
+    r = ref_lib.lib()
+    H, KH, D = rc.REF_Q_HEADS, rc.REF_K_HEADS, rc.REF_HEAD_DIM
+    rng = np.random.default_rng(8000 + seed)
+    q, k, v = (adversarial(rng, 8, n * D).reshape(8, n, D) for n in (H, KH, KH))
+    qg = wl.to_bf16_bits(1.0 + 0.3 * rng.standard_normal(D, dtype=np.float32))
+    kg = wl.to_bf16_bits(1.0 + 0.3 * rng.standard_normal(D, dtype=np.float32))
+    q32, k32, v32, qw, kw = rc.f32_dev(q), rc.f32_dev(k), rc.f32_dev(v), rc.f32_dev(qg), rc.f32_dev(kg)
+    kc = torch.zeros((8, KH * D), dtype=torch.uint8, device="cuda")
+    vc = torch.zeros_like(kc)
+    kref = torch.zeros((8, KH * D), dtype=torch.float32, device="cuda")
+    vref = torch.zeros_like(kref)
+    assert r.ref_qk_norm_partial_rope_cache_temporal8(q32.data_ptr(), k32.data_ptr(), qw.data_ptr(), kw.data_ptr(), v32.data_ptr(),
+                                                      kc.data_ptr(), vc.data_ptr(), kref.data_ptr(), vref.data_ptr(), 0, 8, 1) == 0
+    inv = torch.zeros(32, dtype=torch.float32, device="cuda")
+    assert axk.yarn_inv_freq(0, 64, rc.REF_THETA, rc.REF_YARN_FACTOR, rc.REF_YARN_CTX, 32.0, 1.0, inv) == 0
+    qd, kd, vd, qgd, kgd = dev(q), dev(k), dev(v), dev(qg), dev(kg)
+    k_cache = torch.zeros((8, KH * D), dtype=torch.uint8, device="cuda")
+    v_cache = torch.zeros_like(k_cache)
+    table, positions = dev(np.zeros((1, 1), np.int32)), dev(np.arange(8, dtype=np.uint32))
+    args = axk.make_qk_args(tokens=8, q_heads=H, k_heads=KH, head_dim=D, rope_dim=64, eps=1e-6, mscale=rc.REF_MSCALE,
+                            flags=axk.QK_FLAG_CACHE_E4M3, block_tokens=8, n_layers=1, layer=0, pool_stride=KH * D,
+                            tbl_stride=1, n_blocks=1, q=qd, k=kd, v=vd, q_gamma=qgd, k_gamma=kgd, inv_freq=inv,
+                            positions=positions, block_tables=table, k_pool=k_cache, v_pool=v_cache)
+    assert axk.qk_norm_rope_paged(0, args) == 0
+    torch.cuda.synchronize()
+    assert np.array_equal(k_cache.cpu().numpy(), kc.cpu().numpy())
+    assert np.array_equal(v_cache.cpu().numpy(), vc.cpu().numpy())
