@@ -167,14 +167,16 @@ __device__ __forceinline__ void swiglu8(const float *table, const uint4 &g, cons
 // the canonical NaN that max.NaN.f32 produces (0x7fffffff).  On those the unsigned order of the bit patterns is
 // the order of the values with NaN on top, so the maximum of a warp is one redux.sync instead of five shuffles and
 // five maxima — NaN-propagating where a NaN can occur (the callers that must drop NaN pass none).
+// `warp_max` (32 words) is read by everybody after the one barrier.  A caller that runs row after row gives every row
+// the next of four buffers, two per row (the second for a recount): a buffer comes round again two rows later, and
+// by then every thread has passed the following row's barrier, which it reaches only after its reads of this one.
 __device__ __forceinline__ float cta_max(float m, uint32_t *warp_max) {
     const uint32_t lane = threadIdx.x & 31u, warp = threadIdx.x >> 5, warps = (blockDim.x + 31u) >> 5;
     const uint32_t mine = __reduce_max_sync(0xffffffffu, __float_as_uint(m));
     if (lane == 0u) warp_max[warp] = mine;
     __syncthreads();
     const uint32_t all = __reduce_max_sync(0xffffffffu, lane < warps ? warp_max[lane] : 0u);
-    __syncthreads();  // warp_max is reused; measured: alternating two staging buffers to drop this barrier is 4 % slower
-    return __uint_as_float(all);
+    return __uint_as_float(all);  // no second barrier: the callers rotate their staging buffers
 }
 
 // Two FP8 codes through IEEE divisions, out of line: the rare path of the row kernel (a scale the reciprocal
@@ -201,7 +203,8 @@ fp8_rows_kernel(const uint4 *__restrict__ in, uint32_t rows, uint32_t chunks, ui
                 uint2 *__restrict__ codes, float *__restrict__ scales, const float *__restrict__ device_table,
                 float given_scale) {
     extern __shared__ __align__(16) float silu_table[];
-    __shared__ uint32_t warp_max[32];
+    __shared__ uint32_t warp_max_buffers[4][32];
+    uint32_t max_round = 0u;
     constexpr bool kTable = kOp == row_op::swiglu_table;
     const uint32_t tid = threadIdx.x;
     const uint32_t threads = kThreads ? (uint32_t)kThreads : blockDim.x;
@@ -236,13 +239,15 @@ fp8_rows_kernel(const uint4 *__restrict__ in, uint32_t rows, uint32_t chunks, ui
                 m = max_nan(m, absmax8_nan(y[k]));
             }
         }
+        uint32_t *warp_max = warp_max_buffers[max_round & 3u];
+        max_round += 2u;
         if (!kStatic) m = cta_max(m, warp_max);
         if (!kStatic && !(m == m)) {
             // a NaN somewhere in the row: the reference's maximum drops it
             float d = 0.0f;
 #pragma unroll
             for (int k = 0; k < CPT; ++k) d = fmaxf(d, absmax8_drop_nan(y[k]));
-            m = cta_max(d, warp_max);
+            m = cta_max(d, warp_max + 32);
             nonfinite = true;
         }
         float scale = m == 0.0f ? 1.0f : __fdiv_rn(m, 448.0f);
@@ -328,7 +333,8 @@ __global__ void __launch_bounds__(kMaxRowThreads)
 fp8_plain_rows_kernel(const uint4 *__restrict__ in, uint32_t rows, uint32_t chunks, uint32_t in_chunks_per_row,
                       uint2 *__restrict__ codes, float *__restrict__ scales, uint32_t *__restrict__ status_word,
                       float given_scale) {
-    __shared__ uint32_t warp_max[32];
+    __shared__ uint32_t warp_max_buffers[4][32];
+    uint32_t max_round = 0u;
     const uint32_t tid = threadIdx.x, threads = blockDim.x;
     allow_dependents();
     dependency_wait();
@@ -346,13 +352,15 @@ fp8_plain_rows_kernel(const uint4 *__restrict__ in, uint32_t rows, uint32_t chun
 #pragma unroll
         for (int k = 0; k < CPT; ++k) packed = magnitude_max4(packed, w[k]);
         uint32_t top = max(packed & 0xffffu, packed >> 16);  // BF16 pattern of the largest magnitude, non-finite included
+        uint32_t *warp_max = warp_max_buffers[max_round & 3u];
+        max_round += 2u;
         if (!kStatic) top = __float_as_uint(cta_max(__uint_as_float(top), warp_max));
         bool nonfinite = top >= 0x7f80u;
         if (!kStatic && nonfinite) {
             uint32_t mine = 0u;
 #pragma unroll
             for (int k = 0; k < CPT; ++k) mine = finite_magnitude_max4(mine, w[k]);
-            top = __float_as_uint(cta_max(__uint_as_float(mine), warp_max));
+            top = __float_as_uint(cta_max(__uint_as_float(mine), warp_max + 32));
             if (tid == 0u && status_word) atomicCAS(status_word, AXIOM_STATUS_WORD_OK, AXIOM_STATUS_WORD_NONFINITE);
         }
         // kStatic: this thread's own maximum, for the range test only (non-finite: +infinity fails it)
