@@ -895,8 +895,21 @@ bool launch_qk_stream(const qk_dev_args &a, cudaStream_t stream) {
         if (score > best_score) { best_score = score; best = g; best_npt = npt; }
     }
     if (best_npt == 0u || best.teams == 0u) return false;
+    // Two CTAs of half the teams per SM instead of one: the same threads, slots and registers, but a CTA of the next
+    // launch on the stream becomes resident (and runs its set-up as far as the dependency wait) as soon as ONE of the
+    // two finishes, instead of after the whole SM has drained (8192 tokens of 64 + 8 heads: 56.6 -> 56.4 us, with the
+    // interleaved source 55.7 -> 55.0 us).
+    uint32_t ctas_per_sm = 1u;
+    if (best.teams >= 2u && best.teams % 2u == 0u) {
+        qk_stream_geom half_geom = best;
+        half_geom.teams = best.teams / 2u;
+        if (2u * (qk_stream_smem(a, half_geom) + 1024u) <= 228u * 1024u) {
+            best = half_geom;
+            ctas_per_sm = 2u;
+        }
+    }
     const size_t smem = qk_stream_smem(a, best);
-    const uint32_t ctas = std::min<uint32_t>(kSmCount, (a.tokens + best.teams - 1u) / best.teams);
+    const uint32_t ctas = std::min<uint32_t>(kSmCount * ctas_per_sm, (a.tokens + best.teams - 1u) / best.teams);
     const bool full = a.rope_dim == a.head_dim;
     qk_dev_args a2 = a;
     CUtensorMap q_map;
